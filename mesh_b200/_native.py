@@ -1,0 +1,101 @@
+"""ctypes binding of libmtfc.so, the C ABI declared in include/mtfc.h.
+
+The library is loaded from the package directory.  There is no fallback: if
+the shared object is missing or a call fails, an exception is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmtfc.so")
+
+OK = 0
+ERR_CUDA = -1
+ERR_SHAPE = -2
+ERR_TIMEOUT = -3
+ERR_UNSUPPORTED = -4
+
+F32 = 0
+BF16 = 1
+I32 = 2
+
+EPILOGUE_NONE = 0
+EPILOGUE_RELU = 1
+
+MAX_DIMS = 8
+
+
+class MtfcError(RuntimeError):
+  """A libmtfc call returned a negative status."""
+
+  def __init__(self, code, message):
+    super().__init__("libmtfc error %d: %s" % (code, message))
+    self.code = code
+
+
+class GemmDesc(ctypes.Structure):
+  """Mirror of mtfc_gemm_desc."""
+  _fields_ = [
+      ("batch", ctypes.c_int64), ("m", ctypes.c_int64), ("n", ctypes.c_int64),
+      ("k", ctypes.c_int64),
+      ("a_batch", ctypes.c_int64), ("a_m", ctypes.c_int64), ("a_k", ctypes.c_int64),
+      ("b_batch", ctypes.c_int64), ("b_k", ctypes.c_int64), ("b_n", ctypes.c_int64),
+      ("c_batch", ctypes.c_int64), ("c_m", ctypes.c_int64), ("c_n", ctypes.c_int64),
+      ("in_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
+      ("epilogue", ctypes.c_int32), ("force_path", ctypes.c_int32),
+  ]
+
+
+_lib = None
+
+
+def _declare(lib):
+  vp = ctypes.c_void_p
+  i32 = ctypes.c_int32
+  i64 = ctypes.c_int64
+  lib.mtfc_last_error.restype = ctypes.c_char_p
+  lib.mtfc_last_error.argtypes = []
+  lib.mtfc_version.restype = ctypes.c_int
+  lib.mtfc_version.argtypes = []
+  lib.mtfc_launch_count.restype = i64
+  lib.mtfc_launch_count.argtypes = []
+  lib.mtfc_device_status.restype = ctypes.c_int
+  lib.mtfc_device_status.argtypes = []
+  lib.mtfc_gemm.restype = ctypes.c_int
+  lib.mtfc_gemm.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp]
+  lib.mtfc_gemm_uses_tensor_cores.restype = ctypes.c_int
+  lib.mtfc_gemm_uses_tensor_cores.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp]
+  del i32
+
+
+def lib():
+  """Returns the loaded library, loading it on first use."""
+  global _lib
+  if _lib is None:
+    if not os.path.exists(LIB_PATH):
+      raise MtfcError(
+          ERR_CUDA,
+          "%s is missing; build it with `python -m mesh_b200.csrc.build`" % LIB_PATH)
+    loaded = ctypes.CDLL(LIB_PATH)
+    _declare(loaded)
+    _lib = loaded
+  return _lib
+
+
+def check(code):
+  """Raises MtfcError for a negative status; returns the code otherwise."""
+  if code < 0:
+    raise MtfcError(code, lib().mtfc_last_error().decode("utf-8", "replace"))
+  return code
+
+
+def launch_count():
+  return int(lib().mtfc_launch_count())
+
+
+def device_status():
+  """Synchronises the current device and raises if a kernel reported a timeout."""
+  check(lib().mtfc_device_status())

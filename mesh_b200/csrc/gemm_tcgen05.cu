@@ -1,0 +1,587 @@
+// K1 einsum_gemm: C[b,m,n] = epilogue(sum_k A[b,m,k] * B[b,k,n]) on the sm_100a
+// tensor cores.  bf16 operands, fp32 accumulation in TMEM, bf16 or fp32 output.
+//
+// Replaces the per-slice tf.einsum of MeshImpl.einsum (mesh_tensorflow/ops.py:
+// 1331-1340).  Either operand may be K-major (contracted dim contiguous) or
+// MN-major (free dim contiguous): the shared-memory matrix descriptors and the
+// instruction descriptor's major bits take the layout as it is, so the named
+// dim order of a laid-out tensor never has to be transposed in memory.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0 lane 0 : TMA producer  - cp.async.bulk.tensor loads into a 4-stage
+//                   ring of 128B-swizzled tiles (A 128x64, B 256x64 bf16)
+//   warp 1 lane 0 : MMA issuer    - tcgen05.mma 128x256x16, accumulators in
+//                   TMEM, two accumulator buffers (2 x 256 columns)
+//   warps 2..5    : epilogue      - tcgen05.ld, ReLU/convert, swizzled staging
+//                   in shared memory, TMA store (clipped at the M/N edges)
+// so the epilogue of tile i overlaps the main loop of tile i+1.  No load uses
+// cluster multicast.  Every mbarrier wait is bounded: on expiry the kernel
+// raises a CTA-wide abort flag, records MTFC_ERR_TIMEOUT in the device status
+// word, drains, frees its TMEM and returns.
+
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace mtfc {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int MN_GROUP_BYTES = 64 * BK * 2;  // one 64(MN) x 64(K) box, 8 KiB
+constexpr int EPI_WARPS = 4;
+constexpr int EPI_BUF_BYTES = 32 * 128;  // 32 rows x 128 B per staging buffer
+constexpr int EPI_BYTES = EPI_WARPS * 2 * EPI_BUF_BYTES;
+constexpr int NUM_THREADS = 32 * (2 + EPI_WARPS);
+constexpr int TMEM_COLS = 512;
+
+constexpr int SMEM_A = 0;
+constexpr int SMEM_B = SMEM_A + STAGES * A_STAGE_BYTES;
+constexpr int SMEM_EPI = SMEM_B + STAGES * B_STAGE_BYTES;
+constexpr int SMEM_BAR = SMEM_EPI + EPI_BYTES;
+// barriers: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
+constexpr int NUM_BARS = 2 * STAGES + 4;
+constexpr int SMEM_MISC = SMEM_BAR + NUM_BARS * 8;  // tmem base (4 B) + abort flag (4 B)
+constexpr int SMEM_USED = SMEM_MISC + 16;
+constexpr int SMEM_ALLOC = SMEM_USED + 1024;  // slack for manual 1 KiB alignment
+
+constexpr long long WAIT_BUDGET_CYCLES = 400000000LL;  // ~0.2 s at 1.9 GHz
+
+struct GemmArgs {
+  int m, n, k, batch;
+  int tiles_m, tiles_n;
+  int a_mn_major, b_mn_major;
+  int a_batched, b_batched;
+  int relu;
+  int out_f32;
+  int* status;
+};
+
+// ---------------------------------------------------------------- PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false once the CTA-wide abort flag is up or the cycle
+// budget is spent (raising the flag itself in that case).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 0xff) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > WAIT_BUDGET_CYCLES) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1,
+                                             int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_store_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives row
+// (lane base + i) of the accumulator.
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor for a 128B-swizzled tile (sm_100 format):
+//   [0,14) start address >> 4, [16,30) leading byte offset >> 4,
+//   [32,46) stride byte offset >> 4, [46,48) version = 1, [61,64) layout = 2.
+// K-major : rows of 64 K-elements; 8-row groups SBO = 1024 B apart; LBO unused.
+// MN-major: rows of 64 MN-elements, one row per K index; 8-row K groups are
+//           SBO = 1024 B apart, 64-element MN groups are LBO = 8192 B apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes,
+                                                   uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(lbo_bytes >> 4) << 16;
+  d |= (uint64_t)(sbo_bytes >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::f16: fp32 accumulator, bf16 A and B,
+// major bits, N >> 3 at [17,23), M >> 4 at [24,29).
+__device__ __forceinline__ uint32_t make_idesc(int a_mn, int b_mn) {
+  uint32_t d = 0;
+  d |= 1u << 4;   // D format fp32
+  d |= 1u << 7;   // A format bf16
+  d |= 1u << 10;  // B format bf16
+  d |= (uint32_t)(a_mn & 1) << 15;
+  d |= (uint32_t)(b_mn & 1) << 16;
+  d |= (uint32_t)(BN >> 3) << 17;
+  d |= (uint32_t)(BM >> 4) << 24;
+  return d;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// ------------------------------------------------------------------ the kernel
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+einsum_gemm_tcgen05(const __grid_constant__ CUtensorMap map_a,
+                    const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_c, const GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  // Swizzled tiles need 1 KiB alignment.
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + SMEM_BAR;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + SMEM_MISC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SMEM_MISC + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tmem_full_bar(b), 1);
+      mbar_init(tmem_empty_bar(b), EPI_WARPS);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_base + SMEM_MISC),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_kb = (args.k + BK - 1) / BK;
+  const long long tiles_per_batch = (long long)args.tiles_m * args.tiles_n;
+  const long long num_tiles = tiles_per_batch * args.batch;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int b = (int)(t / tiles_per_batch);
+        const int r = (int)(t % tiles_per_batch);
+        const int m0 = (r / args.tiles_n) * BM;
+        const int n0 = (r % args.tiles_n) * BN;
+        const int ab = args.a_batched ? b : 0;
+        const int bb = args.b_batched ? b : 0;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(full_bar(stage), A_STAGE_BYTES + B_STAGE_BYTES);
+          const uint32_t sa = smem_base + SMEM_A + stage * A_STAGE_BYTES;
+          const uint32_t sb = smem_base + SMEM_B + stage * B_STAGE_BYTES;
+          const int k0 = kb * BK;
+          if (args.a_mn_major) {
+#pragma unroll
+            for (int g = 0; g < BM / 64; ++g)
+              tma_load_3d(sa + g * MN_GROUP_BYTES, &map_a, full_bar(stage), m0 + g * 64, k0, ab);
+          } else {
+            tma_load_3d(sa, &map_a, full_bar(stage), k0, m0, ab);
+          }
+          if (args.b_mn_major) {
+#pragma unroll
+            for (int g = 0; g < BN / 64; ++g)
+              tma_load_3d(sb + g * MN_GROUP_BYTES, &map_b, full_bar(stage), n0 + g * 64, k0, bb);
+          } else {
+            tma_load_3d(sb, &map_b, full_bar(stage), k0, n0, bb);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok && args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(args.a_mn_major, args.b_mn_major);
+      const uint32_t a_lbo = args.a_mn_major ? MN_GROUP_BYTES : 16;
+      const uint32_t b_lbo = args.b_mn_major ? MN_GROUP_BYTES : 16;
+      // bytes to advance the start address per UMMA_K step inside a stage
+      const uint32_t a_kstep = args.a_mn_major ? UMMA_K * 128 : UMMA_K * 2;
+      const uint32_t b_kstep = args.b_mn_major ? UMMA_K * 128 : UMMA_K * 2;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      long long local = 0;
+      for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+        const int buf = (int)(local & 1);
+        const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+        if (!mbar_wait(tmem_empty_bar(buf), acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + SMEM_A + stage * A_STAGE_BYTES;
+          const uint32_t sb = smem_base + SMEM_B + stage * B_STAGE_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+            const uint64_t da = make_smem_desc(sa + ks * a_kstep, a_lbo, 1024);
+            const uint64_t db = make_smem_desc(sb + ks * b_kstep, b_lbo, 1024);
+            tc_mma_bf16(d_tmem, da, db, idesc, (kb | ks) != 0 ? 1u : 0u);
+          }
+          tc_commit(empty_bar(stage));  // frees the stage once these MMAs retire
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(tmem_full_bar(buf));  // accumulator ready for the epilogue
+      }
+      if (!ok && args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int ew = warp - 2;
+    uint8_t* stage_buf = smem + SMEM_EPI + ew * 2 * EPI_BUF_BYTES;
+    const uint32_t stage_u32 = smem_base + SMEM_EPI + ew * 2 * EPI_BUF_BYTES;
+    const int cols_per_store = args.out_f32 ? 32 : 64;  // 128 B of output per row
+    bool ok = true;
+    long long local = 0;
+    int store_idx = 0;
+    for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+      const int buf = (int)(local & 1);
+      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+      const int b = (int)(t / tiles_per_batch);
+      const int r = (int)(t % tiles_per_batch);
+      const int m0 = (r / args.tiles_n) * BM;
+      const int n0 = (r % args.tiles_n) * BN;
+      // Warp-uniform outcome: the .sync.aligned TMEM loads below need all lanes.
+      ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), acc_phase, abort_flag));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+      const bool rows_live = (m0 + q * 32) < args.m;
+      for (int c0 = 0; c0 < BN; c0 += cols_per_store) {
+        if (n0 + c0 >= args.n || !rows_live) break;  // fully clipped: nothing to store
+        const int sbuf = store_idx & 1;
+        // The store issued two steps ago read from this staging buffer.
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint8_t* row = stage_buf + sbuf * EPI_BUF_BYTES + lane * 128;
+        const int sw = lane & 7;
+        if (args.out_f32) {
+          uint32_t v[32];
+          tc_ld_32x32(t_row + c0, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 o;
+            o.x = __uint_as_float(v[4 * j + 0]);
+            o.y = __uint_as_float(v[4 * j + 1]);
+            o.z = __uint_as_float(v[4 * j + 2]);
+            o.w = __uint_as_float(v[4 * j + 3]);
+            if (args.relu) {
+              o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f);
+              o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f);
+            }
+            *reinterpret_cast<float4*>(row + ((j ^ sw) << 4)) = o;
+          }
+        } else {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t v[32];
+            tc_ld_32x32(t_row + c0 + h * 32, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                f[e] = __uint_as_float(v[8 * j + e]);
+                if (args.relu) f[e] = fmaxf(f[e], 0.f);
+              }
+              uint4 o;
+              o.x = pack_bf16x2(f[0], f[1]);
+              o.y = pack_bf16x2(f[2], f[3]);
+              o.z = pack_bf16x2(f[4], f[5]);
+              o.w = pack_bf16x2(f[6], f[7]);
+              *reinterpret_cast<uint4*>(row + (((h * 4 + j) ^ sw) << 4)) = o;
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_3d(&map_c, stage_u32 + sbuf * EPI_BUF_BYTES, n0 + c0, m0 + q * 32, b);
+          tma_store_commit();
+        }
+        ++store_idx;
+      }
+      // All tcgen05.ld of this accumulator have completed (wait::ld above).
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
+    }
+    if (lane == 0) tma_store_wait_all();
+    if (!ok && lane == 0 && args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 3-D map {inner, outer, batch} with a {box_inner, box_outer, 1} box, 128B swizzle.
+int encode_map(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base,
+               int64_t inner, int64_t outer, int64_t batch, int64_t outer_stride,
+               int64_t batch_stride, int box_inner, int box_outer, const char* what) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(MTFC_ERR_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)batch};
+  // Strides of extent-1 dims are never used for addressing but must still be
+  // valid (non-zero multiples of 16 bytes).
+  int64_t os = outer_stride * elem_bytes;
+  if (outer == 1 || os <= 0) os = ((inner * elem_bytes + 15) / 16) * 16;
+  int64_t bs = batch_stride * elem_bytes;
+  if (batch == 1 || bs <= 0) bs = os * outer;
+  cuuint64_t strides[2] = {(cuuint64_t)os, (cuuint64_t)bs};
+  cuuint32_t box[3] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(MTFC_ERR_SHAPE,
+                "tensor map for %s rejected (CUresult %d): inner=%lld outer=%lld batch=%lld "
+                "strides=%lld,%lld B",
+                what, (int)r, (long long)inner, (long long)outer, (long long)batch, (long long)os,
+                (long long)bs);
+  return MTFC_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Operand layout classification: 0 = K-major, 1 = MN-major, -1 = not TMA-able.
+int classify(int64_t mn, int64_t k, int64_t s_mn, int64_t s_k, int64_t batch, int64_t s_batch) {
+  if (batch > 1 && (s_batch % 8 != 0 || s_batch <= 0)) return -1;
+  if ((s_k == 1 || k == 1) && (mn == 1 || (s_mn % 8 == 0 && s_mn >= k))) return 0;
+  if ((s_mn == 1 || mn == 1) && (k == 1 || (s_k % 8 == 0 && s_k >= mn))) return 1;
+  return -1;
+}
+
+}  // namespace
+
+bool gemm_tcgen05_eligible(const mtfc_gemm_desc* d, const void* a, const void* b, const void* c) {
+  if (d->in_dtype != MTFC_BF16) return false;
+  if (d->out_dtype != MTFC_BF16 && d->out_dtype != MTFC_F32) return false;
+  if (d->batch < 1 || d->m < 1 || d->n < 1 || d->k < 1) return false;
+  if (d->m > INT32_MAX || d->n > INT32_MAX || d->k > INT32_MAX || d->batch > INT32_MAX)
+    return false;
+  if (!aligned16(a) || !aligned16(b) || !aligned16(c)) return false;
+  const bool a_b = d->batch > 1 && d->a_batch != 0;
+  const bool b_b = d->batch > 1 && d->b_batch != 0;
+  if (classify(d->m, d->k, d->a_m, d->a_k, a_b ? d->batch : 1, d->a_batch) < 0) return false;
+  if (classify(d->n, d->k, d->b_n, d->b_k, b_b ? d->batch : 1, d->b_batch) < 0) return false;
+  const int64_t oe = d->out_dtype == MTFC_F32 ? 4 : 2;
+  if (d->n > 1 && d->c_n != 1) return false;
+  if (d->m > 1 && ((d->c_m * oe) % 16 != 0 || d->c_m < d->n)) return false;
+  if (d->batch > 1 && ((d->c_batch * oe) % 16 != 0 || d->c_batch <= 0)) return false;
+  return true;
+}
+
+int gemm_tcgen05_launch(const mtfc_gemm_desc* d, const void* a, const void* b, void* c,
+                        cudaStream_t stream) {
+  const bool a_b = d->batch > 1 && d->a_batch != 0;
+  const bool b_b = d->batch > 1 && d->b_batch != 0;
+  const int a_major = classify(d->m, d->k, d->a_m, d->a_k, a_b ? d->batch : 1, d->a_batch);
+  const int b_major = classify(d->n, d->k, d->b_n, d->b_k, b_b ? d->batch : 1, d->b_batch);
+  if (a_major < 0 || b_major < 0) return fail(MTFC_ERR_SHAPE, "operand layout not TMA-able");
+
+  CUtensorMap map_a, map_b, map_c;
+  int rc;
+  if (a_major == 0)
+    rc = encode_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, d->k, d->m,
+                    a_b ? d->batch : 1, d->a_m, d->a_batch, BK, BM, "A (K-major)");
+  else
+    rc = encode_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, d->m, d->k,
+                    a_b ? d->batch : 1, d->a_k, d->a_batch, 64, BK, "A (M-major)");
+  if (rc != MTFC_OK) return rc;
+  if (b_major == 0)
+    rc = encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b, d->k, d->n,
+                    b_b ? d->batch : 1, d->b_n, d->b_batch, BK, BN, "B (K-major)");
+  else
+    rc = encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b, d->n, d->k,
+                    b_b ? d->batch : 1, d->b_k, d->b_batch, 64, BK, "B (N-major)");
+  if (rc != MTFC_OK) return rc;
+  const bool out_f32 = d->out_dtype == MTFC_F32;
+  rc = encode_map(&map_c, out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                  out_f32 ? 4 : 2, c, d->n, d->m, d->batch, d->c_m, d->c_batch, out_f32 ? 32 : 64,
+                  32, "C");
+  if (rc != MTFC_OK) return rc;
+
+  GemmArgs args;
+  args.m = (int)d->m;
+  args.n = (int)d->n;
+  args.k = (int)d->k;
+  args.batch = (int)d->batch;
+  args.tiles_m = (int)((d->m + BM - 1) / BM);
+  args.tiles_n = (int)((d->n + BN - 1) / BN);
+  args.a_mn_major = a_major;
+  args.b_mn_major = b_major;
+  args.a_batched = a_b ? 1 : 0;
+  args.b_batched = b_b ? 1 : 0;
+  args.relu = d->epilogue == MTFC_EPILOGUE_RELU;
+  args.out_f32 = out_f32 ? 1 : 0;
+  args.status = device_status_word();
+
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  MTFC_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    MTFC_CUDA(cudaFuncSetAttribute(einsum_gemm_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   SMEM_ALLOC));
+    attr_set[dev] = true;
+  }
+  const long long num_tiles = (long long)args.tiles_m * args.tiles_n * args.batch;
+  const int sms = sm_count();
+  const unsigned grid = (unsigned)(num_tiles < sms ? num_tiles : sms);
+  einsum_gemm_tcgen05<<<grid, NUM_THREADS, SMEM_ALLOC, stream>>>(map_a, map_b, map_c, args);
+  MTFC_LAUNCH_CHECK("einsum_gemm_tcgen05");
+  return MTFC_OK;
+}
+
+}  // namespace mtfc
