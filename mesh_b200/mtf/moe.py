@@ -1,0 +1,322 @@
+"""Top-2 mixture-of-experts layer on the mesh-tensor language.
+
+Follows mesh_tensorflow/transformer/moe.py: `transformer_moe_layer_v1`
+(191-525), `_top_2_gating` (1312-1513), `_split_into_groups` (1549-1582) and
+`HParams` (1585-1596).  Two graph forms compute the same layer:
+
+  * unfused: the reference's own op chain — softmax, two top_1, triangular
+    cumsum, dense [G,S,E,C] combine/dispatch tensors and two dense einsums;
+  * fused (default): three operations whose per-slice work is one kernel each
+    — gating (logits, softmax, top-2, capacity positions), dispatch (row
+    gather into expert slots) and combine (gated row scatter-add) — with the
+    same reshapes, and therefore the same alltoalls, in between.
+
+Both forms return (output, loss * moe_loss_coef).
+"""
+
+from __future__ import annotations
+
+from mesh_b200.mtf import graph as G
+from mesh_b200.mtf import layers
+from mesh_b200.mtf import ops as mtf
+from mesh_b200.mtf.graph import Operation, Tensor
+from mesh_b200.mtf.layout import tensor_dim_to_mesh_dim_size
+from mesh_b200.mtf.mesh_impl import LazyAllreduceSum
+from mesh_b200.mtf.shapes import Dimension, Shape
+
+
+class HParams(object):
+  """Attribute bag with the reference's MoE hyper-parameter names (moe.py:36-89)."""
+
+  def __init__(self, **kwargs):
+    self.moe_gating = "top_2"
+    self.moe_num_experts = 16
+    self.moe_loss_coef = 1e-2
+    self.moe_hidden_size = 4096
+    self.moe_group_size = 1024
+    self.moe_capacity_factor_train = 1.25
+    self.moe_capacity_factor_eval = 2.0
+    self.moe_use_second_place_loss = False
+    self.moe_second_policy_train = "random"
+    self.moe_second_policy_eval = "random"
+    self.moe_second_threshold_train = 0.2
+    self.moe_second_threshold_eval = 0.2
+    self.moe_dropout_rate = 0.0
+    self.moe_min_expert_capacity = 4
+    self.moe_use_fused_kernels = True
+    for k, v in kwargs.items():
+      if not hasattr(self, k):
+        raise ValueError("unknown hyper-parameter %s" % k)
+      setattr(self, k, v)
+
+
+def _split_into_groups(n, max_group_size, mesh_dim_size):
+  """Largest group_size <= max_group_size with num_groups a multiple of the
+  mesh dimension (moe.py:1549-1582)."""
+  if n % mesh_dim_size != 0:
+    raise ValueError("n=%d is not a multiple of mesh_dim_size=%d" % (n, mesh_dim_size))
+  num_groups = max(1, n // max_group_size)
+  while num_groups % mesh_dim_size != 0 or n % num_groups != 0:
+    num_groups += 1
+  return num_groups, n // num_groups
+
+
+def expert_capacity(group_size, num_experts, capacity_factor, min_capacity):
+  """Slots per expert and group (moe.py:368-371)."""
+  return max(min(group_size, int((group_size * capacity_factor) / num_experts)), min_capacity)
+
+
+def _second_policy(hparams, train):
+  if train:
+    return hparams.moe_second_policy_train, hparams.moe_second_threshold_train
+  return hparams.moe_second_policy_eval, hparams.moe_second_threshold_eval
+
+
+# ------------------------------------------------------------ unfused gating
+def _top_2_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate_weights,
+                  second_noise=None):
+  """The reference's op chain (moe.py:1380-1513); returns dispatch, combine, loss."""
+  group_size_dim = inputs.shape.dims[-2]
+  gate_inputs = mtf.to_float(inputs)
+  raw_gates = layers.dense(gate_inputs, experts_dim, use_bias=False,
+                           kernel_weights=gate_weights, name="gate")
+  raw_gates = mtf.softmax(raw_gates, experts_dim)
+  capacity_f = float(expert_capacity_dim.size)
+
+  gate_1, index_1 = mtf.top_1(raw_gates, experts_dim)
+  mask_1 = mtf.one_hot(index_1, experts_dim, dtype=raw_gates.dtype)
+  density_1_proxy = raw_gates
+  gates_without_top_1 = raw_gates * (1.0 - mask_1)
+  gate_2, index_2 = mtf.top_1(gates_without_top_1, experts_dim)
+  mask_2 = mtf.one_hot(index_2, experts_dim, dtype=raw_gates.dtype)
+
+  denom = gate_1 + gate_2 + 1e-9
+  gate_1 /= denom
+  gate_2 /= denom
+
+  density_1 = mtf.reduce_mean(mask_1, reduced_dim=group_size_dim)
+  density_1_proxy = mtf.reduce_mean(density_1_proxy, reduced_dim=group_size_dim)
+  loss = (mtf.reduce_mean(density_1_proxy * density_1)
+          * float(experts_dim.size * experts_dim.size))
+  if hparams.moe_use_second_place_loss:
+    raise NotImplementedError("second-place loss is not part of the lowered path")
+
+  policy, threshold = _second_policy(hparams, train)
+  if policy == "all":
+    pass
+  elif policy == "none":
+    mask_2 = mtf.zeros_like(mask_2)
+  elif policy == "threshold":
+    mask_2 *= mtf.to_float(mtf.greater(gate_2, threshold))
+  elif policy == "random":
+    if second_noise is None:
+      raise ValueError("policy 'random' needs the uniform noise tensor as an input")
+    mask_2 *= mtf.to_float(mtf.less(second_noise, gate_2 / max(threshold, 1e-9)))
+  else:
+    raise ValueError("Unknown policy %s" % policy)
+
+  position_in_expert_1 = mtf.cumsum(mask_1, group_size_dim, exclusive=True) * mask_1
+  mask_1 *= mtf.to_float(mtf.less(position_in_expert_1, capacity_f))
+  mask_1_count = mtf.reduce_sum(mask_1, reduced_dim=group_size_dim)
+  mask_1_flat = mtf.reduce_sum(mask_1, reduced_dim=experts_dim)
+  position_in_expert_1 = mtf.reduce_sum(position_in_expert_1, reduced_dim=experts_dim)
+  gate_1 *= mask_1_flat
+
+  position_in_expert_2 = mtf.cumsum(mask_2, group_size_dim, exclusive=True) + mask_1_count
+  position_in_expert_2 *= mask_2
+  mask_2 *= mtf.to_float(mtf.less(position_in_expert_2, capacity_f))
+  mask_2_flat = mtf.reduce_sum(mask_2, reduced_dim=experts_dim)
+  gate_2 *= mask_2_flat
+  position_in_expert_2 = mtf.reduce_sum(position_in_expert_2, reduced_dim=experts_dim)
+
+  combine_tensor = (
+      gate_1 * mask_1_flat
+      * mtf.one_hot(index_1, experts_dim)
+      * mtf.one_hot(mtf.to_int32(position_in_expert_1), expert_capacity_dim) +
+      gate_2 * mask_2_flat
+      * mtf.one_hot(index_2, experts_dim)
+      * mtf.one_hot(mtf.to_int32(position_in_expert_2), expert_capacity_dim))
+  combine_tensor = mtf.cast(combine_tensor, inputs.dtype)
+  loss = mtf.cast(loss, inputs.dtype)
+  dispatch_tensor = mtf.cast(mtf.cast(combine_tensor, G.bool_), combine_tensor.dtype)
+  aux = dict(index_1=index_1, index_2=index_2,
+             position_1=mtf.to_int32(position_in_expert_1),
+             position_2=mtf.to_int32(position_in_expert_2),
+             gate_1=gate_1, gate_2=gate_2, raw_gates=raw_gates)
+  return dispatch_tensor, combine_tensor, loss, aux
+
+
+# -------------------------------------------------------------- fused gating
+class Top2GatingOperation(Operation):
+  """Fused `_top_2_gating`: one kernel per slice instead of ~60 operations.
+
+  inputs [O,G,S,M] and gate weights [M,E] -> per token: expert indices,
+  slot positions (position >= capacity means dropped), gates after capacity
+  and bf16 rounding semantics, and the per-slice sum over groups of the
+  load-balancing loss.  Groups are independent, so any split of O or G over
+  the mesh is slice-local; the loss is a LazyAllreduceSum over the mesh axes
+  those dims are split over.
+  """
+
+  def __init__(self, inputs, gate_weights, experts_dim, capacity, policy, threshold,
+               second_noise=None, name=None):
+    xs = [inputs, gate_weights] + ([second_noise] if second_noise is not None else [])
+    super().__init__(xs, name=name or "top_2_gating")
+    token_shape = Shape(inputs.shape.dims[:-1])
+    self._experts_dim = experts_dim
+    self._capacity = capacity
+    self._policy = policy
+    self._threshold = threshold
+    self._outputs = (
+        [Tensor(self, token_shape, G.int32, index=i) for i in range(4)] +
+        [Tensor(self, token_shape, G.float32, index=4), Tensor(self, token_shape, G.float32, index=5),
+         Tensor(self, Shape([]), G.float32, index=6)])
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    ops = impl.slice_ops
+    x, w = self.inputs[0], self.inputs[1]
+    for d in (x.shape.dims[-2], x.shape.dims[-1], self._experts_dim):
+      if impl.tensor_dimension_to_mesh_axis(d) is not None:
+        raise ValueError("fused gating needs %s unsplit" % (d,))
+    capacity, policy, threshold = self._capacity, self._policy, self._threshold
+    num_groups_total = Shape(x.shape.dims[:-2]).size
+
+    def fn(xs, ws, *noise):
+      return ops.moe_top2_gating(xs, ws, capacity, policy, threshold,
+                                 noise[0] if noise else None, num_groups_total)
+    results = impl.slicewise(fn, *[lowering.tensors[t] for t in self.inputs])
+    for out, value in zip(self.outputs[:6], results[:6]):
+      lowering.set_tensor_lowering(out, value)
+    layout = impl.tensor_layout(Shape(x.shape.dims[:-2]))
+    mesh_axes = [a for a in layout.tensor_axis_to_mesh_axis if a is not None]
+    loss = results[6]
+    if mesh_axes:
+      loss = LazyAllreduceSum(impl, loss, mesh_axes)
+    lowering.set_tensor_lowering(self.outputs[6], loss)
+
+
+class MoeDispatchOperation(Operation):
+  """expert_inputs[O,E,G,C,M]: row gather replacing the dispatch einsum
+  `inputs[O,G,S,M] x dispatch[O,G,S,E,C]` (moe.py:443-447)."""
+
+  def __init__(self, inputs, routing, experts_dim, capacity_dim, name=None):
+    super().__init__([inputs] + list(routing), name=name or "moe_dispatch")
+    o, g, _, m = inputs.shape.dims
+    self._num_experts = experts_dim.size
+    self._capacity = capacity_dim.size
+    self._outputs = [Tensor(self, Shape([o, experts_dim, g, capacity_dim, m]), inputs.dtype)]
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    ops = impl.slice_ops
+    e, c = self._num_experts, self._capacity
+    fn = lambda xs, i1, i2, p1, p2, g1, g2: ops.moe_dispatch(xs, i1, i2, p1, p2, g1, g2, e, c)
+    lowering.set_tensor_lowering(
+        self.outputs[0], impl.slicewise(fn, *[lowering.tensors[t] for t in self.inputs]))
+
+
+class MoeCombineOperation(Operation):
+  """output[O,G,S,M]: gated two-row gather replacing the combine einsum
+  `expert_output[O,E,G,C,M] x combine[O,G,S,E,C]` (moe.py:509-510)."""
+
+  def __init__(self, expert_output, routing, group_size_dim, name=None):
+    super().__init__([expert_output] + list(routing), name=name or "moe_combine")
+    o, _, g, _, m = expert_output.shape.dims
+    self._outputs = [Tensor(self, Shape([o, g, group_size_dim, m]), expert_output.dtype)]
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    ops = impl.slice_ops
+    fn = lambda ys, i1, i2, p1, p2, g1, g2: ops.moe_combine(ys, i1, i2, p1, p2, g1, g2)
+    lowering.set_tensor_lowering(
+        self.outputs[0], impl.slicewise(fn, *[lowering.tensors[t] for t in self.inputs]))
+
+
+# ------------------------------------------------------------------ the layer
+def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, layout,
+                             gate_weights, wi, wo, second_noise=None, activation=mtf.relu,
+                             return_aux=False):
+  """Top-2 MoE feed-forward layer (moe.py:191-525).
+
+  inputs: [<batch dims>, length, d_model]; gate_weights [d_model, experts_unsplit];
+  wi [experts, d_model, hidden]; wo [experts, hidden, output_dim].  `mesh_shape`
+  and `layout` are needed at graph-construction time to choose the number of
+  groups, exactly as in the reference.
+  """
+  orig_inputs = inputs
+  hidden_dim = wi.shape.dims[-1]
+  experts_dim = wi.shape.dims[0]
+  batch_and_length_dims, input_dim = orig_inputs.shape.dims[:-1], orig_inputs.shape.dims[-1]
+  if orig_inputs.shape.dims[0].name == "outer_batch":
+    outer_batch_dim, orig_batch_dim = orig_inputs.shape.dims[:2]
+  else:
+    outer_batch_dim, orig_batch_dim = Dimension("outer_batch", 1), orig_inputs.shape.dims[0]
+  n = Shape(batch_and_length_dims).size // outer_batch_dim.size
+  mesh_dim_size = tensor_dim_to_mesh_dim_size(layout, mesh_shape, orig_batch_dim)
+  num_groups, group_size = _split_into_groups(n, hparams.moe_group_size, mesh_dim_size)
+  group_size_dim = Dimension("group", group_size)
+  num_groups_dim = Dimension(orig_batch_dim.name, num_groups)
+  moe_input_dims = [outer_batch_dim, num_groups_dim, group_size_dim, input_dim]
+  inputs = mtf.reshape(inputs, moe_input_dims)
+
+  cf = hparams.moe_capacity_factor_train if train else hparams.moe_capacity_factor_eval
+  capacity = expert_capacity(group_size, experts_dim.size, cf, hparams.moe_min_expert_capacity)
+  capacity_dim = Dimension("expert_capacity", capacity)
+  experts_dim_unsplit = Dimension("expert_unsplit", experts_dim.size)
+  batch_dim_unsplit = Dimension("batch_unsplit", num_groups_dim.size)
+  if hparams.moe_gating != "top_2":
+    raise ValueError("only top_2 gating is implemented, got %s" % hparams.moe_gating)
+  if gate_weights.shape.dims[-1].name != experts_dim_unsplit.name:
+    gate_weights = mtf.reshape(gate_weights, Shape([gate_weights.shape.dims[0], experts_dim_unsplit]))
+  if second_noise is not None:
+    second_noise = mtf.reshape(second_noise, moe_input_dims[:-1])
+
+  aux = {}
+  fused = hparams.moe_use_fused_kernels
+  if fused:
+    policy, threshold = _second_policy(hparams, train)
+    gating = Top2GatingOperation(inputs, gate_weights, experts_dim_unsplit, capacity, policy,
+                                 threshold, second_noise=second_noise)
+    i1, i2, p1, p2, g1, g2, loss_sum = gating.outputs
+    routing = [i1, i2, p1, p2, g1, g2]
+    loss = mtf.cast(loss_sum, inputs.dtype)
+    aux = dict(index_1=i1, index_2=i2, position_1=p1, position_2=p2, gate_1=g1, gate_2=g2)
+    expert_inputs = MoeDispatchOperation(inputs, routing, experts_dim_unsplit,
+                                         capacity_dim).outputs[0]
+  else:
+    dispatch_tensor, combine_tensor, loss, aux = _top_2_gating(
+        inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights,
+        second_noise=second_noise)
+    expert_inputs = mtf.einsum(
+        [inputs, dispatch_tensor],
+        Shape([outer_batch_dim, experts_dim_unsplit, num_groups_dim, capacity_dim, input_dim]))
+
+  d_model_split_dim = Dimension("d_model_split", input_dim.size)
+  expert_inputs = mtf.reshape(expert_inputs, Shape(
+      [outer_batch_dim, experts_dim, batch_dim_unsplit, capacity_dim, d_model_split_dim]))
+  # split over batch -> split over experts (an alltoall when both are split)
+  expert_inputs = mtf.reshape(expert_inputs, Shape(
+      [outer_batch_dim, experts_dim, batch_dim_unsplit, capacity_dim, input_dim]))
+
+  h = layers.dense_product(expert_inputs, reduced_dims=expert_inputs.shape.dims[-1:],
+                           new_dims=[hidden_dim], expert_dims=[experts_dim],
+                           activation_functions=activation, use_bias=False,
+                           kernel_weights=wi, name="wi")
+  expert_output = layers.dense(h, output_dim, expert_dims=[experts_dim], use_bias=False,
+                               reduced_dims=h.shape.dims[-1:], kernel_weights=wo, name="wo")
+  expert_output = mtf.reshape(expert_output, Shape(
+      [outer_batch_dim, experts_dim_unsplit, num_groups_dim, capacity_dim, d_model_split_dim]))
+  # split over experts -> split over batch (the return alltoall)
+  expert_output = mtf.reshape(expert_output, Shape(
+      [outer_batch_dim, experts_dim_unsplit, num_groups_dim, capacity_dim, output_dim]))
+  moe_output_dims = moe_input_dims[:-1] + [output_dim]
+  if fused:
+    output = MoeCombineOperation(expert_output, routing, group_size_dim).outputs[0]
+  else:
+    output = mtf.einsum([expert_output, combine_tensor], Shape(moe_output_dims))
+  output = mtf.reshape(output, batch_and_length_dims + [output_dim])
+  loss = loss * hparams.moe_loss_coef
+  if return_aux:
+    return output, loss, aux
+  return output, loss

@@ -1,0 +1,911 @@
+"""Operations of the mesh-tensor language and their lowerings.
+
+Each Operation.lower() below issues the same MeshImpl calls, in the same
+order, as its counterpart in mesh_tensorflow/ops.py; the per-slice work is
+expressed against `mesh_impl.slice_ops` (the array library of the backend)
+where the reference closes over `tf.*`.  Only the operations the dense FFN,
+top-2 mixture-of-experts and attention layers are built from are present.
+"""
+
+from __future__ import annotations
+
+import functools
+
+import numpy as np
+
+from mesh_b200.mtf import graph as G
+from mesh_b200.mtf.graph import Operation, Tensor
+from mesh_b200.mtf.mesh_impl import LazyAllreduceSum, expand_dims_to
+from mesh_b200.mtf.shapes import (Dimension, Shape, convert_to_dimension,
+                                  convert_to_shape, shape_union)
+
+
+# --------------------------------------------------------------------- import
+class ImportOperation(Operation):
+  """Brings a host array into the graph (mesh_tensorflow/ops.py:3854-3890)."""
+
+  def __init__(self, mesh, value, shape, dtype, name=None):
+    super().__init__([], mesh=mesh, name=name or "import")
+    self._value = value
+    self._outputs = [Tensor(self, shape, dtype)]
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    lowering.set_tensor_lowering(
+        self.outputs[0], impl.import_tf_tensor(self.outputs[0], self._value))
+
+
+_NP_TO_DTYPE = {"float32": G.float32, "float64": G.float32, "int32": G.int32,
+                "int64": G.int32, "bool": G.bool_}
+
+
+def import_tf_tensor(mesh, tf_tensor, shape=None, name=None, dtype=None):
+  """Imports a host array (numpy, or anything np.asarray accepts) as a Tensor.
+
+  `dtype` selects the on-device type; values are rounded to it on import
+  (mtf.bfloat16 rounds float32 data to nearest-even).
+  """
+  value = np.asarray(tf_tensor)
+  if shape is None:
+    shape = Shape([])
+    if value.shape != ():
+      raise ValueError("shape must be given for a non-scalar import")
+  shape = convert_to_shape(shape)
+  if list(value.shape) != shape.to_integer_list:
+    raise ValueError("Incompatible shape: array %s vs %s" % (value.shape, shape))
+  if dtype is None:
+    dtype = _NP_TO_DTYPE.get(value.dtype.name)
+    if dtype is None:
+      raise ValueError("cannot infer an mtf dtype from %s" % value.dtype)
+  return ImportOperation(mesh, value, shape, dtype, name=name).outputs[0]
+
+
+import_tensor = import_tf_tensor
+
+
+def constant(mesh, value, shape=None, dtype=G.float32):
+  """A tensor filled with `value` (mesh_tensorflow/ops.py:4337-4378)."""
+  shape = convert_to_shape(shape) if shape is not None else Shape([])
+  return ConstantOperation(mesh, value, shape, dtype).outputs[0]
+
+
+class ConstantOperation(Operation):
+
+  def __init__(self, mesh, value, shape, dtype, name=None):
+    super().__init__([], mesh=mesh, name=name or "constant")
+    self._value = value
+    self._outputs = [Tensor(self, shape, dtype)]
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    slice_shape = impl.slice_shape(self.outputs[0].shape)
+    ops = impl.slice_ops
+    dtype = self.outputs[0].dtype
+    value = self._value
+    lowering.set_tensor_lowering(
+        self.outputs[0],
+        impl.slicewise(lambda pnum: ops.fill(slice_shape, value, dtype), impl.laid_out_pnum()))
+
+
+def zeros(mesh, shape, dtype=G.float32):
+  return constant(mesh, 0, shape=convert_to_shape(shape), dtype=dtype)
+
+
+def zeros_like(t):
+  return zeros(t.mesh, t.shape, dtype=t.dtype)
+
+
+def mtf_range(mesh, dim, dtype, name=None):
+  """[0, dim.size) along `dim`, imported like any host tensor (ops.py:5544-5584)."""
+  dim = convert_to_dimension(dim)
+  np_dtype = np.int32 if dtype.is_integer else np.float32
+  return ImportOperation(mesh, np.arange(dim.size, dtype=np_dtype), Shape([dim]), dtype,
+                         name=name or "range").outputs[0]
+
+
+# ------------------------------------------------------------------ slicewise
+class SlicewiseOperation(Operation):
+  """Applies a per-slice function to same-shaped inputs (ops.py:1651-1723)."""
+
+  def __init__(self, slice_fn, inputs, output_shape, output_dtype, splittable_dims,
+               name=None):
+    super().__init__(inputs, name=name or "slicewise")
+    self._slice_fn = slice_fn
+    self._outputs = [Tensor(self, output_shape, output_dtype)]
+    self._splittable_dims = [convert_to_dimension(d).name if not isinstance(d, str) else d
+                             for d in splittable_dims]
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    for t in self.inputs + self.outputs:
+      layout = impl.tensor_layout(t)
+      for d, mesh_axis in zip(t.shape.dims, layout.tensor_axis_to_mesh_axis):
+        if mesh_axis is not None and d.name not in self._splittable_dims:
+          raise ValueError("dimension %s is not declared as splittable" % (d,))
+    ops = impl.slice_ops
+    fn = self._slice_fn
+    value = impl.slicewise(lambda *xs: fn(ops, *xs),
+                           *[lowering.tensors[x] for x in self.inputs])
+    lowering.set_tensor_lowering(self.outputs[0], value)
+
+
+def cwise(slice_fn, xs, output_dtype=None, name=None):
+  """Component-wise op on same-shaped tensors; `slice_fn(ops, *slices)`."""
+  return SlicewiseOperation(slice_fn, xs, xs[0].shape, output_dtype or xs[0].dtype,
+                            splittable_dims=xs[0].shape.dims, name=name or "cwise").outputs[0]
+
+
+def _unary(name):
+  def api(x, name=name):
+    return cwise(lambda ops, xs: ops.unary(name, xs), [x], name=name)
+  api.__name__ = name
+  return api
+
+
+relu = _unary("relu")
+exp = _unary("exp")
+log = _unary("log")
+negative = _unary("negative")
+reciprocal = _unary("reciprocal")
+sqrt = _unary("sqrt")
+rsqrt = _unary("rsqrt")
+square = _unary("square")
+tanh = _unary("tanh")
+sigmoid = _unary("sigmoid")
+sign = _unary("sign")
+logical_not = _unary("logical_not")
+identity = _unary("identity")
+stop_gradient = identity
+
+
+def cast(x, dtype, name="cast"):
+  if dtype == x.dtype:
+    return x
+  return cwise(lambda ops, xs: ops.cast(xs, dtype), [x], output_dtype=dtype, name=name)
+
+
+def to_float(x, name="to_float"):
+  return cast(x, G.float32, name=name)
+
+
+def to_bfloat16(x, name="to_bfloat16"):
+  return cast(x, G.bfloat16, name=name)
+
+
+def to_int32(x, name="to_int32"):
+  return cast(x, G.int32, name=name)
+
+
+class ScalarMultiplyOperation(Operation):
+
+  def __init__(self, x, scalar, name=None):
+    super().__init__([x], name=name or "scalar_mul")
+    self._outputs = [Tensor(self, x.shape, x.dtype)]
+    self._scalar = scalar
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    ops, c = impl.slice_ops, self._scalar
+    lowering.set_tensor_lowering(
+        self.outputs[0],
+        impl.slicewise(lambda xs: ops.binary("multiply", xs, c), lowering.tensors[self.inputs[0]]))
+
+
+class ScalarAddOperation(Operation):
+
+  def __init__(self, x, scalar, name=None):
+    super().__init__([x], name=name or "scalar_add")
+    self._outputs = [Tensor(self, x.shape, x.dtype)]
+    self._scalar = scalar
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    ops, c = impl.slice_ops, self._scalar
+    lowering.set_tensor_lowering(
+        self.outputs[0],
+        impl.slicewise(lambda xs: ops.binary("add", xs, c), lowering.tensors[self.inputs[0]]))
+
+
+# --------------------------------------------------------------------- binary
+def is_subsequence(short, long):
+  it = iter(long)
+  return all(d in it for d in short)
+
+
+def _infer_binary_broadcast_shape(shape1, shape2, given_output_shape=None):
+  shape1, shape2 = convert_to_shape(shape1), convert_to_shape(shape2)
+  given_output_shape = convert_to_shape(given_output_shape)
+  if given_output_shape is not None:
+    return given_output_shape
+  if is_subsequence(shape1.dims, shape2.dims):
+    return shape2
+  if is_subsequence(shape2.dims, shape1.dims):
+    return shape1
+  return Shape(shape1.dims + [d for d in shape2.dims if d not in shape1.dims])
+
+
+def binary_arguments_to_tensors(x1, x2):
+  t1, t2 = isinstance(x1, Tensor), isinstance(x2, Tensor)
+  if not t1 and not t2:
+    raise ValueError("at least one of x1 and x2 must be an mtf Tensor")
+  if t1 and t2:
+    return x1, x2
+  if t1:
+    return x1, import_tf_tensor(x1.mesh, np.asarray(x2), Shape([]), dtype=x1.dtype)
+  return import_tf_tensor(x2.mesh, np.asarray(x1), Shape([]), dtype=x2.dtype), x2
+
+
+class BinaryOpWithBroadcasting(Operation):
+  """Binary op with named-dim broadcasting (mesh_tensorflow/ops.py:2044-2084)."""
+
+  def __init__(self, op_name, x1, x2, output_shape, output_dtype, name=None):
+    super().__init__([x1, x2], name=name or op_name)
+    if x1.dtype != x2.dtype:
+      raise ValueError("Dtypes must be equal- got %s and %s" % (x1.dtype, x2.dtype))
+    self._outputs = [Tensor(self, output_shape, output_dtype)]
+    self._op_name = op_name
+
+  def lower(self, lowering):
+    x1, x2 = self.inputs
+    out = self.outputs[0]
+    lx1, lx2 = lowering.tensors[x1], lowering.tensors[x2]
+    impl = lowering.mesh_impl(self)
+    ops = impl.slice_ops
+    if x1.shape != out.shape:
+      lx1 = impl.slicewise(lambda xs: expand_dims_to(ops, xs, x1.shape, out.shape), lx1)
+    if x2.shape != out.shape:
+      lx2 = impl.slicewise(lambda xs: expand_dims_to(ops, xs, x2.shape, out.shape), lx2)
+    op_name = self._op_name
+    fn = lambda a, b: ops.binary(op_name, a, b)
+    if op_name == "add":
+      y = impl.slicewise_delay_allreduce(fn, lx1, lx2)
+    else:
+      y = impl.slicewise(fn, lx1, lx2)
+    lowering.set_tensor_lowering(out, y)
+
+
+def binary_op_with_broadcasting(op_name, x1, x2, output_shape=None, output_dtype=None):
+  x1, x2 = binary_arguments_to_tensors(x1, x2)
+  output_shape = _infer_binary_broadcast_shape(x1.shape, x2.shape, output_shape)
+  return BinaryOpWithBroadcasting(op_name, x1, x2, output_shape,
+                                  output_dtype or x1.dtype).outputs[0]
+
+
+def _compare(op_name):
+  def api(x1, x2, output_shape=None):
+    return binary_op_with_broadcasting(op_name, x1, x2, output_shape=output_shape,
+                                       output_dtype=G.bool_)
+  api.__name__ = op_name
+  return api
+
+
+less = _compare("less")
+greater = _compare("greater")
+less_equal = _compare("less_equal")
+greater_equal = _compare("greater_equal")
+equal = _compare("equal")
+not_equal = _compare("not_equal")
+logical_and = _compare("logical_and")
+logical_or = _compare("logical_or")
+
+
+def maximum(x1, x2, output_shape=None):
+  return binary_op_with_broadcasting("maximum", x1, x2, output_shape=output_shape)
+
+
+def minimum(x1, x2, output_shape=None):
+  return binary_op_with_broadcasting("minimum", x1, x2, output_shape=output_shape)
+
+
+def add(x1, x2, output_shape=None, name=None):
+  output_shape = convert_to_shape(output_shape)
+  if not isinstance(x2, Tensor):
+    return ScalarAddOperation(x1, x2).outputs[0]
+  x1, x2 = binary_arguments_to_tensors(x1, x2)
+  return BinaryOpWithBroadcasting(
+      "add", x1, x2, _infer_binary_broadcast_shape(x1.shape, x2.shape, output_shape),
+      x1.dtype, name=name or "add").outputs[0]
+
+
+def add_n(xs):
+  return functools.reduce(add, xs) if xs else 0
+
+
+def sub(x1, x2, output_shape=None, name=None):
+  output_shape = convert_to_shape(output_shape)
+  if not isinstance(x2, Tensor):
+    return ScalarAddOperation(x1, -x2).outputs[0]
+  x1, x2 = binary_arguments_to_tensors(x1, x2)
+  return add(x1, negative(x2), output_shape=output_shape)
+
+
+def multiply(x1, x2, output_shape=None, name=None):
+  """A product is an einsum whose output keeps every dim (ops.py:5135-5153)."""
+  if not isinstance(x2, Tensor):
+    return ScalarMultiplyOperation(x1, x2).outputs[0]
+  x1, x2 = binary_arguments_to_tensors(x1, x2)
+  return einsum([x1, x2],
+                output_shape=_infer_binary_broadcast_shape(x1.shape, x2.shape, output_shape))
+
+
+def divide(x1, x2, output_shape=None, name=None):
+  """x1 * reciprocal(x2) (mesh_tensorflow/ops.py:5156-5172)."""
+  output_shape = convert_to_shape(output_shape)
+  if not isinstance(x2, Tensor):
+    return ScalarMultiplyOperation(x1, 1.0 / x2).outputs[0]
+  x1, x2 = binary_arguments_to_tensors(x1, x2)
+  return multiply(x1, reciprocal(x2), output_shape=output_shape)
+
+
+# ------------------------------------------------------------ reduce / einsum
+def _reduce_helper(ops, input_shape, output_shape, input_tensor_layout, reduction="SUM"):
+  """Per-slice reduction fn and the mesh axes it leaves unreduced (ops.py:2267-2299)."""
+  reduce_axes = [i for i, d in enumerate(input_shape.dims) if d not in output_shape.dims]
+  kept = [d for d in input_shape.dims if d in output_shape.dims]
+  perm = [kept.index(d) for d in output_shape.dims]
+
+  def reduce_slice_fn(xs):
+    ret = xs
+    if reduce_axes:
+      ret = ops.reduce(reduction, xs, reduce_axes)
+    if perm != list(range(len(perm))):
+      ret = ops.transpose(ret, perm)
+    return ret
+  reduced_mesh_axes = [input_tensor_layout[i] for i in reduce_axes
+                       if input_tensor_layout[i] is not None]
+  return reduce_slice_fn, reduced_mesh_axes
+
+
+class ReduceOperation(Operation):
+  """Output dims are a subset of input dims, in any order (ops.py:2302-2338)."""
+
+  def __init__(self, x, output_shape, reduction, name=None):
+    super().__init__([x], name=name or "reduce")
+    self._outputs = [Tensor(self, output_shape, x.dtype)]
+    self._reduction = reduction
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    x, out = self.inputs[0], self.outputs[0]
+    fn, reduced_mesh_axes = _reduce_helper(
+        impl.slice_ops, x.shape, out.shape, impl.tensor_layout(x), self._reduction)
+    y = impl.slicewise(fn, lowering.tensors[x])
+    if reduced_mesh_axes:
+      def add_counter_fn():
+        lowering.add_counter("allreduce/%s/reduce_op" % reduced_mesh_axes,
+                             lowering.laid_out_size(out))
+      if self._reduction == "SUM":
+        y = LazyAllreduceSum(impl, y, reduced_mesh_axes, add_counter_fn=add_counter_fn)
+      else:
+        y = impl.allreduce(y, reduced_mesh_axes, self._reduction)
+        add_counter_fn()
+    lowering.set_tensor_lowering(out, y)
+
+
+def _reduction_output_shape(x, output_shape, reduced_dim):
+  if output_shape is None:
+    if reduced_dim is None:
+      return Shape([])
+    if reduced_dim not in x.shape.dims:
+      raise ValueError("reduced_dim=%s not in x.shape.dims=%s" % (reduced_dim, x.shape))
+    return x.shape - reduced_dim
+  if reduced_dim is not None:
+    raise ValueError("do not specify both reduced_dim and output_shape")
+  return output_shape
+
+
+def _reduce_api(reduction):
+  def api(x, disable_positional_args=None, output_shape=None, reduced_dim=None, name=None):
+    assert disable_positional_args is None
+    output_shape = _reduction_output_shape(
+        x, convert_to_shape(output_shape), convert_to_dimension(reduced_dim))
+    if output_shape == x.shape:
+      return x
+    return ReduceOperation(x, output_shape, reduction, name=name).outputs[0]
+  return api
+
+
+reduce_sum = _reduce_api("SUM")
+reduce_max = _reduce_api("MAX")
+reduce_min = _reduce_api("MIN")
+
+
+def reduce_mean(x, disable_positional_args=None, output_shape=None, reduced_dim=None,
+                name=None):
+  """reduce_sum scaled by the size ratio (mesh_tensorflow/ops.py:4778-4808)."""
+  assert disable_positional_args is None
+  output_shape = _reduction_output_shape(
+      x, convert_to_shape(output_shape), convert_to_dimension(reduced_dim))
+  if output_shape == x.shape:
+    return x
+  return reduce_sum(x, output_shape=output_shape) * (output_shape.size / x.shape.size)
+
+
+def _einsum_equation(input_shapes, output_shape):
+  """Letters in first-appearance order over inputs then output (ops.py:5346-5371)."""
+  letters = {}
+  parts = []
+  for shape in list(input_shapes) + [output_shape]:
+    term = []
+    for d in shape.dims:
+      if d not in letters:
+        letters[d] = chr(ord("a") + len(letters))
+      term.append(letters[d])
+    parts.append("".join(term))
+  return ",".join(parts[:-1]) + "->" + parts[-1]
+
+
+def _einsum_helper(input_shapes, output_shape, mesh_impl, floating):
+  """Per-slice einsum fn and the mesh axes of split contracted dims (ops.py:2784-2823).
+
+  When some operand or the output already spans every dimension, the product
+  is formed by broadcast-multiply-reduce (`einsum_naive`); otherwise, for
+  floating types, by the backend's contraction hook `mesh_impl.einsum`.
+  """
+  ops = mesh_impl.slice_ops
+  union = shape_union(input_shapes)
+  full_shapes = [s for s in list(input_shapes) + [output_shape] if s.ndims == union.ndims]
+  full_shape = full_shapes[0] if full_shapes else union
+  layout = mesh_impl.tensor_layout(full_shape)
+  reduce_axes = [i for i, d in enumerate(full_shape.dims) if d not in output_shape.dims]
+  reduced_mesh_axes = [layout[i] for i in reduce_axes if layout[i] is not None]
+  equation = _einsum_equation(input_shapes, output_shape)
+  if full_shapes or not floating:
+    fn = lambda *slices: ops.einsum_naive(equation, *slices)
+  else:
+    fn = lambda *slices: mesh_impl.einsum(equation, *slices)
+  return fn, reduced_mesh_axes
+
+
+class EinsumOperation(Operation):
+  """Einstein summation over named dims (mesh_tensorflow/ops.py:2826-2880)."""
+
+  def __init__(self, inputs, output_shape, name=None):
+    super().__init__(inputs, name=name or "einsum")
+    if not inputs:
+      raise ValueError("Einsum needs at least one input")
+    for x in inputs:
+      if x.dtype != inputs[0].dtype:
+        raise ValueError("Input dtypes must be equal got %s" % ([y.dtype for y in inputs],))
+    self._outputs = [Tensor(self, output_shape, inputs[0].dtype)]
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    xs = self.inputs
+    in_dims = set(sum([x.shape.dims for x in xs], []))
+    output_shape = self.outputs[0].shape
+    intersection = Shape([d for d in output_shape.dims if d in in_dims])
+    fn, reduced_mesh_axes = _einsum_helper(
+        [x.shape for x in xs], intersection, impl, xs[0].dtype.is_floating)
+    y = impl.slicewise(fn, *[lowering.tensors[x] for x in xs])
+    if reduced_mesh_axes:
+      def add_counter_fn():
+        lowering.add_counter("allreduce/%s/einsum_op" % reduced_mesh_axes,
+                             impl.laid_out_size(intersection))
+      y = LazyAllreduceSum(impl, y, reduced_mesh_axes, add_counter_fn=add_counter_fn)
+    if intersection != output_shape:
+      y = impl.broadcast_impl(y, intersection, output_shape)
+    lowering.set_tensor_lowering(self.outputs[0], y)
+    computation_shape = Shape(sorted(in_dims))
+    lowering.add_counter("einsum", impl.laid_out_size(computation_shape))
+    lowering.add_counter("einsum_unique", computation_shape.size)
+
+
+def einsum(xs, output_shape=None, reduced_dims=None, name=None):
+  """Einstein summation; exactly one of output_shape / reduced_dims may be given
+  (mesh_tensorflow/ops.py:4656-4726)."""
+  output_shape = convert_to_shape(output_shape)
+  union = shape_union([x.shape for x in xs])
+  if output_shape is None:
+    reduced = [convert_to_dimension(d) for d in (reduced_dims or [])]
+    output_shape = Shape([d for d in union.dims if d not in reduced])
+  elif reduced_dims is not None:
+    computed = [d for d in union.dims if d not in output_shape.dims]
+    if set(computed) != set(convert_to_dimension(d) for d in reduced_dims):
+      raise ValueError("reduced_dims and output_shape disagree")
+  return EinsumOperation(xs, output_shape, name=name).outputs[0]
+
+
+def matmul(a, b, output_shape=None, reduced_dims=None, name=None):
+  return einsum([a, b], output_shape=output_shape, reduced_dims=reduced_dims, name=name)
+
+
+class BroadcastOperation(Operation):
+  """Adds dimensions (mesh_tensorflow/ops.py:2201-2225)."""
+
+  def __init__(self, x, output_shape, name=None):
+    super().__init__([x], name=name or "broadcast")
+    self._outputs = [Tensor(self, output_shape, x.dtype)]
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    x, out = self.inputs[0], self.outputs[0]
+    lowering.set_tensor_lowering(
+        out, impl.broadcast_impl(lowering.tensors[x], x.shape, out.shape))
+
+
+def broadcast(x, new_shape):
+  new_shape = convert_to_shape(new_shape)
+  if x.shape == new_shape:
+    return x
+  return BroadcastOperation(x, new_shape).outputs[0]
+
+
+# -------------------------------------------------------------------- reshape
+class ReshapeOperation(Operation):
+  """Reshape with the layout change it implies (mesh_tensorflow/ops.py:4477-4584).
+
+  Per mesh axis, the product of the tensor dims preceding the dim split over
+  it is compared between old and new shape: newly split -> allsplit (before
+  the local reshape when that boundary exists in the old shape, after it
+  otherwise), no longer split -> allconcat, split differently -> alltoall.
+  """
+
+  def __init__(self, x, new_shape, name=None):
+    super().__init__([x], name=name or "reshape")
+    self._outputs = [Tensor(self, new_shape, x.dtype)]
+
+  def lower(self, lowering):
+    old_shape = self.inputs[0].shape
+    new_shape = self.outputs[0].shape
+    impl = lowering.mesh_impl(self)
+    slices = lowering.tensors[self.inputs[0]]
+    old_cp = impl.mesh_axis_to_cumprod(old_shape)
+    new_cp = impl.mesh_axis_to_cumprod(new_shape)
+    to_split, to_concat, to_exchange = [], [], []
+    for mesh_axis, (old, new) in enumerate(zip(old_cp, new_cp)):
+      if new == old:
+        continue
+      if old is None:
+        to_split.append(mesh_axis)
+      elif new is None:
+        to_concat.append(mesh_axis)
+      else:
+        to_exchange.append(mesh_axis)
+
+    laid_out_size = impl.laid_out_size(old_shape)
+    split_after_reshape = []
+    for mesh_axis in to_split:
+      tensor_axis = old_shape.cumprod_to_tensor_axis(new_cp[mesh_axis])
+      if tensor_axis is None:
+        split_after_reshape.append(
+            (mesh_axis, new_shape.cumprod_to_tensor_axis(new_cp[mesh_axis])))
+      else:
+        slices = impl.allsplit(slices, mesh_axis, tensor_axis)
+        laid_out_size //= impl.shape[mesh_axis].size
+    for mesh_axis in to_exchange:
+      split_axis = old_shape.cumprod_to_tensor_axis(new_cp[mesh_axis])
+      if split_axis is None:
+        raise NotImplementedError(
+            "Try first reshaping to insert a new tf dimension,"
+            " then changing layout. input_shape=%s output_shape=%s" % (old_shape, new_shape))
+      concat_axis = old_shape.cumprod_to_tensor_axis(old_cp[mesh_axis])
+      assert concat_axis is not None
+      slices = impl.alltoall(slices, mesh_axis, split_axis, concat_axis)
+      lowering.add_counter("alltoall/%s/reshape_op" % mesh_axis, laid_out_size)
+    for mesh_axis in to_concat:
+      tensor_axis = old_shape.cumprod_to_tensor_axis(old_cp[mesh_axis])
+      assert tensor_axis is not None
+      slices = impl.allconcat(slices, mesh_axis, tensor_axis)
+      laid_out_size *= impl.shape[mesh_axis].size
+      lowering.add_counter("allconcat/%s/reshape_op" % mesh_axis, laid_out_size)
+
+    new_slice_shape = impl.slice_shape(new_shape)
+    for mesh_axis, tensor_axis in split_after_reshape:
+      new_slice_shape[tensor_axis] *= impl.shape[mesh_axis].size
+    ops = impl.slice_ops
+    slices = impl.slicewise_delay_allreduce(lambda xs: ops.reshape(xs, new_slice_shape), slices)
+    for mesh_axis, tensor_axis in split_after_reshape:
+      slices = impl.allsplit(slices, mesh_axis, tensor_axis)
+    lowering.set_tensor_lowering(self.outputs[0], slices)
+
+
+def reshape(x, new_shape, name="reshape"):
+  new_shape = convert_to_shape(new_shape)
+  if x.shape.size != new_shape.size:
+    raise ValueError("reshape: sizes differ: %s vs %s" % (x.shape, new_shape))
+  if x.shape == new_shape:
+    return x
+  return ReshapeOperation(x, new_shape, name=name).outputs[0]
+
+
+def rename_dimension(x, old_name, new_name):
+  return reshape(x, x.shape.rename_dimension(old_name, new_name))
+
+
+def replace_dimensions(x, old_dim_or_dims, new_dim_or_dims):
+  """Replaces a run of consecutive dims by another run (ops.py:4609-4653)."""
+  old = [old_dim_or_dims] if isinstance(old_dim_or_dims, Dimension) else list(old_dim_or_dims)
+  new = [new_dim_or_dims] if isinstance(new_dim_or_dims, Dimension) else list(new_dim_or_dims)
+  dims = x.shape.dims
+  start = dims.index(old[0])
+  if dims[start:start + len(old)] != old:
+    raise ValueError("old dims must be consecutive in %s: %s" % (x.shape, old))
+  return reshape(x, Shape(dims[:start] + new + dims[start + len(old):]))
+
+
+# ------------------------------------------------------------ top-k / one-hot
+class TopKOperation(Operation):
+  """Top-k values and indices along one dim (mesh_tensorflow/ops.py:4895-4961)."""
+
+  def __init__(self, x, reduced_dim, k_dim, name=None):
+    super().__init__([x], name=name or "top_k")
+    if reduced_dim not in x.shape.dims:
+      raise ValueError("reduced dim %s must be in x.shape %s" % (reduced_dim, x.shape))
+    if k_dim.size > reduced_dim.size:
+      raise ValueError("k_dim.size must be <= reduced_dim.size: %s vs %s" % (k_dim, reduced_dim))
+    output_shape = x.shape - reduced_dim + k_dim
+    self._outputs = [Tensor(self, output_shape, x.dtype, index=0),
+                     Tensor(self, output_shape, G.int32, index=1)]
+    self._reduced_dim = reduced_dim
+    self._k_dim = k_dim
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    ops = impl.slice_ops
+    x = self.inputs[0]
+    ndims = x.shape.ndims
+    reduced_axis = x.shape.dims.index(self._reduced_dim)
+    reduced_mesh_axis = impl.tensor_dimension_to_mesh_axis(self._reduced_dim)
+    if reduced_mesh_axis is not None:
+      per_shard = self._reduced_dim.size // impl.shape[reduced_mesh_axis].size
+    else:
+      per_shard = self._reduced_dim.size
+    k = self._k_dim.size
+
+    def slicewise_top_k(t):
+      t = ops.transpose(t, [i for i in range(ndims) if i != reduced_axis] + [reduced_axis])
+      if k == 1:
+        return (ops.expand_dims(ops.reduce("MAX", t, [ndims - 1]), ndims - 1),
+                ops.expand_dims(ops.argmax(t), ndims - 1))
+      return ops.top_k(t, min(k, per_shard))
+    values, indices = impl.slicewise(slicewise_top_k, lowering.tensors[x])
+    if reduced_mesh_axis is not None:
+      indices = impl.slicewise(
+          lambda idx, pcoord: ops.binary("add", idx, int(pcoord) * per_shard),
+          indices, impl.laid_out_pcoord(reduced_mesh_axis))
+      values = impl.allconcat(values, reduced_mesh_axis, ndims - 1)
+      indices = impl.allconcat(indices, reduced_mesh_axis, ndims - 1)
+
+      def global_top_k(vals, global_indices):
+        vals, local = ops.top_k(vals, k)
+        return vals, ops.gather_last(global_indices, local)
+      values, indices = impl.slicewise(global_top_k, values, indices)
+    lowering.set_tensor_lowering(self.outputs[0], values)
+    lowering.set_tensor_lowering(self.outputs[1], indices)
+
+
+def top_k(x, reduced_dim, k_dim, name=None):
+  """Values and int32 indices, k_dim appended last; k in 2..4 runs as repeated
+  top_1 with the winner pushed down by -1e9 (mesh_tensorflow/ops.py:4964-5015)."""
+  reduced_dim = convert_to_dimension(reduced_dim)
+  k_dim = convert_to_dimension(k_dim)
+  if 1 < k_dim.size < 5:
+    values, indices = [], []
+    for i in range(k_dim.size):
+      v, idx = top_1(x, reduced_dim)
+      values.append(v)
+      indices.append(idx)
+      if i + 1 < k_dim.size:
+        x = x + one_hot(idx, reduced_dim, on_value=-1e9, dtype=x.dtype)
+    return stack(values, k_dim.name, -1), stack(indices, k_dim.name, -1)
+  op = TopKOperation(x, reduced_dim, k_dim, name=name)
+  return op.outputs[0], op.outputs[1]
+
+
+def top_1(x, reduced_dim, name=None):
+  """Max and argmax along `reduced_dim` (mesh_tensorflow/ops.py:5018-5033)."""
+  reduced_dim = convert_to_dimension(reduced_dim)
+  one = Dimension("_one", 1)
+  op = TopKOperation(x, reduced_dim, one, name=name)
+  values, indices = op.outputs
+  return reshape(values, values.shape - one), reshape(indices, indices.shape - one)
+
+
+def argmax(x, reduced_dim, name=None):
+  return top_1(x, convert_to_dimension(reduced_dim), name=name)[1]
+
+
+class StackOperation(Operation):
+  """Stacks same-shaped tensors along a new unsplit dim (ops.py:2592-2630)."""
+
+  def __init__(self, xs, dim_name, axis, name=None):
+    super().__init__(xs, name=name or "stack")
+    self._axis = axis
+    dims = xs[0].shape.dims
+    self._outputs = [Tensor(self, Shape(dims[:axis] + [Dimension(dim_name, len(xs))] + dims[axis:]),
+                            xs[0].dtype)]
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    if impl.tensor_dimension_to_mesh_axis(self.outputs[0].shape.dims[self._axis]) is not None:
+      raise ValueError("can't stack along a split axis")
+    ops, axis = impl.slice_ops, self._axis
+    fn = lambda *xs: ops.concat([ops.expand_dims(x, axis) for x in xs], axis)
+    lowering.set_tensor_lowering(
+        self.outputs[0], impl.slicewise(fn, *[lowering.tensors[x] for x in self.inputs]))
+
+
+def stack(xs, dim_name, axis=0, name=None):
+  if axis < 0:
+    axis = xs[0].shape.ndims + 1 + axis
+  return StackOperation(xs, dim_name, axis, name).outputs[0]
+
+
+class OneHotOperation(Operation):
+  """One-hot along a new last dim (mesh_tensorflow/ops.py:3810-3851).
+
+  An index outside [0, depth) gives an all-`off` row; when the new dim is
+  split, each processor subtracts the offset of its slice first.
+  """
+
+  def __init__(self, indices, output_dim, on_value, off_value, dtype, name=None):
+    super().__init__([indices], name=name or "one_hot")
+    if not indices.dtype.is_integer:
+      raise ValueError("indices requires an integer dtype got %s" % (indices,))
+    self._output_dim = output_dim
+    self._on, self._off, self._dtype = on_value, off_value, dtype
+    self._outputs = [Tensor(self, Shape(indices.shape.dims + [output_dim]), dtype)]
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    ops = impl.slice_ops
+    depth = impl.slice_shape(self.outputs[0].shape)[-1]
+    mesh_axis = impl.tensor_dimension_to_mesh_axis(self._output_dim)
+    if mesh_axis is None:
+      offset = 0
+    else:
+      offset = impl.slicewise(lambda pc: int(pc) * depth, impl.laid_out_pcoord(mesh_axis))
+    on, off, dtype = self._on, self._off, self._dtype
+
+    def fn(idx, off_set):
+      if off_set:
+        idx = ops.binary("add", idx, -int(off_set))
+      return ops.one_hot(idx, depth, on, off, dtype)
+    lowering.set_tensor_lowering(
+        self.outputs[0], impl.slicewise(fn, lowering.tensors[self.inputs[0]], offset))
+
+
+def one_hot(indices, output_dim, on_value=1.0, off_value=0.0, dtype=G.float32, name=None):
+  return OneHotOperation(indices, convert_to_dimension(output_dim), on_value, off_value, dtype,
+                         name=name).outputs[0]
+
+
+# ------------------------------------------------------------ cumsum / softmax
+def cumsum(x, dim, exclusive=False):
+  """Cumulative sum as a product with a 0/1 triangular matrix (ops.py:2761-2781)."""
+  dim = convert_to_dimension(dim)
+  tmp = Dimension("tmp_dim_cumsum", dim.size)
+  new_shape = x.shape.rename_dimension(dim.name, tmp.name)
+  comparator = less if exclusive else less_equal
+  m = cast(comparator(mtf_range(x.mesh, dim, dtype=G.float32),
+                      mtf_range(x.mesh, tmp, dtype=G.float32)), x.dtype)
+  return reshape(einsum([x, m], output_shape=new_shape), x.shape)
+
+
+def reduce_logsumexp(x, reduced_dim, extra_logit=None, name=None):
+  """log(sum(exp(x))) with the max subtracted first (ops.py:5493-5520)."""
+  reduced_dim = convert_to_dimension(reduced_dim)
+  reduced_shape = x.shape - reduced_dim
+  max_logit = reduce_max(stop_gradient(x), output_shape=reduced_shape)
+  if extra_logit is not None:
+    max_logit = maximum(max_logit, extra_logit)
+  x = x - max_logit
+  sum_exp = reduce_sum(exp(x), output_shape=reduced_shape)
+  if extra_logit is not None:
+    sum_exp = sum_exp + exp(extra_logit - max_logit)
+  return log(sum_exp) + max_logit
+
+
+def log_softmax(x, reduced_dim, extra_logit=None, name=None):
+  return x - reduce_logsumexp(x, reduced_dim, extra_logit=extra_logit, name=name)
+
+
+def softmax(x, reduced_dim, extra_logit=None, name=None):
+  """exp(x - logsumexp(x)) (mesh_tensorflow/ops.py:5539-5541)."""
+  return exp(log_softmax(x, reduced_dim, extra_logit=extra_logit))
+
+
+# ----------------------------------------------------------------------- shift
+class ShiftOperation(Operation):
+  """Shifts along a dim, zero-filled or wrapped (mesh_tensorflow/ops.py:3569-3661).
+
+  When the dim is split, whole slices move between neighbouring processors
+  through MeshImpl.shift_by_n_processors.
+  """
+
+  def __init__(self, x, offset, dim, wrap, name=None):
+    super().__init__([x], name=name or "shift")
+    self._dim = dim
+    self._axis = x.shape.dims.index(dim)
+    self._offset = offset
+    self._wrap = wrap
+    self._outputs = [Tensor(self, x.shape, x.dtype)]
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    ops = impl.slice_ops
+    mesh_axis = impl.tensor_dimension_to_mesh_axis(self._dim)
+    inputs = lowering.tensors[self.inputs[0]]
+    ndims = self.inputs[0].shape.ndims
+    axis, wrap = self._axis, self._wrap
+    if mesh_axis is None:
+      off = self._offset
+      n = self._dim.size
+
+      def local_shift(xs):
+        return _shift_slice(ops, xs, axis, off, n, wrap, ndims)
+      lowering.set_tensor_lowering(self.outputs[0], impl.slicewise(local_shift, inputs))
+      return
+    mesh_size = impl.shape[mesh_axis].size
+    partial = self._dim.size // mesh_size
+    inputs = inputs.to_laid_out_tensor()
+    src_a = self._offset // partial          # whole slices to move
+    rem = self._offset - src_a * partial     # 0 <= rem < partial
+    from_a = impl.shift_by_n_processors(inputs, mesh_axis, src_a, wrap)
+    if rem == 0:
+      lowering.set_tensor_lowering(self.outputs[0], from_a)
+      return
+    from_b = impl.shift_by_n_processors(inputs, mesh_axis, src_a + 1, wrap)
+
+    def stitch(a, b):
+      shape = list(ops.shape(a))
+      head_size = list(shape)
+      head_size[axis] = rem
+      tail_size = list(shape)
+      tail_size[axis] = partial - rem
+      begin_b = [0] * ndims
+      begin_b[axis] = partial - rem
+      return ops.concat([ops.slice(b, begin_b, head_size),
+                         ops.slice(a, [0] * ndims, tail_size)], axis)
+    lowering.set_tensor_lowering(self.outputs[0], impl.slicewise(stitch, from_a, from_b))
+
+
+def _shift_slice(ops, xs, axis, offset, n, wrap, ndims):
+  shape = list(ops.shape(xs))
+  offset = offset % n if wrap else offset
+  if offset == 0:
+    return xs
+  if abs(offset) >= n:
+    return ops.fill(shape, 0, ops.dtype(xs))
+  keep = list(shape)
+  keep[axis] = n - abs(offset)
+  lost = list(shape)
+  lost[axis] = abs(offset)
+  begin_keep = [0] * ndims
+  begin_lost = [0] * ndims
+  if offset > 0:
+    begin_lost[axis] = n - offset
+    kept = ops.slice(xs, begin_keep, keep)
+    pad = ops.slice(xs, begin_lost, lost) if wrap else ops.fill(lost, 0, ops.dtype(xs))
+    return ops.concat([pad, kept], axis)
+  begin_keep[axis] = -offset
+  kept = ops.slice(xs, begin_keep, keep)
+  pad = ops.slice(xs, begin_lost, lost) if wrap else ops.fill(lost, 0, ops.dtype(xs))
+  return ops.concat([kept, pad], axis)
+
+
+def shift(x, offset, dim, wrap, name=None):
+  return ShiftOperation(x, offset, convert_to_dimension(dim), wrap, name=name).outputs[0]
+
+
+# --------------------------------------------------------- operator overloads
+def _floordiv(x1, x2):
+  return binary_op_with_broadcasting("floordiv", x1, x2)
+
+
+def _mod(x1, x2):
+  return binary_op_with_broadcasting("mod", x1, x2)
+
+
+Tensor.__add__ = lambda self, other: add(self, other)
+Tensor.__radd__ = lambda self, other: add(self, other)
+Tensor.__sub__ = lambda self, other: sub(self, other)
+Tensor.__rsub__ = lambda self, other: sub(other, self)
+Tensor.__mul__ = lambda self, other: multiply(self, other)
+Tensor.__rmul__ = lambda self, other: multiply(self, other)
+Tensor.__neg__ = lambda self: negative(self)
+Tensor.__truediv__ = lambda self, other: divide(self, other)
+Tensor.__rtruediv__ = lambda self, other: divide(other, self)
+Tensor.__floordiv__ = lambda self, other: _floordiv(self, other)
+Tensor.__mod__ = lambda self, other: _mod(self, other)

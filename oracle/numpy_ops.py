@@ -1,0 +1,272 @@
+"""numpy restatement of the TensorFlow slice arithmetic the reference calls.
+
+TEST INFRASTRUCTURE ONLY (see oracle/__init__.py).
+
+Each function states which tf op it stands for and where the reference calls
+it (mesh_tensorflow/ops.py unless noted).  TensorFlow (an un-vendored
+dependency, `tensorflow>=1.15`, setup.py:26-30) is not installed here, so the
+semantics below are TensorFlow's published ones:
+
+  * bfloat16 tensors are float32 arrays holding bfloat16-representable values;
+    every bfloat16 op computes in float32 and rounds once, to nearest-even;
+  * einsum accumulates in float32 (float64 is used here for float32 inputs to
+    make the oracle's own rounding negligible next to the 1e-5 tolerance);
+  * argmax / top_k ties go to the lowest index;
+  * one_hot of an index outside [0, depth) is an all-`off` row;
+  * float -> int32 casts truncate; casts to bool are `!= 0`.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+from mesh_b200 import mtf
+
+
+def round_to_bf16(x):
+  """float32 -> nearest-even bfloat16, returned as float32."""
+  shape = np.shape(x)
+  x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+  u = x.view(np.uint32)
+  bias = ((u >> np.uint32(16)) & np.uint32(1)) + np.uint32(0x7FFF)
+  r = ((u + bias) & np.uint32(0xFFFF0000)).astype(np.uint32)
+  out = r.view(np.float32).copy()
+  nan = np.isnan(x)
+  if nan.any():
+    out[nan] = np.nan
+  return out.reshape(shape)
+
+
+class Arr(object):
+  """A slice: numpy storage plus the mtf dtype it represents."""
+  __slots__ = ("a", "dtype")
+
+  def __init__(self, a, dtype):
+    self.a = a
+    self.dtype = dtype
+
+  @property
+  def shape(self):
+    return tuple(self.a.shape)
+
+  def __repr__(self):
+    return "Arr(%s, %s)" % (self.a.shape, self.dtype)
+
+
+def _storage(dtype):
+  if dtype.is_floating:
+    return np.float32
+  if dtype.is_bool:
+    return np.bool_
+  return np.int32
+
+
+def _finish(a, dtype):
+  """Applies the dtype's storage type and rounding to a computed array."""
+  a = np.asarray(a)
+  if dtype == mtf.bfloat16:
+    return Arr(round_to_bf16(a.astype(np.float32)), dtype)
+  return Arr(a.astype(_storage(dtype), copy=False), dtype)
+
+
+class NumpyOps(object):
+  """The `slice_ops` array library of the oracle's mesh backend."""
+
+  # ---- host transfer
+  def from_host(self, value, dtype):
+    return _finish(np.array(value), dtype)
+
+  def to_host(self, x):
+    return np.array(x.a)
+
+  # ---- metadata
+  def shape(self, x):
+    return tuple(x.a.shape)
+
+  def dtype(self, x):
+    return x.dtype
+
+  # ---- layout ops: tf.slice / concat / transpose / expand_dims / reshape
+  def slice(self, x, begin, size):
+    idx = tuple(slice(b, b + s) for b, s in zip(begin, size))
+    return Arr(np.ascontiguousarray(x.a[idx]), x.dtype)
+
+  def concat(self, xs, axis):
+    return Arr(np.concatenate([x.a for x in xs], axis=axis), xs[0].dtype)
+
+  def transpose(self, x, perm):
+    return Arr(np.transpose(x.a, perm), x.dtype)
+
+  def expand_dims(self, x, axis):
+    return Arr(np.expand_dims(x.a, axis), x.dtype)
+
+  def reshape(self, x, shape):
+    return Arr(np.reshape(x.a, shape), x.dtype)
+
+  def broadcast_to(self, x, shape):
+    return Arr(np.ascontiguousarray(np.broadcast_to(x.a, shape)), x.dtype)
+
+  # ---- creation: tf.zeros / tf.constant / tf.range
+  def fill(self, shape, value, dtype):
+    return _finish(np.full(shape, value), dtype)
+
+  def range(self, n, dtype):
+    return _finish(np.arange(n), dtype)
+
+  # ---- tf.cast (ops.py:1945-1950)
+  def cast(self, x, dtype):
+    a = x.a
+    if dtype.is_bool:
+      return Arr(a != 0, dtype)
+    if dtype.is_integer:
+      return Arr(np.trunc(a).astype(np.int32) if x.dtype.is_floating else a.astype(np.int32), dtype)
+    return _finish(a.astype(np.float32), dtype)
+
+  # ---- tf.nn.relu, tf.exp, ... via cwise (ops.py:1727-1943)
+  def unary(self, name, x):
+    a = x.a
+    with np.errstate(all="ignore"):
+      if name == "relu":
+        r = np.maximum(a, 0)
+      elif name == "exp":
+        r = np.exp(a.astype(np.float32))
+      elif name == "log":
+        r = np.log(a.astype(np.float32))
+      elif name == "negative":
+        r = -a
+      elif name == "reciprocal":
+        r = np.float32(1.0) / a.astype(np.float32)
+      elif name == "sqrt":
+        r = np.sqrt(a.astype(np.float32))
+      elif name == "rsqrt":
+        r = np.float32(1.0) / np.sqrt(a.astype(np.float32))
+      elif name == "square":
+        r = a * a
+      elif name == "tanh":
+        r = np.tanh(a.astype(np.float32))
+      elif name == "sigmoid":
+        r = np.float32(1.0) / (np.float32(1.0) + np.exp(-a.astype(np.float32)))
+      elif name == "sign":
+        r = np.sign(a)
+      elif name == "logical_not":
+        return Arr(~(a != 0), mtf.bool_)
+      elif name == "identity":
+        r = a
+      else:
+        raise ValueError("unknown unary op %s" % name)
+    return _finish(r, x.dtype)
+
+  # ---- tf.add / multiply / less ... (ops.py:2044-2200)
+  def binary(self, name, a, b):
+    ref = a if isinstance(a, Arr) else b
+    av = a.a if isinstance(a, Arr) else np.asarray(a, dtype=_storage(ref.dtype))
+    bv = b.a if isinstance(b, Arr) else np.asarray(b, dtype=_storage(ref.dtype))
+    with np.errstate(all="ignore"):
+      if name == "add":
+        r = av + bv
+      elif name == "sub":
+        r = av - bv
+      elif name == "multiply":
+        r = av * bv
+      elif name == "divide":
+        r = av / bv
+      elif name == "maximum":
+        r = np.maximum(av, bv)
+      elif name == "minimum":
+        r = np.minimum(av, bv)
+      elif name == "floordiv":
+        r = np.floor_divide(av, bv)
+      elif name == "mod":
+        r = np.mod(av, bv)
+      elif name in ("less", "greater", "less_equal", "greater_equal", "equal", "not_equal"):
+        fn = {"less": np.less, "greater": np.greater, "less_equal": np.less_equal,
+              "greater_equal": np.greater_equal, "equal": np.equal,
+              "not_equal": np.not_equal}[name]
+        return Arr(fn(av, bv), mtf.bool_)
+      elif name == "logical_and":
+        return Arr((av != 0) & (bv != 0), mtf.bool_)
+      elif name == "logical_or":
+        return Arr((av != 0) | (bv != 0), mtf.bool_)
+      else:
+        raise ValueError("unknown binary op %s" % name)
+    return _finish(r, ref.dtype)
+
+  # ---- tf.reduce_sum / max / min (ops.py:5698-5706)
+  def reduce(self, name, x, axes):
+    axes = tuple(axes)
+    if name == "SUM":
+      if x.dtype.is_floating:
+        r = np.sum(x.a.astype(np.float64), axis=axes).astype(np.float32)
+      else:
+        r = np.sum(x.a.astype(np.int64), axis=axes)
+    elif name == "MAX":
+      r = np.max(x.a, axis=axes)
+    elif name == "MIN":
+      r = np.min(x.a, axis=axes)
+    else:
+      raise ValueError("unknown reduction %s" % name)
+    return _finish(r, x.dtype)
+
+  # ---- tf.math.argmax / top_k / gather (ops.py:4937-4958)
+  def argmax(self, x):
+    return Arr(np.argmax(x.a, axis=-1).astype(np.int32), mtf.int32)
+
+  def top_k(self, x, k):
+    order = np.argsort(-x.a, axis=-1, kind="stable")[..., :k]
+    return (Arr(np.take_along_axis(x.a, order, axis=-1), x.dtype),
+            Arr(order.astype(np.int32), mtf.int32))
+
+  def gather_last(self, values, indices):
+    return Arr(np.take_along_axis(values.a, indices.a.astype(np.int64), axis=-1), values.dtype)
+
+  # ---- tf.one_hot (ops.py:3843-3848)
+  def one_hot(self, indices, depth, on_value, off_value, dtype):
+    hit = indices.a[..., None] == np.arange(depth, dtype=np.int64)
+    return _finish(np.where(hit, on_value, off_value), dtype)
+
+  # ---- tf.einsum (ops.py:1340) and the broadcast-multiply-reduce form (2805-2814)
+  def einsum(self, equation, *xs):
+    dtype = xs[0].dtype
+    if dtype.is_floating:
+      r = np.einsum(equation, *[x.a.astype(np.float64) for x in xs], optimize=True)
+      return _finish(r.astype(np.float32), dtype)
+    r = np.einsum(equation, *[x.a.astype(np.int64) for x in xs], optimize=True)
+    return _finish(r, dtype)
+
+  def einsum_naive(self, equation, *xs):
+    return self.einsum(equation, *xs)
+
+  # ---- fused MoE entry points: the scalar specification
+  def moe_top2_gating(self, x, w, capacity, policy, threshold, noise, num_groups_total):
+    from oracle import moe_spec
+    lead = x.a.shape[:-2]
+    s, m = x.a.shape[-2:]
+    xg = x.a.reshape((-1, s, m)).astype(np.float32)
+    ng = None if noise is None else noise.a.reshape((-1, s)).astype(np.float32)
+    r = moe_spec.top2_gating(xg, w.a.astype(np.float32), capacity, policy, threshold, ng)
+    tok = lead + (s,)
+    outs = [Arr(r[k].reshape(tok), mtf.int32) for k in ("index_1", "index_2", "position_1",
+                                                        "position_2")]
+    outs += [Arr(r[k].reshape(tok), mtf.float32) for k in ("gate_1", "gate_2")]
+    loss = np.float32(np.sum(r["loss_per_group"].astype(np.float64)) / num_groups_total)
+    outs.append(Arr(np.asarray(loss, dtype=np.float32), mtf.float32))
+    return tuple(outs)
+
+  def moe_dispatch(self, x, i1, i2, p1, p2, g1, g2, num_experts, capacity):
+    from oracle import moe_spec
+    o, g, s, m = x.a.shape
+    out = moe_spec.dispatch(x.a.reshape(o * g, s, m), i1.a.reshape(-1, s), i2.a.reshape(-1, s),
+                            p1.a.reshape(-1, s), p2.a.reshape(-1, s), g1.a.reshape(-1, s),
+                            g2.a.reshape(-1, s), num_experts, capacity)  # [OG, E, C, M]
+    out = out.reshape(o, g, num_experts, capacity, m).transpose(0, 2, 1, 3, 4)
+    return Arr(np.ascontiguousarray(out), x.dtype)
+
+  def moe_combine(self, y, i1, i2, p1, p2, g1, g2):
+    from oracle import moe_spec
+    o, e, g, c, m = y.a.shape
+    s = i1.a.shape[-1]
+    yg = np.ascontiguousarray(y.a.transpose(0, 2, 1, 3, 4)).reshape(o * g, e, c, m)
+    out = moe_spec.combine(yg, i1.a.reshape(-1, s), i2.a.reshape(-1, s), p1.a.reshape(-1, s),
+                           p2.a.reshape(-1, s), g1.a.reshape(-1, s), g2.a.reshape(-1, s))
+    out = out.reshape(o, g, s, m)
+    return _finish(out, y.dtype)
