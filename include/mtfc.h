@@ -93,6 +93,161 @@ int mtfc_gemm(const mtfc_gemm_desc* desc, const void* a, const void* b, void* c,
 int mtfc_gemm_uses_tensor_cores(const mtfc_gemm_desc* desc, const void* a,
                                 const void* b, const void* c);
 
+/* ---- K8: slice-local array operations ----------------------------------- */
+/*
+ * The op-by-op lowering applies TensorFlow ops to slices inside
+ * MeshImpl.slicewise closures.  These entry points stand for them:
+ *   mtfc_unary            tf.nn.relu / exp / log / negative / reciprocal / sqrt /
+ *                         rsqrt / square / tanh / sigmoid / sign / logical_not and
+ *                         tf.cast (ops.py:1727-1962); IDENTITY with different
+ *                         dtypes is the cast, NONZERO the cast to bool
+ *   mtfc_binary           tf.add / subtract / multiply / divide / maximum /
+ *                         minimum / floordiv / mod / comparisons / logical ops
+ *                         with broadcasting (ops.py:2044-2200); a stride of 0
+ *                         broadcasts; b == NULL uses `scalar_b`
+ *   mtfc_broadcast_reduce broadcast-multiply-reduce form of einsum
+ *                         (ops.py:2805-2814) and tf.reduce_sum / max / min over
+ *                         any axes with an output permutation (ops.py:2267-2338)
+ *   mtfc_topk_last        tf.math.reduce_max + argmax, tf.math.top_k on the last
+ *                         axis (ops.py:4937-4942); ties go to the lowest index;
+ *                         `values` may be NULL
+ *   mtfc_gather_last      tf.gather(..., batch_dims = rank-1) (ops.py:4956-4958)
+ *   mtfc_one_hot          tf.one_hot (ops.py:3843-3848); out-of-range -> all off
+ *   mtfc_fill             tf.zeros / constants / tf.range: out[i] = value + step*i
+ * bool tensors are int32 0/1.  Outputs are contiguous.
+ */
+#define MTFC_UNARY_IDENTITY 0
+#define MTFC_UNARY_RELU 1
+#define MTFC_UNARY_EXP 2
+#define MTFC_UNARY_LOG 3
+#define MTFC_UNARY_NEGATIVE 4
+#define MTFC_UNARY_RECIPROCAL 5
+#define MTFC_UNARY_SQRT 6
+#define MTFC_UNARY_RSQRT 7
+#define MTFC_UNARY_SQUARE 8
+#define MTFC_UNARY_TANH 9
+#define MTFC_UNARY_SIGMOID 10
+#define MTFC_UNARY_SIGN 11
+#define MTFC_UNARY_LOGICAL_NOT 12
+#define MTFC_UNARY_NONZERO 13
+
+#define MTFC_BINARY_ADD 0
+#define MTFC_BINARY_SUB 1
+#define MTFC_BINARY_MULTIPLY 2
+#define MTFC_BINARY_DIVIDE 3
+#define MTFC_BINARY_MAXIMUM 4
+#define MTFC_BINARY_MINIMUM 5
+#define MTFC_BINARY_FLOORDIV 6
+#define MTFC_BINARY_MOD 7
+#define MTFC_BINARY_LESS 8
+#define MTFC_BINARY_GREATER 9
+#define MTFC_BINARY_LESS_EQUAL 10
+#define MTFC_BINARY_GREATER_EQUAL 11
+#define MTFC_BINARY_EQUAL 12
+#define MTFC_BINARY_NOT_EQUAL 13
+#define MTFC_BINARY_LOGICAL_AND 14
+#define MTFC_BINARY_LOGICAL_OR 15
+
+#define MTFC_REDUCE_SUM 0
+#define MTFC_REDUCE_MAX 1
+#define MTFC_REDUCE_MIN 2
+
+int mtfc_unary(int op, const void* x, int x_dtype, void* y, int y_dtype, int64_t n, void* stream);
+
+int mtfc_binary(int op, const void* a, const int64_t* a_strides, const void* b,
+                const int64_t* b_strides, double scalar_b, void* out, int in_dtype,
+                int out_dtype, int ndim, const int64_t* shape, void* stream);
+
+/* out[o] = reduce over r of prod_k in[k][o, r].  `out_strides[k]` / `red_strides[k]`
+ * give operand k's element stride along each kept / reduced axis (0 where the
+ * operand lacks the axis).  Up to 4 operands; products reduce with SUM only. */
+int mtfc_broadcast_reduce(int op, int n_in, const void* const* in, int in_dtype, void* out,
+                          int out_dtype, int ndim_out, const int64_t* out_shape,
+                          const int64_t* const* out_strides, int ndim_red,
+                          const int64_t* red_shape, const int64_t* const* red_strides,
+                          void* stream);
+
+int mtfc_topk_last(const void* x, int dtype, int64_t rows, int32_t cols, int32_t k, void* values,
+                   int32_t* indices, void* stream);
+
+int mtfc_gather_last(const void* values, int dtype, const int32_t* indices, int64_t rows,
+                     int32_t cols, int32_t k, void* out, void* stream);
+
+int mtfc_one_hot(const int32_t* indices, int64_t n, int32_t depth, float on_value,
+                 float off_value, void* out, int out_dtype, void* stream);
+
+int mtfc_fill(void* out, int dtype, int64_t n, float value, float step, void* stream);
+
+/* ---- K7: strided copy ---------------------------------------------------- */
+/*
+ * dst[sum_d i_d * dst_strides[d]] = src[sum_d i_d * src_strides[d]] over `shape`.
+ * Replaces tf.transpose / tf.slice / tf.concat / tf.split on slices: transposes in
+ * _expand_dims and _reduce_helper (ops.py:5322-5343, 2267-2299), make_slices /
+ * combine_slices (ops.py:1249-1305), allsplit (ops.py:1082-1109) and the split /
+ * concat around allconcat and alltoall (placement_mesh_impl.py:436-440, 487,
+ * 509-510).  elem_bytes is 2 or 4; rows that are contiguous on both sides move
+ * as 16-byte vectors.
+ */
+int mtfc_copy_strided(const void* src, const int64_t* src_strides, void* dst,
+                      const int64_t* dst_strides, int ndim, const int64_t* shape, int elem_bytes,
+                      void* stream);
+
+/* ---- K2-K5: top-2 mixture-of-experts routing ----------------------------- */
+/*
+ * Replace the op chain of _top_2_gating (transformer/moe.py:1380-1513) and the
+ * dense one-hot dispatch / combine einsums (moe.py:443-447, 509-510).
+ * Tokens are [groups, group_size]; groups are independent; within a group
+ * tokens are served in index order; ties go to the lowest expert index.
+ */
+#define MTFC_MOE_POLICY_ALL 0       /* moe_second_policy "all"       */
+#define MTFC_MOE_POLICY_NONE 1      /* "none"                        */
+#define MTFC_MOE_POLICY_THRESHOLD 2 /* "threshold": gate_2 > thr     */
+#define MTFC_MOE_POLICY_RANDOM 3    /* "random": noise < gate_2/thr  */
+
+/* fp32 gate kernel [m, experts] -> bf16 [m, 3*experts] = [hi | mid | lo] with
+ * hi + mid + lo == w to fp32 accuracy, so x(bf16) . w runs on the tensor cores
+ * (mtfc_gemm with n = 3*experts) and mtfc_moe_top2_gating sums the 3 parts.
+ * Stands for the fp32 gate dense layer at moe.py:1384-1390. */
+int mtfc_moe_split_gate_weights(const float* w, int64_t m, int32_t experts, void* out_bf16,
+                                void* stream);
+
+/* logits: [groups*group_size, parts*experts] fp32; the `parts` column blocks are
+ * summed.  Outputs per token: expert indices, positions in the expert's buffer
+ * (position >= capacity means the token did not fit), gates after
+ * renormalisation and zeroed where dropped; optional raw softmax outputs;
+ * per-group load-balancing loss (moe.py:1420-1424, before the mean over groups
+ * and before moe_loss_coef). */
+int mtfc_moe_top2_gating(const float* logits, int32_t parts, int64_t groups, int32_t group_size,
+                         int32_t experts, int32_t capacity, int32_t policy, float threshold,
+                         const float* noise, int32_t* idx1, int32_t* idx2, int32_t* pos1,
+                         int32_t* pos2, float* gate1, float* gate2, float* raw_gates,
+                         float* loss_per_group, void* stream);
+
+/* table[g, e, c] = token routed to slot c of expert e in group g, or -1.
+ * With round_gates_to_bf16 a token whose gate rounds to 0 in bfloat16 is not
+ * dispatched (the reference derives dispatch from the rounded combine tensor,
+ * moe.py:1507-1511). */
+int mtfc_moe_slot_table(const int32_t* idx1, const int32_t* idx2, const int32_t* pos1,
+                        const int32_t* pos2, const float* gate1, const float* gate2,
+                        int64_t groups, int32_t group_size, int32_t experts, int32_t capacity,
+                        int32_t round_gates_to_bf16, int32_t* table, void* stream);
+
+/* x: [outer, groups_per_outer, group_size, row] -> out: [outer, experts,
+ * groups_per_outer, capacity, row]; rows of `row_bytes` bytes (multiple of 16);
+ * empty slots are zero rows. */
+int mtfc_moe_dispatch(const void* x, const int32_t* table, void* out, int64_t outer,
+                      int64_t groups_per_outer, int32_t group_size, int32_t experts,
+                      int32_t capacity, int64_t row_bytes, void* stream);
+
+/* y: [outer, experts, groups_per_outer, capacity, row] -> out: [outer,
+ * groups_per_outer, group_size, row] = w1*y[i1, p1] + w2*y[i2, p2] with the gates
+ * rounded to y's dtype first; fp32 arithmetic, one rounding at the store. */
+int mtfc_moe_combine(const void* y, int dtype, const int32_t* idx1, const int32_t* idx2,
+                     const int32_t* pos1, const int32_t* pos2, const float* gate1,
+                     const float* gate2, void* out, int64_t outer, int64_t groups_per_outer,
+                     int32_t group_size, int32_t experts, int32_t capacity, int64_t row_elems,
+                     void* stream);
+
 #ifdef __cplusplus
 }
 #endif

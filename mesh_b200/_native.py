@@ -64,11 +64,32 @@ def _declare(lib):
   lib.mtfc_launch_count.argtypes = []
   lib.mtfc_device_status.restype = ctypes.c_int
   lib.mtfc_device_status.argtypes = []
-  lib.mtfc_gemm.restype = ctypes.c_int
-  lib.mtfc_gemm.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp]
-  lib.mtfc_gemm_uses_tensor_cores.restype = ctypes.c_int
-  lib.mtfc_gemm_uses_tensor_cores.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp]
-  del i32
+  f32 = ctypes.c_float
+  p_i64 = ctypes.POINTER(ctypes.c_int64)
+  pp_i64 = ctypes.POINTER(p_i64)
+  signatures = {
+      "mtfc_gemm": [ctypes.POINTER(GemmDesc), vp, vp, vp, vp],
+      "mtfc_gemm_uses_tensor_cores": [ctypes.POINTER(GemmDesc), vp, vp, vp],
+      "mtfc_unary": [i32, vp, i32, vp, i32, i64, vp],
+      "mtfc_binary": [i32, vp, p_i64, vp, p_i64, ctypes.c_double, vp, i32, i32, i32, p_i64, vp],
+      "mtfc_broadcast_reduce": [i32, i32, ctypes.POINTER(vp), i32, vp, i32, i32, p_i64, pp_i64,
+                                i32, p_i64, pp_i64, vp],
+      "mtfc_topk_last": [vp, i32, i64, i32, i32, vp, vp, vp],
+      "mtfc_gather_last": [vp, i32, vp, i64, i32, i32, vp, vp],
+      "mtfc_one_hot": [vp, i64, i32, f32, f32, vp, i32, vp],
+      "mtfc_fill": [vp, i32, i64, f32, f32, vp],
+      "mtfc_copy_strided": [vp, p_i64, vp, p_i64, i32, p_i64, i32, vp],
+      "mtfc_moe_split_gate_weights": [vp, i64, i32, vp, vp],
+      "mtfc_moe_top2_gating": [vp, i32, i64, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp,
+                               vp, vp, vp],
+      "mtfc_moe_slot_table": [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, vp, vp],
+      "mtfc_moe_dispatch": [vp, vp, vp, i64, i64, i32, i32, i32, i64, vp],
+      "mtfc_moe_combine": [vp, i32, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64, vp],
+  }
+  for name, argtypes in signatures.items():
+    fn = getattr(lib, name)
+    fn.restype = ctypes.c_int
+    fn.argtypes = argtypes
 
 
 def lib():

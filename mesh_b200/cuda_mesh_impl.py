@@ -1,0 +1,458 @@
+"""CudaMeshImpl: a MeshImpl whose slices live on B200 GPUs.
+
+Drop-in for the reference's PlacementMeshImpl
+(mesh_tensorflow/placement_mesh_impl.py:31-355) at the MeshImpl operator API:
+same constructor contract `(shape, layout, devices)`, same LaidOutTensor duck
+type, same methods with the same argument meaning and the same exceptions at
+lowering time.  Slice arithmetic runs on libmtfc kernels (DeviceOps); mesh
+collectives run
+
+  * in-process, when one process holds every slice (`devices` lists the CUDA
+    ordinal of each processor; ordinals may repeat so that n processors share
+    one GPU): group members are combined with the same kernels, following the
+    reference's grouping (`processor_groups`, ascending processor number);
+  * over torch.distributed (NCCL on NVLink / NVSwitch), when the job runs one
+    process per GPU: rank r holds processor r's slice only, and each mesh-axis
+    set gets its process groups once.  allreduce -> all_reduce, allconcat ->
+    all_gather (+ strided-copy kernel when the concat axis is not outermost),
+    alltoall -> all_to_all_single bracketed by pack / unpack copy kernels,
+    receive -> batched isend / irecv.
+
+SlicedMeshImpl holds everything that does not depend on where a slice lives;
+CudaMeshImpl binds it to DeviceOps and CUDA devices.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+from mesh_b200 import mtf
+from mesh_b200.mtf.layout import pnum_to_processor_coordinates, processor_groups
+from mesh_b200.mtf.mesh_impl import convert_args_to_laid_out_tensors
+
+
+class SlicedMeshImpl(mtf.MeshImpl):
+  """MeshImpl machinery over an array library and (optionally) torch.distributed.
+
+  Subclasses provide `_ops_for(pnum)` (array library positioned on the
+  processor's device), `_is_slice(x)`, and the torch bridges `_as_torch(x)` /
+  `_from_torch(t, shape, dtype, pnum)` used by the distributed collectives.
+  """
+
+  def __init__(self, shape, layout, local_pnums, distributed):
+    super().__init__(shape, layout)
+    self._local_pnums = list(local_pnums)
+    self._distributed = distributed
+    self._groups = {}
+    self.copy_master_to_slice_ops = []
+
+  class LaidOutTensor(object):
+    """The slices this process holds, one per local processor
+    (placement_mesh_impl.py:39-65)."""
+
+    def __init__(self, tensor_list):
+      self._tensor_list = list(tensor_list)
+
+    def __repr__(self):
+      return "[" + ",".join(str(t) for t in self._tensor_list) + "]"
+
+    @property
+    def tensor_list(self):
+      return self._tensor_list
+
+    @classmethod
+    def from_tensor_list(cls, tensor_list):
+      return cls(tensor_list)
+
+    @property
+    def all_slices(self):
+      return self._tensor_list
+
+    @property
+    def slice_shape(self):
+      t = self._tensor_list[0]
+      return list(t.shape) if hasattr(t, "shape") else []
+
+    def to_laid_out_tensor(self):
+      return self
+
+  # ------------------------------------------------------------ basics
+  @property
+  def local_pnums(self):
+    return list(self._local_pnums)
+
+  @property
+  def is_distributed(self):
+    return self._distributed
+
+  def _ops_for(self, pnum):
+    raise NotImplementedError
+
+  def _is_slice(self, x):
+    raise NotImplementedError
+
+  def slicewise(self, fn, *inputs):
+    inputs = convert_args_to_laid_out_tensors(inputs)
+    n = len(self._local_pnums)
+    cols = [x.tensor_list if isinstance(x, self.LaidOutTensor) else [x] * n for x in inputs]
+    ret = []
+    for i, pnum in enumerate(self._local_pnums):
+      self._ops_for(pnum)
+      ret.append(fn(*[col[i] for col in cols]))
+    if isinstance(ret[0], tuple):
+      return tuple(self.LaidOutTensor(list(t)) for t in zip(*ret))
+    return self.LaidOutTensor(ret)
+
+  def laid_out_pnum(self):
+    return self.LaidOutTensor(list(self._local_pnums))
+
+  def random(self, shape, tf_fn, kwargs):
+    raise NotImplementedError(
+        "random ops are not lowered; pass the noise tensor in as an imported input")
+
+  # ------------------------------------------------------------ import/export
+  def import_tf_tensor(self, x, tf_x):
+    """Host array -> slices; each processor's part is cut on the host and only
+    that part is uploaded (ops.py:1249-1269 semantics)."""
+    value = np.asarray(tf_x)
+    layout = self.tensor_layout(x.shape)
+    slice_shape = self.slice_shape(x.shape)
+    out = []
+    for pnum in self._local_pnums:
+      ops = self._ops_for(pnum)
+      if layout.is_fully_replicated:
+        part = value
+      else:
+        begin = self.slice_begin(x.shape, pnum)
+        part = value[tuple(slice(b, b + s) for b, s in zip(begin, slice_shape))]
+      out.append(ops.from_host(part, x.dtype))
+    return self.LaidOutTensor(out)
+
+  def export_to_tf_tensor(self, x, laid_out_x):
+    """Slices -> full host array (combine_slices, ops.py:1271-1305)."""
+    laid_out_x = laid_out_x.to_laid_out_tensor()
+    host = [self._ops_for(p).to_host(s) for p, s in zip(self._local_pnums, laid_out_x.all_slices)]
+    if self._distributed:
+      import torch.distributed as dist
+      gathered = [None] * self.size
+      dist.all_gather_object(gathered, host[0])
+      host = gathered
+    return _combine_host(self, host, x.shape)
+
+  # ------------------------------------------------------------ collectives
+  def allreduce(self, x, mesh_axes, reduction_fn_string):
+    if not mesh_axes:
+      return x
+    x = x.to_laid_out_tensor()
+    if reduction_fn_string not in ("SUM", "MAX", "MIN"):
+      raise ValueError("unknown reduction %s" % reduction_fn_string)
+    if self._distributed:
+      return self._dist_allreduce(x, mesh_axes, reduction_fn_string)
+    name = {"SUM": "add", "MAX": "maximum", "MIN": "minimum"}[reduction_fn_string]
+
+    def collective(slices, pnums):
+      # (x0 + ... + x_lc) + (x_rc + ... + x_{n-1}), as the reference's
+      # single-shard chain (placement_mesh_impl.py:378-397)
+      n = len(slices)
+      ops = self._ops_for(pnums[0])
+      local = [self._move(s, pnums[0]) for s in slices]
+      left_center = n // 2 - 1 if n % 2 == 0 else n // 2
+      left = local[0]
+      for i in range(1, left_center + 1):
+        left = ops.binary(name, left, local[i])
+      right = local[n - 1]
+      for i in reversed(range(left_center + 1, n - 1)):
+        right = ops.binary(name, local[i], right)
+      total = ops.binary(name, left, right) if n > 1 else left
+      return [self._move(total, p) for p in pnums]
+    return self._local_groups(x, mesh_axes, collective)
+
+  def allconcat(self, x, mesh_axis, concat_axis):
+    x = x.to_laid_out_tensor()
+    if self.shape[mesh_axis].size == 1:
+      return x
+    if self._distributed:
+      return self._dist_allconcat(x, mesh_axis, concat_axis)
+
+    def collective(slices, pnums):
+      return [self._ops_for(p).concat([self._move(s, p) for s in slices], concat_axis)
+              for p in pnums]
+    return self._local_groups(x, [mesh_axis], collective)
+
+  def alltoall(self, x, mesh_axis, split_axis, concat_axis):
+    x = x.to_laid_out_tensor()
+    n = self.shape[mesh_axis].size
+    if n == 1:
+      return x
+    if x.slice_shape[split_axis] % n != 0:
+      raise ValueError("alltoall: axis %d of slice %s is not divisible by %d"
+                       % (split_axis, x.slice_shape, n))
+    if self._distributed:
+      return self._dist_alltoall(x, mesh_axis, split_axis, concat_axis)
+
+    def collective(slices, pnums):
+      shape = list(slices[0].shape)
+      part = list(shape)
+      part[split_axis] = shape[split_axis] // n
+      out = []
+      for dst, p in enumerate(pnums):
+        ops = self._ops_for(p)
+        begin = [0] * len(shape)
+        begin[split_axis] = dst * part[split_axis]
+        pieces = [self._move(self._ops_for(q).contiguous(self._ops_for(q).slice(s, begin, part)), p)
+                  for s, q in zip(slices, pnums)]
+        self._ops_for(p)
+        out.append(ops.concat(pieces, concat_axis))
+      return out
+    return self._local_groups(x, [mesh_axis], collective)
+
+  def receive(self, x, mesh_axis, source_pcoord):
+    x = x.to_laid_out_tensor()
+    if len(source_pcoord) != self.shape[mesh_axis].size:
+      raise ValueError("source_pcoord must have one entry per processor of the mesh axis")
+    if self._distributed:
+      return self._dist_receive(x, mesh_axis, source_pcoord)
+
+    def collective(slices, pnums):
+      out = []
+      for k, p in enumerate(pnums):
+        ops = self._ops_for(p)
+        src = source_pcoord[k]
+        if src is None:
+          out.append(ops.fill(slices[0].shape, 0, slices[0].dtype))
+        else:
+          moved = self._move(slices[src], p)
+          out.append(_fresh_copy(ops, moved) if moved is slices[src] else moved)
+      return out
+    return self._local_groups(x, [mesh_axis], collective)
+
+  # ------------------------------------------------------------ in-process groups
+  def _move(self, s, pnum):
+    """The slice on processor `pnum`'s device (same object if already there)."""
+    return s
+
+  def _local_groups(self, x, mesh_axes, collective):
+    ret = [None] * self.size
+    for group in processor_groups(self.shape, list(mesh_axes)):
+      for pnum, y in zip(group, collective([x.tensor_list[p] for p in group], group)):
+        ret[pnum] = y
+    return self.LaidOutTensor(ret)
+
+  # ------------------------------------------------------------ distributed
+  def _group(self, mesh_axes):
+    """Process group of this rank for the given mesh axes, with its member pnums.
+
+    Every rank creates every group of the axis set, in the same order, as
+    torch.distributed requires."""
+    import torch.distributed as dist
+    key = tuple(sorted(mesh_axes))
+    if key not in self._groups:
+      mine = None
+      for members in processor_groups(self.shape, list(key)):
+        pg = dist.new_group(ranks=members)
+        if self._local_pnums[0] in members:
+          mine = (pg, members)
+      self._groups[key] = mine
+    return self._groups[key]
+
+  def _as_torch(self, s):
+    raise NotImplementedError
+
+  def _from_torch(self, t, shape, dtype, pnum):
+    raise NotImplementedError
+
+  def _dist_allreduce(self, x, mesh_axes, name):
+    import torch.distributed as dist
+    pg, _ = self._group(mesh_axes)
+    op = {"SUM": dist.ReduceOp.SUM, "MAX": dist.ReduceOp.MAX, "MIN": dist.ReduceOp.MIN}[name]
+    pnum = self._local_pnums[0]
+    s = x.tensor_list[0]
+    t = self._as_torch(s).clone()
+    dist.all_reduce(t, op=op, group=pg)
+    return self.LaidOutTensor([self._from_torch(t, s.shape, s.dtype, pnum)])
+
+  def _dist_allconcat(self, x, mesh_axis, concat_axis):
+    import torch
+    import torch.distributed as dist
+    pg, members = self._group([mesh_axis])
+    n = len(members)
+    pnum = self._local_pnums[0]
+    ops = self._ops_for(pnum)
+    s = x.tensor_list[0]
+    t = self._as_torch(s)
+    out = torch.empty(n * t.numel(), dtype=t.dtype, device=t.device)
+    dist.all_gather_into_tensor(out, t, group=pg)
+    shape = list(s.shape)
+    gathered = self._from_torch(out, [n] + shape, s.dtype, pnum)  # [source, *slice]
+    # [source, d0.., d_axis, ..] -> [d0.., source, d_axis, ..] -> merge source into the axis
+    perm = list(range(1, concat_axis + 1)) + [0] + list(range(concat_axis + 1, len(shape) + 1))
+    merged = list(shape)
+    merged[concat_axis] *= n
+    return self.LaidOutTensor([ops.reshape(ops.transpose(gathered, perm), merged)])
+
+  def _dist_alltoall(self, x, mesh_axis, split_axis, concat_axis):
+    import torch
+    import torch.distributed as dist
+    pg, members = self._group([mesh_axis])
+    n = len(members)
+    pnum = self._local_pnums[0]
+    ops = self._ops_for(pnum)
+    s = x.tensor_list[0]
+    shape = list(s.shape)
+    part = list(shape)
+    part[split_axis] //= n
+    # pack: [.., n*part, ..] -> [n(target), .., part, ..]
+    split = ops.reshape(s, shape[:split_axis] + [n, part[split_axis]] + shape[split_axis + 1:])
+    perm = [split_axis] + [i for i in range(len(shape) + 1) if i != split_axis]
+    packed = ops.contiguous(ops.transpose(split, perm))
+    t = self._as_torch(packed)
+    out = torch.empty_like(t)
+    dist.all_to_all_single(out, t, group=pg)
+    received = self._from_torch(out, [n] + part, s.dtype, pnum)  # [source, *part]
+    perm = list(range(1, concat_axis + 1)) + [0] + list(range(concat_axis + 1, len(part) + 1))
+    merged = list(part)
+    merged[concat_axis] *= n
+    return self.LaidOutTensor([ops.reshape(ops.transpose(received, perm), merged)])
+
+  def _dist_receive(self, x, mesh_axis, source_pcoord):
+    import torch
+    import torch.distributed as dist
+    _, members = self._group([mesh_axis])
+    pnum = self._local_pnums[0]
+    ops = self._ops_for(pnum)
+    me = members.index(pnum)
+    s = x.tensor_list[0]
+    t = self._as_torch(s)
+    p2p = []
+    src = source_pcoord[me]
+    result = None
+    if src is None:
+      result = ops.fill(s.shape, 0, s.dtype)
+    elif src == me:
+      result = _fresh_copy(ops, s)
+    else:
+      buf = torch.empty_like(t)
+      p2p.append(dist.P2POp(dist.irecv, buf, members[src]))
+    for k, wanted in enumerate(source_pcoord):
+      if wanted == me and k != me:
+        p2p.append(dist.P2POp(dist.isend, t, members[k]))
+    if p2p:
+      for work in dist.batch_isend_irecv(p2p):
+        work.wait()
+    if result is None:
+      result = self._from_torch(buf, s.shape, s.dtype, pnum)
+    return self.LaidOutTensor([result])
+
+
+def _fresh_copy(ops, s):
+  """A new buffer holding `s` (collectives return fresh tensors)."""
+  return ops.concat([s], 0) if len(s.shape) else ops.binary("add", s, 0)
+
+
+def _combine_host(impl, slices, tensor_shape):
+  """combine_slices over numpy arrays (mesh_tensorflow/ops.py:1271-1305)."""
+  if tensor_shape.ndims == 0:
+    return np.asarray(slices[0])
+  ret = list(slices)
+  ma2ta = impl.tensor_layout(tensor_shape).mesh_axis_to_tensor_axis(impl.ndims)
+  for mesh_dim, tensor_axis in zip(impl.shape, ma2ta):
+    span = len(ret) // mesh_dim.size
+    if tensor_axis is None:
+      ret = ret[:span]
+    else:
+      ret = [np.concatenate([ret[i + span * j] for j in range(mesh_dim.size)], axis=tensor_axis)
+             for i in range(span)]
+  assert len(ret) == 1
+  return ret[0]
+
+
+class CudaMeshImpl(SlicedMeshImpl):
+  """MeshImpl on CUDA devices through libmtfc.
+
+  Args:
+    shape: mesh Shape, or "rows:2,cols:4".
+    layout: LayoutRules, or "batch:rows;d_ff:cols".
+    devices: one CUDA ordinal (or "cuda:N") per processor, length shape.size.
+      Ordinals may repeat.  When torch.distributed is initialised with a world
+      size equal to the mesh size, the job is one process per processor: this
+      process computes processor `rank` on `devices[rank]`.
+    distributed: force (True) or forbid (False) that mode; None = detect.
+  """
+
+  supports_einsum_epilogue = True
+
+  def __init__(self, shape, layout, devices=None, distributed=None):
+    import torch
+    from mesh_b200 import _native as nat
+    from mesh_b200.device_ops import DeviceArray, DeviceOps
+    mesh_shape = mtf.convert_to_shape(shape)
+    size = mesh_shape.size
+    if distributed is None:
+      import torch.distributed as dist
+      distributed = (dist.is_available() and dist.is_initialized()
+                     and dist.get_world_size() == size and size > 1)
+    if devices is None:
+      devices = [torch.cuda.current_device()] * size if torch.cuda.is_available() else [0] * size
+    if len(devices) != size:
+      raise ValueError("devices must have one entry per processor: got %d for mesh size %d"
+                       % (len(devices), size))
+    if not torch.cuda.is_available():
+      raise nat.MtfcError(nat.ERR_CUDA, "CudaMeshImpl needs a CUDA device; none is visible")
+    nat.lib()  # fail now, loudly, if the kernels are not built
+    self._devices = [torch.device(d if isinstance(d, str) else "cuda:%d" % d) for d in devices]
+    if distributed:
+      import torch.distributed as dist
+      local = [dist.get_rank()]
+    else:
+      local = list(range(size))
+    super().__init__(mesh_shape, layout, local, distributed)
+    self._device_array = DeviceArray
+    self._ops = DeviceOps(self._devices[local[0]])
+
+  @property
+  def devices(self):
+    return list(self._devices)
+
+  @property
+  def slice_ops(self):
+    return self._ops
+
+  def _ops_for(self, pnum):
+    self._ops.device = self._devices[pnum]
+    return self._ops
+
+  def _is_slice(self, x):
+    return isinstance(x, self._device_array)
+
+  def _move(self, s, pnum):
+    dev = self._devices[pnum]
+    if s.device == dev:
+      return s
+    ops = self._ops_for(pnum)
+    packed = self._ops.contiguous(s)
+    flat = packed.buf[packed.offset:packed.offset + max(1, packed.size)].to(dev)
+    del ops
+    return self._device_array(flat, s.shape, s.dtype)
+
+  def einsum(self, equation, *slices, epilogue=None):
+    """Per-slice contraction hook (ops.py:1331-1340) on the GEMM kernels;
+    `epilogue="relu"` fuses tf.nn.relu into the store."""
+    from mesh_b200 import _native as nat
+    code = {None: nat.EPILOGUE_NONE, "relu": nat.EPILOGUE_RELU}[epilogue]
+    self._ops.device = slices[0].device
+    return self._ops.einsum(equation, *slices, epilogue=code)
+
+  def _as_torch(self, s):
+    packed = self._ops.contiguous(s)
+    return packed.buf[packed.offset:packed.offset + max(1, packed.size)]
+
+  def _from_torch(self, t, shape, dtype, pnum):
+    return self._device_array(t, shape, dtype)
+
+  def synchronize(self):
+    """Waits for all enqueued work and raises if a kernel reported a timeout."""
+    import torch
+    from mesh_b200 import _native as nat
+    for dev in sorted(set(self._devices[p] for p in self._local_pnums), key=str):
+      with torch.cuda.device(dev):
+        nat.device_status()

@@ -1,0 +1,523 @@
+"""DeviceOps: the array library CudaMeshImpl computes its slices with.
+
+Plays the role `tf.*` plays inside the reference's slicewise closures
+(mesh_tensorflow/ops.py) but every operation is a libmtfc kernel reached
+through the C ABI of include/mtfc.h.  PyTorch appears only as the owner of
+device memory (torch.empty), the source of the current stream, and for
+host<->device copies; no torch compute op is on any path here.  A missing or
+failing library raises — there is no CPU fallback.
+
+A slice is a DeviceArray: a strided view (shape, element strides, offset) of
+a flat torch buffer.  transpose / expand_dims / slice / broadcast_to only
+rewrite the view; kernels that take strides (binary, broadcast_reduce, GEMM,
+strided copy) read views in place, the others get a packed copy first.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from mesh_b200 import _native as nat
+from mesh_b200.mtf import graph as G
+
+_TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32,
+          "bool": torch.int32}
+_CODE = {"float32": nat.F32, "bfloat16": nat.BF16, "int32": nat.I32, "bool": nat.I32}
+
+_UNARY = {"identity": 0, "relu": 1, "exp": 2, "log": 3, "negative": 4, "reciprocal": 5,
+          "sqrt": 6, "rsqrt": 7, "square": 8, "tanh": 9, "sigmoid": 10, "sign": 11,
+          "logical_not": 12, "nonzero": 13}
+_BINARY = {"add": 0, "sub": 1, "multiply": 2, "divide": 3, "maximum": 4, "minimum": 5,
+           "floordiv": 6, "mod": 7, "less": 8, "greater": 9, "less_equal": 10,
+           "greater_equal": 11, "equal": 12, "not_equal": 13, "logical_and": 14,
+           "logical_or": 15}
+_COMPARISONS = frozenset(["less", "greater", "less_equal", "greater_equal", "equal",
+                          "not_equal", "logical_and", "logical_or"])
+_REDUCE = {"SUM": 0, "MAX": 1, "MIN": 2}
+_POLICY = {"all": 0, "none": 1, "threshold": 2, "random": 3}
+
+
+def _contiguous_strides(shape):
+  strides, acc = [], 1
+  for s in reversed(shape):
+    strides.append(acc)
+    acc *= s
+  return tuple(reversed(strides))
+
+
+def _volume(shape):
+  n = 1
+  for s in shape:
+    n *= s
+  return n
+
+
+class DeviceArray(object):
+  """A strided view of a flat device buffer with an mtf dtype."""
+  __slots__ = ("buf", "shape", "strides", "offset", "dtype")
+
+  def __init__(self, buf, shape, dtype, strides=None, offset=0):
+    self.buf = buf
+    self.shape = tuple(int(s) for s in shape)
+    self.strides = tuple(strides) if strides is not None else _contiguous_strides(self.shape)
+    self.offset = offset
+    self.dtype = dtype
+
+  @property
+  def size(self):
+    return _volume(self.shape)
+
+  @property
+  def ptr(self):
+    return self.buf.data_ptr() + self.offset * self.dtype.itemsize
+
+  @property
+  def device(self):
+    return self.buf.device
+
+  @property
+  def is_contiguous(self):
+    expect = 1
+    for s, st in zip(reversed(self.shape), reversed(self.strides)):
+      if s != 1 and st != expect:
+        return False
+      expect *= s
+    return True
+
+  def __repr__(self):
+    return "DeviceArray(%s, %s, %s)" % (list(self.shape), self.dtype.name, self.device)
+
+
+def _i64(values):
+  return (ctypes.c_int64 * max(1, len(values)))(*values)
+
+
+class DeviceOps(object):
+  """libmtfc-backed array operations on one CUDA device."""
+
+  def __init__(self, device):
+    self.device = torch.device(device)
+    if self.device.type != "cuda":
+      raise nat.MtfcError(nat.ERR_CUDA, "DeviceOps needs a CUDA device, got %s" % (device,))
+    self._lib = nat.lib()
+
+  # ---------------------------------------------------------------- plumbing
+  def _stream(self):
+    return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+  def _empty(self, shape, dtype):
+    n = max(1, _volume(shape))
+    buf = torch.empty(n, dtype=_TORCH[dtype.name], device=self.device)
+    return DeviceArray(buf, shape, dtype)
+
+  def _call(self, fn, *args):
+    with torch.cuda.device(self.device):
+      nat.check(fn(*args))
+
+  def contiguous(self, x):
+    if x.is_contiguous:
+      if x.strides == _contiguous_strides(x.shape):
+        return x
+      return DeviceArray(x.buf, x.shape, x.dtype, offset=x.offset)
+    out = self._empty(x.shape, x.dtype)
+    self._copy(x, out)
+    return out
+
+  def _copy(self, src, dst):
+    """dst view <- src view (same shape)."""
+    assert src.shape == dst.shape, (src.shape, dst.shape)
+    if src.size == 0:
+      return
+    self._call(self._lib.mtfc_copy_strided, ctypes.c_void_p(src.ptr), _i64(src.strides),
+               ctypes.c_void_p(dst.ptr), _i64(dst.strides), len(src.shape), _i64(src.shape),
+               src.dtype.itemsize, self._stream())
+
+  # ---------------------------------------------------------------- host I/O
+  def from_host(self, value, dtype):
+    a = np.ascontiguousarray(np.asarray(value))
+    if dtype.is_floating:
+      t = torch.from_numpy(a.astype(np.float32, copy=False)).to(_TORCH[dtype.name])
+    elif dtype.is_bool:
+      t = torch.from_numpy((a != 0).astype(np.int32))
+    else:
+      t = torch.from_numpy(a.astype(np.int32, copy=False))
+    shape = a.shape
+    buf = t.reshape(-1).to(self.device) if t.numel() else torch.empty(
+        1, dtype=_TORCH[dtype.name], device=self.device)
+    return DeviceArray(buf, shape, dtype)
+
+  def to_host(self, x):
+    x = self.contiguous(x)
+    n = x.size
+    flat = x.buf[x.offset:x.offset + n].cpu()
+    if x.dtype.name == "bfloat16":
+      flat = flat.float()
+    a = flat.numpy().reshape(x.shape)
+    if x.dtype.is_bool:
+      a = a != 0
+    return a
+
+  # ---------------------------------------------------------------- metadata
+  def shape(self, x):
+    return x.shape
+
+  def dtype(self, x):
+    return x.dtype
+
+  # ---------------------------------------------------------------- views
+  def transpose(self, x, perm):
+    return DeviceArray(x.buf, [x.shape[p] for p in perm], x.dtype,
+                       strides=[x.strides[p] for p in perm], offset=x.offset)
+
+  def expand_dims(self, x, axis):
+    shape, strides = list(x.shape), list(x.strides)
+    shape.insert(axis, 1)
+    strides.insert(axis, 0)
+    return DeviceArray(x.buf, shape, x.dtype, strides=strides, offset=x.offset)
+
+  def slice(self, x, begin, size):
+    offset = x.offset + sum(b * st for b, st in zip(begin, x.strides))
+    return DeviceArray(x.buf, size, x.dtype, strides=x.strides, offset=offset)
+
+  def broadcast_to(self, x, shape):
+    shape = tuple(shape)
+    pad = len(shape) - len(x.shape)
+    strides = [0] * pad + [0 if (s == 1 and t != 1) else st
+                           for s, st, t in zip(x.shape, x.strides, shape[pad:])]
+    return DeviceArray(x.buf, shape, x.dtype, strides=strides, offset=x.offset)
+
+  def reshape(self, x, shape):
+    shape = tuple(int(s) for s in shape)
+    if _volume(shape) != x.size:
+      raise ValueError("cannot reshape %s to %s" % (x.shape, shape))
+    x = self.contiguous(x)
+    return DeviceArray(x.buf, shape, x.dtype, offset=x.offset)
+
+  def concat(self, xs, axis):
+    shape = list(xs[0].shape)
+    shape[axis] = sum(x.shape[axis] for x in xs)
+    out = self._empty(shape, xs[0].dtype)
+    at = 0
+    for x in xs:
+      begin = [0] * len(shape)
+      begin[axis] = at
+      self._copy(x, self.slice(out, begin, x.shape))
+      at += x.shape[axis]
+    return out
+
+  # ---------------------------------------------------------------- creation
+  def fill(self, shape, value, dtype):
+    out = self._empty(shape, dtype)
+    self._call(self._lib.mtfc_fill, ctypes.c_void_p(out.ptr), _CODE[dtype.name], out.size,
+               ctypes.c_float(float(value)), ctypes.c_float(0.0), self._stream())
+    return out
+
+  def range(self, n, dtype):
+    out = self._empty([n], dtype)
+    self._call(self._lib.mtfc_fill, ctypes.c_void_p(out.ptr), _CODE[dtype.name], n,
+               ctypes.c_float(0.0), ctypes.c_float(1.0), self._stream())
+    return out
+
+  # ---------------------------------------------------------------- maps
+  def _unary_code(self, code, x, out_dtype):
+    x = self.contiguous(x)
+    out = self._empty(x.shape, out_dtype)
+    self._call(self._lib.mtfc_unary, code, ctypes.c_void_p(x.ptr), _CODE[x.dtype.name],
+               ctypes.c_void_p(out.ptr), _CODE[out_dtype.name], x.size, self._stream())
+    return out
+
+  def unary(self, name, x):
+    out_dtype = G.bool_ if name == "logical_not" else x.dtype
+    return self._unary_code(_UNARY[name], x, out_dtype)
+
+  def cast(self, x, dtype):
+    if dtype == x.dtype:
+      return x
+    if dtype.is_bool:
+      return self._unary_code(_UNARY["nonzero"], x, dtype)
+    return self._unary_code(_UNARY["identity"], x, dtype)
+
+  def binary(self, name, a, b):
+    if not isinstance(a, DeviceArray):
+      # scalar on the left: only commutative ops arrive this way
+      if name in ("add", "multiply", "maximum", "minimum", "equal", "not_equal"):
+        a, b = b, a
+      else:
+        a = self.fill([], a, b.dtype)
+    out_dtype = G.bool_ if name in _COMPARISONS else a.dtype
+    if isinstance(b, DeviceArray):
+      if _CODE[a.dtype.name] != _CODE[b.dtype.name]:
+        raise ValueError("binary %s: dtypes differ (%s, %s)" % (name, a.dtype, b.dtype))
+      nd = max(len(a.shape), len(b.shape))
+      sa = (1,) * (nd - len(a.shape)) + a.shape
+      sb = (1,) * (nd - len(b.shape)) + b.shape
+      shape = []
+      for x, y in zip(sa, sb):
+        if x != y and x != 1 and y != 1:
+          raise ValueError("binary %s: shapes %s and %s do not broadcast" % (name, a.shape, b.shape))
+        shape.append(max(x, y) if min(x, y) != 0 else 0)
+      av, bv = self.broadcast_to(a, shape), self.broadcast_to(b, shape)
+      b_ptr, b_str, scalar = ctypes.c_void_p(bv.ptr), _i64(bv.strides), 0.0
+    else:
+      shape = list(a.shape)
+      av = a
+      b_ptr, b_str, scalar = ctypes.c_void_p(0), _i64([0] * len(shape)), float(b)
+    if len(shape) > nat.MAX_DIMS:
+      raise ValueError("binary %s: rank %d exceeds %d" % (name, len(shape), nat.MAX_DIMS))
+    out = self._empty(shape, out_dtype)
+    self._call(self._lib.mtfc_binary, _BINARY[name], ctypes.c_void_p(av.ptr), _i64(av.strides),
+               b_ptr, b_str, ctypes.c_double(scalar), ctypes.c_void_p(out.ptr),
+               _CODE[a.dtype.name], _CODE[out_dtype.name], len(shape), _i64(shape),
+               self._stream())
+    return out
+
+  # ---------------------------------------------------------------- reductions
+  def _broadcast_reduce(self, op, xs, out_shape, out_strides, red_shape, red_strides, out_dtype):
+    n = len(xs)
+    ptrs = (ctypes.c_void_p * n)(*[x.ptr for x in xs])
+    keep = [_i64(s) for s in out_strides] + [_i64(s) for s in red_strides]
+    o_arr = (ctypes.POINTER(ctypes.c_int64) * n)(
+        *[ctypes.cast(k, ctypes.POINTER(ctypes.c_int64)) for k in keep[:n]])
+    r_arr = (ctypes.POINTER(ctypes.c_int64) * n)(
+        *[ctypes.cast(k, ctypes.POINTER(ctypes.c_int64)) for k in keep[n:]])
+    out = self._empty(out_shape, out_dtype)
+    self._call(self._lib.mtfc_broadcast_reduce, _REDUCE[op], n, ptrs, _CODE[xs[0].dtype.name],
+               ctypes.c_void_p(out.ptr), _CODE[out_dtype.name], len(out_shape), _i64(out_shape),
+               o_arr, len(red_shape), _i64(red_shape), r_arr, self._stream())
+    return out
+
+  def reduce(self, name, x, axes):
+    axes = sorted(a % len(x.shape) for a in axes)
+    kept = [i for i in range(len(x.shape)) if i not in axes]
+    return self._broadcast_reduce(
+        name, [x], [x.shape[i] for i in kept], [[x.strides[i] for i in kept]],
+        [x.shape[i] for i in axes], [[x.strides[i] for i in axes]], x.dtype)
+
+  def argmax(self, x):
+    x = self.contiguous(x)
+    rows, cols = _volume(x.shape[:-1]), x.shape[-1]
+    idx = self._empty(x.shape[:-1], G.int32)
+    self._call(self._lib.mtfc_topk_last, ctypes.c_void_p(x.ptr), _CODE[x.dtype.name], rows, cols,
+               1, ctypes.c_void_p(0), ctypes.c_void_p(idx.ptr), self._stream())
+    return idx
+
+  def top_k(self, x, k):
+    x = self.contiguous(x)
+    rows, cols = _volume(x.shape[:-1]), x.shape[-1]
+    values = self._empty(x.shape[:-1] + (k,), x.dtype)
+    idx = self._empty(x.shape[:-1] + (k,), G.int32)
+    self._call(self._lib.mtfc_topk_last, ctypes.c_void_p(x.ptr), _CODE[x.dtype.name], rows, cols,
+               k, ctypes.c_void_p(values.ptr), ctypes.c_void_p(idx.ptr), self._stream())
+    return values, idx
+
+  def gather_last(self, values, indices):
+    values, indices = self.contiguous(values), self.contiguous(indices)
+    rows, cols, k = _volume(values.shape[:-1]), values.shape[-1], indices.shape[-1]
+    out = self._empty(indices.shape, values.dtype)
+    self._call(self._lib.mtfc_gather_last, ctypes.c_void_p(values.ptr), _CODE[values.dtype.name],
+               ctypes.c_void_p(indices.ptr), rows, cols, k, ctypes.c_void_p(out.ptr),
+               self._stream())
+    return out
+
+  def one_hot(self, indices, depth, on_value, off_value, dtype):
+    indices = self.contiguous(indices)
+    out = self._empty(indices.shape + (depth,), dtype)
+    self._call(self._lib.mtfc_one_hot, ctypes.c_void_p(indices.ptr), indices.size, depth,
+               ctypes.c_float(float(on_value)), ctypes.c_float(float(off_value)),
+               ctypes.c_void_p(out.ptr), _CODE[dtype.name], self._stream())
+    return out
+
+  # ---------------------------------------------------------------- einsum
+  @staticmethod
+  def _parse(equation, n):
+    lhs, rhs = equation.replace(" ", "").split("->")
+    terms = lhs.split(",")
+    if len(terms) != n:
+      raise ValueError("einsum %s: expected %d operands" % (equation, n))
+    return terms, rhs
+
+  def einsum_naive(self, equation, *xs):
+    """Broadcast-multiply-reduce: out[o] = sum_r prod_k x_k[o, r]."""
+    terms, out_term = self._parse(equation, len(xs))
+    if len(xs) > 4:
+      head = self.einsum_naive(",".join(terms[:2]) + "->" + _union(terms[:2]), *xs[:2])
+      return self.einsum_naive(",".join([_union(terms[:2])] + terms[2:]) + "->" + out_term,
+                               head, *xs[2:])
+    sizes = {}
+    for term, x in zip(terms, xs):
+      for letter, s in zip(term, x.shape):
+        sizes[letter] = s
+    red = [l for l in _union(terms) if l not in out_term]
+    stride_of = lambda term, x, l: x.strides[term.index(l)] if l in term else 0
+    out_strides = [[stride_of(t, x, l) for l in out_term] for t, x in zip(terms, xs)]
+    red_strides = [[stride_of(t, x, l) for l in red] for t, x in zip(terms, xs)]
+    return self._broadcast_reduce("SUM", list(xs), [sizes[l] for l in out_term], out_strides,
+                                  [sizes[l] for l in red], red_strides, xs[0].dtype)
+
+  def einsum(self, equation, *xs, epilogue=nat.EPILOGUE_NONE, out_dtype=None):
+    """Contraction on the GEMM kernels; operand layouts are read in place.
+
+    Dims are classed as batch (in both operands and the output), M (first
+    operand and output), N (second operand and output) and K (both operands,
+    not the output).  When each class collapses to one stride per tensor the
+    named-dim order goes to the kernel as strides; otherwise the operands are
+    packed first and the result is unpacked.
+    """
+    terms, out_term = self._parse(equation, len(xs))
+    if len(xs) == 1:
+      return self.einsum_naive(equation, *xs)
+    if len(xs) > 2:
+      later = set("".join(terms[2:]) + out_term)
+      mid = "".join(l for l in _union(terms[:2]) if l in later)
+      head = self.einsum(",".join(terms[:2]) + "->" + mid, xs[0], xs[1])
+      return self.einsum(",".join([mid] + terms[2:]) + "->" + out_term, head, *xs[2:],
+                         epilogue=epilogue, out_dtype=out_dtype)
+    ta, tb = terms
+    a, b = xs
+    out_dtype = out_dtype or a.dtype
+    # dims that occur in one operand only and not in the output are summed first
+    for which, (t, other) in enumerate(((ta, tb), (tb, ta))):
+      lone = [l for l in t if l not in other and l not in out_term]
+      if lone:
+        kept = "".join(l for l in t if l not in lone)
+        reduced = self.einsum_naive(t + "->" + kept, a if which == 0 else b)
+        if which == 0:
+          a, ta = reduced, kept
+        else:
+          b, tb = reduced, kept
+    sizes = {}
+    for term, x in ((ta, a), (tb, b)):
+      for letter, s in zip(term, x.shape):
+        sizes[letter] = s
+    batch = [l for l in out_term if l in ta and l in tb]
+    m_dims = [l for l in out_term if l in ta and l not in tb]
+    n_dims = [l for l in out_term if l in tb and l not in ta]
+    k_dims = [l for l in ta if l in tb and l not in out_term]
+    if not k_dims or not a.dtype.is_floating:
+      return self.einsum_naive(ta + "," + tb + "->" + out_term, a, b)
+    out_shape = [sizes[l] for l in out_term]
+    out = self._empty(out_shape, out_dtype)
+    out_strides = dict(zip(out_term, out.strides))
+    sa, sb = dict(zip(ta, a.strides)), dict(zip(tb, b.strides))
+
+    def collapse(dims, strides):
+      """(extent, stride) of the dims taken as one axis, or None."""
+      dims = [d for d in dims if sizes[d] != 1]
+      if not dims:
+        return 1, 0
+      for hi, lo in zip(dims[:-1], dims[1:]):
+        if strides[hi] != strides[lo] * sizes[lo]:
+          return None
+      return _volume([sizes[d] for d in dims]), strides[dims[-1]]
+
+    plan = [collapse(batch, sa), collapse(batch, sb), collapse(batch, out_strides),
+            collapse(m_dims, sa), collapse(m_dims, out_strides),
+            collapse(n_dims, sb), collapse(n_dims, out_strides),
+            collapse(k_dims, sa), collapse(k_dims, sb)]
+    if any(p is None for p in plan):
+      # pack to [batch, M, K] x [batch, K, N] -> [batch, M, N], then unpack
+      pa = self.contiguous(self.transpose(a, [ta.index(l) for l in batch + m_dims + k_dims]))
+      pb = self.contiguous(self.transpose(b, [tb.index(l) for l in batch + k_dims + n_dims]))
+      packed_term = "".join(batch + m_dims + n_dims)
+      res = self.einsum("".join(batch + m_dims + k_dims) + "," + "".join(batch + k_dims + n_dims)
+                        + "->" + packed_term, pa, pb, epilogue=epilogue, out_dtype=out_dtype)
+      if packed_term == out_term:
+        return res
+      self._copy(self.transpose(res, [packed_term.index(l) for l in out_term]), out)
+      return out
+    (nb, a_b), (_, b_b), (_, c_b), (m, a_m), (_, c_m), (n, b_n), (_, c_n), (k, a_k), (_, b_k) = plan
+    d = nat.GemmDesc()
+    d.batch, d.m, d.n, d.k = nb, m, n, k
+    d.a_batch, d.a_m, d.a_k = a_b, a_m, a_k
+    d.b_batch, d.b_k, d.b_n = b_b, b_k, b_n
+    d.c_batch, d.c_m, d.c_n = c_b, c_m, c_n
+    d.in_dtype = _CODE[a.dtype.name]
+    d.out_dtype = _CODE[out_dtype.name]
+    d.epilogue = epilogue
+    d.force_path = 0
+    self._call(self._lib.mtfc_gemm, ctypes.byref(d), ctypes.c_void_p(a.ptr),
+               ctypes.c_void_p(b.ptr), ctypes.c_void_p(out.ptr), self._stream())
+    return out
+
+  # ---------------------------------------------------------------- fused MoE
+  def moe_gate_logits(self, x, w):
+    """[tokens, parts*experts] fp32 gate logits and `parts`.
+
+    bf16 activations against the fp32 gate kernel run on the tensor cores with
+    the kernel split in three bf16 terms; fp32 activations use the FFMA GEMM.
+    """
+    m, e = w.shape
+    tokens = x.size // m
+    x2 = self.reshape(x, [tokens, m])
+    w = self.contiguous(w)
+    if x.dtype.name == "bfloat16":
+      w3 = self._empty([m, 3 * e], G.bfloat16)
+      self._call(self._lib.mtfc_moe_split_gate_weights, ctypes.c_void_p(w.ptr), m, e,
+                 ctypes.c_void_p(w3.ptr), self._stream())
+      return self.einsum("tm,me->te", x2, w3, out_dtype=G.float32), 3
+    return self.einsum("tm,me->te", self.cast(x2, G.float32), w), 1
+
+  def moe_top2_gating_from_logits(self, logits, parts, lead_shape, group_size, experts, capacity,
+                                  policy, threshold, noise, num_groups_total, want_raw=False):
+    groups = _volume(lead_shape)
+    tok_shape = tuple(lead_shape) + (group_size,)
+    logits = self.contiguous(logits)
+    i1, i2, p1, p2 = [self._empty(tok_shape, G.int32) for _ in range(4)]
+    g1, g2 = self._empty(tok_shape, G.float32), self._empty(tok_shape, G.float32)
+    raw = self._empty(tok_shape + (experts,), G.float32) if want_raw else None
+    loss_per_group = self._empty([groups], G.float32)
+    noise_ptr = ctypes.c_void_p(self.contiguous(noise).ptr) if noise is not None else ctypes.c_void_p(0)
+    self._call(self._lib.mtfc_moe_top2_gating, ctypes.c_void_p(logits.ptr), parts, groups,
+               group_size, experts, capacity, _POLICY[policy], ctypes.c_float(threshold),
+               noise_ptr, ctypes.c_void_p(i1.ptr), ctypes.c_void_p(i2.ptr),
+               ctypes.c_void_p(p1.ptr), ctypes.c_void_p(p2.ptr), ctypes.c_void_p(g1.ptr),
+               ctypes.c_void_p(g2.ptr), ctypes.c_void_p(raw.ptr if raw is not None else 0),
+               ctypes.c_void_p(loss_per_group.ptr), self._stream())
+    loss = self.binary("multiply", self.reduce("SUM", loss_per_group, [0]),
+                       1.0 / float(num_groups_total))
+    result = (i1, i2, p1, p2, g1, g2, loss)
+    return result + (raw,) if want_raw else result
+
+  def moe_top2_gating(self, x, w, capacity, policy, threshold, noise, num_groups_total):
+    """Fused `_top_2_gating` on one slice: x [..., S, M], w [M, E]."""
+    logits, parts = self.moe_gate_logits(x, w)
+    return self.moe_top2_gating_from_logits(
+        logits, parts, x.shape[:-2], x.shape[-2], w.shape[1], capacity, policy, threshold, noise,
+        num_groups_total)
+
+  def moe_dispatch(self, x, i1, i2, p1, p2, g1, g2, num_experts, capacity):
+    o, g, s, m = x.shape
+    x = self.contiguous(x)
+    args = [self.contiguous(t) for t in (i1, i2, p1, p2, g1, g2)]
+    table = self._empty([o * g, num_experts, capacity], G.int32)
+    self._call(self._lib.mtfc_moe_slot_table, *[ctypes.c_void_p(t.ptr) for t in args], o * g, s,
+               num_experts, capacity, 1 if x.dtype.name == "bfloat16" else 0,
+               ctypes.c_void_p(table.ptr), self._stream())
+    out = self._empty([o, num_experts, g, capacity, m], x.dtype)
+    self._call(self._lib.mtfc_moe_dispatch, ctypes.c_void_p(x.ptr), ctypes.c_void_p(table.ptr),
+               ctypes.c_void_p(out.ptr), o, g, s, num_experts, capacity, m * x.dtype.itemsize,
+               self._stream())
+    return out
+
+  def moe_combine(self, y, i1, i2, p1, p2, g1, g2):
+    o, e, g, c, m = y.shape
+    s = i1.shape[-1]
+    y = self.contiguous(y)
+    args = [self.contiguous(t) for t in (i1, i2, p1, p2, g1, g2)]
+    out = self._empty([o, g, s, m], y.dtype)
+    self._call(self._lib.mtfc_moe_combine, ctypes.c_void_p(y.ptr), _CODE[y.dtype.name],
+               *[ctypes.c_void_p(t.ptr) for t in args], ctypes.c_void_p(out.ptr), o, g, s, e, c,
+               m, self._stream())
+    return out
+
+
+def _union(terms):
+  seen = []
+  for t in terms:
+    for l in t:
+      if l not in seen:
+        seen.append(l)
+  return "".join(seen)

@@ -71,7 +71,12 @@ def dense(x, new_dims, reduced_dims=None, expert_dims=None, use_bias=True, activ
     kernel_weights = get_dense_kernel_weights(
         x, new_dims, reduced_dims, expert_dims, weights, name=name,
         variable_dtype=variable_dtype)
-  y = mtf.einsum([x, kernel_weights], output_shape)
+  # ReLU straight after the product rides in the einsum (a GEMM epilogue on
+  # backends that support it) instead of a separate pass over the output.
+  fused_relu = activation is mtf.relu and not use_bias
+  y = mtf.einsum([x, kernel_weights], output_shape, activation="relu" if fused_relu else None)
+  if fused_relu:
+    return y
   if use_bias:
     if bias is None:
       bias = mtf.zeros(x.mesh, Shape(expert_dims + new_dims), dtype=x.dtype)

@@ -435,12 +435,15 @@ def _einsum_equation(input_shapes, output_shape):
   return ",".join(parts[:-1]) + "->" + parts[-1]
 
 
-def _einsum_helper(input_shapes, output_shape, mesh_impl, floating):
+def _einsum_helper(input_shapes, output_shape, mesh_impl, floating, activation=None):
   """Per-slice einsum fn and the mesh axes of split contracted dims (ops.py:2784-2823).
 
   When some operand or the output already spans every dimension, the product
   is formed by broadcast-multiply-reduce (`einsum_naive`); otherwise, for
   floating types, by the backend's contraction hook `mesh_impl.einsum`.
+  `activation` ("relu") is applied to the slice result; a backend that
+  declares `supports_einsum_epilogue` gets it as the hook's `epilogue`
+  argument and fuses it into the contraction.
   """
   ops = mesh_impl.slice_ops
   union = shape_union(input_shapes)
@@ -450,8 +453,16 @@ def _einsum_helper(input_shapes, output_shape, mesh_impl, floating):
   reduce_axes = [i for i, d in enumerate(full_shape.dims) if d not in output_shape.dims]
   reduced_mesh_axes = [layout[i] for i in reduce_axes if layout[i] is not None]
   equation = _einsum_equation(input_shapes, output_shape)
+  fuse = activation is not None and not reduced_mesh_axes
   if full_shapes or not floating:
-    fn = lambda *slices: ops.einsum_naive(equation, *slices)
+    if fuse:
+      fn = lambda *slices: ops.unary(activation, ops.einsum_naive(equation, *slices))
+    else:
+      fn = lambda *slices: ops.einsum_naive(equation, *slices)
+  elif fuse and getattr(mesh_impl, "supports_einsum_epilogue", False):
+    fn = lambda *slices: mesh_impl.einsum(equation, *slices, epilogue=activation)
+  elif fuse:
+    fn = lambda *slices: ops.unary(activation, mesh_impl.einsum(equation, *slices))
   else:
     fn = lambda *slices: mesh_impl.einsum(equation, *slices)
   return fn, reduced_mesh_axes
@@ -460,8 +471,9 @@ def _einsum_helper(input_shapes, output_shape, mesh_impl, floating):
 class EinsumOperation(Operation):
   """Einstein summation over named dims (mesh_tensorflow/ops.py:2826-2880)."""
 
-  def __init__(self, inputs, output_shape, name=None):
+  def __init__(self, inputs, output_shape, name=None, activation=None):
     super().__init__(inputs, name=name or "einsum")
+    self._activation = activation
     if not inputs:
       raise ValueError("Einsum needs at least one input")
     for x in inputs:
@@ -476,13 +488,17 @@ class EinsumOperation(Operation):
     output_shape = self.outputs[0].shape
     intersection = Shape([d for d in output_shape.dims if d in in_dims])
     fn, reduced_mesh_axes = _einsum_helper(
-        [x.shape for x in xs], intersection, impl, xs[0].dtype.is_floating)
+        [x.shape for x in xs], intersection, impl, xs[0].dtype.is_floating, self._activation)
     y = impl.slicewise(fn, *[lowering.tensors[x] for x in xs])
     if reduced_mesh_axes:
       def add_counter_fn():
         lowering.add_counter("allreduce/%s/einsum_op" % reduced_mesh_axes,
                              impl.laid_out_size(intersection))
       y = LazyAllreduceSum(impl, y, reduced_mesh_axes, add_counter_fn=add_counter_fn)
+      if self._activation is not None:
+        # the activation has to see the reduced sum
+        ops, act = impl.slice_ops, self._activation
+        y = impl.slicewise(lambda t: ops.unary(act, t), y)
     if intersection != output_shape:
       y = impl.broadcast_impl(y, intersection, output_shape)
     lowering.set_tensor_lowering(self.outputs[0], y)
@@ -491,9 +507,10 @@ class EinsumOperation(Operation):
     lowering.add_counter("einsum_unique", computation_shape.size)
 
 
-def einsum(xs, output_shape=None, reduced_dims=None, name=None):
+def einsum(xs, output_shape=None, reduced_dims=None, name=None, activation=None):
   """Einstein summation; exactly one of output_shape / reduced_dims may be given
-  (mesh_tensorflow/ops.py:4656-4726)."""
+  (mesh_tensorflow/ops.py:4656-4726).  `activation="relu"` applies the ReLU of
+  a following mtf.relu inside the same operation."""
   output_shape = convert_to_shape(output_shape)
   union = shape_union([x.shape for x in xs])
   if output_shape is None:
@@ -503,7 +520,7 @@ def einsum(xs, output_shape=None, reduced_dims=None, name=None):
     computed = [d for d in union.dims if d not in output_shape.dims]
     if set(computed) != set(convert_to_dimension(d) for d in reduced_dims):
       raise ValueError("reduced_dims and output_shape disagree")
-  return EinsumOperation(xs, output_shape, name=name).outputs[0]
+  return EinsumOperation(xs, output_shape, name=name, activation=activation).outputs[0]
 
 
 def matmul(a, b, output_shape=None, reduced_dims=None, name=None):
@@ -769,6 +786,30 @@ class OneHotOperation(Operation):
 def one_hot(indices, output_dim, on_value=1.0, off_value=0.0, dtype=G.float32, name=None):
   return OneHotOperation(indices, convert_to_dimension(output_dim), on_value, off_value, dtype,
                          name=name).outputs[0]
+
+
+def gather(weights, indices, dim, output_shape=None):
+  """einsum(one_hot(indices, dim), weights) reducing `dim` (ops.py:5231-5251)."""
+  dim = convert_to_dimension(dim)
+  output_shape = convert_to_shape(output_shape)
+  if not isinstance(indices, Tensor):
+    indices = constant(weights.mesh, indices, dtype=G.int32)
+  if weights.dtype.is_bool:
+    return cast(gather(to_float(weights), indices, dim, output_shape), G.bool_)
+  return einsum([one_hot(indices, dim, dtype=weights.dtype), weights],
+                reduced_dims=[dim], output_shape=output_shape)
+
+
+def nth_largest_element(x, n, reduced_dim, name=None):
+  """n-th largest (zero-indexed) along `reduced_dim` (ops.py:6589-6605)."""
+  reduced_dim = convert_to_dimension(reduced_dim)
+  k_dim = Dimension("_top_k_", n + 1)
+  values, _ = top_k(x, reduced_dim=reduced_dim, k_dim=k_dim, name=name)
+  return gather(values, n, k_dim)
+
+
+def nth_smallest_element(x, n, reduced_dim, name=None):
+  return -nth_largest_element(-x, n, reduced_dim, name=name)
 
 
 # ------------------------------------------------------------ cumsum / softmax

@@ -86,6 +86,9 @@ class NumpyOps(object):
   def dtype(self, x):
     return x.dtype
 
+  def contiguous(self, x):
+    return Arr(np.ascontiguousarray(x.a), x.dtype)
+
   # ---- layout ops: tf.slice / concat / transpose / expand_dims / reshape
   def slice(self, x, begin, size):
     idx = tuple(slice(b, b + s) for b, s in zip(begin, size))

@@ -1,0 +1,170 @@
+"""Top-2 MoE kernels against the per-group specification and the op-by-op oracle.
+
+Stage A: gate logits numerically.  Stage B: the gating kernel fed the oracle's
+own logits must reproduce indices, positions and keep masks bit for bit
+(tokens whose top-1/top-2 or top-2/top-3 raw-gate margin is under 1e-6 are
+excluded and counted: exp() differs between libraries in the last ulp).
+Stage C: the whole layer on CudaMeshImpl against NumpyMeshImpl.
+"""
+
+import numpy as np
+import pytest
+
+from mesh_b200 import mtf
+from helpers import rel_err, rng
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev_ops(cuda_device):
+  from mesh_b200.device_ops import DeviceOps
+  return DeviceOps(cuda_device)
+
+
+def _safe_tokens(raw, margin=1e-6):
+  top = np.sort(raw, axis=-1)[..., ::-1]
+  return ((top[..., 0] - top[..., 1]) > margin) & ((top[..., 1] - top[..., 2]) > margin)
+
+
+def _gating_case(dev_ops, groups, s, e, capacity, policy, threshold, seed):
+  from oracle import moe_spec
+  r = rng(seed)
+  logits = (r.standard_normal((groups, s, e)) * 2).astype(np.float32)
+  noise = r.random((groups, s)).astype(np.float32)
+  spec = moe_spec.gating_from_raw(moe_spec.softmax_f32(logits), capacity, policy, threshold, noise)
+  dl = dev_ops.from_host(logits.reshape(groups * s, e), mtf.float32)
+  dn = dev_ops.from_host(noise, mtf.float32)
+  out = dev_ops.moe_top2_gating_from_logits(dl, 1, (groups,), s, e, capacity, policy, threshold,
+                                            dn, groups, want_raw=True)
+  names = ["index_1", "index_2", "position_1", "position_2", "gate_1", "gate_2"]
+  got = {k: dev_ops.to_host(v) for k, v in zip(names, out[:6])}
+  got["loss"] = float(dev_ops.to_host(out[6]))
+  got["raw_gates"] = dev_ops.to_host(out[7])
+  return spec, got
+
+
+@pytest.mark.parametrize("policy", ["all", "none", "threshold", "random"])
+@pytest.mark.parametrize("groups,s,e,cap", [(3, 1024, 32, 40), (2, 300, 8, 20), (5, 64, 4, 4),
+                                            (1, 1024, 64, 1024), (2, 257, 16, 3)])
+def test_gating_bit_exact_given_logits(dev_ops, groups, s, e, cap, policy):
+  spec, got = _gating_case(dev_ops, groups, s, e, cap, policy, 0.2, seed=11)
+  assert rel_err(got["raw_gates"], spec["raw_gates"]) < 1e-6
+  safe_tok = _safe_tokens(spec["raw_gates"])
+  # a group is comparable when every token of it is: positions depend on all earlier tokens
+  safe = np.all(safe_tok, axis=-1)
+  assert safe.sum() >= 1, "margin filter removed every group"
+  for k in ("index_1", "index_2", "position_1", "position_2"):
+    np.testing.assert_array_equal(got[k][safe], spec[k][safe], err_msg=k)
+  for k in ("gate_1", "gate_2"):
+    np.testing.assert_array_equal(got[k][safe] != 0, spec[k][safe] != 0, err_msg=k + " keep mask")
+    if policy not in ("threshold", "random"):
+      assert np.max(np.abs(got[k][safe] - spec[k][safe])) < 1e-6
+  ref_loss = float(np.mean(spec["loss_per_group"]))
+  assert abs(got["loss"] - ref_loss) <= 1e-5 * max(1.0, abs(ref_loss))
+
+
+def test_gating_is_deterministic(dev_ops):
+  a = _gating_case(dev_ops, 4, 1024, 32, 40, "all", 0.2, seed=5)[1]
+  b = _gating_case(dev_ops, 4, 1024, 32, 40, "all", 0.2, seed=5)[1]
+  for k in a:
+    np.testing.assert_array_equal(a[k], b[k])
+
+
+def test_gate_logits_on_tensor_cores(dev_ops):
+  """bf16 activations x fp32 gate kernel split in three bf16 terms: fp32-level accuracy."""
+  r = rng(12)
+  x = r.standard_normal((2, 512, 1024)).astype(np.float32)
+  w = (r.standard_normal((1024, 32)) / 32).astype(np.float32)
+  from oracle.numpy_ops import round_to_bf16
+  xb = round_to_bf16(x)
+  ref = np.einsum("gsm,me->gse", xb.astype(np.float64), w.astype(np.float64))
+  logits, parts = dev_ops.moe_gate_logits(dev_ops.from_host(x, mtf.bfloat16), dev_ops.from_host(w, mtf.float32))
+  assert parts == 3
+  got = dev_ops.to_host(logits).reshape(2, 512, 3, 32).sum(axis=2)
+  assert rel_err(got, ref) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [mtf.bfloat16, mtf.float32])
+def test_dispatch_and_combine(dev_ops, dtype):
+  from oracle import moe_spec
+  from oracle.numpy_ops import NumpyOps
+  ora = NumpyOps()
+  r = rng(13)
+  o, g, s, m, e, cap = 2, 3, 128, 64, 8, 20
+  logits = (r.standard_normal((o * g, s, e)) * 2).astype(np.float32)
+  spec = moe_spec.gating_from_raw(moe_spec.softmax_f32(logits), cap, "all")
+  x = r.standard_normal((o, g, s, m)).astype(np.float32)
+  names = ["index_1", "index_2", "position_1", "position_2", "gate_1", "gate_2"]
+  tok = (o, g, s)
+  routing_h = [spec[k].reshape(tok) for k in names]
+  dts = [mtf.int32] * 4 + [mtf.float32] * 2
+  routing_d = [dev_ops.from_host(v, dt) for v, dt in zip(routing_h, dts)]
+  routing_o = [ora.from_host(v, dt) for v, dt in zip(routing_h, dts)]
+  got = dev_ops.to_host(dev_ops.moe_dispatch(dev_ops.from_host(x, dtype), *routing_d, e, cap))
+  ref = ora.to_host(ora.moe_dispatch(ora.from_host(x, dtype), *routing_o, e, cap))
+  assert got.shape == (o, e, g, cap, m)
+  np.testing.assert_array_equal(got, ref)   # pure row copies: exact (-0.0 == 0.0)
+  y = r.standard_normal((o, e, g, cap, m)).astype(np.float32)
+  got = dev_ops.to_host(dev_ops.moe_combine(dev_ops.from_host(y, dtype), *routing_d))
+  ref = ora.to_host(ora.moe_combine(ora.from_host(y, dtype), *routing_o))
+  assert rel_err(got, ref) < (1e-6 if dtype == mtf.float32 else 8e-3)
+
+
+def _moe_layer(impl_factory, mesh_shape, layout, fused, b=8, l=64, d=64, f=128, e=8, group=64, policy="all"):
+  r = rng(21)
+  g = mtf.Graph()
+  mesh = mtf.Mesh(g, "m")
+  x = r.standard_normal((b, l, d)).astype(np.float32)
+  wg = (r.standard_normal((d, e)) / np.sqrt(d)).astype(np.float32)
+  wi = (r.standard_normal((e, d, f)) / np.sqrt(d)).astype(np.float32)
+  wo = (r.standard_normal((e, f, d)) / np.sqrt(f)).astype(np.float32)
+  X = mtf.import_tf_tensor(mesh, x, "batch:%d,length:%d,d_model:%d" % (b, l, d), dtype=mtf.bfloat16)
+  WG = mtf.import_tf_tensor(mesh, wg, "d_model:%d,expert_unsplit:%d" % (d, e), dtype=mtf.float32)
+  WI = mtf.import_tf_tensor(mesh, wi, "experts:%d,d_model:%d,d_ff:%d" % (e, d, f), dtype=mtf.bfloat16)
+  WO = mtf.import_tf_tensor(mesh, wo, "experts:%d,d_ff:%d,d_model:%d" % (e, f, d), dtype=mtf.bfloat16)
+  hp = mtf.moe.HParams(moe_group_size=group, moe_second_policy_train=policy, moe_use_fused_kernels=fused)
+  out, loss, aux = mtf.moe.transformer_moe_layer_v1(
+      X, mtf.Dimension("d_model", d), hp, True, mesh_shape, layout, WG, WI, WO, return_aux=True)
+  low = mtf.Lowering(g, {mesh: impl_factory(mesh_shape, layout)})
+  res = {k: low.export_to_tf_tensor(v) for k, v in aux.items()}
+  res["output"] = low.export_to_tf_tensor(out)
+  res["loss"] = low.export_to_tf_tensor(loss)
+  return res, low
+
+
+@pytest.mark.parametrize("mesh_shape", ["all:1", "all:4"])
+@pytest.mark.parametrize("fused", [True, False])
+def test_moe_layer_matches_oracle(cuda_device, mesh_shape, fused):
+  from mesh_b200.cuda_mesh_impl import CudaMeshImpl
+  from oracle.numpy_mesh_impl import NumpyMeshImpl
+  layout = "batch:all;experts:all"
+  n = mtf.convert_to_shape(mesh_shape).size
+  ref, _ = _moe_layer(lambda s, l: NumpyMeshImpl(s, l), mesh_shape, layout, fused=False)
+  got, low = _moe_layer(lambda s, l: CudaMeshImpl(s, l, [0] * n), mesh_shape, layout, fused=fused)
+  raw = ref["raw_gates"].reshape(-1, ref["raw_gates"].shape[-2], ref["raw_gates"].shape[-1])
+  safe = np.all(_safe_tokens(raw, margin=1e-5), axis=-1).reshape(ref["index_1"].shape[:-1])
+  assert safe.sum() >= 1
+  for k in ("index_1", "index_2", "position_1", "position_2"):
+    np.testing.assert_array_equal(got[k][safe], ref[k][safe], err_msg=k)
+  for k in ("gate_1", "gate_2"):
+    assert np.max(np.abs(got[k][safe] - ref[k][safe])) < 1e-5
+  # output rows of comparable groups
+  b, l, d = ref["output"].shape
+  go = got["output"].reshape(safe.shape + (-1, d))[safe]
+  ro = ref["output"].reshape(safe.shape + (-1, d))[safe]
+  assert rel_err(go, ro) < 2e-2
+  assert abs(float(got["loss"]) - float(ref["loss"])) <= 2e-2 * abs(float(ref["loss"]))
+  if n > 1:
+    totals = low.counter_totals()
+    assert totals.get("alltoall/0/reshape_op", 0) > 0
+
+
+def test_fused_equals_unfused_on_device(cuda_device):
+  from mesh_b200.cuda_mesh_impl import CudaMeshImpl
+  layout = "batch:all;experts:all"
+  a, _ = _moe_layer(lambda s, l: CudaMeshImpl(s, l, [0, 0]), "all:2", layout, fused=True)
+  b, _ = _moe_layer(lambda s, l: CudaMeshImpl(s, l, [0, 0]), "all:2", layout, fused=False)
+  for k in ("index_1", "index_2", "position_1", "position_2"):
+    np.testing.assert_array_equal(a[k], b[k], err_msg=k)
+  assert rel_err(a["output"], b["output"]) < 2e-2
