@@ -1,0 +1,351 @@
+"""Benchmark of the MeshImpl hot path: laid-out einsums of the dense FFN block.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the configuration the metric is quoted on): Transformer
+dense_relu_dense, x[batch=64, length=1024, d_model=1024] ~ N(0,1),
+wi[1024, 4096] ~ N(0, 1/1024), wo[4096, 1024] ~ N(0, 1/4096), bf16 weights and
+activations, fp32 accumulation, ReLU between; 1.0995 TFLOP per step.  One step
+is one lowering of that graph through `mtf.Lowering` on `CudaMeshImpl`.
+At N GPUs the same global problem is laid out on a rows x cols mesh with
+`batch:rows;d_ff:cols` (1: 1x1, 2: 2x1, 4: 2x2, 8: 2x4), so the second einsum
+contracts a split dim and is followed by an allreduce over `cols` — strong
+scaling.  Inputs are seeded synthetic data (no dataset is involved).
+
+Rank 0 prints one JSON line.  `value` is einsum TFLOP/s with the inputs already
+on the device; `e2e` is the same through host buffers (pinned-memory upload of
+the step's activations and download of its output inside the timed region).
+`--impl reference` times the reference's CPU lowering of the same graph: the
+restated PlacementMeshImpl semantics on host cores (TensorFlow, and therefore
+the reference itself, is not installable here).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+  sys.path.insert(0, ROOT)
+
+BATCH, LENGTH, D_MODEL, D_FF = 64, 1024, 1024, 4096
+SEED = 1235  # 1234 + configuration index
+FLOPS_PER_STEP = 2.0 * BATCH * LENGTH * D_MODEL * D_FF * 2.0
+MESHES = {1: "rows:1,cols:1", 2: "rows:2,cols:1", 4: "rows:2,cols:2", 8: "rows:2,cols:4"}
+LAYOUT = "batch:rows;d_ff:cols"
+METRIC = "einsum TFLOP/s (dense_relu_dense FFN, bf16, fp32 accumulate)"
+CPU_SAMPLE_BATCH = 8  # sequences of the 64 the CPU arms run per step
+
+# DRAM bytes per launch of einsum_gemm_tcgen05 on the wi GEMM of this workload,
+# dram__bytes_read.sum + dram__bytes_write.sum from the ncu capture summarised in
+# profiles/einsum_gemm_tcgen05_ffn.md (algorithmic bytes: 679.5 MB and 679.5 MB).
+GEMM_DRAM_TRAFFIC_BYTES = 644.4e6  # mean of the wi (624.6 MB) and wo (664.2 MB) launches
+
+
+def measured_peaks():
+  path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+  if os.path.exists(path):
+    with open(path) as f:
+      p = json.load(f)
+    return {"tflops_sustained": p.get("bf16_tflops_sustained"), "tflops_burst": p.get("bf16_tflops"),
+            "hbm_gbs": p.get("hbm_gbs"), "source": "measured"}
+  return {"tflops_sustained": 1400.0, "tflops_burst": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler(object):
+  """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+  FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+            "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+            "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+  def __init__(self, index):
+    self._index = index
+    self._proc = None
+    self._lines = []
+    self._thread = None
+
+  def start(self):
+    try:
+      self._proc = subprocess.Popen(
+          ["nvidia-smi", "-i", str(self._index), "--query-gpu=" + self.FIELDS,
+           "--format=csv,noheader,nounits", "-lms", "100"],
+          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+    except OSError:
+      self._proc = None
+      return
+    self._thread = threading.Thread(target=self._pump, daemon=True)
+    self._thread.start()
+
+  def _pump(self):
+    for line in self._proc.stdout:
+      self._lines.append(line.strip())
+
+  def stop(self):
+    if self._proc is None:
+      return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+    self._proc.terminate()
+    try:
+      self._proc.wait(timeout=5)
+    except subprocess.TimeoutExpired:
+      self._proc.kill()
+    clocks, max_clock, reasons = [], None, set()
+    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    for line in self._lines:
+      parts = [p.strip() for p in line.split(",")]
+      if len(parts) < 8:
+        continue
+      try:
+        clocks.append(float(parts[0]))
+        max_clock = float(parts[1])
+      except ValueError:
+        continue
+      for name, flag in zip(names, parts[4:8]):
+        if flag.lower().startswith("active"):
+          reasons.add(name)
+    return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
+            "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+def run_reference(args):
+  """The reference's CPU lowering of the same graph, timed on the host cores."""
+  rank = int(os.environ.get("RANK", "0"))
+  if rank != 0:
+    return
+  from oracle import cpu_baseline
+  cores = cpu_baseline.host_threads()
+  seconds, _ = cpu_baseline.time_ffn(CPU_SAMPLE_BATCH, LENGTH, D_MODEL, D_FF, "", "",
+                                     steps=max(1, args.steps), warmup=max(1, min(args.warmup, 1)))
+  flops = cpu_baseline.ffn_flops(CPU_SAMPLE_BATCH, LENGTH, D_MODEL, D_FF)
+  value = flops / seconds / 1e12
+  sample = "%d of %d sequences per step (%.1f GFLOP)" % (CPU_SAMPLE_BATCH, BATCH, flops / 1e9)
+  line = {
+      "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s",
+      "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+      "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "strong",
+      "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+      "config": {"workload": "dense_relu_dense FFN x[64,1024,1024] wi[1024,4096] wo[4096,1024]",
+                 "note": "restated PlacementMeshImpl lowering on host cores; TensorFlow absent, "
+                         "so the reference package itself cannot be installed or run"},
+      "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                       "sample": sample},
+      "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+      "gpu_launches": 0,
+  }
+  print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+  import numpy as np
+  import torch
+  import torch.distributed as dist
+
+  from mesh_b200 import _native as nat
+  from mesh_b200 import mtf
+  from mesh_b200.cuda_mesh_impl import CudaMeshImpl
+
+  n = args.gpus
+  if n not in MESHES:
+    raise SystemExit("--gpus must be one of %s" % sorted(MESHES))
+  rank = int(os.environ.get("RANK", "0"))
+  local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+  world = int(os.environ.get("WORLD_SIZE", "1"))
+  if world != n:
+    raise SystemExit("WORLD_SIZE=%d but --gpus %d: launch with torch.distributed.run" % (world, n))
+  if not torch.cuda.is_available():
+    raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+  torch.cuda.set_device(local_rank)
+  device = torch.device("cuda", local_rank)
+  if n > 1:
+    dist.init_process_group("nccl", device_id=device)
+
+  mesh_shape = MESHES[n]
+  impl = CudaMeshImpl(mesh_shape, LAYOUT, devices=list(range(n)) if n > 1 else [local_rank],
+                      distributed=(n > 1))
+  rows = impl.shape.dims[0].size
+  cols = impl.shape.dims[1].size
+  coord = mtf.pnum_to_processor_coordinates(impl.shape, rank)
+
+  # Seeded synthetic inputs, generated on the host and rounded to bf16 once.
+  r = np.random.Generator(np.random.PCG64(SEED))
+  x_full = r.standard_normal((BATCH, LENGTH, D_MODEL), dtype=np.float32)
+  wi_full = r.standard_normal((D_MODEL, D_FF), dtype=np.float32) * np.float32(D_MODEL ** -0.5)
+  wo_full = r.standard_normal((D_FF, D_MODEL), dtype=np.float32) * np.float32(D_FF ** -0.5)
+  b_loc, f_loc = BATCH // rows, D_FF // cols
+  x_full_host = torch.from_numpy(x_full).to(torch.bfloat16).pin_memory()
+  x_host = x_full_host[coord[0] * b_loc:(coord[0] + 1) * b_loc]
+  wi_host = torch.from_numpy(np.ascontiguousarray(wi_full[:, coord[1] * f_loc:(coord[1] + 1) * f_loc])).to(torch.bfloat16)
+  wo_host = torch.from_numpy(np.ascontiguousarray(wo_full[coord[1] * f_loc:(coord[1] + 1) * f_loc])).to(torch.bfloat16)
+  y_host = torch.empty((b_loc, LENGTH, D_MODEL), dtype=torch.bfloat16).pin_memory()
+  del x_full
+
+  ops = impl.slice_ops
+  x_dev = impl.LaidOutTensor([ops.from_host(x_host, mtf.bfloat16)])
+  wi_dev = impl.LaidOutTensor([ops.from_host(wi_host, mtf.bfloat16)])
+  wo_dev = impl.LaidOutTensor([ops.from_host(wo_host, mtf.bfloat16)])
+
+  x_shape = "batch:%d,length:%d,d_model:%d" % (BATCH, LENGTH, D_MODEL)
+  wi_shape = "d_model:%d,d_ff:%d" % (D_MODEL, D_FF)
+  wo_shape = "d_ff:%d,d_model:%d" % (D_FF, D_MODEL)
+
+  def build(x_source):
+    g = mtf.Graph()
+    mesh = mtf.Mesh(g, "mesh")
+    X = x_source(mesh)
+    WI = mtf.import_laid_out_tensor(mesh, wi_dev, wi_shape, mtf.bfloat16)
+    WO = mtf.import_laid_out_tensor(mesh, wo_dev, wo_shape, mtf.bfloat16)
+    y = mtf.layers.dense_relu_dense(X, mtf.Dimension("d_ff", D_FF), wi=WI, wo=WO)
+    return g, mesh, y
+
+  # device-resident graph: activations already in HBM
+  g_dev, mesh_dev, y_dev = build(lambda m: mtf.import_laid_out_tensor(m, x_dev, x_shape, mtf.bfloat16))
+
+  def step_device():
+    low = mtf.Lowering(g_dev, {mesh_dev: impl})
+    return low.tensors[y_dev].to_laid_out_tensor()
+
+  # end-to-end graph: the whole x sits in pinned host memory; each step's
+  # import_tf_tensor cuts this rank's slice on the host and uploads only that,
+  # and the step's output slice is downloaded into pinned memory
+  g_e2e, mesh_e2e, y_e2e = build(lambda m: mtf.import_tf_tensor(m, x_full_host, x_shape, dtype=mtf.bfloat16))
+
+  def step_e2e():
+    low = mtf.Lowering(g_e2e, {mesh_e2e: impl})
+    out = low.tensors[y_e2e].to_laid_out_tensor()
+    impl.export_to_host_tensors(out, out=[y_host])
+
+  def barrier():
+    if n > 1:
+      dist.barrier()
+    torch.cuda.synchronize()
+
+  def timed(step, steps, warmup):
+    for _ in range(warmup):
+      step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = nat.launch_count()
+    e0.record()
+    for _ in range(steps):
+      step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = nat.launch_count() - launches0
+    if n > 1:
+      t = torch.tensor([ms], device=device)
+      dist.all_reduce(t, op=dist.ReduceOp.MAX)
+      ms = float(t.item())
+    return ms / steps, launches
+
+  # The lowering is a fixed launch sequence: record it once as a CUDA graph and
+  # replay it per step (eager lowering per step with --eager).  `launches_per_step`
+  # counts the libmtfc kernels one lowering enqueues.
+  before = nat.launch_count()
+  step_device()
+  launches_per_step = nat.launch_count() - before
+  run_device, run_e2e = step_device, step_e2e
+  if not args.eager:
+    _, run_device = impl.capture(step_device)
+    _, run_e2e = impl.capture(step_e2e)
+
+  # clocks are sampled across both timed regions (the GPU is under load throughout)
+  sampler = ClockSampler(local_rank)
+  if rank == 0:
+    sampler.start()
+  ms_step, launches = timed(run_device, args.steps, args.warmup)
+  impl.synchronize()
+  ms_e2e, _ = timed(run_e2e, args.steps, max(3, args.warmup // 2))
+  clocks = sampler.stop() if rank == 0 else None
+  impl.synchronize()
+  if not args.eager:
+    launches = launches_per_step * args.steps
+
+  # dominant kernel: per-launch duration of the two GEMMs of this rank, timed with
+  # events on the launching stream inside the same kind of step
+  gemm_ms = []
+  x_arr, wi_arr, wo_arr = x_dev.tensor_list[0], wi_dev.tensor_list[0], wo_dev.tensor_list[0]
+  for _ in range(3):
+    h = impl.einsum("abc,cd->abd", x_arr, wi_arr, epilogue="relu")
+    impl.einsum("abc,cd->abd", h, wo_arr)
+  torch.cuda.synchronize()
+  for _ in range(max(5, args.steps)):
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    ev[0].record()
+    h = impl.einsum("abc,cd->abd", x_arr, wi_arr, epilogue="relu")
+    ev[1].record()
+    impl.einsum("abc,cd->abd", h, wo_arr)
+    ev[2].record()
+    torch.cuda.synchronize()
+    gemm_ms.append((ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])))
+  del h
+  flops_per_launch = 2.0 * b_loc * LENGTH * D_MODEL * f_loc
+  avg_launch_ms = statistics.mean([a + b for a, b in gemm_ms]) / 2.0
+  achieved = flops_per_launch / (avg_launch_ms * 1e-3) / 1e12
+  peaks = measured_peaks()
+
+  cpu = None
+  if rank == 0 and n == 1 and not args.skip_cpu_baseline:
+    from oracle import cpu_baseline
+    cores = cpu_baseline.host_threads()
+    seconds, _ = cpu_baseline.time_ffn(CPU_SAMPLE_BATCH, LENGTH, D_MODEL, D_FF, "", "", steps=3, warmup=1)
+    flops = cpu_baseline.ffn_flops(CPU_SAMPLE_BATCH, LENGTH, D_MODEL, D_FF)
+    cpu = {"value": flops / seconds / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+           "sample": "%d of %d sequences per step (%.1f GFLOP), median of 3"
+                     % (CPU_SAMPLE_BATCH, BATCH, flops / 1e9)}
+
+  if rank == 0:
+    h2d = x_host.numel() * 2 * n
+    d2h = y_host.numel() * 2 * n
+    line = {
+        "metric": METRIC, "value": FLOPS_PER_STEP / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "n_gpus": n, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "dense_relu_dense FFN x[64,1024,1024] wi[1024,4096] wo[4096,1024]",
+                   "mesh": mesh_shape, "layout": LAYOUT,
+                   "stepping": "eager lowering" if args.eager else "CUDA-graph replay of the lowering",
+                   "l2": "working set per step (>=384 MiB of activations) exceeds the 126 MB L2"},
+        "e2e": {"value": FLOPS_PER_STEP / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops_sustained"],
+                     "unit": "TFLOP/s", "frac": achieved / peaks["tflops_sustained"],
+                     "frac_of_burst_peak": achieved / peaks["tflops_burst"],
+                     "peak_source": "%s bf16 GEMM, sustained (kernel timed inside the step loop)"
+                                    % peaks["source"],
+                     "kernel": "einsum_gemm_tcgen05", "launch_ms": avg_launch_ms,
+                     "flops_per_launch": flops_per_launch, "traffic": GEMM_DRAM_TRAFFIC_BYTES},
+        "cpu_baseline": cpu,
+        "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+  if n > 1:
+    dist.destroy_process_group()
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--gpus", type=int, default=1)
+  ap.add_argument("--steps", type=int, default=200)
+  ap.add_argument("--warmup", type=int, default=10)
+  ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+  ap.add_argument("--skip-cpu-baseline", action="store_true")
+  ap.add_argument("--eager", action="store_true",
+                  help="lower the graph afresh every step instead of replaying a CUDA graph")
+  args = ap.parse_args()
+  if args.impl == "reference":
+    run_reference(args)
+  else:
+    run_ours(args)
+
+
+if __name__ == "__main__":
+  main()

@@ -114,7 +114,7 @@ class SlicedMeshImpl(mtf.MeshImpl):
   def import_tf_tensor(self, x, tf_x):
     """Host array -> slices; each processor's part is cut on the host and only
     that part is uploaded (ops.py:1249-1269 semantics)."""
-    value = np.asarray(tf_x)
+    value = tf_x if hasattr(tf_x, "data_ptr") else np.asarray(tf_x)
     layout = self.tensor_layout(x.shape)
     slice_shape = self.slice_shape(x.shape)
     out = []
@@ -448,6 +448,43 @@ class CudaMeshImpl(SlicedMeshImpl):
 
   def _from_torch(self, t, shape, dtype, pnum):
     return self._device_array(t, shape, dtype)
+
+  def export_to_host_tensors(self, laid_out_x, out=None):
+    """Copies this process's slices to host torch tensors in their own dtype.
+
+    `out`, a list of (pinned) CPU tensors, one per local slice, makes the
+    copies asynchronous on the current stream; call synchronize() before
+    reading them.  The cheap sibling of export_to_tf_tensor for callers that
+    consume slices rather than the assembled full tensor."""
+    laid_out_x = laid_out_x.to_laid_out_tensor()
+    result = []
+    for i, (pnum, s) in enumerate(zip(self._local_pnums, laid_out_x.all_slices)):
+      ops = self._ops_for(pnum)
+      result.append(ops.to_host_tensor(s, None if out is None else out[i]))
+    return result
+
+  def capture(self, fn, warmup=2):
+    """Records `fn` (e.g. a whole `mtf.Lowering` of a graph) into a CUDA graph.
+
+    The lowering of a Mesh TensorFlow graph is a fixed sequence of kernel
+    launches, copies and collectives; replaying it as one CUDA graph removes
+    the per-operation host work from every later step.  `fn` runs `warmup`
+    times eagerly (first-use set-up must not happen during capture), then once
+    under capture.  Returns `(result, replay)`: `result` is what the captured
+    run of `fn` returned — its slices are rewritten in place by every
+    `replay()`.  `fn` must not synchronise with the host (no export).
+    """
+    import torch
+    dev = self._devices[self._local_pnums[0]]
+    with torch.cuda.device(dev):
+      for _ in range(max(1, warmup)):
+        fn()
+      torch.cuda.synchronize()
+      graph = torch.cuda.CUDAGraph()
+      with torch.cuda.graph(graph):
+        result = fn()
+      torch.cuda.synchronize()
+    return result, graph.replay
 
   def synchronize(self):
     """Waits for all enqueued work and raises if a kernel reported a timeout."""

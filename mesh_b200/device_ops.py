@@ -137,17 +137,39 @@ class DeviceOps(object):
 
   # ---------------------------------------------------------------- host I/O
   def from_host(self, value, dtype):
-    a = np.ascontiguousarray(np.asarray(value))
+    """Uploads a host array.  A torch CPU tensor (e.g. pinned memory already in
+    the target dtype) is copied as it is, asynchronously on the current stream;
+    anything else goes through numpy and is converted on the host first."""
+    if isinstance(value, torch.Tensor):
+      t = value if value.dtype == _TORCH[dtype.name] else value.to(_TORCH[dtype.name])
+      t = t.contiguous().reshape(-1)
+      with torch.cuda.device(self.device):
+        buf = t.to(self.device, non_blocking=True) if t.numel() else torch.empty(
+            1, dtype=_TORCH[dtype.name], device=self.device)
+      return DeviceArray(buf, tuple(value.shape), dtype)
+    shape = np.shape(value)
+    a = np.ascontiguousarray(np.asarray(value)).reshape(-1)
     if dtype.is_floating:
       t = torch.from_numpy(a.astype(np.float32, copy=False)).to(_TORCH[dtype.name])
     elif dtype.is_bool:
       t = torch.from_numpy((a != 0).astype(np.int32))
     else:
       t = torch.from_numpy(a.astype(np.int32, copy=False))
-    shape = a.shape
     buf = t.reshape(-1).to(self.device) if t.numel() else torch.empty(
         1, dtype=_TORCH[dtype.name], device=self.device)
     return DeviceArray(buf, shape, dtype)
+
+  def to_host_tensor(self, x, out=None):
+    """Downloads a slice into a torch CPU tensor of the slice's own dtype
+    (bfloat16 stays bfloat16).  With `out` (ideally pinned) the copy is
+    asynchronous on the current stream; synchronise before reading it."""
+    x = self.contiguous(x)
+    flat = x.buf[x.offset:x.offset + x.size]
+    if out is None:
+      return flat.cpu().reshape(x.shape)
+    with torch.cuda.device(self.device):
+      out.reshape(-1).copy_(flat, non_blocking=True)
+    return out
 
   def to_host(self, x):
     x = self.contiguous(x)

@@ -36,31 +36,52 @@ class ImportOperation(Operation):
 
 
 _NP_TO_DTYPE = {"float32": G.float32, "float64": G.float32, "int32": G.int32,
-                "int64": G.int32, "bool": G.bool_}
+                "int64": G.int32, "bool": G.bool_, "bfloat16": G.bfloat16}
 
 
 def import_tf_tensor(mesh, tf_tensor, shape=None, name=None, dtype=None):
-  """Imports a host array (numpy, or anything np.asarray accepts) as a Tensor.
+  """Imports a host array (numpy, a torch CPU tensor, or anything np.asarray
+  accepts) as a Tensor.
 
   `dtype` selects the on-device type; values are rounded to it on import
   (mtf.bfloat16 rounds float32 data to nearest-even).
   """
-  value = np.asarray(tf_tensor)
+  value = tf_tensor if hasattr(tf_tensor, "data_ptr") else np.asarray(tf_tensor)
   if shape is None:
     shape = Shape([])
-    if value.shape != ():
+    if tuple(value.shape) != ():
       raise ValueError("shape must be given for a non-scalar import")
   shape = convert_to_shape(shape)
   if list(value.shape) != shape.to_integer_list:
     raise ValueError("Incompatible shape: array %s vs %s" % (value.shape, shape))
   if dtype is None:
-    dtype = _NP_TO_DTYPE.get(value.dtype.name)
+    dtype = _NP_TO_DTYPE.get(getattr(value.dtype, "name", str(value.dtype).replace("torch.", "")))
     if dtype is None:
       raise ValueError("cannot infer an mtf dtype from %s" % value.dtype)
   return ImportOperation(mesh, value, shape, dtype, name=name).outputs[0]
 
 
 import_tensor = import_tf_tensor
+
+
+class ImportLaidOutTensorOperation(Operation):
+  """Brings slices that already live on the mesh into the graph
+  (mesh_tensorflow/ops.py:3893-3938)."""
+
+  def __init__(self, mesh, laid_out_tensor, shape, dtype, name=None):
+    super().__init__([], mesh=mesh, name=name or "import")
+    self._laid_out_tensor = laid_out_tensor
+    self._outputs = [Tensor(self, shape, dtype)]
+
+  def lower(self, lowering):
+    lowering.set_tensor_lowering(self.outputs[0], self._laid_out_tensor)
+
+
+def import_laid_out_tensor(mesh, laid_out_tensor, shape, dtype, name=None):
+  """Imports a LaidOutTensor (one slice per processor, already on the devices);
+  lowering checks its slice shape against the layout."""
+  return ImportLaidOutTensorOperation(
+      mesh, laid_out_tensor, convert_to_shape(shape), dtype, name=name).outputs[0]
 
 
 def constant(mesh, value, shape=None, dtype=G.float32):

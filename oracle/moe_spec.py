@@ -90,16 +90,17 @@ def top2_gating(x, w, capacity, policy="all", threshold=0.2, noise=None):
   return out
 
 
-def combine_weights(gate):
-  """Gate as it enters the combine tensor: rounded to bfloat16 (moe.py:1507)."""
-  return round_to_bf16(gate)
+def combine_weights(gate, bf16=True):
+  """Gate as it enters the combine tensor: cast to the activation dtype
+  (moe.py:1507) — rounded to bfloat16 for bfloat16 activations, unchanged for float32."""
+  return round_to_bf16(gate) if bf16 else np.asarray(gate, dtype=np.float32)
 
 
-def dispatch(x, i1, i2, p1, p2, g1, g2, num_experts, capacity):
+def dispatch(x, i1, i2, p1, p2, g1, g2, num_experts, capacity, bf16=True):
   """x [G,S,M] -> expert inputs [G,E,C,M]; a slot holds at most one token."""
   g_, s_, m_ = x.shape
   out = np.zeros((g_, num_experts, capacity, m_), dtype=np.float32)
-  w1, w2 = combine_weights(g1), combine_weights(g2)
+  w1, w2 = combine_weights(g1, bf16), combine_weights(g2, bf16)
   for g in range(g_):
     for s in range(s_):
       if w1[g, s] != 0 and p1[g, s] < capacity:
@@ -109,12 +110,12 @@ def dispatch(x, i1, i2, p1, p2, g1, g2, num_experts, capacity):
   return out
 
 
-def combine(y, i1, i2, p1, p2, g1, g2):
+def combine(y, i1, i2, p1, p2, g1, g2, bf16=True):
   """y [G,E,C,M] -> [G,S,M]: w1*y[i1,p1] + w2*y[i2,p2] in float32 (caller rounds)."""
   g_, e_, c_, m_ = y.shape
   s_ = i1.shape[-1]
   out = np.zeros((g_, s_, m_), dtype=np.float32)
-  w1, w2 = combine_weights(g1), combine_weights(g2)
+  w1, w2 = combine_weights(g1, bf16), combine_weights(g2, bf16)
   y = y.astype(np.float32)
   for g in range(g_):
     for s in range(s_):

@@ -22,12 +22,12 @@ from oracle.numpy_ops import Arr, NumpyOps, _finish
 class NumpyMeshImpl(mtf.MeshImpl):
   """CPU mesh backend with PlacementMeshImpl semantics."""
 
-  def __init__(self, shape, layout, devices=None):
+  def __init__(self, shape, layout, devices=None, fast=False):
     super().__init__(shape, layout)
     self._devices = list(devices) if devices is not None else [""] * self.size
     if len(self._devices) != self.size:
       raise ValueError("devices must have one entry per processor")
-    self._ops = NumpyOps()
+    self._ops = NumpyOps(fast=fast)
 
   class LaidOutTensor(object):
     """One slice per processor (placement_mesh_impl.py:39-65)."""

@@ -70,7 +70,16 @@ def _finish(a, dtype):
 
 
 class NumpyOps(object):
-  """The `slice_ops` array library of the oracle's mesh backend."""
+  """The `slice_ops` array library of the oracle's mesh backend.
+
+  `fast=True` is the timed CPU-baseline flavour: floating einsums run as
+  float32 torch CPU contractions on all host threads (what TensorFlow's
+  Eigen/MKL kernels would do) instead of float64 numpy; everything else is
+  unchanged.  Parity checks use the default (float64 accumulate) flavour.
+  """
+
+  def __init__(self, fast=False):
+    self._fast = fast
 
   # ---- host transfer
   def from_host(self, value, dtype):
@@ -230,6 +239,11 @@ class NumpyOps(object):
   # ---- tf.einsum (ops.py:1340) and the broadcast-multiply-reduce form (2805-2814)
   def einsum(self, equation, *xs):
     dtype = xs[0].dtype
+    if dtype.is_floating and self._fast:
+      import torch
+      r = torch.einsum(equation, *[torch.from_numpy(np.ascontiguousarray(x.a, dtype=np.float32))
+                                   for x in xs]).numpy()
+      return _finish(r, dtype)
     if dtype.is_floating:
       r = np.einsum(equation, *[x.a.astype(np.float64) for x in xs], optimize=True)
       return _finish(r.astype(np.float32), dtype)
@@ -260,7 +274,8 @@ class NumpyOps(object):
     o, g, s, m = x.a.shape
     out = moe_spec.dispatch(x.a.reshape(o * g, s, m), i1.a.reshape(-1, s), i2.a.reshape(-1, s),
                             p1.a.reshape(-1, s), p2.a.reshape(-1, s), g1.a.reshape(-1, s),
-                            g2.a.reshape(-1, s), num_experts, capacity)  # [OG, E, C, M]
+                            g2.a.reshape(-1, s), num_experts, capacity,
+                            bf16=(x.dtype == mtf.bfloat16))  # [OG, E, C, M]
     out = out.reshape(o, g, num_experts, capacity, m).transpose(0, 2, 1, 3, 4)
     return Arr(np.ascontiguousarray(out), x.dtype)
 
@@ -270,6 +285,7 @@ class NumpyOps(object):
     s = i1.a.shape[-1]
     yg = np.ascontiguousarray(y.a.transpose(0, 2, 1, 3, 4)).reshape(o * g, e, c, m)
     out = moe_spec.combine(yg, i1.a.reshape(-1, s), i2.a.reshape(-1, s), p1.a.reshape(-1, s),
-                           p2.a.reshape(-1, s), g1.a.reshape(-1, s), g2.a.reshape(-1, s))
+                           p2.a.reshape(-1, s), g1.a.reshape(-1, s), g2.a.reshape(-1, s),
+                           bf16=(y.dtype == mtf.bfloat16))
     out = out.reshape(o, g, s, m)
     return _finish(out, y.dtype)

@@ -1,0 +1,179 @@
+"""Mesh collectives of SlicedMeshImpl (the class CudaMeshImpl derives from)
+without a GPU: the in-process group path against the oracle backend, and the
+one-process-per-processor path over torch.distributed with the gloo backend
+(world sizes 2 and 4), slice by slice against the oracle's slices."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from mesh_b200 import mtf
+from oracle.numpy_mesh_impl import NumpyMeshImpl
+from oracle.numpy_ops import Arr
+from helpers import NumpySlicedMeshImpl, rel_err, rng
+
+MESHES = [("all:4", "batch:all"), ("rows:2,cols:4", "batch:rows;d:cols"), ("all:2", "x:all")]
+
+
+def _laid_out(impl, values, dtype=mtf.float32):
+  return impl.LaidOutTensor([Arr(v.copy(), dtype) for v in values])
+
+
+def _same(x, y, exact=True):
+  for p, q in zip(x.tensor_list, y.tensor_list):
+    assert p.a.shape == q.a.shape
+    if exact:
+      np.testing.assert_array_equal(p.a, q.a)
+    else:
+      assert rel_err(p.a, q.a) < 1e-6
+
+
+@pytest.mark.parametrize("mesh,layout", MESHES)
+def test_in_process_collectives_match_oracle(mesh, layout):
+  ora, impl = NumpyMeshImpl(mesh, layout), NumpySlicedMeshImpl(mesh, layout)
+  r = rng(0)
+  vals = [r.standard_normal((4, 8, 6)).astype(np.float32) for _ in range(ora.size)]
+  a, b = _laid_out(ora, vals), _laid_out(impl, vals)
+  for axis in range(ora.ndims):
+    n = ora.shape[axis].size
+    for name in ("SUM", "MAX", "MIN"):
+      _same(ora.allreduce(a, [axis], name), impl.allreduce(b, [axis], name), exact=(name != "SUM"))
+    for ca in range(3):
+      _same(ora.allconcat(a, axis, ca), impl.allconcat(b, axis, ca))
+      for sa in range(3):
+        if vals[0].shape[sa] % n == 0:
+          _same(ora.alltoall(a, axis, sa, ca), impl.alltoall(b, axis, sa, ca))
+    for offset, wrap in ((1, False), (-1, True), (n, False), (2, True)):
+      _same(ora.shift_by_n_processors(a, axis, offset, wrap),
+            impl.shift_by_n_processors(b, axis, offset, wrap))
+    _same(ora.allsplit(a, axis, 1), impl.allsplit(b, axis, 1))
+  every = list(range(ora.ndims))
+  _same(ora.allreduce(a, every, "SUM"), impl.allreduce(b, every, "SUM"), exact=False)
+  assert impl.allreduce(b, [], "SUM") is b
+
+
+def test_collective_argument_errors():
+  impl = NumpySlicedMeshImpl("all:4", "batch:all")
+  x = _laid_out(impl, [np.zeros((6, 3), np.float32)] * 4)
+  with pytest.raises(ValueError):
+    impl.alltoall(x, 0, 0, 1)          # 6 rows do not split 4 ways
+  with pytest.raises(ValueError):
+    impl.allreduce(x, [0], "PROD")
+  with pytest.raises(ValueError):
+    impl.receive(x, 0, [0, 1])         # one source per group member is required
+
+
+def _free_port():
+  s = socket.socket()
+  s.bind(("127.0.0.1", 0))
+  port = s.getsockname()[1]
+  s.close()
+  return port
+
+
+def _worker(rank, world, port, mesh, layout, out_dir):
+  os.environ["MASTER_ADDR"] = "127.0.0.1"
+  os.environ["MASTER_PORT"] = str(port)
+  dist.init_process_group("gloo", rank=rank, world_size=world)
+  try:
+    ora = NumpyMeshImpl(mesh, layout)
+    impl = NumpySlicedMeshImpl(mesh, layout, distributed=True, rank=rank)
+    assert impl.local_pnums == [rank]
+    r = rng(1)
+    vals = [r.standard_normal((4, 8, 6)).astype(np.float32) for _ in range(world)]
+    a = _laid_out(ora, vals)
+    b = impl.LaidOutTensor([Arr(vals[rank].copy(), mtf.float32)])
+
+    def check(x, y, exact=True):
+      p, q = x.tensor_list[rank].a, y.tensor_list[0].a
+      assert p.shape == q.shape, (p.shape, q.shape)
+      if exact:
+        np.testing.assert_array_equal(p, q)
+      else:
+        assert rel_err(q, p) < 1e-6
+    for axis in range(ora.ndims):
+      n = ora.shape[axis].size
+      for name in ("SUM", "MAX", "MIN"):
+        check(ora.allreduce(a, [axis], name), impl.allreduce(b, [axis], name), exact=(name != "SUM"))
+      for ca in range(3):
+        check(ora.allconcat(a, axis, ca), impl.allconcat(b, axis, ca))
+        for sa in range(3):
+          if vals[0].shape[sa] % n == 0:
+            check(ora.alltoall(a, axis, sa, ca), impl.alltoall(b, axis, sa, ca))
+      for offset, wrap in ((1, False), (-1, True), (2, True)):
+        check(ora.shift_by_n_processors(a, axis, offset, wrap),
+              impl.shift_by_n_processors(b, axis, offset, wrap))
+    check(ora.allreduce(a, list(range(ora.ndims)), "SUM"),
+          impl.allreduce(b, list(range(ora.ndims)), "SUM"), exact=False)
+
+    # a whole graph: FFN with the contracted dim split, then export on every rank
+    def ffn(backend):
+      rr = rng(2)
+      g = mtf.Graph()
+      m = mtf.Mesh(g, "m")
+      x = rr.standard_normal((8, 4, 16)).astype(np.float32)
+      wi = rr.standard_normal((16, 32)).astype(np.float32) / 4
+      wo = rr.standard_normal((32, 16)).astype(np.float32) / 6
+      X = mtf.import_tf_tensor(m, x, "batch:8,length:4,d_model:16")
+      WI = mtf.import_tf_tensor(m, wi, "d_model:16,d:32")
+      WO = mtf.import_tf_tensor(m, wo, "d:32,d_model:16")
+      y = mtf.layers.dense_relu_dense(X, mtf.Dimension("d", 32), wi=WI, wo=WO)
+      low = mtf.Lowering(g, {m: backend})
+      return low.export_to_tf_tensor(y), low.counter_totals()
+    if "d:" in layout:
+      got, cg = ffn(impl)
+      ref, cr = ffn(ora)
+      assert rel_err(got, ref) < 1e-6 and cg == cr
+    open(os.path.join(out_dir, "ok%d" % rank), "w").write("ok")
+  finally:
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,mesh,layout", [(2, "all:2", "d:all"),
+                                               (4, "rows:2,cols:2", "batch:rows;d:cols")])
+def test_distributed_collectives_over_gloo(tmp_path, world, mesh, layout):
+  mp.spawn(_worker, args=(world, _free_port(), mesh, layout, str(tmp_path)), nprocs=world, join=True)
+  assert sorted(os.listdir(str(tmp_path))) == ["ok%d" % r for r in range(world)]
+
+
+def _moe_worker(rank, world, port, out_dir):
+  os.environ["MASTER_ADDR"] = "127.0.0.1"
+  os.environ["MASTER_PORT"] = str(port)
+  dist.init_process_group("gloo", rank=rank, world_size=world)
+  try:
+    mesh_shape, layout = "all:%d" % world, "batch:all;experts:all"
+
+    def layer(backend):
+      r = rng(6)
+      g = mtf.Graph()
+      m = mtf.Mesh(g, "m")
+      b, l, d, f, e = 8, 32, 16, 32, 8
+      x = r.standard_normal((b, l, d)).astype(np.float32)
+      wg = (r.standard_normal((d, e)) / 4).astype(np.float32)
+      wi = (r.standard_normal((e, d, f)) / 4).astype(np.float32)
+      wo = (r.standard_normal((e, f, d)) / 6).astype(np.float32)
+      X = mtf.import_tf_tensor(m, x, "batch:8,length:32,d_model:16", dtype=mtf.bfloat16)
+      WG = mtf.import_tf_tensor(m, wg, "d_model:16,expert_unsplit:8", dtype=mtf.float32)
+      WI = mtf.import_tf_tensor(m, wi, "experts:8,d_model:16,d_ff:32", dtype=mtf.bfloat16)
+      WO = mtf.import_tf_tensor(m, wo, "experts:8,d_ff:32,d_model:16", dtype=mtf.bfloat16)
+      hp = mtf.moe.HParams(moe_group_size=32, moe_second_policy_train="all")
+      out, loss = mtf.moe.transformer_moe_layer_v1(
+          X, mtf.Dimension("d_model", d), hp, True, mesh_shape, layout, WG, WI, WO)
+      low = mtf.Lowering(g, {m: backend})
+      return low.export_to_tf_tensor(out), float(low.export_to_tf_tensor(loss)), low.counter_totals()
+    got, gl, cg = layer(NumpySlicedMeshImpl(mesh_shape, layout, distributed=True, rank=rank))
+    ref, rl, cr = layer(NumpyMeshImpl(mesh_shape, layout))
+    np.testing.assert_array_equal(got, ref)
+    assert abs(gl - rl) < 1e-7 and cg == cr and cg["alltoall/0/reshape_op"] > 0
+    open(os.path.join(out_dir, "ok%d" % rank), "w").write("ok")
+  finally:
+    dist.destroy_process_group()
+
+
+def test_moe_layer_with_alltoall_over_gloo(tmp_path):
+  mp.spawn(_moe_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+  assert sorted(os.listdir(str(tmp_path))) == ["ok0", "ok1"]
