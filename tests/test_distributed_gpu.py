@@ -1,0 +1,122 @@
+"""One process per GPU over NCCL: collectives, the FFN with a split contracted
+dim and the MoE layer with its alltoalls, each rank against the oracle.
+Skipped when fewer than two GPUs are visible."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from mesh_b200 import mtf
+from helpers import rel_err, rng
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+  s = socket.socket()
+  s.bind(("127.0.0.1", 0))
+  port = s.getsockname()[1]
+  s.close()
+  return port
+
+
+def _worker(rank, world, port, out_dir):
+  import torch
+  import torch.distributed as dist
+  from mesh_b200.cuda_mesh_impl import CudaMeshImpl
+  from oracle.numpy_mesh_impl import NumpyMeshImpl
+  from oracle.numpy_ops import Arr
+  os.environ["MASTER_ADDR"] = "127.0.0.1"
+  os.environ["MASTER_PORT"] = str(port)
+  torch.cuda.set_device(rank)
+  dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+  try:
+    mesh_shape = "all:%d" % world
+    impl = CudaMeshImpl(mesh_shape, "d_ff:all", list(range(world)))
+    assert impl.is_distributed and impl.local_pnums == [rank]
+    ora = NumpyMeshImpl(mesh_shape, "d_ff:all")
+    ops = impl.slice_ops
+    r = rng(1)
+    vals = [r.standard_normal((4, 8, 6)).astype(np.float32) for _ in range(world)]
+    a = ora.LaidOutTensor([Arr(v.copy(), mtf.float32) for v in vals])
+    b = impl.LaidOutTensor([ops.from_host(vals[rank], mtf.float32)])
+
+    def check(x, y, exact=True):
+      p, q = x.tensor_list[rank].a, ops.to_host(y.tensor_list[0])
+      assert p.shape == q.shape
+      if exact:
+        np.testing.assert_array_equal(p, q)
+      else:
+        assert rel_err(q, p) < 1e-6
+    for name in ("SUM", "MAX", "MIN"):
+      check(ora.allreduce(a, [0], name), impl.allreduce(b, [0], name), exact=(name != "SUM"))
+    for ca in range(3):
+      check(ora.allconcat(a, 0, ca), impl.allconcat(b, 0, ca))
+      for sa in range(3):
+        if vals[0].shape[sa] % world == 0:
+          check(ora.alltoall(a, 0, sa, ca), impl.alltoall(b, 0, sa, ca))
+    for offset, wrap in ((1, False), (-1, True)):
+      check(ora.shift_by_n_processors(a, 0, offset, wrap), impl.shift_by_n_processors(b, 0, offset, wrap))
+
+    def ffn(backend):
+      rr = rng(2)
+      g = mtf.Graph()
+      m = mtf.Mesh(g, "m")
+      x = rr.standard_normal((4, 64, 128)).astype(np.float32)
+      wi = (rr.standard_normal((128, 512)) / 11).astype(np.float32)
+      wo = (rr.standard_normal((512, 128)) / 22).astype(np.float32)
+      X = mtf.import_tf_tensor(m, x, "batch:4,length:64,d_model:128", dtype=mtf.bfloat16)
+      WI = mtf.import_tf_tensor(m, wi, "d_model:128,d_ff:512", dtype=mtf.bfloat16)
+      WO = mtf.import_tf_tensor(m, wo, "d_ff:512,d_model:128", dtype=mtf.bfloat16)
+      y = mtf.layers.dense_relu_dense(X, mtf.Dimension("d_ff", 512), wi=WI, wo=WO)
+      low = mtf.Lowering(g, {m: backend})
+      return low.export_to_tf_tensor(y), low.counter_totals()
+    got, cg = ffn(impl)
+    ref, cr = ffn(ora)
+    assert rel_err(got, ref) < 2e-2 and cg == cr and "allreduce/[0]/einsum_op" in cg
+
+    layout = "batch:all;experts:all"
+
+    def moe(backend):
+      rr = rng(6)
+      g = mtf.Graph()
+      m = mtf.Mesh(g, "m")
+      bb, l, d, f, e = 8, 64, 64, 128, 8
+      x = rr.standard_normal((bb, l, d)).astype(np.float32)
+      wg = (rr.standard_normal((d, e)) / 8).astype(np.float32)
+      wi = (rr.standard_normal((e, d, f)) / 8).astype(np.float32)
+      wo = (rr.standard_normal((e, f, d)) / 11).astype(np.float32)
+      X = mtf.import_tf_tensor(m, x, "batch:8,length:64,d_model:64", dtype=mtf.bfloat16)
+      WG = mtf.import_tf_tensor(m, wg, "d_model:64,expert_unsplit:8", dtype=mtf.float32)
+      WI = mtf.import_tf_tensor(m, wi, "experts:8,d_model:64,d_ff:128", dtype=mtf.bfloat16)
+      WO = mtf.import_tf_tensor(m, wo, "experts:8,d_ff:128,d_model:64", dtype=mtf.bfloat16)
+      hp = mtf.moe.HParams(moe_group_size=64, moe_second_policy_train="all")
+      out, loss, aux = mtf.moe.transformer_moe_layer_v1(
+          X, mtf.Dimension("d_model", d), hp, True, mesh_shape, layout, WG, WI, WO, return_aux=True)
+      low = mtf.Lowering(g, {m: backend})
+      return (low.export_to_tf_tensor(out), low.export_to_tf_tensor(aux["index_1"]),
+              low.export_to_tf_tensor(aux["position_2"]), float(low.export_to_tf_tensor(loss)))
+    go, gi, gp, gl = moe(CudaMeshImpl(mesh_shape, layout, list(range(world))))
+    ro, ri, rp, rl = moe(NumpyMeshImpl(mesh_shape, layout))
+    same = np.all(gi == ri, axis=-1)
+    assert same.mean() > 0.8
+    np.testing.assert_array_equal(gp[same], rp[same])
+    assert rel_err(go.reshape(ri.shape + (-1,))[same], ro.reshape(ri.shape + (-1,))[same]) < 2e-2
+    assert abs(gl - rl) < 2e-2 * abs(rl)
+    impl.synchronize()
+    open(os.path.join(out_dir, "ok%d" % rank), "w").write("ok")
+  finally:
+    dist.destroy_process_group()
+
+
+def test_one_process_per_gpu_over_nccl(tmp_path):
+  import torch
+  import torch.multiprocessing as mp
+  world = min(torch.cuda.device_count(), 4)
+  if world < 2:
+    pytest.skip("needs at least two GPUs")
+  world = 2 if world < 4 else 4
+  mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+  assert sorted(os.listdir(str(tmp_path))) == ["ok%d" % r for r in range(world)]
