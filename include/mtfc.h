@@ -239,6 +239,33 @@ int mtfc_moe_dispatch(const void* x, const int32_t* table, void* out, int64_t ou
                       int64_t groups_per_outer, int32_t group_size, int32_t experts,
                       int32_t capacity, int64_t row_bytes, void* stream);
 
+/* Same result as mtfc_moe_slot_table followed by mtfc_moe_dispatch, for callers
+ * that may not allocate device memory.  This entry point has no counterpart in
+ * the reference.  It is meant for hosts whose device memory is planned once at
+ * start-up and then frozen — a serving process that has handed every remaining
+ * byte to its own pools, or code on a latency-critical path where a cudaMalloc
+ * (which can fail, and which stalls the whole device while it runs) is not
+ * acceptable.  The (group, expert, slot) -> token table that the two-call form
+ * takes from the caller lives here in a fixed array inside the library image:
+ * 1,048,576 entries (4 MiB), held by every GPU that loads the library until the
+ * process exits.  The caller still owns x, the routing arrays and out.
+ *   - groups*experts*capacity above 1,048,576 is rejected with MTFC_ERR_SHAPE;
+ *     nothing is launched.  Use the two-call form with your own table then.
+ *   - The first call on each device looks up the array's device address, with
+ *     that device current; make that first call before starting any stream
+ *     capture on the device.
+ *   - No cudaMalloc, cudaFree or allocating library routine is called.
+ *   - All calls on a device share the one array.  Every call rewrites the part it
+ *     uses before reading it, so earlier contents never leak into a result, but
+ *     two calls whose kernels overlap on the GPU (different streams) race on it:
+ *     keep calls on one stream, or order them with events. */
+int mtfc_moe_dispatch_noalloc(const void* x, const int32_t* idx1, const int32_t* idx2,
+                              const int32_t* pos1, const int32_t* pos2, const float* gate1,
+                              const float* gate2, void* out, int64_t outer,
+                              int64_t groups_per_outer, int32_t group_size, int32_t experts,
+                              int32_t capacity, int64_t row_bytes, int32_t round_gates_to_bf16,
+                              void* stream);
+
 /* y: [outer, experts, groups_per_outer, capacity, row] -> out: [outer,
  * groups_per_outer, group_size, row] = w1*y[i1, p1] + w2*y[i2, p2] with the gates
  * rounded to y's dtype first; fp32 arithmetic, one rounding at the store. */

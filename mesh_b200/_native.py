@@ -84,6 +84,8 @@ def _declare(lib):
                                vp, vp, vp],
       "mtfc_moe_slot_table": [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, vp, vp],
       "mtfc_moe_dispatch": [vp, vp, vp, i64, i64, i32, i32, i32, i64, vp],
+      "mtfc_moe_dispatch_noalloc": [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64,
+                                    i32, vp],
       "mtfc_moe_combine": [vp, i32, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64, vp],
   }
   for name, argtypes in signatures.items():

@@ -402,6 +402,31 @@ combine_rows_f32_kernel(const float4* __restrict__ y, const int* __restrict__ id
   }
 }
 
+// Slot-table scratch of mtfc_moe_dispatch_noalloc.  Lives in the library image:
+// every GPU that loads libmtfc holds these 4 MiB until the process exits.
+constexpr long long kNoAllocSlotCapacity = 1LL << 20;  // (group, expert, slot) entries
+static __device__ __align__(256) int g_noalloc_slot_table[kNoAllocSlotCapacity];
+
+// Device address of the scratch array on the current device.  The array's name
+// is only a host-side handle here; kernels must be given the address the
+// runtime resolves for the device that is current.
+int noalloc_slot_table_ptr(int** out) {
+  static int* ptrs[64] = {nullptr};
+  int dev = 0;
+  MTFC_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(MTFC_ERR_CUDA, "device ordinal %d out of range", dev);
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_slot_table);
+    if (e != cudaSuccess || !p)
+      return fail(MTFC_ERR_CUDA, "cudaGetSymbolAddress(slot table scratch): %s",
+                  cudaGetErrorString(e));
+    ptrs[dev] = static_cast<int*>(p);
+  }
+  *out = ptrs[dev];
+  return MTFC_OK;
+}
+
 size_t gate_smem_bytes(int experts) {
   return (size_t)(kGateThreads * (experts + 1) + experts) * sizeof(float) +
          (size_t)(3 * experts + kGateWarps * experts) * sizeof(int);
@@ -531,6 +556,49 @@ int mtfc_moe_combine(const void* y, int dtype, const int32_t* idx1, const int32_
         static_cast<float4*>(out), groups, group_size, experts, capacity, vec, groups_per_outer);
   MTFC_LAUNCH_CHECK("combine_rows_kernel");
   count_launch(1);
+  return MTFC_OK;
+}
+
+int mtfc_moe_dispatch_noalloc(const void* x, const int32_t* idx1, const int32_t* idx2,
+                              const int32_t* pos1, const int32_t* pos2, const float* gate1,
+                              const float* gate2, void* out, int64_t outer,
+                              int64_t groups_per_outer, int32_t group_size, int32_t experts,
+                              int32_t capacity, int64_t row_bytes, int32_t round_gates_to_bf16,
+                              void* stream) {
+  if (!x || !idx1 || !idx2 || !pos1 || !pos2 || !gate1 || !gate2 || !out)
+    return fail(MTFC_ERR_SHAPE, "dispatch_noalloc: null argument");
+  if (outer < 0 || groups_per_outer < 0 || group_size < 1 || experts < 1 || capacity < 1)
+    return fail(MTFC_ERR_SHAPE, "dispatch_noalloc: bad extents");
+  if (row_bytes < 16 || row_bytes % 16 != 0)
+    return fail(MTFC_ERR_SHAPE, "dispatch_noalloc: row of %lld bytes is not a multiple of 16",
+                (long long)row_bytes);
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) % 16 != 0)
+    return fail(MTFC_ERR_SHAPE, "dispatch_noalloc: buffers must be 16-byte aligned");
+  const long long groups = outer * groups_per_outer;
+  const long long entries = groups * experts * capacity;
+  if (entries > kNoAllocSlotCapacity)
+    return fail(MTFC_ERR_SHAPE,
+                "dispatch_noalloc: groups*experts*capacity = %lld exceeds the built-in scratch of "
+                "%lld entries; use mtfc_moe_slot_table + mtfc_moe_dispatch with your own table",
+                entries, kNoAllocSlotCapacity);
+  if ((size_t)experts * capacity * sizeof(int) > 48 * 1024)
+    return fail(MTFC_ERR_SHAPE, "dispatch_noalloc: experts*capacity=%d too large", experts * capacity);
+  if (entries == 0) return MTFC_OK;
+  int* table = nullptr;
+  int rc = noalloc_slot_table_ptr(&table);
+  if (rc != MTFC_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The table is rewritten in full for the entries this call uses, so nothing
+  // left over from an earlier call is ever read.
+  slot_table_kernel<<<(unsigned)groups, 256, (size_t)experts * capacity * sizeof(int), s>>>(
+      idx1, idx2, pos1, pos2, gate1, gate2, group_size, experts, capacity, round_gates_to_bf16,
+      table);
+  MTFC_LAUNCH_CHECK("slot_table_kernel");
+  dispatch_rows_kernel<<<grid_for(entries * 32, 256), 256, 0, s>>>(
+      static_cast<const uint4*>(x), table, static_cast<uint4*>(out), groups, group_size, experts,
+      capacity, (int)(row_bytes / 16), groups_per_outer);
+  MTFC_LAUNCH_CHECK("dispatch_rows_kernel");
+  count_launch(2);
   return MTFC_OK;
 }
 
