@@ -79,7 +79,8 @@ typedef struct {
   int32_t in_dtype;          /* MTFC_BF16 / MTFC_F32 / MTFC_I32 (A and B)     */
   int32_t out_dtype;         /* MTFC_BF16 / MTFC_F32 / MTFC_I32               */
   int32_t epilogue;          /* 0 = none, 1 = ReLU (tf.nn.relu, ops.py:1921)  */
-  int32_t force_path;        /* 0 = auto, 1 = tcgen05 or fail, 2 = FFMA       */
+  int32_t force_path;        /* 0 = auto, 1 = tcgen05 or fail, 2 = FFMA,
+                                3 / 4 = tcgen05 single-CTA / CTA-pair kernel   */
 } mtfc_gemm_desc;
 
 #define MTFC_EPILOGUE_NONE 0

@@ -55,7 +55,7 @@ int sm_count() {
 
 bool gemm_tcgen05_eligible(const mtfc_gemm_desc* d, const void* a, const void* b, const void* c);
 int gemm_tcgen05_launch(const mtfc_gemm_desc* d, const void* a, const void* b, void* c,
-                        cudaStream_t stream);
+                        cudaStream_t stream, int cta_group);
 int gemm_simt_launch(const mtfc_gemm_desc* d, const void* a, const void* b, void* c,
                      cudaStream_t stream);
 
@@ -107,10 +107,12 @@ int mtfc_gemm(const mtfc_gemm_desc* d, const void* a, const void* b, void* c, vo
   if (d->batch == 0 || d->m == 0 || d->n == 0) return MTFC_OK;  // empty output
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tc_ok = d->k > 0 && gemm_tcgen05_eligible(d, a, b, c);
-  if (d->force_path == 1 && !tc_ok)
+  const bool forced_tc = d->force_path == 1 || d->force_path == 3 || d->force_path == 4;
+  if (forced_tc && !tc_ok)
     return fail(MTFC_ERR_SHAPE, "gemm: tensor-core path forced but the problem is not eligible");
   if (tc_ok && d->force_path != 2) {
-    rc = gemm_tcgen05_launch(d, a, b, c, s);
+    rc = gemm_tcgen05_launch(d, a, b, c, s,
+                             d->force_path == 3 ? 1 : (d->force_path == 4 ? 2 : 0));
   } else {
     rc = gemm_simt_launch(d, a, b, c, s);
   }

@@ -444,6 +444,321 @@ einsum_gemm_tcgen05(const __grid_constant__ CUtensorMap map_a,
   }
 }
 
+// ------------------------------------------------- the 2-CTA (cta_group::2) kernel
+// A cluster of two CTAs on neighbouring SMs computes one 256x256 tile: CTA r
+// holds rows [128r, 128r+128) of A and columns [128r, 128r+128) of B for each
+// K block, the leader (rank 0) issues tcgen05.mma.cta_group::2 128x256 per SM
+// reading both CTAs' shared memory, and each CTA's TMEM receives its 128 rows
+// of the accumulator.  B crosses L2->SM once per pair instead of once per SM
+// and each SM's shared memory serves 64 B/clk of operand reads instead of 96,
+// which is what lifts the single-CTA kernel's shared-memory bandwidth ceiling.
+// No load uses multicast: each CTA fetches its own halves with plain TMA loads
+// that report to the leader's mbarrier.
+constexpr int STAGES2 = 6;
+constexpr int B2_STAGE_BYTES = (BN / 2) * BK * 2;  // 16 KiB: this CTA's half of B
+constexpr int SMEM2_A = 0;
+constexpr int SMEM2_B = SMEM2_A + STAGES2 * A_STAGE_BYTES;
+constexpr int SMEM2_EPI = SMEM2_B + STAGES2 * B2_STAGE_BYTES;
+constexpr int SMEM2_BAR = SMEM2_EPI + EPI_BYTES;
+constexpr int NUM_BARS2 = 2 * STAGES2 + 4;
+constexpr int SMEM2_MISC = SMEM2_BAR + NUM_BARS2 * 8;
+constexpr int SMEM2_USED = SMEM2_MISC + 16;
+constexpr int SMEM2_ALLOC = SMEM2_USED + 1024;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// shared::cluster address of `addr` (a shared::cta address) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+
+// TMA load whose completion bytes are reported to an mbarrier that may live in
+// the peer CTA of the pair (cluster address), data landing in this CTA.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map,
+                                                 uint32_t bar_cluster_addr, int c0, int c1,
+                                                 int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1),
+        "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar_cluster_addr)
+               : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ uint32_t make_idesc_pair(int a_mn, int b_mn) {
+  uint32_t d = 0;
+  d |= 1u << 4;
+  d |= 1u << 7;
+  d |= 1u << 10;
+  d |= (uint32_t)(a_mn & 1) << 15;
+  d |= (uint32_t)(b_mn & 1) << 16;
+  d |= (uint32_t)(BN >> 3) << 17;
+  d |= (uint32_t)((2 * BM) >> 4) << 24;  // M = 256 across the pair
+  return d;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+einsum_gemm_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a,
+                         const __grid_constant__ CUtensorMap map_b,
+                         const __grid_constant__ CUtensorMap map_c, const GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + SMEM2_BAR;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES2 + s); };
+  auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES2 + b); };
+  auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES2 + 2 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + SMEM2_MISC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SMEM2_MISC + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) {
+      mbar_init(full_bar(s), 1);   // leader's: its producer's expect_tx arrival
+      mbar_init(empty_bar(s), 1);  // one tcgen05.commit per use, in each CTA
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tmem_full_bar(b), 1);
+      mbar_init(tmem_empty_bar(b), 2 * EPI_WARPS);  // leader's: epilogue warps of both CTAs
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_base + SMEM2_MISC),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_kb = (args.k + BK - 1) / BK;
+  const long long tiles_per_batch = (long long)args.tiles_m * args.tiles_n;  // 256x256 tiles
+  const long long num_tiles = tiles_per_batch * args.batch;
+  const long long cluster_id = blockIdx.x >> 1;
+  const long long num_clusters = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        const int b = (int)(t / tiles_per_batch);
+        const int r = (int)(t % tiles_per_batch);
+        const int m0 = (r / args.tiles_n) * (2 * BM) + (int)rank * BM;
+        const int n0 = (r % args.tiles_n) * BN + (int)rank * (BN / 2);
+        const int ab = args.a_batched ? b : 0;
+        const int bb = args.b_batched ? b : 0;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
+          if (leader) mbar_expect_tx(full_bar(stage), 2 * (A_STAGE_BYTES + B2_STAGE_BYTES));
+          const uint32_t lead_full = map_to_cta(full_bar(stage), 0);
+          const uint32_t sa = smem_base + SMEM2_A + stage * A_STAGE_BYTES;
+          const uint32_t sb = smem_base + SMEM2_B + stage * B2_STAGE_BYTES;
+          const int k0 = kb * BK;
+          if (args.a_mn_major) {
+#pragma unroll
+            for (int g = 0; g < BM / 64; ++g)
+              tma_load_3d_pair(sa + g * MN_GROUP_BYTES, &map_a, lead_full, m0 + g * 64, k0, ab);
+          } else {
+            tma_load_3d_pair(sa, &map_a, lead_full, k0, m0, ab);
+          }
+          if (args.b_mn_major) {
+#pragma unroll
+            for (int g = 0; g < BN / 128; ++g)
+              tma_load_3d_pair(sb + g * MN_GROUP_BYTES, &map_b, lead_full, n0 + g * 64, k0, bb);
+          } else {
+            tma_load_3d_pair(sb, &map_b, lead_full, k0, n0, bb);
+          }
+          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok && args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer (leader only)
+    if (lane == 0 && leader) {
+      const uint32_t idesc = make_idesc_pair(args.a_mn_major, args.b_mn_major);
+      const uint32_t a_lbo = args.a_mn_major ? MN_GROUP_BYTES : 16;
+      const uint32_t b_lbo = args.b_mn_major ? MN_GROUP_BYTES : 16;
+      const uint32_t a_kstep = args.a_mn_major ? UMMA_K * 128 : UMMA_K * 2;
+      const uint32_t b_kstep = args.b_mn_major ? UMMA_K * 128 : UMMA_K * 2;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      long long local = 0;
+      for (long long t = cluster_id; t < num_tiles && ok; t += num_clusters, ++local) {
+        const int buf = (int)(local & 1);
+        const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+        if (!mbar_wait(tmem_empty_bar(buf), acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + SMEM2_A + stage * A_STAGE_BYTES;
+          const uint32_t sb = smem_base + SMEM2_B + stage * B2_STAGE_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+            const uint64_t da = make_smem_desc(sa + ks * a_kstep, a_lbo, 1024);
+            const uint64_t db = make_smem_desc(sb + ks * b_kstep, b_lbo, 1024);
+            tc_mma_bf16_pair(d_tmem, da, db, idesc, (kb | ks) != 0 ? 1u : 0u);
+          }
+          // free the stage in both CTAs once these MMAs have read it
+          tc_commit_pair(map_to_cta(empty_bar(stage), 0));
+          tc_commit_pair(map_to_cta(empty_bar(stage), 1));
+          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit_pair(map_to_cta(tmem_full_bar(buf), 0));
+        tc_commit_pair(map_to_cta(tmem_full_bar(buf), 1));
+      }
+      if (!ok && args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
+    }
+  } else {
+    // ------------------------------------------------ epilogue (both CTAs)
+    const int q = warp & 3;
+    const int ew = warp - 2;
+    uint8_t* stage_buf = smem + SMEM2_EPI + ew * 2 * EPI_BUF_BYTES;
+    const uint32_t stage_u32 = smem_base + SMEM2_EPI + ew * 2 * EPI_BUF_BYTES;
+    const int cols_per_store = args.out_f32 ? 32 : 64;
+    bool ok = true;
+    long long local = 0;
+    int store_idx = 0;
+    for (long long t = cluster_id; t < num_tiles && ok; t += num_clusters, ++local) {
+      const int buf = (int)(local & 1);
+      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+      const int b = (int)(t / tiles_per_batch);
+      const int r = (int)(t % tiles_per_batch);
+      const int m0 = (r / args.tiles_n) * (2 * BM) + (int)rank * BM;
+      const int n0 = (r % args.tiles_n) * BN;
+      ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), acc_phase, abort_flag));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+      const bool rows_live = (m0 + q * 32) < args.m;
+      for (int c0 = 0; c0 < BN; c0 += cols_per_store) {
+        if (n0 + c0 >= args.n || !rows_live) break;
+        const int sbuf = store_idx & 1;
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint8_t* row = stage_buf + sbuf * EPI_BUF_BYTES + lane * 128;
+        const int sw = lane & 7;
+        if (args.out_f32) {
+          uint32_t v[32];
+          tc_ld_32x32(t_row + c0, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 o;
+            o.x = __uint_as_float(v[4 * j + 0]);
+            o.y = __uint_as_float(v[4 * j + 1]);
+            o.z = __uint_as_float(v[4 * j + 2]);
+            o.w = __uint_as_float(v[4 * j + 3]);
+            if (args.relu) {
+              o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f);
+              o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f);
+            }
+            *reinterpret_cast<float4*>(row + ((j ^ sw) << 4)) = o;
+          }
+        } else {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t v[32];
+            tc_ld_32x32(t_row + c0 + h * 32, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                f[e] = __uint_as_float(v[8 * j + e]);
+                if (args.relu) f[e] = fmaxf(f[e], 0.f);
+              }
+              uint4 o;
+              o.x = pack_bf16x2(f[0], f[1]);
+              o.y = pack_bf16x2(f[2], f[3]);
+              o.z = pack_bf16x2(f[4], f[5]);
+              o.w = pack_bf16x2(f[6], f[7]);
+              *reinterpret_cast<uint4*>(row + (((h * 4 + j) ^ sw) << 4)) = o;
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_3d(&map_c, stage_u32 + sbuf * EPI_BUF_BYTES, n0 + c0, m0 + q * 32, b);
+          tma_store_commit();
+        }
+        ++store_idx;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(tmem_empty_bar(buf), 0));
+    }
+    if (lane == 0) tma_store_wait_all();
+    if (!ok && lane == 0 && args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
+  }
+
+  // Neither CTA may leave while the pair's MMAs can still read its shared memory.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
 // ------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -523,8 +838,46 @@ bool gemm_tcgen05_eligible(const mtfc_gemm_desc* d, const void* a, const void* b
   return true;
 }
 
+// Resident 2-CTA clusters the device can hold for the pair kernel (0 if the
+// query fails); cached per device.
+int max_pair_clusters() {
+  static int cached[64];
+  static bool known[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (!known[dev]) {
+    int n = 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (unsigned)sm_count(), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM2_ALLOC;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaFuncSetAttribute(einsum_gemm_tcgen05_2cta, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SMEM2_ALLOC) != cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&n, einsum_gemm_tcgen05_2cta, &cfg) != cudaSuccess)
+      n = 0;
+    (void)cudaGetLastError();
+    cached[dev] = n;
+    known[dev] = true;
+  }
+  return cached[dev];
+}
+
+// cta_group: 0 = choose, 1 = single-CTA kernel, 2 = CTA-pair kernel.
 int gemm_tcgen05_launch(const mtfc_gemm_desc* d, const void* a, const void* b, void* c,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, int cta_group) {
+  int pair_clusters = 0;
+  if (cta_group != 1) pair_clusters = max_pair_clusters();
+  // The pair kernel works on 256-row tiles: worth it once M fills them.
+  bool use_pair = pair_clusters > 0 && (cta_group == 2 || d->m >= 256);
+  if (cta_group == 2 && pair_clusters <= 0)
+    return fail(MTFC_ERR_CUDA, "CTA-pair GEMM forced but no 2-CTA cluster can be resident");
   const bool a_b = d->batch > 1 && d->a_batch != 0;
   const bool b_b = d->batch > 1 && d->b_batch != 0;
   const int a_major = classify(d->m, d->k, d->a_m, d->a_k, a_b ? d->batch : 1, d->a_batch);
@@ -542,7 +895,8 @@ int gemm_tcgen05_launch(const mtfc_gemm_desc* d, const void* a, const void* b, v
   if (rc != MTFC_OK) return rc;
   if (b_major == 0)
     rc = encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b, d->k, d->n,
-                    b_b ? d->batch : 1, d->b_n, d->b_batch, BK, BN, "B (K-major)");
+                    b_b ? d->batch : 1, d->b_n, d->b_batch, BK, use_pair ? BN / 2 : BN,
+                    "B (K-major)");
   else
     rc = encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b, d->n, d->k,
                     b_b ? d->batch : 1, d->b_k, d->b_batch, 64, BK, "B (N-major)");
@@ -558,7 +912,8 @@ int gemm_tcgen05_launch(const mtfc_gemm_desc* d, const void* a, const void* b, v
   args.n = (int)d->n;
   args.k = (int)d->k;
   args.batch = (int)d->batch;
-  args.tiles_m = (int)((d->m + BM - 1) / BM);
+  const int tile_rows = use_pair ? 2 * BM : BM;
+  args.tiles_m = (int)((d->m + tile_rows - 1) / tile_rows);
   args.tiles_n = (int)((d->n + BN - 1) / BN);
   args.a_mn_major = a_major;
   args.b_mn_major = b_major;
@@ -568,6 +923,25 @@ int gemm_tcgen05_launch(const mtfc_gemm_desc* d, const void* a, const void* b, v
   args.out_f32 = out_f32 ? 1 : 0;
   args.status = device_status_word();
 
+  const long long num_tiles = (long long)args.tiles_m * args.tiles_n * args.batch;
+  if (use_pair) {
+    const long long clusters = num_tiles < pair_clusters ? num_tiles : pair_clusters;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM2_ALLOC;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MTFC_CUDA(cudaLaunchKernelEx(&cfg, einsum_gemm_tcgen05_2cta, map_a, map_b, map_c, args));
+    return MTFC_OK;
+  }
+
   static bool attr_set[64] = {false};
   int dev = 0;
   MTFC_CUDA(cudaGetDevice(&dev));
@@ -576,7 +950,6 @@ int gemm_tcgen05_launch(const mtfc_gemm_desc* d, const void* a, const void* b, v
                                    SMEM_ALLOC));
     attr_set[dev] = true;
   }
-  const long long num_tiles = (long long)args.tiles_m * args.tiles_n * args.batch;
   const int sms = sm_count();
   const unsigned grid = (unsigned)(num_tiles < sms ? num_tiles : sms);
   einsum_gemm_tcgen05<<<grid, NUM_THREADS, SMEM_ALLOC, stream>>>(map_a, map_b, map_c, args);

@@ -50,16 +50,20 @@ def _run(dev, batch, m, n, k, a_mn, b_mn, out_f32, relu, in_dtype="bf16", force=
   return C.float().cpu().numpy(), ref, used_tc
 
 
+@pytest.mark.parametrize("force", [3, 4], ids=["single-cta", "cta-pair"])
 @pytest.mark.parametrize("a_mn", [0, 1])
 @pytest.mark.parametrize("b_mn", [0, 1])
 @pytest.mark.parametrize("shape", [(1, 128, 256, 64), (1, 200, 264, 72), (3, 136, 80, 200),
-                                   (1, 1024, 512, 1024), (1, 9728, 512, 128), (2, 8, 8, 8)])
-def test_tcgen05_layouts(cuda_device, shape, a_mn, b_mn):
+                                   (1, 1024, 512, 1024), (1, 9728, 512, 128), (2, 8, 8, 8),
+                                   (2, 600, 520, 328)])
+def test_tcgen05_layouts(cuda_device, shape, a_mn, b_mn, force):
+  """Both tensor-core kernels (force_path 3: one CTA per 128x256 tile, 4: a CTA
+  pair per 256x256 tile) over all four operand-majorness combinations."""
   batch, m, n, k = shape
-  got, ref, used = _run(cuda_device, batch, m, n, k, a_mn, b_mn, out_f32=True, relu=False, force=1)
+  got, ref, used = _run(cuda_device, batch, m, n, k, a_mn, b_mn, out_f32=True, relu=False, force=force)
   assert used == 1
   assert rel_err(got, ref) < 1e-5   # exact bf16 products, fp32 accumulation
-  got, ref, _ = _run(cuda_device, batch, m, n, k, a_mn, b_mn, out_f32=False, relu=True, force=1)
+  got, ref, _ = _run(cuda_device, batch, m, n, k, a_mn, b_mn, out_f32=False, relu=True, force=force)
   assert rel_err(got, ref) < 2e-2
 
 
