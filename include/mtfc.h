@@ -94,6 +94,14 @@ int mtfc_gemm(const mtfc_gemm_desc* desc, const void* a, const void* b, void* c,
 int mtfc_gemm_uses_tensor_cores(const mtfc_gemm_desc* desc, const void* a,
                                 const void* b, const void* c);
 
+/* K1f on the tensor cores: fp32 [batch, rows, k] (element strides s_*) -> bf16
+ * [batch, rows, 6k], every value split into three bf16 terms laid along K
+ * (pattern 0 for the left operand, 1 for the right) so that one mtfc_gemm over
+ * 6k with fp32 output equals the fp32 contraction to ~1e-6 relative.  Serves the
+ * same tf.einsum call as mtfc_gemm (ops.py:1331-1340) for float32 tensors. */
+int mtfc_split_bf16x3(const float* src, int64_t s_batch, int64_t s_row, int64_t s_k, void* dst_bf16,
+                      int64_t batch, int64_t rows, int64_t k, int pattern, void* stream);
+
 /* ---- K8: slice-local array operations ----------------------------------- */
 /*
  * The op-by-op lowering applies TensorFlow ops to slices inside

@@ -172,7 +172,7 @@ def config_einsum_fp32(args):
   w = ops.from_host(r.standard_normal((1024, 4096), dtype=np.float32) / 32, mtf.float32)
   ms = _time(lambda: ops.einsum("ab,bc->ac", x, w), flush=_Flusher(ops))
   _emit(config="einsum_fp32", quantity="x[4096,1024].w[1024,4096]", ms=ms,
-        tflops=2.0 * 4096 * 1024 * 4096 / (ms * 1e-3) / 1e12, kernel="gemm_simt_kernel (FFMA)")
+        tflops=2.0 * 4096 * 1024 * 4096 / (ms * 1e-3) / 1e12, kernel="split_bf16x3 x2 + einsum_gemm_tcgen05 over 6K")
 
 
 def config_attention(args):

@@ -331,6 +331,40 @@ __global__ void fill_kernel(TO* __restrict__ out, long long n, float value, floa
     st<TO>(out, i, value + step_value * (float)i);
 }
 
+// fp32 [batch, rows, k] (any strides) -> bf16 [batch, rows, 6k]: each value is
+// split as hi + mid + lo (three bf16 terms carrying 24 mantissa bits) and the
+// terms are laid along K in the order `pattern` names, so that one bf16 GEMM
+// over 6k with fp32 accumulation sums hi*lo + lo*hi + mid*mid + hi*mid + mid*hi +
+// hi*hi — every product exact in fp32 — i.e. an fp32-accurate contraction on
+// the tensor cores.  The K blocks are ordered smallest products first: the
+// tensor core truncates when it adds into the fp32 accumulator, so the many
+// correction terms are added while the accumulator is still ~2^-8 of its final
+// size and only the k/16 additions of the hi*hi block see its full magnitude.
+// pattern 0 (left operand): hi lo mid hi mid hi;
+// pattern 1 (right operand): lo hi mid mid hi hi.
+__global__ void split_bf16x3_kernel(const float* __restrict__ src, long long s_batch,
+                                    long long s_row, long long s_k, __nv_bfloat16* __restrict__ dst,
+                                    long long batch, long long rows, long long k, int pattern) {
+  const long long n = batch * rows * k;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+    const long long kk = i % k;
+    const long long r = (i / k) % rows;
+    const long long b = i / (k * rows);
+    const float v = src[b * s_batch + r * s_row + kk * s_k];
+    const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(hi);
+    const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+    const __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+    __nv_bfloat16* o = dst + (b * rows + r) * 6 * k + kk;
+    if (pattern == 0) {
+      o[0] = hi; o[k] = lo; o[2 * k] = mid; o[3 * k] = hi; o[4 * k] = mid; o[5 * k] = hi;
+    } else {
+      o[0] = lo; o[k] = hi; o[2 * k] = mid; o[3 * k] = mid; o[4 * k] = hi; o[5 * k] = hi;
+    }
+  }
+}
+
 // ------------------------------------------------------------ host helpers
 int fill_dims(Dims* d, int ndim, const int64_t* shape, const int64_t* const* strides, int n_str) {
   if (ndim < 0 || ndim > MTFC_MAX_DIMS) return fail(MTFC_ERR_SHAPE, "ndim %d out of range", ndim);
@@ -568,6 +602,20 @@ int mtfc_fill(void* out, int dtype, int64_t n, float value, float step, void* st
   DISPATCH_ONE(dtype, (fill_kernel<T><<<grid_for(n, kThreads * 4), kThreads, 0, s>>>(
                           static_cast<T*>(out), n, value, step)));
   MTFC_LAUNCH_CHECK("fill_kernel");
+  count_launch(1);
+  return MTFC_OK;
+}
+
+int mtfc_split_bf16x3(const float* src, int64_t s_batch, int64_t s_row, int64_t s_k, void* dst_bf16,
+                      int64_t batch, int64_t rows, int64_t k, int pattern, void* stream) {
+  if (batch < 0 || rows < 0 || k < 0 || (pattern != 0 && pattern != 1))
+    return fail(MTFC_ERR_SHAPE, "split_bf16x3: bad arguments");
+  const long long n = batch * rows * k;
+  if (n == 0) return MTFC_OK;
+  if (!src || !dst_bf16) return fail(MTFC_ERR_SHAPE, "split_bf16x3: null argument");
+  split_bf16x3_kernel<<<grid_for(n, kThreads * 2), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      src, s_batch, s_row, s_k, static_cast<__nv_bfloat16*>(dst_bf16), batch, rows, k, pattern);
+  MTFC_LAUNCH_CHECK("split_bf16x3_kernel");
   count_launch(1);
   return MTFC_OK;
 }

@@ -28,9 +28,8 @@
 namespace mtfc {
 namespace {
 
-constexpr int kGateThreads = 256;
-constexpr int kGateWarps = kGateThreads / 32;
 constexpr int kMaxExperts = 256;
+constexpr int kGateSegments = 32;  // row segments of the per-expert column sums
 
 __global__ void split_gate_weights_kernel(const float* __restrict__ w, long long m, int e,
                                           __nv_bfloat16* __restrict__ out) {
@@ -73,21 +72,26 @@ struct GateArgs {
   float* loss_per_group;  // [groups]
 };
 
+// One CTA of T = blockDim.x threads per group; tokens are taken T at a time.
 // Dynamic shared memory layout (floats / ints):
-//   row   [kGateThreads][experts + 1]  logits then raw gates of the chunk
+//   row   [T][experts + 1]             logits then raw gates of the chunk
 //   proxy [experts]                    running sum over tokens of raw gates
+//   part  [kGateSegments][experts]     partial column sums (fixed order: deterministic)
 //   base1 [experts], base2 [experts]   running per-expert counts (1st / 2nd)
-//   wcnt  [kGateWarps][experts]        per-warp counts of the chunk
-//   first/second choice of every token of the group are kept in global outputs
-__global__ void __launch_bounds__(kGateThreads)
+//   wcnt  [T / 32][experts]            per-warp counts of the chunk
+//   cnt1  [experts]                    kept first-choice count
+__global__ void __launch_bounds__(1024)
 top2_gating_kernel(GateArgs a) {
   extern __shared__ float smem[];
   const int E = a.experts;
   const int S = a.group_size;
   const int ld = E + 1;
+  const int kGateThreads = blockDim.x;
+  const int kGateWarps = kGateThreads >> 5;
   float* row = smem;
   float* proxy = row + kGateThreads * ld;
-  int* base1 = reinterpret_cast<int*>(proxy + E);
+  float* part = proxy + E;
+  int* base1 = reinterpret_cast<int*>(part + kGateSegments * E);
   int* base2 = base1 + E;
   int* wcnt = base2 + E;
   int* cnt1 = wcnt + kGateWarps * E;
@@ -152,10 +156,24 @@ top2_gating_kernel(GateArgs a) {
     const int rank = __popc(same & lt_mask);
     if (live && rank == 0) wcnt[warp * E + i1] = __popc(same);
     __syncthreads();
-    // column sums of the raw gates for the loss, and cross-warp offsets
+    // column sums of the raw gates for the loss: kGateSegments partial sums per
+    // expert, combined in a fixed order below
+    {
+      const int rows_per_seg = (chunk + kGateSegments - 1) / kGateSegments;
+      for (int i = tid; i < kGateSegments * E; i += kGateThreads) {
+        const int seg = i / E, e = i - seg * E;
+        const int r0 = seg * rows_per_seg;
+        const int r1 = min(chunk, r0 + rows_per_seg);
+        float s = 0.f;
+        for (int t = r0; t < r1; ++t) s += row[t * ld + e];
+        part[seg * E + e] = s;
+      }
+    }
+    __syncthreads();
+    // cross-warp offsets of the first-choice counts
     for (int e = tid; e < E; e += kGateThreads) {
       float s = 0.f;
-      for (int t = 0; t < chunk; ++t) s += row[t * ld + e];
+      for (int seg = 0; seg < kGateSegments; ++seg) s += part[seg * E + e];
       proxy[e] += s;
       int run = base1[e];
       for (int w = 0; w < kGateWarps; ++w) {
@@ -427,9 +445,17 @@ int noalloc_slot_table_ptr(int** out) {
   return MTFC_OK;
 }
 
-size_t gate_smem_bytes(int experts) {
-  return (size_t)(kGateThreads * (experts + 1) + experts) * sizeof(float) +
-         (size_t)(3 * experts + kGateWarps * experts) * sizeof(int);
+size_t gate_smem_bytes(int experts, int threads) {
+  return (size_t)(threads * (experts + 1) + experts + kGateSegments * experts) * sizeof(float) +
+         (size_t)(3 * experts + (threads / 32) * experts) * sizeof(int);
+}
+
+// Largest power-of-two block (<= 1024, <= the group rounded up to a warp) whose
+// chunk of logits fits in shared memory.
+int gate_threads(int experts, int group_size) {
+  int t = 1024;
+  while (t > 32 && (gate_smem_bytes(experts, t) > 200 * 1024 || t / 2 >= group_size)) t >>= 1;
+  return t;
 }
 
 }  // namespace
@@ -472,7 +498,8 @@ int mtfc_moe_top2_gating(const float* logits, int32_t parts, int64_t groups, int
   a.capacity = capacity; a.policy = policy; a.threshold = threshold; a.noise = noise;
   a.idx1 = idx1; a.idx2 = idx2; a.pos1 = pos1; a.pos2 = pos2; a.gate1 = gate1; a.gate2 = gate2;
   a.raw_gates = raw_gates; a.loss_per_group = loss_per_group;
-  const size_t smem = gate_smem_bytes(experts);
+  const int threads = gate_threads(experts, group_size);
+  const size_t smem = gate_smem_bytes(experts, threads);
   if (smem > 48 * 1024) {
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -483,7 +510,7 @@ int mtfc_moe_top2_gating(const float* logits, int32_t parts, int64_t groups, int
       attr_set[dev] = true;
     }
   }
-  top2_gating_kernel<<<(unsigned)groups, kGateThreads, smem, static_cast<cudaStream_t>(stream)>>>(a);
+  top2_gating_kernel<<<(unsigned)groups, threads, smem, static_cast<cudaStream_t>(stream)>>>(a);
   MTFC_LAUNCH_CHECK("top2_gating_kernel");
   count_launch(1);
   return MTFC_OK;

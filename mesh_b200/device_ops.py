@@ -98,6 +98,13 @@ def _i64(values):
 class DeviceOps(object):
   """libmtfc-backed array operations on one CUDA device."""
 
+  # fp32 contractions with at least this many multiply-adds go to the tensor
+  # cores as 3-term bf16 splits; smaller ones stay on the FFMA kernel
+  FP32_TENSOR_CORE_MIN_WORK = 1 << 22
+  # longer contractions stay on the FFMA kernel: the tensor core truncates on
+  # every accumulation, and beyond this many terms that bias nears 1e-5
+  FP32_TENSOR_CORE_MAX_K = 2048
+
   def __init__(self, device):
     self.device = torch.device(device)
     if self.device.type != "cuda":
@@ -451,6 +458,27 @@ class DeviceOps(object):
       self._copy(self.transpose(res, [packed_term.index(l) for l in out_term]), out)
       return out
     (nb, a_b), (_, b_b), (_, c_b), (m, a_m), (_, c_m), (n, b_n), (_, c_n), (k, a_k), (_, b_k) = plan
+    if (a.dtype.name == "float32" and out_dtype.name == "float32" and k % 4 == 0
+        and k <= self.FP32_TENSOR_CORE_MAX_K and c_n == 1
+        and nb * m * n * k >= self.FP32_TENSOR_CORE_MIN_WORK):
+      # fp32 on the tensor cores: split both operands into three bf16 terms along
+      # K and run one bf16 GEMM over 6K with fp32 accumulation
+      a3 = self._empty([nb, m, 6 * k], G.bfloat16)
+      b3 = self._empty([nb if b_b else 1, n, 6 * k], G.bfloat16)
+      self._call(self._lib.mtfc_split_bf16x3, ctypes.c_void_p(a.ptr), a_b, a_m, a_k,
+                 ctypes.c_void_p(a3.ptr), nb, m, k, 0, self._stream())
+      self._call(self._lib.mtfc_split_bf16x3, ctypes.c_void_p(b.ptr), b_b, b_n, b_k,
+                 ctypes.c_void_p(b3.ptr), nb if b_b else 1, n, k, 1, self._stream())
+      d = nat.GemmDesc()
+      d.batch, d.m, d.n, d.k = nb, m, n, 6 * k
+      d.a_batch, d.a_m, d.a_k = m * 6 * k, 6 * k, 1
+      d.b_batch, d.b_k, d.b_n = (n * 6 * k if b_b else 0), 1, 6 * k
+      d.c_batch, d.c_m, d.c_n = c_b, c_m, c_n
+      d.in_dtype, d.out_dtype = nat.BF16, nat.F32
+      d.epilogue, d.force_path = epilogue, 0
+      self._call(self._lib.mtfc_gemm, ctypes.byref(d), ctypes.c_void_p(a3.ptr),
+                 ctypes.c_void_p(b3.ptr), ctypes.c_void_p(out.ptr), self._stream())
+      return out
     d = nat.GemmDesc()
     d.batch, d.m, d.n, d.k = nb, m, n, k
     d.a_batch, d.a_m, d.a_k = a_b, a_m, a_k

@@ -180,3 +180,21 @@ def test_einsum_tensor_core_shapes(both):
     _check(both, dev.einsum(eq, *da), ora.einsum(eq, *oa), 2e-2)
   from mesh_b200 import _native as nat
   nat.device_status()
+
+
+@pytest.mark.parametrize("eq,shapes", [("ab,bc->ac", [(1024, 1024), (1024, 2048)]),
+                                       ("ab,bc->ac", [(4096, 256), (256, 4096)]),
+                                       ("abc,cd->abd", [(4, 300, 512), (512, 264)]),
+                                       ("bmk,bkn->bmn", [(3, 256, 128), (3, 128, 320)])])
+def test_fp32_einsum_on_tensor_cores(both, eq, shapes):
+  """float32 contractions large enough for the 3-term bf16 split path must still
+  meet the float32 tolerance (1e-5 relative) against a float64 reference."""
+  dev, ora = both
+  r = rng(9)
+  vals = [r.standard_normal(s).astype(np.float32) for s in shapes]
+  vals[1] = (vals[1] / np.sqrt(shapes[1][-2])).astype(np.float32)
+  got = dev.to_host(dev.einsum(eq, *[dev.from_host(v, mtf.float32) for v in vals]))
+  ref = np.einsum(eq, *[v.astype(np.float64) for v in vals])
+  assert rel_err(got, ref) < 1e-5
+  from mesh_b200 import _native as nat
+  nat.device_status()
