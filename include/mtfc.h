@@ -187,6 +187,26 @@ int mtfc_one_hot(const int32_t* indices, int64_t n, int32_t depth, float on_valu
 
 int mtfc_fill(void* out, int dtype, int64_t n, float value, float step, void* stream);
 
+/* ---- K6: fused attention -------------------------------------------------- */
+/*
+ * out = softmax(scale * q.k^T + causal bias) . v for bf16 q, k, v, fp32 softmax,
+ * weights rounded to bf16 before the second product; the logits are never
+ * written to memory.  Replaces the einsum / add-mask / softmax / cast / einsum
+ * chain of dot_product_attention (layers.py:1640-1652, transformer/attention.py:
+ * 71-88).  `causal` applies the autoregressive bias of layers.py:1839-1850
+ * (keys right of the query get weight exactly 0).  Tensors are logical
+ * [batch, heads, length, d]; *_strides give the element strides of those four
+ * axes in that order, so [b,h,l,d] and [b,l,h,d] storage are both read in place.
+ * d must be 64 or 128 with stride 1; other strides multiples of 8.
+ * mtfc_attention_supported returns 1 when a problem meets these conditions. */
+int mtfc_attention_supported(int64_t d, const int64_t* q_strides, const int64_t* k_strides,
+                             const int64_t* v_strides, const int64_t* o_strides);
+
+int mtfc_attention_fwd(const void* q, const void* k, const void* v, void* out, int64_t batch,
+                       int64_t heads, int64_t lq, int64_t lk, int64_t d, const int64_t* q_strides,
+                       const int64_t* k_strides, const int64_t* v_strides,
+                       const int64_t* o_strides, int32_t causal, float scale, void* stream);
+
 /* ---- K7: strided copy ---------------------------------------------------- */
 /*
  * dst[sum_d i_d * dst_strides[d]] = src[sum_d i_d * src_strides[d]] over `shape`.

@@ -71,6 +71,9 @@ def _declare(lib):
       "mtfc_gemm": [ctypes.POINTER(GemmDesc), vp, vp, vp, vp],
       "mtfc_gemm_uses_tensor_cores": [ctypes.POINTER(GemmDesc), vp, vp, vp],
       "mtfc_split_bf16x3": [vp, i64, i64, i64, vp, i64, i64, i64, i32, vp],
+      "mtfc_attention_supported": [i64, p_i64, p_i64, p_i64, p_i64],
+      "mtfc_attention_fwd": [vp, vp, vp, vp, i64, i64, i64, i64, i64, p_i64, p_i64, p_i64, p_i64,
+                             i32, f32, vp],
       "mtfc_unary": [i32, vp, i32, vp, i32, i64, vp],
       "mtfc_binary": [i32, vp, p_i64, vp, p_i64, ctypes.c_double, vp, i32, i32, i32, p_i64, vp],
       "mtfc_broadcast_reduce": [i32, i32, ctypes.POINTER(vp), i32, vp, i32, i32, p_i64, pp_i64,

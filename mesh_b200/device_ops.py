@@ -492,6 +492,59 @@ class DeviceOps(object):
                ctypes.c_void_p(b.ptr), ctypes.c_void_p(out.ptr), self._stream())
     return out
 
+  # ---------------------------------------------------------------- attention
+  def attention(self, q, k, v, causal):
+    """softmax(q.k^T [+ causal bias]).v over [..., heads, length, d] slices.
+
+    bf16 inputs with head size 64 or 128 run on the fused flash-style kernel
+    (logits stay in TMEM); anything else is composed from the einsum / softmax
+    kernels with the same arithmetic as the op-by-op lowering.
+    """
+    lead = q.shape[:-3]
+    h, lq, d = q.shape[-3:]
+    lk = k.shape[-2]
+
+    def as_bhld(x):
+      """View as [batch, h, l, d] with one batch stride (packing if necessary)."""
+      nb = _volume(lead)
+      dims = [i for i, s_ in enumerate(lead) if s_ != 1]
+      ok = all(x.strides[a] == x.strides[b] * x.shape[b] for a, b in zip(dims[:-1], dims[1:]))
+      if not ok:
+        x = self.contiguous(x)
+      bstride = x.strides[dims[-1]] if dims else 0
+      return DeviceArray(x.buf, (nb,) + tuple(x.shape[-3:]), x.dtype,
+                         strides=(bstride,) + tuple(x.strides[-3:]), offset=x.offset)
+    if q.dtype.name == "bfloat16":
+      qv, kv, vv = as_bhld(q), as_bhld(k), as_bhld(v)
+      out = self._empty(tuple(lead) + (h, lq, v.shape[-1]), q.dtype)
+      ov = as_bhld(out)
+      strides = [_i64(t.strides) for t in (qv, kv, vv, ov)]
+      if v.shape[-1] == d and self._lib.mtfc_attention_supported(d, *strides) == 1 and all(
+          t.ptr % 16 == 0 for t in (qv, kv, vv, ov)):
+        self._call(self._lib.mtfc_attention_fwd, ctypes.c_void_p(qv.ptr), ctypes.c_void_p(kv.ptr),
+                   ctypes.c_void_p(vv.ptr), ctypes.c_void_p(ov.ptr), qv.shape[0], h, lq, lk, d,
+                   *strides, 1 if causal else 0, ctypes.c_float(1.0), self._stream())
+        return out
+    return self._attention_unfused(q, k, v, causal)
+
+  def _attention_unfused(self, q, k, v, causal):
+    lq, lk = q.shape[-2], k.shape[-2]
+    nd = len(q.shape)
+    letters = "abcdefgh"[:nd - 2]
+    qf, kf = self.cast(q, G.float32), self.cast(k, G.float32)
+    logits = self.einsum("%sxd,%syd->%sxy" % (letters, letters, letters), qf, kf)
+    if causal:
+      qpos = self.reshape(self.range(lq, G.float32), [lq, 1])
+      kpos = self.reshape(self.range(lk, G.float32), [1, lk])
+      bias = self.binary("multiply", self.cast(self.binary("less", qpos, kpos), G.float32), -1e9)
+      logits = self.binary("add", logits, bias)
+    mx = self.expand_dims(self.reduce("MAX", logits, [nd - 1]), nd - 1)
+    shifted = self.binary("sub", logits, mx)
+    lse = self.binary("add", self.unary("log", self.expand_dims(
+        self.reduce("SUM", self.unary("exp", shifted), [nd - 1]), nd - 1)), mx)
+    w = self.cast(self.unary("exp", self.binary("sub", logits, lse)), v.dtype)
+    return self.einsum("%sxy,%sye->%sxe" % (letters, letters, letters), w, v)
+
   # ---------------------------------------------------------------- fused MoE
   def moe_gate_logits(self, x, w):
     """[tokens, parts*experts] fp32 gate logits and `parts`.

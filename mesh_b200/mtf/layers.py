@@ -126,9 +126,45 @@ def rename_length_to_memory_length(x, length_name="length", memory_length_name="
 
 
 def attention_mask_autoregressive(query_pos, dtype=G.float32):
-  """-1e9 where a query would look right of itself (mesh_tensorflow/layers.py:1839-1850)."""
+  """-1e9 where a query would look right of itself (mesh_tensorflow/layers.py:1839-1850).
+
+  When `query_pos` is the plain range over the length dim the returned tensor is
+  tagged as the causal mask, which lets dot_product_attention use the fused
+  kernel's built-in masking instead of adding this tensor to the logits.
+  """
   memory_pos = rename_length_to_memory_length(query_pos)
-  return mtf.cast(mtf.less(query_pos, memory_pos), dtype) * -1e9
+  mask = mtf.cast(mtf.less(query_pos, memory_pos), dtype) * -1e9
+  if getattr(query_pos.operation, "is_plain_range", False):
+    mask.causal_hint = True
+  return mask
+
+
+class FusedAttentionOperation(mtf.Operation):
+  """softmax(q.k + causal bias).v as one operation per slice.
+
+  q [..., length_q, d_k], k [..., length_kv, d_k], v [..., length_kv, d_v] with the
+  same leading dims (typically batch, heads).  Leading dims may be split over
+  the mesh freely; the two length dims and the depth dims must not be, because
+  the softmax statistics are slice-local.
+  """
+
+  def __init__(self, q, k, v, causal, name=None):
+    super().__init__([q, k, v], name=name or "fused_attention")
+    self._causal = causal
+    self._outputs = [mtf.Tensor(self, Shape(q.shape.dims[:-1] + [v.shape.dims[-1]]), v.dtype)]
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    q, k, v = self.inputs
+    for d in (q.shape.dims[-2], q.shape.dims[-1], k.shape.dims[-2], v.shape.dims[-1]):
+      if impl.tensor_dimension_to_mesh_axis(d) is not None:
+        raise ValueError("fused attention needs %s unsplit; pass fused=False to "
+                         "dot_product_attention for this layout" % (d,))
+    ops, causal = impl.slice_ops, self._causal
+    lowering.set_tensor_lowering(
+        self.outputs[0],
+        impl.slicewise(lambda a, b, c: ops.attention(a, b, c, causal),
+                       *[lowering.tensors[t] for t in self.inputs]))
 
 
 def multihead_attention_params(mesh, heads, io_channels, kv_channels, weights, dtype):
@@ -143,15 +179,25 @@ def multihead_attention_params(mesh, heads, io_channels, kv_channels, weights, d
 
 
 def dot_product_attention(q, k, v, mask, is_training=False, dropout=0.0, extra_logit=None,
-                          float32_logits=True):
+                          float32_logits=True, fused=None):
   """softmax(q.k + mask).v (mesh_tensorflow/layers.py:1614-1652).
 
   With float32_logits the logits and softmax are computed in float32 and the
   weights cast back to v.dtype, as transformer/attention.py:71-88 does.
+  `fused` selects the single-operation form (FusedAttentionOperation); the
+  default fuses bfloat16 attention whose mask is absent or the causal mask.
   """
   del is_training
   if dropout != 0.0:
     raise NotImplementedError("dropout is outside the lowered forward path")
+  fusable = (extra_logit is None and float32_logits
+             and (mask is None or getattr(mask, "causal_hint", False)))
+  if fused is None:
+    fused = fusable and q.dtype == G.bfloat16
+  if fused:
+    if not fusable:
+      raise ValueError("fused attention supports no mask or the causal mask only")
+    return FusedAttentionOperation(q, k, v, causal=mask is not None).outputs[0]
   length_kv = k.shape.dims[-2]
   logits_shape = Shape(q.shape.dims[:-1] + [length_kv])
   if float32_logits:
@@ -167,7 +213,7 @@ def dot_product_attention(q, k, v, mask, is_training=False, dropout=0.0, extra_l
 
 def multihead_attention(query_antecedent, memory_antecedent, mask, kv_channels, heads,
                         is_training=False, dropout=0.0, weights=None, params=None,
-                        float32_logits=True, name="multihead_attention"):
+                        float32_logits=True, fused=None, name="multihead_attention"):
   """Projections, attention and output projection (mesh_tensorflow/layers.py:1655-1723).
 
   The output projection contracts (heads, kv_channels); with `heads` split
@@ -191,5 +237,6 @@ def multihead_attention(query_antecedent, memory_antecedent, mask, kv_channels, 
   q = mtf.einsum([query_antecedent, wq], Shape(batch_dims + [heads, query_length, kv_channels]))
   k = mtf.einsum([memory_antecedent, wk], Shape(batch_dims + [heads, memory_length, kv_channels]))
   v = mtf.einsum([memory_antecedent, wv], Shape(batch_dims + [heads, memory_length, kv_channels]))
-  o = dot_product_attention(q, k, v, mask, is_training, dropout, float32_logits=float32_logits)
+  o = dot_product_attention(q, k, v, mask, is_training, dropout, float32_logits=float32_logits,
+                            fused=fused)
   return mtf.einsum([o, wo], Shape(batch_dims + [query_length, io_channels]))

@@ -120,8 +120,10 @@ def mtf_range(mesh, dim, dtype, name=None):
   """[0, dim.size) along `dim`, imported like any host tensor (ops.py:5544-5584)."""
   dim = convert_to_dimension(dim)
   np_dtype = np.int32 if dtype.is_integer else np.float32
-  return ImportOperation(mesh, np.arange(dim.size, dtype=np_dtype), Shape([dim]), dtype,
-                         name=name or "range").outputs[0]
+  op = ImportOperation(mesh, np.arange(dim.size, dtype=np_dtype), Shape([dim]), dtype,
+                       name=name or "range")
+  op.is_plain_range = True
+  return op.outputs[0]
 
 
 # ------------------------------------------------------------------ slicewise

@@ -253,6 +253,21 @@ class NumpyOps(object):
   def einsum_naive(self, equation, *xs):
     return self.einsum(equation, *xs)
 
+  # ---- fused attention entry point: the op chain of layers.py:1640-1652 with
+  # float32 logits and softmax (transformer/attention.py:71-88), in one call
+  def attention(self, q, k, v, causal):
+    qf, kf = q.a.astype(np.float64), k.a.astype(np.float64)
+    logits = np.einsum("...xd,...yd->...xy", qf, kf).astype(np.float32)
+    if causal:
+      lq, lk = logits.shape[-2:]
+      logits = logits + np.where(np.arange(lq)[:, None] < np.arange(lk)[None, :],
+                                 np.float32(-1e9), np.float32(0))
+    mx = logits.max(axis=-1, keepdims=True)
+    lse = np.log(np.sum(np.exp(logits - mx), axis=-1, keepdims=True)) + mx
+    w = _finish(np.exp(logits - lse), v.dtype).a
+    out = np.einsum("...xy,...ye->...xe", w.astype(np.float64), v.a.astype(np.float64))
+    return _finish(out.astype(np.float32), v.dtype)
+
   # ---- fused MoE entry points: the scalar specification
   def moe_top2_gating(self, x, w, capacity, policy, threshold, noise, num_groups_total):
     from oracle import moe_spec
