@@ -361,7 +361,7 @@ def run_ours(args):
                      "frac_of_burst_peak": achieved / peaks["tflops_burst"],
                      "peak_source": "%s bf16 GEMM, sustained (kernel timed inside the step loop)"
                                     % peaks["source"],
-                     "kernel": "einsum_gemm_tcgen05", "launch_ms": avg_launch_ms,
+                     "kernel": "einsum_gemm_tcgen05_2cta", "launch_ms": avg_launch_ms,
                      "flops_per_launch": flops_per_launch, "traffic": GEMM_DRAM_TRAFFIC_BYTES},
         "cpu_baseline": cpu,
         "clocks": clocks,

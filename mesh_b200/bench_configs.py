@@ -176,28 +176,54 @@ def config_einsum_fp32(args):
 
 
 def config_attention(args):
-  """Multi-head attention, unfused lowering (einsum + softmax ops); reduced batch."""
+  """Multi-head attention: x[batch,2048,4096] bf16, 32 heads of 128, causal;
+  q/k/v projections, fused attention kernel, output projection; one GPU,
+  inputs and weights resident, the lowering replayed as a CUDA graph."""
+  peaks = _peaks()
   torch.cuda.set_device(0)
   impl = CudaMeshImpl("all:1", "", [0])
+  ops = impl.slice_ops
   b, l, d, h, kv = args.attention_batch, 2048, 4096, 32, 128
   r = np.random.Generator(np.random.PCG64(1237))
+  x = torch.from_numpy(r.standard_normal((b, l, d), dtype=np.float32)).to(torch.bfloat16)
+  lx = impl.LaidOutTensor([ops.from_host(x, mtf.bfloat16)])
+  stds = [d ** -0.5 * kv ** -0.25] * 2 + [d ** -0.5, (d * h) ** -0.5]
+  lws = [impl.LaidOutTensor([ops.from_host(torch.from_numpy(
+      r.standard_normal((h, d, kv), dtype=np.float32) * np.float32(sd)).to(torch.bfloat16), mtf.bfloat16)])
+         for sd in stds]
   g = mtf.Graph()
   mesh = mtf.Mesh(g, "mesh")
-  x = torch.from_numpy(r.standard_normal((b, l, d), dtype=np.float32)).to(torch.bfloat16)
-  X = mtf.import_tf_tensor(mesh, x, "batch:%d,length:%d,d_model:%d" % (b, l, d), dtype=mtf.bfloat16)
+  X = mtf.import_laid_out_tensor(mesh, lx, "batch:%d,length:%d,d_model:%d" % (b, l, d), mtf.bfloat16)
   heads, kvd = mtf.Dimension("heads", h), mtf.Dimension("d_kv", kv)
-  params = mtf.layers.multihead_attention_params(mesh, heads, X.shape.dims[-1], kvd,
-                                                 mtf.layers.WeightSource(7), mtf.bfloat16)
+  params = [mtf.import_laid_out_tensor(mesh, w, "heads:%d,d_model:%d,d_kv:%d" % (h, d, kv), mtf.bfloat16)
+            for w in lws]
   pos = mtf.mtf_range(mesh, X.shape.dims[1], mtf.float32)
   mask = mtf.layers.attention_mask_autoregressive(pos)
   y = mtf.layers.multihead_attention(X, None, mask, kvd, heads, params=params)
 
   def step():
     return mtf.Lowering(g, {mesh: impl}).tensors[y].to_laid_out_tensor()
-  ms = _time(step, iters=3, warmup=1)
-  flops = 4 * 2.0 * b * l * d * d + 2 * 2.0 * b * h * l * l * kv
-  _emit(config="attention", quantity="unfused multihead_attention", batch=b, ms=ms,
-        tflops=flops / (ms * 1e-3) / 1e12)
+  before = nat.launch_count()
+  step()
+  launches = nat.launch_count() - before
+  _, run = impl.capture(step)
+  ms = _time(run, iters=args.iters, warmup=3)
+  proj = 4 * 2.0 * b * l * d * h * kv
+  attn_full = 2 * 2.0 * b * h * l * l * kv
+  _emit(config="attention", quantity="multihead_attention layer (fused kernel)", batch=b, ms=ms,
+        tflops_full=(proj + attn_full) / (ms * 1e-3) / 1e12,
+        tflops_causal_work=(proj + attn_full / 2 * (1 + 128.0 / l)) / (ms * 1e-3) / 1e12,
+        libmtfc_launches_per_step=launches, peak_tflops=peaks["tflops"], peak_source=peaks["source"])
+  # the fused kernel alone on q, k, v [batch, heads, length, d_kv]
+  q, k, v = [ops.from_host(torch.from_numpy(
+      r.standard_normal((b, h, l, kv), dtype=np.float32) * np.float32(0.3)).to(torch.bfloat16), mtf.bfloat16)
+             for _ in range(3)]
+  for causal in (True, False):
+    t = _time(lambda: ops.attention(q, k, v, causal), iters=args.iters, warmup=3)
+    work = attn_full * ((0.5 * (1 + 128.0 / l)) if causal else 1.0)
+    _emit(config="attention", quantity="attn_fwd_tcgen05 alone", causal=causal, batch=b, ms=t,
+          tflops_executed=work / (t * 1e-3) / 1e12,
+          frac_of_peak=work / (t * 1e-3) / 1e12 / peaks["tflops"])
 
 
 def config_collectives(args):

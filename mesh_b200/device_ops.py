@@ -427,58 +427,70 @@ class DeviceOps(object):
     k_dims = [l for l in ta if l in tb and l not in out_term]
     if not k_dims or not a.dtype.is_floating:
       return self.einsum_naive(ta + "," + tb + "->" + out_term, a, b)
-    out_shape = [sizes[l] for l in out_term]
-    out = self._empty(out_shape, out_dtype)
-    out_strides = dict(zip(out_term, out.strides))
     sa, sb = dict(zip(ta, a.strides)), dict(zip(tb, b.strides))
 
     def collapse(dims, strides):
-      """(extent, stride) of the dims taken as one axis, or None."""
+      """(extent, stride) of the dims taken as one axis, or None; a dim the
+      tensor lacks has stride 0."""
       dims = [d for d in dims if sizes[d] != 1]
       if not dims:
         return 1, 0
       for hi, lo in zip(dims[:-1], dims[1:]):
-        if strides[hi] != strides[lo] * sizes[lo]:
+        if strides.get(hi, 0) != strides.get(lo, 0) * sizes[lo]:
           return None
-      return _volume([sizes[d] for d in dims]), strides[dims[-1]]
+      return _volume([sizes[d] for d in dims]), strides.get(dims[-1], 0)
 
-    plan = [collapse(batch, sa), collapse(batch, sb), collapse(batch, out_strides),
-            collapse(m_dims, sa), collapse(m_dims, out_strides),
-            collapse(n_dims, sb), collapse(n_dims, out_strides),
-            collapse(k_dims, sa), collapse(k_dims, sb)]
-    if any(p is None for p in plan):
-      # pack to [batch, M, K] x [batch, K, N] -> [batch, M, N], then unpack
+    def plan_for(bt, md, nd):
+      p = [collapse(bt, sa), collapse(bt, sb), collapse(md, sa), collapse(nd, sb),
+           collapse(k_dims, sa), collapse(k_dims, sb)]
+      return None if any(x is None for x in p) else p
+
+    # The output is stored as [batch, M, N] and handed back as a view in the
+    # requested dim order, so only the operands' layouts constrain the plan.
+    plan = plan_for(batch, m_dims, n_dims)
+    if plan is None and not batch:
+      # a leading free dim that breaks the collapse (weights [heads, io, kv]) can
+      # serve as the batch axis: the other operand is simply reused for each
+      for cand in ((n_dims[:1], m_dims, n_dims[1:]), (m_dims[:1], m_dims[1:], n_dims)):
+        if cand[0] and plan_for(*cand) is not None:
+          batch, m_dims, n_dims = cand
+          plan = plan_for(batch, m_dims, n_dims)
+          break
+    store = batch + m_dims + n_dims
+    view_perm = [store.index(l) for l in out_term]
+    if plan is None:
+      # pack to [batch, M, K] x [batch, K, N] first
       pa = self.contiguous(self.transpose(a, [ta.index(l) for l in batch + m_dims + k_dims]))
       pb = self.contiguous(self.transpose(b, [tb.index(l) for l in batch + k_dims + n_dims]))
-      packed_term = "".join(batch + m_dims + n_dims)
       res = self.einsum("".join(batch + m_dims + k_dims) + "," + "".join(batch + k_dims + n_dims)
-                        + "->" + packed_term, pa, pb, epilogue=epilogue, out_dtype=out_dtype)
-      if packed_term == out_term:
-        return res
-      self._copy(self.transpose(res, [packed_term.index(l) for l in out_term]), out)
-      return out
-    (nb, a_b), (_, b_b), (_, c_b), (m, a_m), (_, c_m), (n, b_n), (_, c_n), (k, a_k), (_, b_k) = plan
+                        + "->" + "".join(store), pa, pb, epilogue=epilogue, out_dtype=out_dtype)
+      return self.transpose(res, view_perm)
+    (nb, a_b), (_, b_b), (m, a_m), (n, b_n), (k, a_k), (_, b_k) = plan
+    out = self._empty([sizes[l] for l in store], out_dtype)
+    c_b, c_m, c_n = m * n, n, 1
+    result = out if view_perm == list(range(len(store))) else self.transpose(out, view_perm)
     if (a.dtype.name == "float32" and out_dtype.name == "float32" and k % 4 == 0
-        and k <= self.FP32_TENSOR_CORE_MAX_K and c_n == 1
+        and k <= self.FP32_TENSOR_CORE_MAX_K
         and nb * m * n * k >= self.FP32_TENSOR_CORE_MIN_WORK):
       # fp32 on the tensor cores: split both operands into three bf16 terms along
       # K and run one bf16 GEMM over 6K with fp32 accumulation
-      a3 = self._empty([nb, m, 6 * k], G.bfloat16)
-      b3 = self._empty([nb if b_b else 1, n, 6 * k], G.bfloat16)
+      na, nbb = (nb if a_b else 1), (nb if b_b else 1)
+      a3 = self._empty([na, m, 6 * k], G.bfloat16)
+      b3 = self._empty([nbb, n, 6 * k], G.bfloat16)
       self._call(self._lib.mtfc_split_bf16x3, ctypes.c_void_p(a.ptr), a_b, a_m, a_k,
-                 ctypes.c_void_p(a3.ptr), nb, m, k, 0, self._stream())
+                 ctypes.c_void_p(a3.ptr), na, m, k, 0, self._stream())
       self._call(self._lib.mtfc_split_bf16x3, ctypes.c_void_p(b.ptr), b_b, b_n, b_k,
-                 ctypes.c_void_p(b3.ptr), nb if b_b else 1, n, k, 1, self._stream())
+                 ctypes.c_void_p(b3.ptr), nbb, n, k, 1, self._stream())
       d = nat.GemmDesc()
       d.batch, d.m, d.n, d.k = nb, m, n, 6 * k
-      d.a_batch, d.a_m, d.a_k = m * 6 * k, 6 * k, 1
+      d.a_batch, d.a_m, d.a_k = (m * 6 * k if a_b else 0), 6 * k, 1
       d.b_batch, d.b_k, d.b_n = (n * 6 * k if b_b else 0), 1, 6 * k
       d.c_batch, d.c_m, d.c_n = c_b, c_m, c_n
       d.in_dtype, d.out_dtype = nat.BF16, nat.F32
       d.epilogue, d.force_path = epilogue, 0
       self._call(self._lib.mtfc_gemm, ctypes.byref(d), ctypes.c_void_p(a3.ptr),
                  ctypes.c_void_p(b3.ptr), ctypes.c_void_p(out.ptr), self._stream())
-      return out
+      return result
     d = nat.GemmDesc()
     d.batch, d.m, d.n, d.k = nb, m, n, k
     d.a_batch, d.a_m, d.a_k = a_b, a_m, a_k
@@ -490,7 +502,7 @@ class DeviceOps(object):
     d.force_path = 0
     self._call(self._lib.mtfc_gemm, ctypes.byref(d), ctypes.c_void_p(a.ptr),
                ctypes.c_void_p(b.ptr), ctypes.c_void_p(out.ptr), self._stream())
-    return out
+    return result
 
   # ---------------------------------------------------------------- attention
   def attention(self, q, k, v, causal):
@@ -516,7 +528,11 @@ class DeviceOps(object):
                          strides=(bstride,) + tuple(x.strides[-3:]), offset=x.offset)
     if q.dtype.name == "bfloat16":
       qv, kv, vv = as_bhld(q), as_bhld(k), as_bhld(v)
-      out = self._empty(tuple(lead) + (h, lq, v.shape[-1]), q.dtype)
+      # stored [..., length, heads, d] so that a following output projection can
+      # contract (heads, d) as one contiguous axis; returned as a [..., heads, length, d] view
+      nl = len(lead)
+      stored = self._empty(tuple(lead) + (lq, h, v.shape[-1]), q.dtype)
+      out = self.transpose(stored, list(range(nl)) + [nl + 1, nl, nl + 2])
       ov = as_bhld(out)
       strides = [_i64(t.strides) for t in (qv, kv, vv, ov)]
       if v.shape[-1] == d and self._lib.mtfc_attention_supported(d, *strides) == 1 and all(

@@ -28,11 +28,21 @@ class ImportOperation(Operation):
     super().__init__([], mesh=mesh, name=name or "import")
     self._value = value
     self._outputs = [Tensor(self, shape, dtype)]
+    self._uploaded = {}
 
   def lower(self, lowering):
     impl = lowering.mesh_impl(self)
-    lowering.set_tensor_lowering(
-        self.outputs[0], impl.import_tf_tensor(self.outputs[0], self._value))
+    # A numpy array is a constant of the graph: it is laid out once per backend
+    # and later lowerings of the same graph reuse the slices (which also keeps
+    # host copies out of a lowering that is being recorded as a CUDA graph).
+    # Torch host tensors are live inputs and are copied on every lowering.
+    constant = isinstance(self._value, np.ndarray)
+    laid_out = self._uploaded.get(id(impl)) if constant else None
+    if laid_out is None:
+      laid_out = impl.import_tf_tensor(self.outputs[0], self._value)
+      if constant:
+        self._uploaded[id(impl)] = laid_out
+    lowering.set_tensor_lowering(self.outputs[0], laid_out)
 
 
 _NP_TO_DTYPE = {"float32": G.float32, "float64": G.float32, "int32": G.int32,

@@ -30,13 +30,14 @@ def test_attention_kernel(both, b, h, lq, lk, d, causal):
   v = r.standard_normal((b, h, lk, d)).astype(np.float32)
   dq, dk, dv = [dev.from_host(t, mtf.bfloat16) for t in (q, k, v)]
   oq, ok_, ov = [ora.from_host(t, mtf.bfloat16) for t in (q, k, v)]
-  launches = __import__("mesh_b200._native", fromlist=["x"]).launch_count()
-  got = dev.to_host(dev.attention(dq, dk, dv, causal))
-  assert __import__("mesh_b200._native", fromlist=["x"]).launch_count() - launches == 1   # fused
+  from mesh_b200 import _native as nat
+  launches = nat.launch_count()
+  out = dev.attention(dq, dk, dv, causal)
+  assert nat.launch_count() - launches == 1   # one fused kernel, nothing else
+  got = dev.to_host(out)
   ref = ora.to_host(ora.attention(oq, ok_, ov, causal))
   assert got.shape == ref.shape
   assert rel_err(got, ref) < 2e-2
-  from mesh_b200 import _native as nat
   nat.device_status()
 
 
