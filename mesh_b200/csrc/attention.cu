@@ -265,21 +265,24 @@ attn_fwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const uint32_t t_s = tmem_s0 + lane_base + (uint32_t)(st * ABN);
       const int k0 = j * ABN;
       const bool need_mask = (args.causal && k0 + ABN - 1 > q0) || (k0 + ABN > args.lk);
-      // pass 1: row maximum of the (scaled, masked) logits
+      // the whole S row into registers (four loads in flight, one wait), scaled and
+      // masked in place, and its maximum
+      uint32_t sv[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tc_ld_32x32(t_s + c * 32, sv[c]);
+      tc_wait_ld();
       float m_blk = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < ABN; c += 32) {
-        uint32_t v[32];
-        tc_ld_32x32(t_s + c, v);
-        tc_wait_ld();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]) * args.scale_log2e;
+          float sc = __uint_as_float(sv[c][i]) * args.scale_log2e;
           if (need_mask) {
-            const int kp = k0 + c + i;
-            if (kp >= args.lk || (args.causal && kp > q_pos)) s = -INFINITY;
+            const int kp = k0 + c * 32 + i;
+            if (kp >= args.lk || (args.causal && kp > q_pos)) sc = -INFINITY;
           }
-          m_blk = fmaxf(m_blk, s);
+          sv[c][i] = __float_as_uint(sc);
+          m_blk = fmaxf(m_blk, sc);
         }
       }
       const float m_new = fmaxf(m_run, m_blk);
@@ -305,25 +308,16 @@ attn_fwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           tc_wait_st();
         }
       }
-      // pass 2: p = 2^(s - m), row sum, bf16 P into the swizzled A-operand tile
+      // p = 2^(s - m), row sum, bf16 P into the swizzled A-operand tile
       float l_blk = 0.f;
       uint8_t* p_row = smem + SM::P + row * 128;
       const int sw = row & 7;
-#pragma unroll 1
-      for (int c = 0; c < ABN; c += 32) {
-        uint32_t v[32];
-        tc_ld_32x32(t_s + c, v);
-        tc_wait_ld();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
         float p[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]) * args.scale_log2e;
-          bool masked = false;
-          if (need_mask) {
-            const int kp = k0 + c + i;
-            masked = kp >= args.lk || (args.causal && kp > q_pos);
-          }
-          p[i] = masked ? 0.f : fast_exp2(s - m_use);
+          p[i] = fast_exp2(__uint_as_float(sv[c][i]) - m_use);  // masked: 2^(-inf) = 0
           l_blk += p[i];
         }
 #pragma unroll
@@ -333,7 +327,7 @@ attn_fwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           o.y = pack_bf16x2(p[8 * g + 2], p[8 * g + 3]);
           o.z = pack_bf16x2(p[8 * g + 4], p[8 * g + 5]);
           o.w = pack_bf16x2(p[8 * g + 6], p[8 * g + 7]);
-          const int chunk = (c / 8) + g;           // 16-byte chunk index along the 128 keys
+          const int chunk = c * 4 + g;             // 16-byte chunk index along the 128 keys
           const int atom = chunk >> 3, cc = chunk & 7;
           *reinterpret_cast<uint4*>(p_row + atom * ATOM_BYTES + ((cc ^ sw) << 4)) = o;
         }

@@ -76,6 +76,45 @@ class SlicedMeshImpl(mtf.MeshImpl):
     def to_laid_out_tensor(self):
       return self
 
+  class LaidOutVariable(object):
+    """Per-processor slices of a variable with copies to and from its master
+    (placement_mesh_impl.py:67-157).  The master is a host array; here the
+    copies are methods that run at once instead of graph operations.
+
+    `variable` needs `outputs[0]` (shape, dtype), `get_master()` returning the
+    host array and `assign_to_master(array)`.
+    """
+
+    def __init__(self, variable, mesh_impl):
+      self._variable = variable
+      self._mesh_impl = mesh_impl
+      self._laid_out_tensor = mesh_impl.import_tf_tensor(variable.outputs[0],
+                                                         variable.get_master())
+
+    @property
+    def laid_out_tensor(self):
+      return self._laid_out_tensor
+
+    def assign_to_slices(self, assign_fn, values):
+      """Replaces every local slice by assign_fn(variable, old_slice, value)."""
+      impl = self._mesh_impl
+      new = []
+      for pnum, old, value in zip(impl.local_pnums, self._laid_out_tensor.all_slices, values):
+        impl._ops_for(pnum)
+        new.append(assign_fn(self._variable, old, value))
+      self._laid_out_tensor = impl.LaidOutTensor(new)
+      return self._laid_out_tensor
+
+    def copy_master_to_slices(self):
+      tensor = self._variable.outputs[0]
+      fresh = self._mesh_impl.import_tf_tensor(tensor, self._variable.get_master())
+      return self.assign_to_slices(lambda var, old, value: value, fresh.all_slices)
+
+    def copy_slices_to_master(self):
+      tensor = self._variable.outputs[0]
+      self._variable.assign_to_master(
+          self._mesh_impl.export_to_tf_tensor(tensor, self._laid_out_tensor))
+
   # ------------------------------------------------------------ basics
   @property
   def local_pnums(self):

@@ -94,6 +94,46 @@ def import_laid_out_tensor(mesh, laid_out_tensor, shape, dtype, name=None):
       mesh, laid_out_tensor, convert_to_shape(shape), dtype, name=name).outputs[0]
 
 
+class Variable(Operation):
+  """A tensor with a host-resident master copy (mesh_tensorflow/ops.py:3961-4070,
+  reduced to what a forward lowering needs): lowering lays the master out
+  through `mesh_impl.LaidOutVariable` and records it in `lowering.variables`,
+  so slices can be copied back to the master after the lowering."""
+
+  def __init__(self, mesh, name, shape, dtype, initial_value):
+    super().__init__([], mesh=mesh, name=name)
+    shape = convert_to_shape(shape)
+    value = np.asarray(initial_value)
+    if list(value.shape) != shape.to_integer_list:
+      raise ValueError("initial value %s does not match %s" % (value.shape, shape))
+    self._master = value
+    self._outputs = [Tensor(self, shape, dtype)]
+
+  def get_master(self):
+    return self._master
+
+  def assign_to_master(self, value):
+    self._master = np.asarray(value)
+
+  @property
+  def value(self):
+    return self.outputs[0]
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    laid_out_variable = impl.LaidOutVariable(self, impl)
+    lowering.variables[self] = laid_out_variable
+    lowering.set_tensor_lowering(self.outputs[0], laid_out_variable.laid_out_tensor)
+
+
+def get_variable(mesh, name, shape, dtype=G.float32, initial_value=None):
+  """Creates a Variable and returns its tensor; `.operation` is the Variable."""
+  shape = convert_to_shape(shape)
+  if initial_value is None:
+    initial_value = np.zeros(shape.to_integer_list, dtype=np.float32)
+  return Variable(mesh, name, shape, dtype, initial_value).outputs[0]
+
+
 def constant(mesh, value, shape=None, dtype=G.float32):
   """A tensor filled with `value` (mesh_tensorflow/ops.py:4337-4378)."""
   shape = convert_to_shape(shape) if shape is not None else Shape([])

@@ -58,6 +58,34 @@ class NumpyMeshImpl(mtf.MeshImpl):
     def to_laid_out_tensor(self):
       return self
 
+  class LaidOutVariable(object):
+    """Slices of a variable and the copies to / from its host master
+    (placement_mesh_impl.py:67-157)."""
+
+    def __init__(self, variable, mesh_impl):
+      self._variable, self._mesh_impl = variable, mesh_impl
+      self._laid_out_tensor = mesh_impl.import_tf_tensor(variable.outputs[0],
+                                                         variable.get_master())
+
+    @property
+    def laid_out_tensor(self):
+      return self._laid_out_tensor
+
+    def assign_to_slices(self, assign_fn, values):
+      self._laid_out_tensor = self._mesh_impl.LaidOutTensor(
+          [assign_fn(self._variable, old, v)
+           for old, v in zip(self._laid_out_tensor.all_slices, values)])
+      return self._laid_out_tensor
+
+    def copy_master_to_slices(self):
+      fresh = self._mesh_impl.import_tf_tensor(self._variable.outputs[0],
+                                               self._variable.get_master())
+      return self.assign_to_slices(lambda var, old, value: value, fresh.all_slices)
+
+    def copy_slices_to_master(self):
+      self._variable.assign_to_master(self._mesh_impl.export_to_tf_tensor(
+          self._variable.outputs[0], self._laid_out_tensor))
+
   @property
   def slice_ops(self):
     return self._ops

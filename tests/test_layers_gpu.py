@@ -132,3 +132,22 @@ def test_reshape_collectives_and_shift(cuda_device):
   for a, b in zip(got, ref):
     np.testing.assert_array_equal(a, b)
   assert cg == cr
+
+
+def test_variable_on_device(cuda_device):
+  cuda, _ = _impls("rows:2,cols:2", "a:rows;b:cols")
+  w0 = rng(36).standard_normal((8, 6)).astype(np.float32)
+  g = mtf.Graph()
+  mesh = mtf.Mesh(g, "m")
+  w = mtf.get_variable(mesh, "w", "a:8,b:6", initial_value=w0)
+  y = w * 2.0
+  low = mtf.Lowering(g, {mesh: cuda})
+  np.testing.assert_array_equal(low.export_to_tf_tensor(y), w0 * 2)
+  lov = low.variables[w.operation]
+  ops = cuda.slice_ops
+  lov.assign_to_slices(lambda var, old, value: ops.binary("add", old, value), [1.0] * 4)
+  lov.copy_slices_to_master()
+  np.testing.assert_array_equal(w.operation.get_master(), w0 + 1)
+  w.operation.assign_to_master(w0 * 3)
+  lov.copy_master_to_slices()
+  np.testing.assert_array_equal(cuda.export_to_tf_tensor(w, lov.laid_out_tensor), w0 * 3)

@@ -245,3 +245,24 @@ def test_attention_causal_mask():
   p /= p.sum(-1, keepdims=True)
   ref = np.einsum("bhlk,hdk->bld", np.einsum("bhlm,bhmk->bhlk", p, v), wo)
   assert rel_err(y, ref) < 1e-5
+
+
+def test_variable_master_and_slices_round_trip():
+  w0 = rng(10).standard_normal((8, 6)).astype(np.float32)
+  g = mtf.Graph()
+  mesh = mtf.Mesh(g, "my_mesh")
+  w = mtf.get_variable(mesh, "w", "a:8,b:6", initial_value=w0)
+  y = w * 2.0
+  impl = NumpyMeshImpl("rows:2,cols:2", "a:rows;b:cols")
+  low = mtf.Lowering(g, {mesh: impl})
+  np.testing.assert_array_equal(low.export_to_tf_tensor(y), w0 * 2)
+  lov = low.variables[w.operation]
+  assert lov.laid_out_tensor.slice_shape == [4, 3]
+  ops = impl.slice_ops
+  lov.assign_to_slices(lambda var, old, value: ops.binary("add", old, value),
+                       [ops.fill([4, 3], 1.0, mtf.float32)] * 4)
+  lov.copy_slices_to_master()
+  np.testing.assert_array_equal(w.operation.get_master(), w0 + 1)
+  w.operation.assign_to_master(w0 * 3)
+  lov.copy_master_to_slices()
+  np.testing.assert_array_equal(impl.export_to_tf_tensor(w, lov.laid_out_tensor), w0 * 3)
