@@ -166,7 +166,13 @@ def run_ours(args):
   if n > 1:
     dist.init_process_group("nccl", device_id=device)
 
-  mesh_shape = MESHES[n]
+  mesh_shape = args.mesh or MESHES[n]
+  stall = args.stall_dump_s if args.stall_dump_s > 0 else (600 if n > 1 else 0)
+  if stall > 0:
+    # a rank that stops making progress dumps its Python stacks and exits, which
+    # makes the launcher end the other ranks too
+    import faulthandler
+    faulthandler.dump_traceback_later(stall, exit=True)
   impl = CudaMeshImpl(mesh_shape, LAYOUT, devices=list(range(n)) if n > 1 else [local_rank],
                       distributed=(n > 1))
   rows = impl.shape.dims[0].size
@@ -368,7 +374,13 @@ def run_ours(args):
     }
     print(json.dumps(line), flush=True)
   if n > 1:
-    dist.destroy_process_group()
+    # Nothing is in flight after this barrier.  Recorded CUDA graphs that hold NCCL
+    # kernels make the process-group destructor wait forever, so the ranks leave
+    # through os._exit once their output is flushed instead of tearing NCCL down.
+    barrier()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 def main():
@@ -378,6 +390,10 @@ def main():
   ap.add_argument("--warmup", type=int, default=10)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
   ap.add_argument("--skip-cpu-baseline", action="store_true")
+  ap.add_argument("--mesh", default=None,
+                  help="override the rows x cols mesh, e.g. rows:1,cols:2 (size must equal --gpus)")
+  ap.add_argument("--stall-dump-s", type=int, default=0,
+                  help="dump all Python stacks and exit if the run takes longer than this")
   ap.add_argument("--eager", action="store_true",
                   help="lower the graph afresh every step instead of replaying a CUDA graph")
   args = ap.parse_args()

@@ -64,6 +64,18 @@ def _time(fn, iters=10, warmup=3, flush=None):
   return statistics.median(times)
 
 
+def _leave(dist_module=None):
+  """Ends a multi-rank run: barrier, flush, exit.  Recorded CUDA graphs holding
+  NCCL kernels make the process-group destructor wait forever, so the ranks
+  leave without tearing NCCL down once nothing is in flight."""
+  import torch.distributed as dist
+  dist.barrier()
+  torch.cuda.synchronize()
+  sys.stdout.flush()
+  sys.stderr.flush()
+  os._exit(0)
+
+
 def _emit(**kw):
   print(json.dumps(kw), flush=True)
 
@@ -158,8 +170,7 @@ def config_moe(args):
             gb_per_s=gbs, frac_of_hbm_peak=gbs / peaks["hbm_gbs"], peak_gbs=peaks["hbm_gbs"],
             peak_source=peaks["source"], kept_choices_per_token=kept)
   if n > 1:
-    import torch.distributed as dist
-    dist.destroy_process_group()
+    _leave(dist_module=None)
 
 
 def config_einsum_fp32(args):
@@ -254,7 +265,7 @@ def config_collectives(args):
         if rank == 0:
           _emit(config="collectives", op=name, dtype=dtype.name, n_gpus=n, slice_bytes=nbytes,
                 ms=ms, bus_gb_per_s=nbytes * factor / (ms * 1e-3) / 1e9)
-  dist.destroy_process_group()
+  _leave(dist_module=dist)
 
 
 def main():
