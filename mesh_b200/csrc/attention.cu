@@ -265,26 +265,26 @@ attn_fwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       const uint32_t t_s = tmem_s0 + lane_base + (uint32_t)(st * ABN);
       const int k0 = j * ABN;
       const bool need_mask = (args.causal && k0 + ABN - 1 > q0) || (k0 + ABN > args.lk);
-      // the whole S row into registers (four loads in flight, one wait), scaled and
-      // masked in place, and its maximum
+      // the whole S row into registers (four loads in flight, one wait), masked in
+      // place, and its maximum (four independent chains; the scale is positive,
+      // so it is applied to the maximum instead of to every logit)
       uint32_t sv[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tc_ld_32x32(t_s + c * 32, sv[c]);
       tc_wait_ld();
-      float m_blk = -INFINITY;
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float sc = __uint_as_float(sv[c][i]) * args.scale_log2e;
           if (need_mask) {
             const int kp = k0 + c * 32 + i;
-            if (kp >= args.lk || (args.causal && kp > q_pos)) sc = -INFINITY;
+            if (kp >= args.lk || (args.causal && kp > q_pos)) sv[c][i] = 0xff800000u;  // -inf
           }
-          sv[c][i] = __float_as_uint(sc);
-          m_blk = fmaxf(m_blk, sc);
+          mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sv[c][i]));
         }
       }
+      const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * args.scale_log2e;
       const float m_new = fmaxf(m_run, m_blk);
       // a fully masked row (only possible for rows past the end) keeps m = -inf
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
@@ -308,17 +308,19 @@ attn_fwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           tc_wait_st();
         }
       }
-      // p = 2^(s - m), row sum, bf16 P into the swizzled A-operand tile
-      float l_blk = 0.f;
+      // p = 2^(scale * s - m), row sum, bf16 P into the swizzled A-operand tile
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
       uint8_t* p_row = smem + SM::P + row * 128;
       const int sw = row & 7;
+      const float neg_m = -m_use;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         float p[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          p[i] = fast_exp2(__uint_as_float(sv[c][i]) - m_use);  // masked: 2^(-inf) = 0
-          l_blk += p[i];
+          // masked logits are -inf: 2^(-inf) = 0
+          p[i] = fast_exp2(fmaf(__uint_as_float(sv[c][i]), args.scale_log2e, neg_m));
+          ls[i & 3] += p[i];
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -332,6 +334,7 @@ attn_fwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           *reinterpret_cast<uint4*>(p_row + atom * ATOM_BYTES + ((cc ^ sw) << 4)) = o;
         }
       }
+      const float l_blk = (ls[0] + ls[1]) + (ls[2] + ls[3]);
       l_run = l_run * alpha + l_blk;
       m_run = m_new;
       fence_proxy_async_smem();
