@@ -202,6 +202,11 @@ int mtfc_fill(void* out, int dtype, int64_t n, float value, float step, void* st
 int mtfc_attention_supported(int64_t d, const int64_t* q_strides, const int64_t* k_strides,
                              const int64_t* v_strides, const int64_t* o_strides);
 
+/* Kernel variant mtfc_attention_fwd uses: 0 = by query length (default), 1 = one
+ * 128-row query tile per CTA, 2 = two tiles per CTA with the weights kept in TMEM.
+ * Process-wide; meant for tests and tuning. */
+int mtfc_attention_set_variant(int variant);
+
 int mtfc_attention_fwd(const void* q, const void* k, const void* v, void* out, int64_t batch,
                        int64_t heads, int64_t lq, int64_t lk, int64_t d, const int64_t* q_strides,
                        const int64_t* k_strides, const int64_t* v_strides,

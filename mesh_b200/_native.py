@@ -71,6 +71,7 @@ def _declare(lib):
       "mtfc_gemm": [ctypes.POINTER(GemmDesc), vp, vp, vp, vp],
       "mtfc_gemm_uses_tensor_cores": [ctypes.POINTER(GemmDesc), vp, vp, vp],
       "mtfc_split_bf16x3": [vp, i64, i64, i64, vp, i64, i64, i64, i32, vp],
+      "mtfc_attention_set_variant": [i32],
       "mtfc_attention_supported": [i64, p_i64, p_i64, p_i64, p_i64],
       "mtfc_attention_fwd": [vp, vp, vp, vp, i64, i64, i64, i64, i64, p_i64, p_i64, p_i64, p_i64,
                              i32, f32, vp],

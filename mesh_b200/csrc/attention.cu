@@ -399,6 +399,339 @@ attn_fwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   }
 }
 
+// ------------------------------------------------------------ two-tile variant
+// Two query tiles (A, B: 2 x 128 rows of one (batch, head)) per CTA, each with
+// its own warpgroup of four softmax warps, sharing every K / V block.  The MMA
+// issuer alternates S_A, S_B, P_A.V, P_B.V so that one tile's softmax always
+// overlaps the other tile's tensor-core work, and there are two softmax warps
+// per scheduler instead of one.  P never touches shared memory: the bf16 weights
+// are stored back into TMEM over the first 64 columns of their S tile and feed
+// the second MMA as its A operand from TMEM.
+// TMEM columns: S_A/P_A [0,128)  S_B/P_B [128,256)  O_A [256,256+D)  O_B [384,384+D).
+constexpr int A2THREADS = 320;
+
+template <int D>
+struct Attn2Smem {
+  static constexpr int DA = D / 64;
+  static constexpr int Q = 0;                              // 2 tiles x DA atoms
+  static constexpr int K = Q + 2 * DA * ATOM_BYTES;        // 2 stages x DA atoms
+  static constexpr int V = K + 2 * DA * ATOM_BYTES;        // 2 stages x DA atoms
+  static constexpr int BAR = V + 2 * DA * ATOM_BYTES;
+  static constexpr int NUM_BARS = 16;
+  static constexpr int MISC = BAR + NUM_BARS * 8;
+  static constexpr int USED = MISC + 16;
+  static constexpr int ALLOC = USED + 1024;
+};
+
+__device__ __forceinline__ void tc_mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(A2THREADS, 1)
+attn_fwd_tcgen05_2tile(const __grid_constant__ CUtensorMap map_q,
+                       const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v,
+                       const __grid_constant__ CUtensorMap map_o, const AttnArgs args) {
+  using SM = Attn2Smem<D>;
+  constexpr int DA = SM::DA;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_base + SM::BAR;
+  const uint32_t q_full = bar_base;
+  auto k_full = [&](int s) { return bar_base + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bar_base + 8u * (3 + s); };
+  auto v_full = [&](int s) { return bar_base + 8u * (5 + s); };
+  auto v_empty = [&](int s) { return bar_base + 8u * (7 + s); };
+  auto s_full = [&](int t) { return bar_base + 8u * (9 + t); };    // per tile
+  auto p_full = [&](int t) { return bar_base + 8u * (11 + t); };   // per tile
+  auto pv_done = [&](int t) { return bar_base + 8u * (13 + t); };  // per tile
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + SM::MISC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::MISC + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_qb = (args.lq + 2 * ABM - 1) / (2 * ABM);
+  const int qb = num_qb - 1 - (int)blockIdx.x;  // heaviest blocks first under the causal mask
+  const int head = blockIdx.y;
+  const int bat = blockIdx.z;
+  const int q0 = qb * 2 * ABM;
+  // key blocks each tile needs (tile B sits 128 rows lower, so one more when causal)
+  int n_tile[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    int kv_len = args.lk;
+    if (args.causal) kv_len = min(kv_len, q0 + t * ABM + ABM);
+    n_tile[t] = (q0 + t * ABM < args.lq) ? (kv_len + ABN - 1) / ABN : 0;
+  }
+  const int num_kv = max(n_tile[0], n_tile[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full(s), 1);
+      mbar_init(k_empty(s), 1);
+      mbar_init(v_full(s), 1);
+      mbar_init(v_empty(s), 1);
+      mbar_init(s_full(s), 1);
+      mbar_init(p_full(s), 4);
+      mbar_init(pv_done(s), 1);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_base + SM::MISC),
+                 "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  auto tmem_s = [&](int t) { return tmem_base + (uint32_t)(t * ABN); };
+  auto tmem_o = [&](int t) { return tmem_base + (uint32_t)(2 * ABN + t * 128); };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      bool ok = true;
+      mbar_expect_tx(q_full, 2 * DA * ATOM_BYTES);
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int a = 0; a < DA; ++a)
+          tma_load_4d(smem_base + SM::Q + (t * DA + a) * ATOM_BYTES, &map_q, q_full, a * 64,
+                      q0 + t * ABM, head, bat);
+      for (int j = 0; j < num_kv && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        if (!mbar_wait(k_empty(st), ph ^ 1, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(k_full(st), DA * ATOM_BYTES);
+#pragma unroll
+        for (int a = 0; a < DA; ++a)
+          tma_load_4d(smem_base + SM::K + (st * DA + a) * ATOM_BYTES, &map_k, k_full(st), a * 64,
+                      j * ABN, head, bat);
+        if (!mbar_wait(v_empty(st), ph ^ 1, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(v_full(st), DA * ATOM_BYTES);
+#pragma unroll
+        for (int a = 0; a < DA; ++a)
+          tma_load_4d(smem_base + SM::V + (st * DA + a) * ATOM_BYTES, &map_v, v_full(st), a * 64,
+                      j * ABN, head, bat);
+      }
+      if (!ok && args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = attn_idesc(ABN, 0);
+      const uint32_t idesc_o = attn_idesc(D, 1);
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      auto issue_s = [&](int t, int j) {   // S_t(j) = Q_t . K_j^T
+        const int st = j & 1;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks / 4) * ATOM_BYTES + (ks % 4) * 32;
+          const uint64_t da = make_smem_desc(smem_base + SM::Q + t * DA * ATOM_BYTES + off, 16, 1024);
+          const uint64_t db = make_smem_desc(smem_base + SM::K + st * DA * ATOM_BYTES + off, 16, 1024);
+          tc_mma_bf16(tmem_s(t), da, db, idesc_s, ks != 0 ? 1u : 0u);
+        }
+        tc_commit(s_full(t));
+      };
+      auto issue_pv = [&](int t, int j) {  // O_t += P_t(j) . V_j, P from TMEM
+        const int st = j & 1;
+#pragma unroll
+        for (int ks = 0; ks < ABN / 16; ++ks) {
+          const uint64_t db = make_smem_desc(
+              smem_base + SM::V + st * DA * ATOM_BYTES + ks * 16 * 128, ATOM_BYTES, 1024);
+          tc_mma_bf16_ts(tmem_o(t), tmem_s(t) + (uint32_t)(ks * 8), db, idesc_o,
+                         (j | ks) != 0 ? 1u : 0u);
+        }
+        tc_commit(pv_done(t));
+      };
+      if (ok && num_kv > 0) {
+        ok = mbar_wait(k_full(0), 0, abort_flag);
+        if (ok) {
+          tc_fence_after();
+          if (n_tile[0] > 0) issue_s(0, 0);
+          if (n_tile[1] > 0) issue_s(1, 0);
+          tc_commit(k_empty(0));
+        }
+      }
+      for (int j = 0; j < num_kv && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        const bool next = j + 1 < num_kv;
+        if (!mbar_wait(v_full(st), ph, abort_flag)) { ok = false; break; }
+        if (next && !mbar_wait(k_full((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1), abort_flag)) {
+          ok = false;
+          break;
+        }
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (j < n_tile[t]) {
+            if (!mbar_wait(p_full(t), (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            issue_pv(t, j);
+            // the tensor pipe runs this thread's MMAs in order, so S_t(j+1) may
+            // overwrite the columns P_t(j) occupies as soon as P.V is queued
+            if (j + 1 < n_tile[t]) issue_s(t, j + 1);
+          }
+        }
+        if (!ok) break;
+        tc_commit(v_empty(st));
+        if (next) tc_commit(k_empty((j + 1) & 1));
+      }
+      if (!ok && args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
+    }
+  } else {
+    // ------------------------------------------------- softmax warpgroups (tile 0: warps 2-5, tile 1: 6-9)
+    const int t = (warp - 2) >> 2;
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    const int q_pos = q0 + t * ABM + row;
+    const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+    const uint32_t t_s = tmem_s(t) + lane_base;
+    const uint32_t t_o = tmem_o(t) + lane_base;
+    const int n_mine = n_tile[t];
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_mine && ok; ++j) {
+      ok = __all_sync(0xffffffffu, mbar_wait(s_full(t), (uint32_t)(j & 1), abort_flag));
+      if (!ok) break;
+      tc_fence_after();
+      const int k0 = j * ABN;
+      const bool need_mask = (args.causal && k0 + ABN - 1 > q0 + t * ABM) || (k0 + ABN > args.lk);
+      uint32_t sv[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tc_ld_32x32(t_s + c * 32, sv[c]);
+      tc_wait_ld();
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (need_mask) {
+            const int kp = k0 + c * 32 + i;
+            if (kp >= args.lk || (args.causal && kp > q_pos)) sv[c][i] = 0xff800000u;
+          }
+          mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sv[c][i]));
+        }
+      }
+      const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * args.scale_log2e;
+      const float m_new = fmaxf(m_run, m_blk);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_use);
+      const float neg_m = -m_use;
+      // bf16 weights, packed two per register, stored over the first 64 columns of
+      // this tile's S region 64 keys at a time (S itself is already in registers,
+      // and the previous P.V — which read these columns — retired before S_t(j) was
+      // written), and the row sum
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[2 * h + cc][i]), args.scale_log2e, neg_m));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[2 * h + cc][i + 1]), args.scale_log2e, neg_m));
+            ls[(i >> 1) & 3] += p0 + p1;
+            pk[cc * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
+          }
+        }
+        tc_st_32x32(t_s + h * 32, pk);
+      }
+      const float l_blk = (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      // O_t is free for rescaling once the previous P.V has retired
+      if (j > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(pv_done(t), (uint32_t)((j - 1) & 1), abort_flag));
+        if (!ok) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t v[32];
+            tc_ld_32x32(t_o + c, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tc_st_32x32(t_o + c, v);
+          }
+        }
+      }
+      tc_wait_st();
+      l_run = l_run * alpha + l_blk;
+      m_run = m_new;
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full(t));
+    }
+    if (ok && n_mine > 0)
+      ok = __all_sync(0xffffffffu, mbar_wait(pv_done(t), (uint32_t)((n_mine - 1) & 1), abort_flag));
+    if (ok && n_mine > 0) {
+      // O / l -> bf16 -> this tile's Q region (no longer read: every S MMA of the
+      // tile retired before its last P.V) -> TMA store
+      tc_fence_after();
+      const float inv_l = l_run > 0.f ? 1.0f / l_run : 0.f;
+      uint8_t* o_row = smem + SM::Q + t * DA * ATOM_BYTES + q * 32 * 128 + lane * 128;
+      const int sw = lane & 7;
+      if ((q0 + t * ABM + q * 32) < args.lq) {
+#pragma unroll 1
+        for (int a = 0; a < DA; ++a) {
+#pragma unroll 1
+          for (int h = 0; h < 2; ++h) {
+            uint32_t v[32];
+            tc_ld_32x32(t_o + a * 64 + h * 32, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(v[8 * g + 0]) * inv_l, __uint_as_float(v[8 * g + 1]) * inv_l);
+              o.y = pack_bf16x2(__uint_as_float(v[8 * g + 2]) * inv_l, __uint_as_float(v[8 * g + 3]) * inv_l);
+              o.z = pack_bf16x2(__uint_as_float(v[8 * g + 4]) * inv_l, __uint_as_float(v[8 * g + 5]) * inv_l);
+              o.w = pack_bf16x2(__uint_as_float(v[8 * g + 6]) * inv_l, __uint_as_float(v[8 * g + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(o_row + a * ATOM_BYTES + (((h * 4 + g) ^ sw) << 4)) = o;
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll 1
+          for (int a = 0; a < DA; ++a)
+            tma_store_4d(&map_o, smem_base + SM::Q + (t * DA + a) * ATOM_BYTES + q * 32 * 128,
+                         a * 64, q0 + t * ABM + q * 32, head, bat);
+          tma_store_commit();
+          tma_store_wait_all();
+        }
+      }
+    }
+    if (!ok && lane == 0 && args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512)
+                 : "memory");
+  }
+}
+
 }  // namespace
 }  // namespace mtfc
 
@@ -464,12 +797,38 @@ int attn_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap&
   return MTFC_OK;
 }
 
+template <int D>
+int attn2_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                 const CUtensorMap& mo, const AttnArgs& args, cudaStream_t stream) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  MTFC_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    MTFC_CUDA(cudaFuncSetAttribute(attn_fwd_tcgen05_2tile<D>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, Attn2Smem<D>::ALLOC));
+    attr_set[dev] = true;
+  }
+  dim3 grid((unsigned)((args.lq + 2 * ABM - 1) / (2 * ABM)), (unsigned)args.heads,
+            (unsigned)args.batch);
+  attn_fwd_tcgen05_2tile<D><<<grid, A2THREADS, Attn2Smem<D>::ALLOC, stream>>>(mq, mk, mv, mo, args);
+  MTFC_LAUNCH_CHECK("attn_fwd_tcgen05_2tile");
+  return MTFC_OK;
+}
+
+int g_attn_variant = 0;  // 0 = choose by length, 1 = one tile per CTA, 2 = two tiles per CTA
+
 }  // namespace
 }  // namespace mtfc
 
 using namespace mtfc;
 
 extern "C" {
+
+int mtfc_attention_set_variant(int variant) {
+  if (variant < 0 || variant > 2) return fail(MTFC_ERR_SHAPE, "attention variant %d unknown", variant);
+  g_attn_variant = variant;
+  return MTFC_OK;
+}
 
 int mtfc_attention_supported(int64_t d, const int64_t* q_strides, const int64_t* k_strides,
                              const int64_t* v_strides, const int64_t* o_strides) {
@@ -518,7 +877,11 @@ int mtfc_attention_fwd(const void* q, const void* k, const void* v, void* out, i
   args.scale_log2e = scale * 1.4426950408889634f;
   args.status = device_status_word();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  rc = d == 128 ? attn_launch<128>(mq, mk, mv, mo, args, s) : attn_launch<64>(mq, mk, mv, mo, args, s);
+  const bool two_tiles = g_attn_variant == 2 || (g_attn_variant == 0 && lq > ABM);
+  if (two_tiles)
+    rc = d == 128 ? attn2_launch<128>(mq, mk, mv, mo, args, s) : attn2_launch<64>(mq, mk, mv, mo, args, s);
+  else
+    rc = d == 128 ? attn_launch<128>(mq, mk, mv, mo, args, s) : attn_launch<64>(mq, mk, mv, mo, args, s);
   if (rc == MTFC_OK) count_launch(1);
   return rc;
 }

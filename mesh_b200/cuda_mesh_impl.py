@@ -383,6 +383,26 @@ class SlicedMeshImpl(mtf.MeshImpl):
     return self.LaidOutTensor([result])
 
 
+class _PendingAllreduce(object):
+  """Result of einsum_allreduce: the reduced slice once its chunked allreduces
+  are waited for (the wait is a stream dependency, not a host block)."""
+
+  def __init__(self, mesh_impl, out, works):
+    self._mesh_impl = mesh_impl
+    self._out = out
+    self._works = works
+
+  @property
+  def slice_shape(self):
+    return list(self._out.shape)
+
+  def to_laid_out_tensor(self):
+    for w in self._works:
+      w.wait()
+    self._works = []
+    return self._mesh_impl.LaidOutTensor([self._out])
+
+
 def _fresh_copy(ops, s):
   """A new buffer holding `s` (collectives return fresh tensors)."""
   return ops.concat([s], 0) if len(s.shape) else ops.binary("add", s, 0)
@@ -480,6 +500,58 @@ class CudaMeshImpl(SlicedMeshImpl):
     code = {None: nat.EPILOGUE_NONE, "relu": nat.EPILOGUE_RELU}[epilogue]
     self._ops.device = slices[0].device
     return self._ops.einsum(equation, *slices, epilogue=code)
+
+  # chunks a contraction is cut into when its allreduce is overlapped with it,
+  # and the smallest number of output rows per chunk worth a separate launch
+  OVERLAP_CHUNKS = 4
+  OVERLAP_MIN_ROWS = 2048
+
+  def einsum_allreduce(self, equation, inputs, mesh_axes):
+    """Contraction whose SUM allreduce over `mesh_axes` starts chunk by chunk.
+
+    One process per GPU only.  The output's leading dim must be a free dim of
+    the first operand and that operand's leading dim; the contraction then runs
+    as OVERLAP_CHUNKS launches over row blocks, and each block's NCCL allreduce
+    (asynchronous, on the process group's own stream) overlaps the next block's
+    GEMM.  Returns an object with to_laid_out_tensor(), or None when the plain
+    einsum-then-allreduce sequence should be used.
+    """
+    if not self._distributed:
+      return None
+    import torch.distributed as dist
+    inputs = convert_args_to_laid_out_tensors(inputs)
+    a, b = inputs[0].tensor_list[0], inputs[1].tensor_list[0]
+    lhs, out_term = equation.split("->")
+    ta, tb = lhs.split(",")
+    lead = out_term[0] if out_term else None
+    if (lead is None or ta[0] != lead or lead in tb or not a.dtype.is_floating
+        or a.shape[0] % self.OVERLAP_CHUNKS != 0):
+      return None
+    rows_per_chunk = a.shape[0] // self.OVERLAP_CHUNKS
+    other_rows = 1
+    for letter, size in zip(ta[1:], a.shape[1:]):
+      if letter in out_term:
+        other_rows *= size
+    if rows_per_chunk * other_rows < self.OVERLAP_MIN_ROWS:
+      return None
+    pnum = self._local_pnums[0]
+    ops = self._ops_for(pnum)
+    pg, _ = self._group(mesh_axes)
+    sizes = dict(zip(ta, a.shape))
+    sizes.update(zip(tb, b.shape))
+    out = ops._empty([sizes[l] for l in out_term], a.dtype)
+    flat = out.buf[out.offset:out.offset + out.size]
+    chunk_elems = out.size // self.OVERLAP_CHUNKS
+    works = []
+    for i in range(self.OVERLAP_CHUNKS):
+      a_i = ops.slice(a, [i * rows_per_chunk] + [0] * (len(a.shape) - 1),
+                      [rows_per_chunk] + list(a.shape[1:]))
+      out_i = ops.slice(out, [i * rows_per_chunk] + [0] * (len(out.shape) - 1),
+                        [rows_per_chunk] + list(out.shape[1:]))
+      ops.einsum(equation, a_i, b, out=out_i)
+      works.append(dist.all_reduce(flat[i * chunk_elems:(i + 1) * chunk_elems],
+                                   op=dist.ReduceOp.SUM, group=pg, async_op=True))
+    return _PendingAllreduce(self, out, works)
 
   def _as_torch(self, s):
     packed = self._ops.contiguous(s)

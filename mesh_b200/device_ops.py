@@ -386,15 +386,24 @@ class DeviceOps(object):
     return self._broadcast_reduce("SUM", list(xs), [sizes[l] for l in out_term], out_strides,
                                   [sizes[l] for l in red], red_strides, xs[0].dtype)
 
-  def einsum(self, equation, *xs, epilogue=nat.EPILOGUE_NONE, out_dtype=None):
+  def einsum(self, equation, *xs, epilogue=nat.EPILOGUE_NONE, out_dtype=None, out=None):
     """Contraction on the GEMM kernels; operand layouts are read in place.
 
     Dims are classed as batch (in both operands and the output), M (first
     operand and output), N (second operand and output) and K (both operands,
     not the output).  When each class collapses to one stride per tensor the
     named-dim order goes to the kernel as strides; otherwise the operands are
-    packed first and the result is unpacked.
+    packed first and the result is unpacked.  `out`, a contiguous array of the
+    result's shape, receives the result in place when given.
     """
+    if out is not None:
+      res = self._einsum_impl(equation, xs, epilogue, out_dtype, out)
+      if res is not out:
+        self._copy(res, out)
+      return out
+    return self._einsum_impl(equation, xs, epilogue, out_dtype, None)
+
+  def _einsum_impl(self, equation, xs, epilogue, out_dtype, out_buf):
     terms, out_term = self._parse(equation, len(xs))
     if len(xs) == 1:
       return self.einsum_naive(equation, *xs)
@@ -466,7 +475,11 @@ class DeviceOps(object):
                         + "->" + "".join(store), pa, pb, epilogue=epilogue, out_dtype=out_dtype)
       return self.transpose(res, view_perm)
     (nb, a_b), (_, b_b), (m, a_m), (n, b_n), (k, a_k), (_, b_k) = plan
-    out = self._empty([sizes[l] for l in store], out_dtype)
+    if (out_buf is not None and view_perm == list(range(len(store))) and out_buf.is_contiguous
+        and out_buf.dtype == out_dtype):
+      out = out_buf
+    else:
+      out = self._empty([sizes[l] for l in store], out_dtype)
     c_b, c_m, c_n = m * n, n, 1
     result = out if view_perm == list(range(len(store))) else self.transpose(out, view_perm)
     if (a.dtype.name == "float32" and out_dtype.name == "float32" and k % 4 == 0

@@ -527,6 +527,7 @@ def _einsum_helper(input_shapes, output_shape, mesh_impl, floating, activation=N
   reduced_mesh_axes = [layout[i] for i in reduce_axes if layout[i] is not None]
   equation = _einsum_equation(input_shapes, output_shape)
   fuse = activation is not None and not reduced_mesh_axes
+  uses_hook = not (full_shapes or not floating)
   if full_shapes or not floating:
     if fuse:
       fn = lambda *slices: ops.unary(activation, ops.einsum_naive(equation, *slices))
@@ -538,7 +539,7 @@ def _einsum_helper(input_shapes, output_shape, mesh_impl, floating, activation=N
     fn = lambda *slices: ops.unary(activation, mesh_impl.einsum(equation, *slices))
   else:
     fn = lambda *slices: mesh_impl.einsum(equation, *slices)
-  return fn, reduced_mesh_axes
+  return fn, reduced_mesh_axes, equation, uses_hook
 
 
 class EinsumOperation(Operation):
@@ -560,13 +561,28 @@ class EinsumOperation(Operation):
     in_dims = set(sum([x.shape.dims for x in xs], []))
     output_shape = self.outputs[0].shape
     intersection = Shape([d for d in output_shape.dims if d in in_dims])
-    fn, reduced_mesh_axes = _einsum_helper(
+    fn, reduced_mesh_axes, equation, uses_hook = _einsum_helper(
         [x.shape for x in xs], intersection, impl, xs[0].dtype.is_floating, self._activation)
-    y = impl.slicewise(fn, *[lowering.tensors[x] for x in xs])
-    if reduced_mesh_axes:
-      def add_counter_fn():
-        lowering.add_counter("allreduce/%s/einsum_op" % reduced_mesh_axes,
-                             impl.laid_out_size(intersection))
+
+    def add_counter_fn():
+      lowering.add_counter("allreduce/%s/einsum_op" % reduced_mesh_axes,
+                           impl.laid_out_size(intersection))
+    overlapped = None
+    if reduced_mesh_axes and uses_hook and len(xs) == 2 and hasattr(impl, "einsum_allreduce"):
+      # a backend may run the contraction in chunks and start each chunk's
+      # allreduce while the next chunk is still being computed; it returns None
+      # when it prefers the plain sequence
+      overlapped = impl.einsum_allreduce(
+          equation, [lowering.tensors[x] for x in xs], reduced_mesh_axes)
+    if overlapped is not None:
+      y = overlapped
+      add_counter_fn()
+      if self._activation is not None:
+        ops, act = impl.slice_ops, self._activation
+        y = impl.slicewise(lambda t: ops.unary(act, t), y)
+    else:
+      y = impl.slicewise(fn, *[lowering.tensors[x] for x in xs])
+    if reduced_mesh_axes and overlapped is None:
       y = LazyAllreduceSum(impl, y, reduced_mesh_axes, add_counter_fn=add_counter_fn)
       if self._activation is not None:
         # the activation has to see the reduced sum

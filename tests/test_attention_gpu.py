@@ -16,11 +16,20 @@ def both(cuda_device):
   return DeviceOps(cuda_device), NumpyOps()
 
 
+@pytest.fixture(params=[1, 2], ids=["one-tile", "two-tile"])
+def variant(request):
+  """Runs a test under each kernel variant (one / two query tiles per CTA)."""
+  from mesh_b200 import _native as nat
+  nat.check(nat.lib().mtfc_attention_set_variant(request.param))
+  yield request.param
+  nat.check(nat.lib().mtfc_attention_set_variant(0))
+
+
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("b,h,lq,lk,d", [(1, 1, 128, 128, 128), (2, 3, 256, 256, 128),
                                          (1, 2, 300, 300, 64), (2, 2, 512, 512, 128),
                                          (1, 2, 96, 200, 128), (1, 1, 1024, 1024, 64)])
-def test_attention_kernel(both, b, h, lq, lk, d, causal):
+def test_attention_kernel(both, variant, b, h, lq, lk, d, causal):
   dev, ora = both
   if causal and lq != lk:
     pytest.skip("causal mask is defined for self-attention lengths")
@@ -41,7 +50,7 @@ def test_attention_kernel(both, b, h, lq, lk, d, causal):
   nat.device_status()
 
 
-def test_attention_reads_blhd_storage_in_place(both):
+def test_attention_reads_blhd_storage_in_place(both, variant):
   """[batch, length, heads, d] storage viewed as [batch, heads, length, d]."""
   dev, ora = both
   r = rng(52)

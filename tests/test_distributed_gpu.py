@@ -76,6 +76,13 @@ def _worker(rank, world, port, out_dir):
     got, cg = ffn(impl)
     ref, cr = ffn(ora)
     assert rel_err(got, ref) < 2e-2 and cg == cr and "allreduce/[0]/einsum_op" in cg
+    # the same with the contraction cut in chunks whose allreduces overlap it
+    eager = CudaMeshImpl(mesh_shape, "d_ff:all", list(range(world)))
+    eager.OVERLAP_MIN_ROWS = 1
+    launches = __import__("mesh_b200._native", fromlist=["x"]).launch_count()
+    got2, cg2 = ffn(eager)
+    assert __import__("mesh_b200._native", fromlist=["x"]).launch_count() - launches >= 1 + eager.OVERLAP_CHUNKS
+    assert rel_err(got2, ref) < 2e-2 and cg2 == cr
 
     layout = "batch:all;experts:all"
 
