@@ -266,3 +266,34 @@ def test_variable_master_and_slices_round_trip():
   w.operation.assign_to_master(w0 * 3)
   lov.copy_master_to_slices()
   np.testing.assert_array_equal(impl.export_to_tf_tensor(w, lov.laid_out_tensor), w0 * 3)
+
+
+def _attention_layer(mesh_shape, layout, fused, dtype=mtf.bfloat16):
+  r = rng(11)
+  x = r.standard_normal((2, 32, 64)).astype(np.float32)
+
+  def build(mesh):
+    X = mtf.import_tf_tensor(mesh, x, "batch:2,length:32,d_model:64", dtype=dtype)
+    heads, kv = mtf.Dimension("heads", 4), mtf.Dimension("d_kv", 16)
+    params = mtf.layers.multihead_attention_params(mesh, heads, X.shape.dims[-1], kv,
+                                                   mtf.layers.WeightSource(3), dtype)
+    pos = mtf.mtf_range(mesh, X.shape.dims[1], mtf.float32)
+    mask = mtf.layers.attention_mask_autoregressive(pos)
+    assert getattr(mask, "causal_hint", False)
+    return [mtf.layers.multihead_attention(X, None, mask, kv, heads, params=params, fused=fused)]
+  (y,), low = _lower(build, mesh_shape, layout)
+  return y, low
+
+
+def test_fused_attention_operation_matches_op_chain():
+  ref, low_ref = _attention_layer("", "", fused=False)
+  for mesh_shape, layout in [("", ""), ("all:4", "heads:all"), ("all:2", "batch:all")]:
+    got, low = _attention_layer(mesh_shape, layout, fused=None)   # bfloat16 + causal mask: fuses
+    assert "output/FusedAttentionOperation" in low.counter_totals()
+    assert rel_err(got, ref) < 2e-2
+  assert "output/FusedAttentionOperation" not in low_ref.counter_totals()
+  # float32 stays on the op chain by default
+  _, low32 = _attention_layer("", "", fused=None, dtype=mtf.float32)
+  assert "output/FusedAttentionOperation" not in low32.counter_totals()
+  with pytest.raises(ValueError):
+    _attention_layer("all:2", "memory_length:all", fused=True)
