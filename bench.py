@@ -46,7 +46,7 @@ CPU_SAMPLE_BATCH = 8  # sequences of the 64 the CPU arms run per step
 # DRAM bytes per launch of einsum_gemm_tcgen05 on the wi GEMM of this workload,
 # dram__bytes_read.sum + dram__bytes_write.sum from the ncu capture summarised in
 # profiles/einsum_gemm_tcgen05_ffn.md (algorithmic bytes: 679.5 MB and 679.5 MB).
-GEMM_DRAM_TRAFFIC_BYTES = 644.4e6  # mean of the wi (624.6 MB) and wo (664.2 MB) launches
+GEMM_DRAM_TRAFFIC_BYTES = 650.1e6  # mean of the wi (625.3 MB) and wo (674.9 MB) launches
 
 
 def measured_peaks():
@@ -368,7 +368,9 @@ def run_ours(args):
                      "peak_source": "%s bf16 GEMM, sustained (kernel timed inside the step loop)"
                                     % peaks["source"],
                      "kernel": "einsum_gemm_tcgen05_2cta", "launch_ms": avg_launch_ms,
-                     "flops_per_launch": flops_per_launch, "traffic": GEMM_DRAM_TRAFFIC_BYTES},
+                     "flops_per_launch": flops_per_launch,
+                     # measured on the 1-GPU launch; a rank's launch at N GPUs moves 1/N of it
+                     "traffic": GEMM_DRAM_TRAFFIC_BYTES / n},
         "cpu_baseline": cpu,
         "clocks": clocks,
     }

@@ -477,7 +477,9 @@ class CudaMeshImpl(SlicedMeshImpl):
     return self._ops
 
   def _ops_for(self, pnum):
-    self._ops.device = self._devices[pnum]
+    dev = self._devices[pnum]
+    if self._ops.device != dev:
+      self._ops.device = dev
     return self._ops
 
   def _is_slice(self, x):
@@ -498,7 +500,8 @@ class CudaMeshImpl(SlicedMeshImpl):
     `epilogue="relu"` fuses tf.nn.relu into the store."""
     from mesh_b200 import _native as nat
     code = {None: nat.EPILOGUE_NONE, "relu": nat.EPILOGUE_RELU}[epilogue]
-    self._ops.device = slices[0].device
+    if self._ops.device != slices[0].device:
+      self._ops.device = slices[0].device
     return self._ops.einsum(equation, *slices, epilogue=code)
 
   # chunks a contraction is cut into when its allreduce is overlapped with it,

@@ -106,14 +106,32 @@ class DeviceOps(object):
   FP32_TENSOR_CORE_MAX_K = 2048
 
   def __init__(self, device):
-    self.device = torch.device(device)
-    if self.device.type != "cuda":
-      raise nat.MtfcError(nat.ERR_CUDA, "DeviceOps needs a CUDA device, got %s" % (device,))
     self._lib = nat.lib()
+    self.device = device
 
   # ---------------------------------------------------------------- plumbing
+  @property
+  def device(self):
+    return self._device
+
+  @device.setter
+  def device(self, value):
+    dev = torch.device(value)
+    if dev.type != "cuda":
+      raise nat.MtfcError(nat.ERR_CUDA, "DeviceOps needs a CUDA device, got %s" % (value,))
+    self._device = dev
+    self._index = dev.index if dev.index is not None else torch.cuda.current_device()
+
+  def _activate(self):
+    """Makes this object's device the current CUDA device (libmtfc works on the
+    current device).  A plain check-and-set: entering a torch.cuda.device context
+    on every call costs milliseconds of host time per operation."""
+    if torch.cuda.current_device() != self._index:
+      torch.cuda.set_device(self._index)
+
   def _stream(self):
-    return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+    self._activate()
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
   def _empty(self, shape, dtype):
     n = max(1, _volume(shape))
@@ -121,8 +139,8 @@ class DeviceOps(object):
     return DeviceArray(buf, shape, dtype)
 
   def _call(self, fn, *args):
-    with torch.cuda.device(self.device):
-      nat.check(fn(*args))
+    self._activate()
+    nat.check(fn(*args))
 
   def contiguous(self, x):
     if x.is_contiguous:
@@ -150,9 +168,9 @@ class DeviceOps(object):
     if isinstance(value, torch.Tensor):
       t = value if value.dtype == _TORCH[dtype.name] else value.to(_TORCH[dtype.name])
       t = t.contiguous().reshape(-1)
-      with torch.cuda.device(self.device):
-        buf = t.to(self.device, non_blocking=True) if t.numel() else torch.empty(
-            1, dtype=_TORCH[dtype.name], device=self.device)
+      self._activate()
+      buf = t.to(self.device, non_blocking=True) if t.numel() else torch.empty(
+          1, dtype=_TORCH[dtype.name], device=self.device)
       return DeviceArray(buf, tuple(value.shape), dtype)
     shape = np.shape(value)
     a = np.ascontiguousarray(np.asarray(value)).reshape(-1)
@@ -174,8 +192,8 @@ class DeviceOps(object):
     flat = x.buf[x.offset:x.offset + x.size]
     if out is None:
       return flat.cpu().reshape(x.shape)
-    with torch.cuda.device(self.device):
-      out.reshape(-1).copy_(flat, non_blocking=True)
+    self._activate()
+    out.reshape(-1).copy_(flat, non_blocking=True)
     return out
 
   def to_host(self, x):
