@@ -40,6 +40,43 @@ struct AttnArgs {
   int* status;
 };
 
+constexpr float RESCALE_SLACK = 8.0f;
+
+// max(a, b, c) in one instruction.
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// Sets the logits of masked keys (past the end of the keys, or after the query
+// under the causal mask) to -inf.  One compare and one select per logit, no
+// branches: the last visible key is a per-thread number and the key offsets are
+// compile-time constants.
+__device__ __forceinline__ void mask_row(uint32_t (&sv)[4][32], int k0, int q_pos,
+                                         const AttnArgs& args) {
+  int last = args.lk - 1;
+  if (args.causal) last = min(last, q_pos);
+  const int last_rel = last - k0;
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+#pragma unroll
+    for (int i = 0; i < 32; ++i) sv[c][i] = (c * 32 + i > last_rel) ? 0xff800000u : sv[c][i];
+}
+
+// Maximum of a 128-logit row: four independent chains of 3-input maxima.
+__device__ __forceinline__ float row_max(const uint32_t (&sv)[4][32]) {
+  float mx[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    mx[c] = fmaxf(__uint_as_float(sv[c][0]), __uint_as_float(sv[c][1]));
+#pragma unroll
+    for (int i = 2; i < 32; i += 2)
+      mx[c] = fmax3(mx[c], __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
+  }
+  return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+}
+
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int c0, int c1, int c2, int c3) {
   asm volatile(
@@ -272,19 +309,8 @@ attn_fwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
       for (int c = 0; c < 4; ++c) tc_ld_32x32(t_s + c * 32, sv[c]);
       tc_wait_ld();
-      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (need_mask) {
-            const int kp = k0 + c * 32 + i;
-            if (kp >= args.lk || (args.causal && kp > q_pos)) sv[c][i] = 0xff800000u;  // -inf
-          }
-          mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sv[c][i]));
-        }
-      }
-      const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * args.scale_log2e;
+      if (need_mask) mask_row(sv, k0, q_pos, args);
+      const float m_blk = row_max(sv) * args.scale_log2e;
       const float m_new = fmaxf(m_run, m_blk);
       // a fully masked row (only possible for rows past the end) keeps m = -inf
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
@@ -618,22 +644,16 @@ attn_fwd_tcgen05_2tile(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
       for (int c = 0; c < 4; ++c) tc_ld_32x32(t_s + c * 32, sv[c]);
       tc_wait_ld();
-      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (need_mask) {
-            const int kp = k0 + c * 32 + i;
-            if (kp >= args.lk || (args.causal && kp > q_pos)) sv[c][i] = 0xff800000u;
-          }
-          mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sv[c][i]));
-        }
-      }
-      const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * args.scale_log2e;
-      const float m_new = fmaxf(m_run, m_blk);
+      if (need_mask) mask_row(sv, k0, q_pos, args);
+      const float m_blk = row_max(sv) * args.scale_log2e;
+      // The running reference m_run only moves when the block maximum exceeds it
+      // by more than RESCALE_SLACK (in log2 units): weights then reach at most
+      // 2^RESCALE_SLACK, harmless in bf16 / fp32, the common factor cancels in O / l,
+      // and O is rescaled in a small fraction of the blocks instead of nearly all.
+      const bool moved = m_blk > m_run + RESCALE_SLACK;   // also true for m_run = -inf
+      const float m_new = moved ? m_blk : m_run;
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_use);
+      const float alpha = !moved ? 1.0f : ((m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_use));
       const float neg_m = -m_use;
       // bf16 weights, packed two per register, stored over the first 64 columns of
       // this tile's S region 64 keys at a time (S itself is already in registers,
@@ -657,20 +677,25 @@ attn_fwd_tcgen05_2tile(const __grid_constant__ CUtensorMap map_q,
       }
       const float l_blk = (ls[0] + ls[1]) + (ls[2] + ls[3]);
       // O_t is free for rescaling once the previous P.V has retired
-      if (j > 0) {
+      // (S_t(j) was queued behind P.V(j-1), so that product has retired by now; the
+      // wait only orders this thread's O accesses after it)
+      if (j > 0 && __any_sync(0xffffffffu, moved)) {
         ok = __all_sync(0xffffffffu, mbar_wait(pv_done(t), (uint32_t)((j - 1) & 1), abort_flag));
         if (!ok) break;
         tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
-          for (int c = 0; c < D; c += 32) {
-            uint32_t v[32];
-            tc_ld_32x32(t_o + c, v);
-            tc_wait_ld();
+        for (int c = 0; c < D; c += 64) {
+          uint32_t v[2][32];
+          tc_ld_32x32(t_o + c, v[0]);
+          tc_ld_32x32(t_o + c + 32, v[1]);
+          tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tc_st_32x32(t_o + c, v);
+          for (int i = 0; i < 32; ++i) {
+            v[0][i] = __float_as_uint(__uint_as_float(v[0][i]) * alpha);
+            v[1][i] = __float_as_uint(__uint_as_float(v[1][i]) * alpha);
           }
+          tc_st_32x32(t_o + c, v[0]);
+          tc_st_32x32(t_o + c + 32, v[1]);
         }
       }
       tc_wait_st();

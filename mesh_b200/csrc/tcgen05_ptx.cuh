@@ -30,16 +30,19 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// One try_wait with a suspend-time hint: the thread sleeps inside the instruction
+// (waking as soon as the phase completes) instead of spinning on it, which keeps
+// waiting warps from eating the issue slots of the warps doing the arithmetic.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t"
       "}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(100000u)
       : "memory");
   return ok != 0;
 }
@@ -49,14 +52,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  for (uint32_t spin = 1;; ++spin) {
+  for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 0xff) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > WAIT_BUDGET_CYCLES) {
-        *abort_flag = 1;
-        return false;
-      }
+    if (*abort_flag) return false;
+    if (clock64() - t0 > WAIT_BUDGET_CYCLES) {
+      *abort_flag = 1;
+      return false;
     }
   }
 }
