@@ -42,6 +42,14 @@ struct AttnArgs {
 
 constexpr float RESCALE_SLACK = 8.0f;
 
+// Keeps sixteen registers' values where they are in program order: arithmetic on
+// them cannot be moved above this point (no instruction is emitted).
+__device__ __forceinline__ void pin16(uint32_t* r) {
+  asm volatile("" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]),
+                    "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]),
+                    "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]));
+}
+
 // max(a, b, c) in one instruction.
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
@@ -111,6 +119,33 @@ __device__ __forceinline__ void tc_wait_st() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tc_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+        "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// Eight columns at a time, for the rarely taken output rescale, which runs while a
+// whole row of logits is live in registers.
+__device__ __forceinline__ void tc_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_st_32x8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7])
+      : "memory");
+}
+
 // kind::f16 instruction descriptor, fp32 accumulate, bf16 operands, M = 128.
 __device__ __forceinline__ uint32_t attn_idesc(int n, int b_mn_major) {
   uint32_t d = 0;
@@ -125,7 +160,7 @@ __device__ __forceinline__ uint32_t attn_idesc(int n, int b_mn_major) {
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
@@ -434,7 +469,7 @@ attn_fwd_tcgen05(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 // are stored back into TMEM over the first 64 columns of their S tile and feed
 // the second MMA as its A operand from TMEM.
 // TMEM columns: S_A/P_A [0,128)  S_B/P_B [128,256)  O_A [256,256+D)  O_B [384,384+D).
-constexpr int A2THREADS = 320;
+constexpr int A2THREADS = 352;
 
 template <int D>
 struct Attn2Smem {
@@ -443,7 +478,7 @@ struct Attn2Smem {
   static constexpr int K = Q + 2 * DA * ATOM_BYTES;        // 2 stages x DA atoms
   static constexpr int V = K + 2 * DA * ATOM_BYTES;        // 2 stages x DA atoms
   static constexpr int BAR = V + 2 * DA * ATOM_BYTES;
-  static constexpr int NUM_BARS = 16;
+  static constexpr int NUM_BARS = 20;
   static constexpr int MISC = BAR + NUM_BARS * 8;
   static constexpr int USED = MISC + 16;
   static constexpr int ALLOC = USED + 1024;
@@ -480,8 +515,10 @@ attn_fwd_tcgen05_2tile(const __grid_constant__ CUtensorMap map_q,
   auto v_full = [&](int s) { return bar_base + 8u * (5 + s); };
   auto v_empty = [&](int s) { return bar_base + 8u * (7 + s); };
   auto s_full = [&](int t) { return bar_base + 8u * (9 + t); };    // per tile
-  auto p_full = [&](int t) { return bar_base + 8u * (11 + t); };   // per tile
-  auto pv_done = [&](int t) { return bar_base + 8u * (13 + t); };  // per tile
+  auto pv_done = [&](int t) { return bar_base + 8u * (11 + t); };  // per tile
+  // weights of keys 0-63 (h = 0) and 64-127 (h = 1) of a tile stored to TMEM
+  auto p_half = [&](int t, int h) { return bar_base + 8u * (13 + 2 * t + h); };
+  auto exp_done = [&](int t) { return bar_base + 8u * (17 + t); };  // tile t finished a block's exponentials
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + SM::MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::MISC + 4);
 
@@ -506,12 +543,14 @@ attn_fwd_tcgen05_2tile(const __grid_constant__ CUtensorMap map_q,
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(k_full(s), 1);
-      mbar_init(k_empty(s), 1);
+      mbar_init(k_empty(s), 2);   // one arrival per MMA issuer
       mbar_init(v_full(s), 1);
-      mbar_init(v_empty(s), 1);
+      mbar_init(v_empty(s), 2);
       mbar_init(s_full(s), 1);
-      mbar_init(p_full(s), 4);
+      mbar_init(p_half(s, 0), 4);
+      mbar_init(p_half(s, 1), 4);
       mbar_init(pv_done(s), 1);
+      mbar_init(exp_done(s), 4);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -559,13 +598,18 @@ attn_fwd_tcgen05_2tile(const __grid_constant__ CUtensorMap map_q,
       }
       if (!ok && args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
     }
-  } else if (warp == 1) {
-    // -------------------------------------------------------------- MMA issuer
+  } else if (warp == 1 || warp == 10) {
+    // ------------------------------------------- MMA issuers, one thread per tile
+    // Each tile's products are issued in order by its own thread, so the tensor
+    // pipe interleaves the two tiles by itself and neither tile's issue ever waits
+    // on the other tile's softmax.  K / V stages are released by both threads.
     if (lane == 0) {
+      const int t = warp == 1 ? 0 : 1;
+      const int n_mine = n_tile[t];
       const uint32_t idesc_s = attn_idesc(ABN, 0);
       const uint32_t idesc_o = attn_idesc(D, 1);
       bool ok = mbar_wait(q_full, 0, abort_flag);
-      auto issue_s = [&](int t, int j) {   // S_t(j) = Q_t . K_j^T
+      auto issue_s = [&](int j) {   // S_t(j) = Q_t . K_j^T
         const int st = j & 1;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
@@ -576,23 +620,22 @@ attn_fwd_tcgen05_2tile(const __grid_constant__ CUtensorMap map_q,
         }
         tc_commit(s_full(t));
       };
-      auto issue_pv = [&](int t, int j) {  // O_t += P_t(j) . V_j, P from TMEM
+      auto issue_pv_half = [&](int j, int h) {  // O_t += P_t(j)[:, 64h:64h+64] . V_j[64h:64h+64], P from TMEM
         const int st = j & 1;
 #pragma unroll
-        for (int ks = 0; ks < ABN / 16; ++ks) {
+        for (int kk = 0; kk < ABN / 32; ++kk) {
+          const int ks = h * (ABN / 32) + kk;
           const uint64_t db = make_smem_desc(
               smem_base + SM::V + st * DA * ATOM_BYTES + ks * 16 * 128, ATOM_BYTES, 1024);
           tc_mma_bf16_ts(tmem_o(t), tmem_s(t) + (uint32_t)(ks * 8), db, idesc_o,
                          (j | ks) != 0 ? 1u : 0u);
         }
-        tc_commit(pv_done(t));
       };
       if (ok && num_kv > 0) {
         ok = mbar_wait(k_full(0), 0, abort_flag);
         if (ok) {
           tc_fence_after();
-          if (n_tile[0] > 0) issue_s(0, 0);
-          if (n_tile[1] > 0) issue_s(1, 0);
+          if (n_mine > 0) issue_s(0);
           tc_commit(k_empty(0));
         }
       }
@@ -600,23 +643,25 @@ attn_fwd_tcgen05_2tile(const __grid_constant__ CUtensorMap map_q,
         const int st = j & 1;
         const uint32_t ph = (uint32_t)((j >> 1) & 1);
         const bool next = j + 1 < num_kv;
+        // waited for even when this tile skips the block, so that the two issuers
+        // release a stage exactly once each per block
         if (!mbar_wait(v_full(st), ph, abort_flag)) { ok = false; break; }
         if (next && !mbar_wait(k_full((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1), abort_flag)) {
           ok = false;
           break;
         }
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          if (j < n_tile[t]) {
-            if (!mbar_wait(p_full(t), (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            issue_pv(t, j);
-            // the tensor pipe runs this thread's MMAs in order, so S_t(j+1) may
-            // overwrite the columns P_t(j) occupies as soon as P.V is queued
-            if (j + 1 < n_tile[t]) issue_s(t, j + 1);
-          }
+        if (j < n_mine) {
+          if (!mbar_wait(p_half(t, 0), (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          issue_pv_half(j, 0);
+          if (!mbar_wait(p_half(t, 1), (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          issue_pv_half(j, 1);
+          tc_commit(pv_done(t));
+          // the tensor pipe runs this thread's MMAs in order, so S_t(j+1) may
+          // overwrite the columns P_t(j) occupies as soon as P.V is queued
+          if (j + 1 < n_mine) issue_s(j + 1);
         }
-        if (!ok) break;
         tc_commit(v_empty(st));
         if (next) tc_commit(k_empty((j + 1) & 1));
       }
@@ -655,55 +700,90 @@ attn_fwd_tcgen05_2tile(const __grid_constant__ CUtensorMap map_q,
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = !moved ? 1.0f : ((m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_use));
       const float neg_m = -m_use;
-      // bf16 weights, packed two per register, stored over the first 64 columns of
-      // this tile's S region 64 keys at a time (S itself is already in registers,
-      // and the previous P.V — which read these columns — retired before S_t(j) was
-      // written), and the row sum
-      float ls[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t pk[32];
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[2 * h + cc][i]), args.scale_log2e, neg_m));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[2 * h + cc][i + 1]), args.scale_log2e, neg_m));
-            ls[(i >> 1) & 3] += p0 + p1;
-            pk[cc * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
-          }
-        }
-        tc_st_32x32(t_s + h * 32, pk);
-      }
-      const float l_blk = (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      // O_t is free for rescaling once the previous P.V has retired
-      // (S_t(j) was queued behind P.V(j-1), so that product has retired by now; the
-      // wait only orders this thread's O accesses after it)
+      // O_t is rescaled (rarely) before any of this block's P.V is queued.  S_t(j)
+      // was queued behind P.V(j-1), so that product has retired by now; the wait
+      // only orders this thread's O accesses after it.
       if (j > 0 && __any_sync(0xffffffffu, moved)) {
         ok = __all_sync(0xffffffffu, mbar_wait(pv_done(t), (uint32_t)((j - 1) & 1), abort_flag));
         if (!ok) break;
         tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < D; c += 64) {
-          uint32_t v[2][32];
-          tc_ld_32x32(t_o + c, v[0]);
-          tc_ld_32x32(t_o + c + 32, v[1]);
+        for (int c = 0; c < D; c += 8) {
+          uint32_t v[8];
+          tc_ld_32x8(t_o + c, v);
           tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            v[0][i] = __float_as_uint(__uint_as_float(v[0][i]) * alpha);
-            v[1][i] = __float_as_uint(__uint_as_float(v[1][i]) * alpha);
-          }
-          tc_st_32x32(t_o + c, v[0]);
-          tc_st_32x32(t_o + c + 32, v[1]);
+          for (int i = 0; i < 8; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tc_st_32x8(t_o + c, v);
         }
       }
-      tc_wait_st();
-      l_run = l_run * alpha + l_blk;
+      // bf16 weights, packed two per register, stored over the first 64 columns of
+      // this tile's S region 64 keys at a time (S itself is already in registers,
+      // and the previous P.V — which read these columns — retired before S_t(j) was
+      // written), and the row sum.  Each half is handed to the MMA issuer as soon
+      // as it is stored, so P.V starts on keys 0-63 while keys 64-127 are still
+      // being exponentiated.
+      //
+      // The two tiles take turns at the exponentials (tile 0 block j, tile 1 block j,
+      // tile 0 block j+1, ...): the special-function unit is the scarcest resource
+      // of this loop (4 lanes per clock per scheduler, and a warp that runs into a
+      // busy unit issues nothing else meanwhile), and two tiles exponentiating at
+      // once would each run at half speed while the tensor pipe idles; in turns,
+      // one tile's exponentials hide behind the other tile's products.  What needs
+      // no special-function unit stays out of the turn: the scaling of the logits
+      // is done before it (in the issue slots the other tile leaves free) and the
+      // row sum after the weights have been handed over.
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          sv[c][i] = __float_as_uint(fmaf(__uint_as_float(sv[c][i]), args.scale_log2e, neg_m));
+      {
+        const int n_other = n_tile[1 - t];
+        bool turn = true;
+        if (t == 0) {
+          if (j > 0 && j - 1 < n_other) turn = mbar_wait(exp_done(1), (uint32_t)((j - 1) & 1), abort_flag);
+        } else {
+          if (j < n_other) turn = mbar_wait(exp_done(0), (uint32_t)(j & 1), abort_flag);
+        }
+        ok = __all_sync(0xffffffffu, turn);
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = fast_exp2(__uint_as_float(sv[2 * h + cc][i]));       // masked: 2^-inf = 0
+            const float p1 = fast_exp2(__uint_as_float(sv[2 * h + cc][i + 1]));
+            sv[2 * h + cc][i] = __float_as_uint(p0);
+            sv[2 * h + cc][i + 1] = __float_as_uint(p1);
+            pk[i >> 1] = pack_bf16x2(p0, p1);
+          }
+          tc_st_32x16(t_s + h * 32 + cc * 16, pk);
+        }
+        if (h == 1) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(exp_done(t));
+        }
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_half(t, h));
+      }
+      // row sum of the (unrounded) weights, while the tensor pipe works on them
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        pin16(&sv[c][0]);
+        pin16(&sv[c][16]);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) ls[i & 3] += __uint_as_float(sv[c][i]);
+      }
+      l_run = l_run * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
       m_run = m_new;
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full(t));
     }
     if (ok && n_mine > 0)
       ok = __all_sync(0xffffffffu, mbar_wait(pv_done(t), (uint32_t)((n_mine - 1) & 1), abort_flag));
