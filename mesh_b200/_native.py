@@ -70,6 +70,10 @@ def _declare(lib):
   signatures = {
       "mtfc_gemm": [ctypes.POINTER(GemmDesc), vp, vp, vp, vp],
       "mtfc_gemm_uses_tensor_cores": [ctypes.POINTER(GemmDesc), vp, vp, vp],
+      "mtfc_gemm_allreduce_flag_bytes": [],
+      "mtfc_gemm_allreduce_stage_bytes": [i64, i64, i32],
+      "mtfc_gemm_allreduce": [ctypes.POINTER(GemmDesc), vp, vp, ctypes.POINTER(vp), ctypes.POINTER(vp),
+                              ctypes.POINTER(vp), vp, i32, i32, i32, vp],
       "mtfc_split_bf16x3": [vp, i64, i64, i64, vp, i64, i64, i64, i32, vp],
       "mtfc_attention_set_variant": [i32],
       "mtfc_attention_supported": [i64, p_i64, p_i64, p_i64, p_i64],
@@ -95,7 +99,7 @@ def _declare(lib):
   }
   for name, argtypes in signatures.items():
     fn = getattr(lib, name)
-    fn.restype = ctypes.c_int
+    fn.restype = i64 if name == "mtfc_gemm_allreduce_stage_bytes" else ctypes.c_int
     fn.argtypes = argtypes
 
 

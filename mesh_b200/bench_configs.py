@@ -188,20 +188,33 @@ def config_einsum_fp32(args):
 
 def config_attention(args):
   """Multi-head attention: x[batch,2048,4096] bf16, 32 heads of 128, causal;
-  q/k/v projections, fused attention kernel, output projection; one GPU,
-  inputs and weights resident, the lowering replayed as a CUDA graph."""
+  q/k/v projections, fused attention kernel, output projection; inputs and
+  weights resident, the lowering replayed as a CUDA graph.  With --gpus N the
+  heads are split over a 1-D mesh (layout heads:all): every rank holds the whole
+  x, its own heads' weights, and the output projection ends in an allreduce."""
   peaks = _peaks()
-  torch.cuda.set_device(0)
-  impl = CudaMeshImpl("all:1", "", [0])
+  n = args.gpus
+  rank = int(os.environ.get("RANK", "0"))
+  local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+  torch.cuda.set_device(local_rank)
+  if n > 1:
+    import torch.distributed as dist
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+  mesh_shape, layout = "all:%d" % n, ("heads:all" if n > 1 else "")
+  impl = CudaMeshImpl(mesh_shape, layout, list(range(n)) if n > 1 else [local_rank], distributed=n > 1)
   ops = impl.slice_ops
   b, l, d, h, kv = args.attention_batch, 2048, 4096, 32, 128
+  h_loc = h // n
   r = np.random.Generator(np.random.PCG64(1237))
   x = torch.from_numpy(r.standard_normal((b, l, d), dtype=np.float32)).to(torch.bfloat16)
   lx = impl.LaidOutTensor([ops.from_host(x, mtf.bfloat16)])
   stds = [d ** -0.5 * kv ** -0.25] * 2 + [d ** -0.5, (d * h) ** -0.5]
-  lws = [impl.LaidOutTensor([ops.from_host(torch.from_numpy(
-      r.standard_normal((h, d, kv), dtype=np.float32) * np.float32(sd)).to(torch.bfloat16), mtf.bfloat16)])
-         for sd in stds]
+  lws = []
+  for sd in stds:
+    w = r.standard_normal((h, d, kv), dtype=np.float32) * np.float32(sd)
+    w = w[rank * h_loc:(rank + 1) * h_loc]
+    lws.append(impl.LaidOutTensor([ops.from_host(torch.from_numpy(np.ascontiguousarray(w)).to(torch.bfloat16),
+                                                 mtf.bfloat16)]))
   g = mtf.Graph()
   mesh = mtf.Mesh(g, "mesh")
   X = mtf.import_laid_out_tensor(mesh, lx, "batch:%d,length:%d,d_model:%d" % (b, l, d), mtf.bfloat16)
@@ -217,14 +230,26 @@ def config_attention(args):
   before = nat.launch_count()
   step()
   launches = nat.launch_count() - before
-  _, run = impl.capture(step)
+  impl.synchronize()
+  run = step
+  if not args.eager:
+    _, run = impl.capture(step)
   ms = _time(run, iters=args.iters, warmup=3)
+  if n > 1:
+    t = torch.tensor([ms], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
   proj = 4 * 2.0 * b * l * d * h * kv
   attn_full = 2 * 2.0 * b * h * l * l * kv
-  _emit(config="attention", quantity="multihead_attention layer (fused kernel)", batch=b, ms=ms,
-        tflops_full=(proj + attn_full) / (ms * 1e-3) / 1e12,
-        tflops_causal_work=(proj + attn_full / 2 * (1 + 128.0 / l)) / (ms * 1e-3) / 1e12,
-        libmtfc_launches_per_step=launches, peak_tflops=peaks["tflops"], peak_source=peaks["source"])
+  if rank == 0:
+    _emit(config="attention", quantity="multihead_attention layer (fused kernel)", n_gpus=n, batch=b, ms=ms,
+          tflops_full=(proj + attn_full) / (ms * 1e-3) / 1e12,
+          tflops_causal_work=(proj + attn_full / 2 * (1 + 128.0 / l)) / (ms * 1e-3) / 1e12,
+          allreduce_bytes_per_gpu=(b * l * d * 2 if n > 1 else 0),
+          libmtfc_launches_per_step=launches, peak_tflops=peaks["tflops"], peak_source=peaks["source"],
+          stepping="eager" if args.eager else "cuda-graph replay")
+  if n > 1:
+    _leave(dist_module=None)
   # the fused kernel alone on q, k, v [batch, heads, length, d_kv]
   q, k, v = [ops.from_host(torch.from_numpy(
       r.standard_normal((b, h, l, kv), dtype=np.float32) * np.float32(0.3)).to(torch.bfloat16), mtf.bfloat16)

@@ -58,6 +58,11 @@ int gemm_tcgen05_launch(const mtfc_gemm_desc* d, const void* a, const void* b, v
                         cudaStream_t stream, int cta_group);
 int gemm_simt_launch(const mtfc_gemm_desc* d, const void* a, const void* b, void* c,
                      cudaStream_t stream);
+int gemm_allreduce_flag_bytes();
+long long gemm_allreduce_stage_bytes(long long m, long long n, int nranks);
+int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
+                          void* const* stage, void* const* out, void* const* flags, void* ctl,
+                          int rank, int nranks, int comm_clusters, cudaStream_t stream);
 
 }  // namespace mtfc
 
@@ -116,6 +121,24 @@ int mtfc_gemm(const mtfc_gemm_desc* d, const void* a, const void* b, void* c, vo
   } else {
     rc = gemm_simt_launch(d, a, b, c, s);
   }
+  if (rc == MTFC_OK) count_launch(1);
+  return rc;
+}
+
+int mtfc_gemm_allreduce_flag_bytes(void) { return gemm_allreduce_flag_bytes(); }
+
+int64_t mtfc_gemm_allreduce_stage_bytes(int64_t m, int64_t n, int nranks) {
+  return gemm_allreduce_stage_bytes(m, n, nranks);
+}
+
+int mtfc_gemm_allreduce(const mtfc_gemm_desc* d, const void* a, const void* b,
+                        void* const* stage_ptrs, void* const* out_ptrs, void* const* flag_ptrs,
+                        void* ctl, int rank, int nranks, int comm_clusters, void* stream) {
+  if (!d || !a || !b) return fail(MTFC_ERR_SHAPE, "gemm_allreduce: null argument");
+  if (d->batch < 1 || d->m < 1 || d->n < 1 || d->k < 1)
+    return fail(MTFC_ERR_SHAPE, "gemm_allreduce: empty problem");
+  int rc = gemm_allreduce_launch(d, a, b, stage_ptrs, out_ptrs, flag_ptrs, ctl, rank, nranks,
+                                 comm_clusters, static_cast<cudaStream_t>(stream));
   if (rc == MTFC_OK) count_launch(1);
   return rc;
 }

@@ -19,6 +19,7 @@
 // raises a CTA-wide abort flag, records MTFC_ERR_TIMEOUT in the device status
 // word, drains, frees its TMEM and returns.
 
+#include <cstring>
 #include "tcgen05_ptx.cuh"
 
 namespace mtfc {
@@ -372,6 +373,165 @@ __device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_des
       : "memory");
 }
 
+// ------------------------------------------------ GEMM fused with its allreduce
+// The same pair kernel with the SUM allreduce of its output over `nranks` GPUs
+// (one process each) folded in.  Row blocks of 256 output rows are owned
+// round-robin (block rb by rank rb % nranks).  The epilogue of every rank stores
+// its partial tile straight into the OWNER's staging buffer (a TMA store into
+// peer memory: slot [source rank][k-th owned block]), so the reduce-scatter half
+// of the exchange rides on stores the epilogue issues anyway.  A few clusters of
+// the grid (the "comm" CTAs) do no MMA work: once all ranks have delivered a row
+// block this rank owns, they add its nranks partial copies (local reads, fp32,
+// in rank order, one rounding to bf16) and write the sum into every rank's
+// output buffer (plain 16-byte stores, local and peer).  GEMM clusters walk the
+// tiles row block by row block, so block i is exchanged while the blocks after
+// it are still being multiplied.
+//
+// Flags (uint32, in peer-visible memory, never reset; a launch compares against
+// epoch * count): flags[rb] on the owner of row block rb counts epilogue warps
+// of all ranks that have delivered their part of rb; flags[FLAG_DONE] on every
+// rank counts row blocks written into that rank's output.  `ctl` is this rank's
+// private pair {launches completed, comm CTAs finished in this launch}; keeping
+// the epoch on the device lets a captured launch be replayed.  Every wait is
+// bounded: a rank whose peers never show up raises MTFC_ERR_TIMEOUT in the status
+// word and returns.
+constexpr int MAX_RANKS = 8;
+constexpr int FLAG_DONE = 4096;  // row-block counters live in [0, FLAG_DONE)
+constexpr int COMM_UNROLL = 8;   // 16-byte vectors per thread and source in flight
+constexpr long long PEER_WAIT_CYCLES = 6000000000LL;  // ~3 s
+
+struct FusedArgs {
+  CUtensorMap stage_map[MAX_RANKS];  // rank o's staging buffer [nranks * blocks_per_rank * 256, n]
+  const uint8_t* stage;              // this rank's staging buffer
+  uint8_t* out[MAX_RANKS];
+  uint32_t* flags[MAX_RANKS];
+  uint32_t* ctl;
+  int rank, nranks;
+  int blocks_per_rank;
+  int gemm_clusters;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Waits (bounded) until *p has reached `target` (wrap-safe comparison).
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target) {
+  const long long t0 = clock64();
+  for (;;) {
+    if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
+    if (clock64() - t0 > PEER_WAIT_CYCLES) return false;
+    __nanosleep(128);
+  }
+}
+// 16-byte load that never hits a stale L1 line (the data was written by TMA
+// stores of other SMs and other GPUs during this launch).
+__device__ __forceinline__ uint4 ld_cv_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cv.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_v4(void* p, const uint4& v) {
+  asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
+// One comm CTA: reduces the row blocks this rank owns, every num_comm-th of them.
+__device__ void allreduce_comm_cta(uint8_t* smem, const GemmArgs& args, const FusedArgs& fa,
+                                   int comm_idx, int num_comm) {
+  const int n = fa.nranks;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SMEM2_MISC + 4);
+  volatile uint32_t* epoch_slot = reinterpret_cast<volatile uint32_t*>(smem + SMEM2_MISC + 8);
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    *abort_flag = 0;
+    *epoch_slot = ld_acquire_sys(fa.ctl) + 1u;
+  }
+  __syncthreads();
+  const uint32_t epoch = *epoch_slot;
+  const long long row_bytes = (long long)args.n * 2;
+  const long long block_bytes = 2LL * BM * row_bytes;
+  const int num_rb = args.tiles_m;
+  const uint32_t ready_target = epoch * (uint32_t)(n * args.tiles_n * 2 * EPI_WARPS);
+  bool ok = true;
+  for (int k = comm_idx; ok; k += num_comm) {
+    const int rb = fa.rank + n * k;
+    if (rb >= num_rb) break;
+    if (tid == 0 && !wait_flag_ge(fa.flags[fa.rank] + rb, ready_target)) *abort_flag = 1;
+    __syncthreads();
+    if (*abort_flag) { ok = false; break; }
+    const int rows = min(2 * BM, args.m - rb * 2 * BM);
+    const long long nvec = (rows * row_bytes) >> 4;
+    const long long out_base = (long long)rb * block_bytes;
+    for (long long v0 = tid; v0 < nvec; v0 += (long long)NUM_THREADS * COMM_UNROLL) {
+      float acc[COMM_UNROLL][8];
+#pragma unroll
+      for (int u = 0; u < COMM_UNROLL; ++u)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+      for (int s = 0; s < n; ++s) {
+        const uint8_t* src = fa.stage + ((long long)s * fa.blocks_per_rank + k) * block_bytes;
+        uint4 x[COMM_UNROLL];
+#pragma unroll
+        for (int u = 0; u < COMM_UNROLL; ++u) {
+          const long long v = v0 + (long long)u * NUM_THREADS;
+          x[u] = v < nvec ? ld_cv_v4(src + v * 16) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < COMM_UNROLL; ++u) {
+          const uint32_t w[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc[u][2 * e] += __uint_as_float(w[e] << 16);
+            acc[u][2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < COMM_UNROLL; ++u) {
+        const long long v = v0 + (long long)u * NUM_THREADS;
+        if (v < nvec) {
+          uint4 o;
+          o.x = pack_bf16x2(acc[u][0], acc[u][1]);
+          o.y = pack_bf16x2(acc[u][2], acc[u][3]);
+          o.z = pack_bf16x2(acc[u][4], acc[u][5]);
+          o.w = pack_bf16x2(acc[u][6], acc[u][7]);
+          for (int p = 0; p < n; ++p) st_v4(fa.out[p] + out_base + v * 16, o);
+        }
+      }
+    }
+    // every thread's stores are ordered before the flag update made on its behalf
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0)
+      for (int p = 0; p < n; ++p) red_release_sys_add(fa.flags[p] + FLAG_DONE, 1u);
+  }
+  if (tid == 0) {
+    if (!ok) {
+      if (args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
+    } else if (atomicAdd(fa.ctl + 1, 1u) == (uint32_t)(num_comm - 1)) {
+      // last comm CTA of this launch: the output is whole once every row block
+      // has been written here, and only then may the next launch start
+      if (wait_flag_ge(fa.flags[fa.rank] + FLAG_DONE, epoch * (uint32_t)num_rb)) {
+        fa.ctl[1] = 0u;
+        __threadfence();
+        fa.ctl[0] = epoch;
+      } else if (args.status) {
+        atomicExch(args.status, MTFC_ERR_TIMEOUT);
+      }
+    }
+  }
+}
+
+
 __device__ __forceinline__ uint32_t make_idesc_pair(int a_mn, int b_mn) {
   uint32_t d = 0;
   d |= 1u << 4;
@@ -384,10 +544,10 @@ __device__ __forceinline__ uint32_t make_idesc_pair(int a_mn, int b_mn) {
   return d;
 }
 
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-einsum_gemm_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a,
-                         const __grid_constant__ CUtensorMap map_b,
-                         const __grid_constant__ CUtensorMap map_c, const GemmArgs args) {
+template <bool FUSED>
+__device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const CUtensorMap& map_b,
+                                               const CUtensorMap& map_c, const GemmArgs& args,
+                                               const FusedArgs* fa) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -404,6 +564,13 @@ einsum_gemm_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a,
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const bool leader = rank == 0;
+
+  if (FUSED && (int)(blockIdx.x >> 1) >= fa->gemm_clusters) {
+    // comm cluster: no MMA work, no TMEM, no cluster barriers
+    allreduce_comm_cta(smem, args, *fa, (int)blockIdx.x - 2 * fa->gemm_clusters,
+                       (int)gridDim.x - 2 * fa->gemm_clusters);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES2; ++s) {
@@ -434,7 +601,7 @@ einsum_gemm_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a,
   const long long tiles_per_batch = (long long)args.tiles_m * args.tiles_n;  // 256x256 tiles
   const long long num_tiles = tiles_per_batch * args.batch;
   const long long cluster_id = blockIdx.x >> 1;
-  const long long num_clusters = gridDim.x >> 1;
+  const long long num_clusters = FUSED ? (long long)fa->gemm_clusters : (long long)(gridDim.x >> 1);
 
   if (warp == 0) {
     // ------------------------------------------------ TMA producer (both CTAs)
@@ -532,6 +699,14 @@ einsum_gemm_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a,
       const int r = (int)(t % tiles_per_batch);
       const int m0 = (r / args.tiles_n) * (2 * BM) + (int)rank * BM;
       const int n0 = (r % args.tiles_n) * BN;
+      // fused: the tile goes to the staging buffer of its row block's owner
+      const int rb = r / args.tiles_n;
+      const CUtensorMap* dst_map = &map_c;
+      int dst_row = m0 + q * 32;
+      if (FUSED) {
+        dst_map = &fa->stage_map[rb % fa->nranks];
+        dst_row = (fa->rank * fa->blocks_per_rank + rb / fa->nranks) * (2 * BM) + (int)rank * BM + q * 32;
+      }
       ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), acc_phase, abort_flag));
       if (!ok) break;
       tc_fence_after();
@@ -587,7 +762,7 @@ einsum_gemm_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a,
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          tma_store_3d(&map_c, stage_u32 + sbuf * EPI_BUF_BYTES, n0 + c0, m0 + q * 32, b);
+          tma_store_3d(dst_map, stage_u32 + sbuf * EPI_BUF_BYTES, n0 + c0, dst_row, b);
           tma_store_commit();
         }
         ++store_idx;
@@ -595,6 +770,13 @@ einsum_gemm_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a,
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(tmem_empty_bar(buf), 0));
+      if (FUSED && lane == 0) {
+        // this warp's part of the tile has arrived at its owner (complete, not
+        // merely read out of the staging buffers): count it there
+        tma_store_wait_all();
+        __threadfence_system();
+        red_release_sys_add(fa->flags[rb % fa->nranks] + rb, 1u);
+      }
     }
     if (lane == 0) tma_store_wait_all();
     if (!ok && lane == 0 && args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
@@ -610,6 +792,20 @@ einsum_gemm_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a,
                  "r"(TMEM_COLS)
                  : "memory");
   }
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+einsum_gemm_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a,
+                         const __grid_constant__ CUtensorMap map_b,
+                         const __grid_constant__ CUtensorMap map_c, const GemmArgs args) {
+  pair_gemm_body<false>(map_a, map_b, map_c, args, nullptr);
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+einsum_gemm_allreduce_2cta(const __grid_constant__ CUtensorMap map_a,
+                           const __grid_constant__ CUtensorMap map_b, const GemmArgs args,
+                           const __grid_constant__ FusedArgs fa) {
+  pair_gemm_body<true>(map_a, map_b, fa.stage_map[0], args, &fa);
 }
 
 // ------------------------------------------------------------------- host side
@@ -807,6 +1003,121 @@ int gemm_tcgen05_launch(const mtfc_gemm_desc* d, const void* a, const void* b, v
   const unsigned grid = (unsigned)(num_tiles < sms ? num_tiles : sms);
   einsum_gemm_tcgen05<<<grid, NUM_THREADS, SMEM_ALLOC, stream>>>(map_a, map_b, map_c, args);
   MTFC_LAUNCH_CHECK("einsum_gemm_tcgen05");
+  return MTFC_OK;
+}
+
+int gemm_allreduce_flag_bytes() { return (FLAG_DONE + 1) * 4; }
+
+long long gemm_allreduce_stage_bytes(long long m, long long n, int nranks) {
+  if (m < 1 || n < 1 || nranks < 1) return 0;
+  const long long num_rb = (m + 2 * BM - 1) / (2 * BM);
+  const long long bpr = (num_rb + nranks - 1) / nranks;
+  return (long long)nranks * bpr * 2 * BM * n * 2;
+}
+
+// GEMM with the allreduce of its bf16 [m, n] row-major output folded in (see
+// the kernel comment).  `stage`, `out` and `flags` hold every rank's buffer
+// address as seen from this process; `ctl` is this rank's private 8 bytes.
+int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
+                          void* const* stage, void* const* out, void* const* flags, void* ctl,
+                          int rank, int nranks, int comm_clusters, cudaStream_t stream) {
+  if (nranks < 2 || nranks > MAX_RANKS || rank < 0 || rank >= nranks)
+    return fail(MTFC_ERR_SHAPE, "gemm_allreduce: %d ranks (2..%d supported), rank %d", nranks,
+                MAX_RANKS, rank);
+  if (!stage || !out || !flags || !ctl) return fail(MTFC_ERR_SHAPE, "gemm_allreduce: null argument");
+  if (d->batch != 1 || d->out_dtype != MTFC_BF16 || d->c_n != 1 || d->c_m != d->n || d->n % 8 != 0)
+    return fail(MTFC_ERR_UNSUPPORTED,
+                "gemm_allreduce: needs batch 1 and a dense row-major bf16 [m, n] output with n a "
+                "multiple of 8");
+  if (d->epilogue != MTFC_EPILOGUE_NONE)
+    return fail(MTFC_ERR_UNSUPPORTED, "gemm_allreduce: no epilogue on a partial sum");
+  for (int p = 0; p < nranks; ++p)
+    if (!stage[p] || !out[p] || !flags[p] || !aligned16(stage[p]) || !aligned16(out[p]))
+      return fail(MTFC_ERR_SHAPE, "gemm_allreduce: buffer of rank %d missing or not 16-byte aligned", p);
+  if (!gemm_tcgen05_eligible(d, a, b, stage[rank]))
+    return fail(MTFC_ERR_UNSUPPORTED, "gemm_allreduce: operands not eligible for the tcgen05 path");
+  const int pair_clusters = max_pair_clusters();
+  if (pair_clusters < 2) return fail(MTFC_ERR_CUDA, "gemm_allreduce: no room for 2-CTA clusters");
+  if (comm_clusters < 1) comm_clusters = 1;
+  if (comm_clusters > pair_clusters - 1) comm_clusters = pair_clusters - 1;
+  const int a_major = classify(d->m, d->k, d->a_m, d->a_k, 1, 0);
+  const int b_major = classify(d->n, d->k, d->b_n, d->b_k, 1, 0);
+  if (a_major < 0 || b_major < 0) return fail(MTFC_ERR_SHAPE, "operand layout not TMA-able");
+  CUtensorMap map_a, map_b;
+  int rc;
+  if (a_major == 0)
+    rc = encode_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, d->k, d->m, 1, d->a_m, 0, BK, BM,
+                    "A (K-major)");
+  else
+    rc = encode_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a, d->m, d->k, 1, d->a_k, 0, 64, BK,
+                    "A (M-major)");
+  if (rc != MTFC_OK) return rc;
+  if (b_major == 0)
+    rc = encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b, d->k, d->n, 1, d->b_n, 0, BK,
+                    BN / 2, "B (K-major)");
+  else
+    rc = encode_map(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b, d->n, d->k, 1, d->b_k, 0, 64, BK,
+                    "B (N-major)");
+  if (rc != MTFC_OK) return rc;
+
+  GemmArgs args;
+  args.m = (int)d->m;
+  args.n = (int)d->n;
+  args.k = (int)d->k;
+  args.batch = 1;
+  args.tiles_m = (int)((d->m + 2 * BM - 1) / (2 * BM));
+  args.tiles_n = (int)((d->n + BN - 1) / BN);
+  args.a_mn_major = a_major;
+  args.b_mn_major = b_major;
+  args.a_batched = 0;
+  args.b_batched = 0;
+  args.relu = 0;
+  args.out_f32 = 0;
+  args.status = device_status_word();
+  if (args.tiles_m > FLAG_DONE)
+    return fail(MTFC_ERR_UNSUPPORTED, "gemm_allreduce: more than %d row blocks", FLAG_DONE);
+
+  FusedArgs fa;
+  memset(&fa, 0, sizeof(fa));
+  fa.blocks_per_rank = (args.tiles_m + nranks - 1) / nranks;
+  const long long stage_rows = (long long)nranks * fa.blocks_per_rank * 2 * BM;
+  for (int p = 0; p < nranks; ++p) {
+    rc = encode_map(&fa.stage_map[p], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, stage[p], d->n, stage_rows,
+                    1, d->n, 0, 64, 32, "staging buffer");
+    if (rc != MTFC_OK) return rc;
+    fa.out[p] = static_cast<uint8_t*>(out[p]);
+    fa.flags[p] = static_cast<uint32_t*>(flags[p]);
+  }
+  fa.stage = static_cast<const uint8_t*>(stage[rank]);
+  fa.ctl = static_cast<uint32_t*>(ctl);
+  fa.rank = rank;
+  fa.nranks = nranks;
+  const long long num_tiles = (long long)args.tiles_m * args.tiles_n;
+  long long gemm_clusters = pair_clusters - comm_clusters;
+  if (num_tiles < gemm_clusters) gemm_clusters = num_tiles;
+  fa.gemm_clusters = (int)gemm_clusters;
+
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  MTFC_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !attr_set[dev]) {
+    MTFC_CUDA(cudaFuncSetAttribute(einsum_gemm_allreduce_2cta,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_ALLOC));
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * (gemm_clusters + comm_clusters)), 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = SMEM2_ALLOC;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MTFC_CUDA(cudaLaunchKernelEx(&cfg, einsum_gemm_allreduce_2cta, map_a, map_b, args, fa));
   return MTFC_OK;
 }
 

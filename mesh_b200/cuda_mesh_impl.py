@@ -383,6 +383,12 @@ class SlicedMeshImpl(mtf.MeshImpl):
     return self.LaidOutTensor([result])
 
 
+class _PeerWorkspace(object):
+  """Buffers of one fused einsum+allreduce shape (see CudaMeshImpl._peer_workspace)."""
+  __slots__ = ("tensors", "handles", "out_tensor", "ctl", "stage_ptrs", "out_ptrs", "flag_ptrs",
+               "rank", "nranks")
+
+
 class _PendingAllreduce(object):
   """Result of einsum_allreduce: the reduced slice once its chunked allreduces
   are waited for (the wait is a stream dependency, not a host block)."""
@@ -508,6 +514,12 @@ class CudaMeshImpl(SlicedMeshImpl):
   # and the smallest number of output rows per chunk worth a separate launch
   OVERLAP_CHUNKS = 4
   OVERLAP_MIN_ROWS = 2048
+  # GEMM and allreduce in one kernel over peer memory (mtfc_gemm_allreduce);
+  # falls back to the chunked GEMM + NCCL sequence when the einsum is not a
+  # single bf16 GEMM or peer memory cannot be set up.
+  FUSED_ALLREDUCE = False
+  FUSED_COMM_CLUSTERS = 8
+  FUSED_MIN_BYTES = 1 << 20
 
   def einsum_allreduce(self, equation, inputs, mesh_axes):
     """Contraction whose SUM allreduce over `mesh_axes` starts chunk by chunk.
@@ -539,9 +551,13 @@ class CudaMeshImpl(SlicedMeshImpl):
       return None
     pnum = self._local_pnums[0]
     ops = self._ops_for(pnum)
-    pg, _ = self._group(mesh_axes)
+    pg, members = self._group(mesh_axes)
     sizes = dict(zip(ta, a.shape))
     sizes.update(zip(tb, b.shape))
+    if self.FUSED_ALLREDUCE and 2 <= len(members) <= 8 and a.dtype.name == "bfloat16":
+      fused = self._einsum_allreduce_fused(ops, equation, a, b, pg, members, pnum)
+      if fused is not None:
+        return _PendingAllreduce(self, fused, [])
     out = ops._empty([sizes[l] for l in out_term], a.dtype)
     flat = out.buf[out.offset:out.offset + out.size]
     chunk_elems = out.size // self.OVERLAP_CHUNKS
@@ -555,6 +571,87 @@ class CudaMeshImpl(SlicedMeshImpl):
       works.append(dist.all_reduce(flat[i * chunk_elems:(i + 1) * chunk_elems],
                                    op=dist.ReduceOp.SUM, group=pg, async_op=True))
     return _PendingAllreduce(self, out, works)
+
+  def _einsum_allreduce_fused(self, ops, equation, a, b, pg, members, pnum):
+    """The einsum and its allreduce over `members` as one kernel launch per
+    rank, or None when the contraction is not a single bf16 GEMM (then nothing
+    has been launched)."""
+    import ctypes
+    import torch
+    from mesh_b200 import _native as nat
+    lib = nat.lib()
+    state = {}
+
+    def hook(desc, a_ptr, b_ptr, stored_shape):
+      nbytes = int(desc.m) * int(desc.n) * 2
+      if desc.n % 8 != 0 or nbytes < self.FUSED_MIN_BYTES:
+        return None
+      ws = self._peer_workspace(pg, members, pnum, int(desc.m), int(desc.n))
+      if ws is None:
+        return None
+      nat.check(lib.mtfc_gemm_allreduce(
+          ctypes.byref(desc), ctypes.c_void_p(a_ptr), ctypes.c_void_p(b_ptr), ws.stage_ptrs,
+          ws.out_ptrs, ws.flag_ptrs, ctypes.c_void_p(ws.ctl.data_ptr()), ws.rank, ws.nranks,
+          self.FUSED_COMM_CLUSTERS, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+      state["ran"] = True
+      # the workspace is reused by the next contraction of this size: hand back a copy
+      flat = ws.out_tensor[:nbytes].view(torch.bfloat16).clone()
+      return self._device_array(flat, stored_shape, a.dtype)
+
+    res = ops.einsum(equation, a, b, gemm_hook=hook)
+    return res if state.get("ran") else None
+
+  def _peer_workspace(self, pg, members, pnum, m, n):
+    """Peer-mapped staging / output / flag buffers for an [m, n] bf16 GEMM that
+    is allreduced over `members` (created collectively on first use: every rank
+    of the group reaches this point for the same contraction).  None when
+    symmetric memory is unavailable."""
+    import ctypes
+    import torch
+    import torch.distributed as dist
+    from mesh_b200 import _native as nat
+    key = (tuple(members), m, n)
+    if not hasattr(self, "_peer_ws"):
+      self._peer_ws = {}
+    if key in self._peer_ws:
+      return self._peer_ws[key]
+    ws = None
+    try:
+      import torch.distributed._symmetric_memory as symm
+      dev = torch.device("cuda", torch.cuda.current_device())
+      lib = nat.lib()
+      nbytes = m * n * 2
+
+      def alloc(size):
+        t = symm.empty(size, dtype=torch.uint8, device=dev)
+        return t, symm.rendezvous(t, pg)
+      part_t, part_h = alloc(int(lib.mtfc_gemm_allreduce_stage_bytes(m, n, len(members))))
+      out_t, out_h = alloc(nbytes)
+      flag_t, flag_h = alloc(int(lib.mtfc_gemm_allreduce_flag_bytes()))
+      flag_t.zero_()
+      ctl = torch.zeros(2, dtype=torch.int32, device=dev)
+      torch.cuda.synchronize()
+      dist.barrier(group=pg)
+
+      def ptr_array(handle):
+        ptrs = list(handle.buffer_ptrs)
+        return (ctypes.c_void_p * len(ptrs))(*[ctypes.c_void_p(int(p)) for p in ptrs])
+      ws = _PeerWorkspace()
+      ws.tensors = (part_t, out_t, flag_t)
+      ws.handles = (part_h, out_h, flag_h)
+      ws.out_tensor = out_t
+      ws.ctl = ctl
+      ws.stage_ptrs, ws.out_ptrs, ws.flag_ptrs = ptr_array(part_h), ptr_array(out_h), ptr_array(flag_h)
+      ws.rank, ws.nranks = members.index(pnum), len(members)
+      if int(part_h.rank) != ws.rank or int(part_h.world_size) != ws.nranks:
+        raise RuntimeError("symmetric-memory rank %d/%d does not match mesh group position %d/%d"
+                           % (part_h.rank, part_h.world_size, ws.rank, ws.nranks))
+    except Exception as e:  # pylint: disable=broad-except
+      import warnings
+      warnings.warn("peer memory for the fused einsum+allreduce unavailable (%r); using NCCL" % (e,))
+      ws = None
+    self._peer_ws[key] = ws
+    return ws
 
   def _as_torch(self, s):
     packed = self._ops.contiguous(s)

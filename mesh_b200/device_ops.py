@@ -404,7 +404,8 @@ class DeviceOps(object):
     return self._broadcast_reduce("SUM", list(xs), [sizes[l] for l in out_term], out_strides,
                                   [sizes[l] for l in red], red_strides, xs[0].dtype)
 
-  def einsum(self, equation, *xs, epilogue=nat.EPILOGUE_NONE, out_dtype=None, out=None):
+  def einsum(self, equation, *xs, epilogue=nat.EPILOGUE_NONE, out_dtype=None, out=None,
+             gemm_hook=None):
     """Contraction on the GEMM kernels; operand layouts are read in place.
 
     Dims are classed as batch (in both operands and the output), M (first
@@ -413,7 +414,17 @@ class DeviceOps(object):
     named-dim order goes to the kernel as strides; otherwise the operands are
     packed first and the result is unpacked.  `out`, a contiguous array of the
     result's shape, receives the result in place when given.
+
+    `gemm_hook(desc, a_ptr, b_ptr, stored_shape)` is offered the launch when
+    the contraction comes down to ONE bf16 -> bf16 GEMM without batch or
+    epilogue (desc describes a dense row-major [m, n] output): it may run the
+    product itself (e.g. fused with an allreduce) and return the array of
+    `stored_shape` that holds the result, or return None to decline.  An
+    einsum that needs packing, a pre-reduction or another kernel never reaches
+    the hook (the hook itself knows whether it ran).
     """
+    if gemm_hook is not None:
+      return self._einsum_impl(equation, xs, epilogue, out_dtype, None, gemm_hook)
     if out is not None:
       res = self._einsum_impl(equation, xs, epilogue, out_dtype, out)
       if res is not out:
@@ -421,7 +432,7 @@ class DeviceOps(object):
       return out
     return self._einsum_impl(equation, xs, epilogue, out_dtype, None)
 
-  def _einsum_impl(self, equation, xs, epilogue, out_dtype, out_buf):
+  def _einsum_impl(self, equation, xs, epilogue, out_dtype, out_buf, gemm_hook=None):
     terms, out_term = self._parse(equation, len(xs))
     if len(xs) == 1:
       return self.einsum_naive(equation, *xs)
@@ -531,6 +542,13 @@ class DeviceOps(object):
     d.out_dtype = _CODE[out_dtype.name]
     d.epilogue = epilogue
     d.force_path = 0
+    if (gemm_hook is not None and nb == 1 and epilogue == nat.EPILOGUE_NONE
+        and a.dtype.name == "bfloat16" and b.dtype.name == "bfloat16"
+        and out_dtype.name == "bfloat16"):
+      hooked = gemm_hook(d, a.ptr, b.ptr, [sizes[l] for l in store])
+      if hooked is not None:
+        res = hooked if view_perm == list(range(len(store))) else self.transpose(hooked, view_perm)
+        return res
     self._call(self._lib.mtfc_gemm, ctypes.byref(d), ctypes.c_void_p(a.ptr),
                ctypes.c_void_p(b.ptr), ctypes.c_void_p(out.ptr), self._stream())
     return result

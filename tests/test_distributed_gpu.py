@@ -84,6 +84,53 @@ def _worker(rank, world, port, out_dir):
     assert __import__("mesh_b200._native", fromlist=["x"]).launch_count() - launches >= 1 + eager.OVERLAP_CHUNKS
     assert rel_err(got2, ref) < 2e-2 and cg2 == cr
 
+    # the same with the contraction and its allreduce as ONE kernel over peer memory
+    # (mtfc_gemm_allreduce): three lowerings on the same buffers (the flag epochs
+    # advance), then the recorded lowering replayed as a CUDA graph
+    def ffn_big(backend, replay=False):
+      rr = rng(3)
+      g = mtf.Graph()
+      m = mtf.Mesh(g, "m")
+      x = rr.standard_normal((8, 150, 128)).astype(np.float32)
+      wi = (rr.standard_normal((128, 512)) / 11).astype(np.float32)
+      wo = (rr.standard_normal((512, 128)) / 22).astype(np.float32)
+      X = mtf.import_tf_tensor(m, x, "batch:8,length:150,d_model:128", dtype=mtf.bfloat16)
+      WI = mtf.import_tf_tensor(m, wi, "d_model:128,d_ff:512", dtype=mtf.bfloat16)
+      WO = mtf.import_tf_tensor(m, wo, "d_ff:512,d_model:128", dtype=mtf.bfloat16)
+      y = mtf.layers.dense_relu_dense(X, mtf.Dimension("d_ff", 512), wi=WI, wo=WO)
+      if not replay:
+        return mtf.Lowering(g, {m: backend}).export_to_tf_tensor(y)
+      res, run = backend.capture(lambda: mtf.Lowering(g, {m: backend}).tensors[y].to_laid_out_tensor())
+      outs = []
+      for _ in range(3):
+        run()
+        outs.append(ops.to_host(res.tensor_list[0]))
+      return outs
+    fused = CudaMeshImpl(mesh_shape, "d_ff:all", list(range(world)))
+    fused.OVERLAP_MIN_ROWS = 1
+    fused.FUSED_ALLREDUCE = True
+    fused.FUSED_MIN_BYTES = 1
+    ref_big = ffn_big(ora)
+    nat_mod = __import__("mesh_b200._native", fromlist=["x"])
+    for _ in range(3):
+      before = nat_mod.launch_count()
+      got_big = ffn_big(fused)
+      used = nat_mod.launch_count() - before
+      assert rel_err(got_big, ref_big) < 2e-2
+    ws = [w for w in getattr(fused, "_peer_ws", {}).values()]
+    assert ws and all(w is not None for w in ws), "the fused einsum+allreduce path did not run"
+    assert used < 1 + fused.OVERLAP_CHUNKS + 4   # one launch for the contraction, not one per chunk
+    assert nat_mod.device_status() == 0
+    for o in ffn_big(fused, replay=True):
+      assert rel_err(o, ref_big) < 2e-2
+    # every rank holds the same bits
+    import torch
+    mine = torch.from_numpy(np.ascontiguousarray(got_big).view(np.int32).astype(np.int64)).cuda().sum().reshape(1)
+    hi, lo = mine.clone(), mine.clone()
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    assert int(hi.item()) == int(lo.item())
+
     layout = "batch:all;experts:all"
 
     def moe(backend):
