@@ -101,17 +101,17 @@ int mtfc_gemm_uses_tensor_cores(const mtfc_gemm_desc* desc, const void* a,
  * allreduce itself: placement_mesh_impl.py:358-391).  One kernel launch per rank.
  * Row blocks of 256 output rows are owned round-robin; every rank's epilogue
  * stores its partial tiles into the owner's staging buffer (peer memory), and
- * `comm_clusters` CTA pairs of the grid add the nranks copies of each owned block
- * (fp32, rank order, one rounding to bf16) and write the sum into every rank's
- * `out` buffer while the other CTAs are still multiplying.  All ranks of the
- * group must call it in the same order with the same shapes.
+ * four extra warps in every CTA add the nranks copies of the owned blocks (fp32,
+ * rank order, one rounding to bf16) and write the sums into every rank's `out`
+ * buffer while the MMA pipeline is still multiplying the later blocks.  All ranks
+ * of the group must call it in the same order with the same shapes.
  *
  * desc: batch 1, bf16 in, bf16 out, c_m == n, c_n == 1, n % 8 == 0, no epilogue.
  * stage_ptrs / out_ptrs / flag_ptrs: nranks device addresses each, index r =
  * rank r's buffer as mapped into THIS process (peer-accessible: CUDA VMM or IPC
  * mappings).  stage is mtfc_gemm_allreduce_stage_bytes(m, n, nranks) bytes, out
  * is m*n bf16, flags is mtfc_gemm_allreduce_flag_bytes() bytes zeroed once before
- * first use and owned by this (m, n, group) from then on.  ctl: 8 bytes of this
+ * first use and owned by this (m, n, group) from then on.  ctl: 16 bytes of this
  * rank's own device memory, zeroed once.  Waits on peers are bounded (~3 s); a
  * peer that never arrives gives MTFC_ERR_TIMEOUT in mtfc_device_status, after
  * which the buffers must be re-created.
@@ -121,7 +121,7 @@ int64_t mtfc_gemm_allreduce_stage_bytes(int64_t m, int64_t n, int nranks);
 int mtfc_gemm_allreduce(const mtfc_gemm_desc* desc, const void* a, const void* b,
                         void* const* stage_ptrs, void* const* out_ptrs,
                         void* const* flag_ptrs, void* ctl, int rank, int nranks,
-                        int comm_clusters, void* stream);
+                        void* stream);
 
 /* K1f on the tensor cores: fp32 [batch, rows, k] (element strides s_*) -> bf16
  * [batch, rows, 6k], every value split into three bf16 terms laid along K

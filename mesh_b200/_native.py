@@ -73,7 +73,7 @@ def _declare(lib):
       "mtfc_gemm_allreduce_flag_bytes": [],
       "mtfc_gemm_allreduce_stage_bytes": [i64, i64, i32],
       "mtfc_gemm_allreduce": [ctypes.POINTER(GemmDesc), vp, vp, ctypes.POINTER(vp), ctypes.POINTER(vp),
-                              ctypes.POINTER(vp), vp, i32, i32, i32, vp],
+                              ctypes.POINTER(vp), vp, i32, i32, vp],
       "mtfc_split_bf16x3": [vp, i64, i64, i64, vp, i64, i64, i64, i32, vp],
       "mtfc_attention_set_variant": [i32],
       "mtfc_attention_supported": [i64, p_i64, p_i64, p_i64, p_i64],

@@ -62,7 +62,7 @@ int gemm_allreduce_flag_bytes();
 long long gemm_allreduce_stage_bytes(long long m, long long n, int nranks);
 int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
                           void* const* stage, void* const* out, void* const* flags, void* ctl,
-                          int rank, int nranks, int comm_clusters, cudaStream_t stream);
+                          int rank, int nranks, cudaStream_t stream);
 
 }  // namespace mtfc
 
@@ -133,12 +133,12 @@ int64_t mtfc_gemm_allreduce_stage_bytes(int64_t m, int64_t n, int nranks) {
 
 int mtfc_gemm_allreduce(const mtfc_gemm_desc* d, const void* a, const void* b,
                         void* const* stage_ptrs, void* const* out_ptrs, void* const* flag_ptrs,
-                        void* ctl, int rank, int nranks, int comm_clusters, void* stream) {
+                        void* ctl, int rank, int nranks, void* stream) {
   if (!d || !a || !b) return fail(MTFC_ERR_SHAPE, "gemm_allreduce: null argument");
   if (d->batch < 1 || d->m < 1 || d->n < 1 || d->k < 1)
     return fail(MTFC_ERR_SHAPE, "gemm_allreduce: empty problem");
   int rc = gemm_allreduce_launch(d, a, b, stage_ptrs, out_ptrs, flag_ptrs, ctl, rank, nranks,
-                                 comm_clusters, static_cast<cudaStream_t>(stream));
+                                 static_cast<cudaStream_t>(stream));
   if (rc == MTFC_OK) count_launch(1);
   return rc;
 }

@@ -379,26 +379,35 @@ __device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_des
 // round-robin (block rb by rank rb % nranks).  The epilogue of every rank stores
 // its partial tile straight into the OWNER's staging buffer (a TMA store into
 // peer memory: slot [source rank][k-th owned block]), so the reduce-scatter half
-// of the exchange rides on stores the epilogue issues anyway.  A few clusters of
-// the grid (the "comm" CTAs) do no MMA work: once all ranks have delivered a row
-// block this rank owns, they add its nranks partial copies (local reads, fp32,
-// in rank order, one rounding to bf16) and write the sum into every rank's
-// output buffer (plain 16-byte stores, local and peer).  GEMM clusters walk the
-// tiles row block by row block, so block i is exchanged while the blocks after
-// it are still being multiplied.
+// of the exchange rides on stores the epilogue issues anyway.  Every CTA carries
+// four extra "comm" warps that take no part in the product: once all ranks have
+// delivered a row block this rank owns, the comm warps of one CTA add the nranks
+// partial copies of a slice of it (local reads, fp32, in rank order, one rounding
+// to bf16) and write the sum into every rank's output buffer (plain 16-byte
+// stores, local and peer).  The loop is bound by memory latency, so spreading it
+// over all SMs (beside the MMA pipeline, which leaves the load/store units idle)
+// buys the bytes in flight that a few dedicated CTAs cannot have.  Clusters walk
+// the tiles row block by row block, so block i is exchanged while the blocks
+// after it are still being multiplied.
 //
 // Flags (uint32, in peer-visible memory, never reset; a launch compares against
 // epoch * count): flags[rb] on the owner of row block rb counts epilogue warps
 // of all ranks that have delivered their part of rb; flags[FLAG_DONE] on every
-// rank counts row blocks written into that rank's output.  `ctl` is this rank's
-// private pair {launches completed, comm CTAs finished in this launch}; keeping
+// rank counts row-block slices written into that rank's output.  `ctl` is this rank's
+// private triple {launches completed, CTAs whose comm warps finished in this launch,
+// next slice to hand out}; keeping
 // the epoch on the device lets a captured launch be replayed.  Every wait is
 // bounded: a rank whose peers never show up raises MTFC_ERR_TIMEOUT in the status
 // word and returns.
 constexpr int MAX_RANKS = 8;
 constexpr int FLAG_DONE = 4096;  // row-block counters live in [0, FLAG_DONE)
-constexpr int COMM_UNROLL = 8;   // 16-byte vectors per thread and source in flight
+constexpr int COMM_UNROLL = 8;   // 16-byte vectors per thread in flight, general rank count
+constexpr int COMM_LOADS = 32;   // 16-byte loads per thread in flight for 2, 4 or 8 ranks
 constexpr long long PEER_WAIT_CYCLES = 6000000000LL;  // ~3 s
+constexpr int COMM_UNIT_ROWS = 32;
+constexpr int COMM_WARPS = 4;
+constexpr int COMM_THREADS = 32 * COMM_WARPS;
+constexpr int NUM_THREADS_FUSED = NUM_THREADS + COMM_THREADS;
 
 struct FusedArgs {
   CUtensorMap stage_map[MAX_RANKS];  // rank o's staging buffer [nranks * blocks_per_rank * 256, n]
@@ -408,7 +417,6 @@ struct FusedArgs {
   uint32_t* ctl;
   int rank, nranks;
   int blocks_per_rank;
-  int gemm_clusters;
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -428,15 +436,26 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target)
     __nanosleep(128);
   }
 }
-// 16-byte load that never hits a stale L1 line (the data was written by TMA
+// 16-byte load served from L2, which never hits a stale L1 line (the data was written by TMA
 // stores of other SMs and other GPUs during this launch).
-__device__ __forceinline__ uint4 ld_cv_v4(const void* p) {
+__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
   uint4 v;
-  asm volatile("ld.global.cv.v4.u32 {%0, %1, %2, %3}, [%4];"
+  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(p)
                : "memory");
   return v;
+}
+// cp.async.bulk.wait_group with a run-time count: returns once at most `pending`
+// of this thread's newest bulk groups are still incomplete (0..4).
+__device__ __forceinline__ void bulk_wait_upto(int pending) {
+  switch (pending) {
+    case 0: asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.bulk.wait_group 3;" ::: "memory"); break;
+    default: asm volatile("cp.async.bulk.wait_group 4;" ::: "memory"); break;
+  }
 }
 __device__ __forceinline__ void st_v4(void* p, const uint4& v) {
   asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
@@ -444,84 +463,137 @@ __device__ __forceinline__ void st_v4(void* p, const uint4& v) {
                : "memory");
 }
 
-// One comm CTA: reduces the row blocks this rank owns, every num_comm-th of them.
-__device__ void allreduce_comm_cta(uint8_t* smem, const GemmArgs& args, const FusedArgs& fa,
-                                   int comm_idx, int num_comm) {
+// acc += the eight bf16 values of x, widened exactly to fp32.
+__device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4& x) {
+  const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    acc[2 * e] += __uint_as_float(w[e] << 16);
+    acc[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+  }
+}
+
+// Sum of the n copies of part of a row block (src0 + s * src_stride, s < n),
+// nvec 16-byte vectors, written to every rank's output at out_off.  NR = n when
+// n is 2, 4 or 8: the loads of all copies of COMM_LOADS / NR vectors are in
+// flight together; NR = 1 is the general form, one copy at a time.
+template <int NR>
+__device__ __forceinline__ void reduce_block(const uint8_t* src0, long long src_stride,
+                                             uint8_t* const* out, long long out_off,
+                                             long long nvec, int n, int tid) {
+  constexpr int U = NR == 1 ? COMM_UNROLL : COMM_LOADS / NR;
+  for (long long v0 = tid; v0 < nvec; v0 += (long long)COMM_THREADS * U) {
+    float acc[U][8];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+    if (NR == 1) {
+      for (int s = 0; s < n; ++s) {
+        uint4 x[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long v = v0 + (long long)u * COMM_THREADS;
+          x[u] = v < nvec ? ld_cg_v4(src0 + s * src_stride + v * 16) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) add_bf16x8(acc[u], x[u]);
+      }
+    } else {
+      uint4 x[NR][U];
+#pragma unroll
+      for (int s = 0; s < NR; ++s)
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long v = v0 + (long long)u * COMM_THREADS;
+          x[s][u] = v < nvec ? ld_cg_v4(src0 + s * src_stride + v * 16) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+      for (int s = 0; s < NR; ++s)   // rank order, the same on every owner
+#pragma unroll
+        for (int u = 0; u < U; ++u) add_bf16x8(acc[u], x[s][u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + (long long)u * COMM_THREADS;
+      if (v < nvec) {
+        uint4 o;
+        o.x = pack_bf16x2(acc[u][0], acc[u][1]);
+        o.y = pack_bf16x2(acc[u][2], acc[u][3]);
+        o.z = pack_bf16x2(acc[u][4], acc[u][5]);
+        o.w = pack_bf16x2(acc[u][6], acc[u][7]);
+        for (int p = 0; p < n; ++p) st_v4(out[p] + out_off + v * 16, o);
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void comm_warps_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(COMM_THREADS) : "memory");
+}
+
+// The comm warps of one CTA (threads NUM_THREADS ..).  Work units are slices of
+// COMM_UNIT_ROWS rows of the row blocks this rank owns, numbered in the order the
+// blocks complete and claimed one at a time from a counter (ctl[2]): whichever
+// CTA is free takes the next slice, so the slices of the last blocks - the only
+// ones not hidden behind the product - spread over all SMs.
+__device__ void allreduce_comm_warps(uint8_t* smem, const GemmArgs& args, const FusedArgs& fa) {
   const int n = fa.nranks;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SMEM2_MISC + 4);
-  volatile uint32_t* epoch_slot = reinterpret_cast<volatile uint32_t*>(smem + SMEM2_MISC + 8);
-  const int tid = threadIdx.x;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SMEM2_MISC + 12);
+  volatile uint32_t* word = reinterpret_cast<volatile uint32_t*>(smem + SMEM2_MISC + 8);
+  const int tid = (int)threadIdx.x - NUM_THREADS;
   if (tid == 0) {
     *abort_flag = 0;
-    *epoch_slot = ld_acquire_sys(fa.ctl) + 1u;
+    *word = ld_acquire_sys(fa.ctl) + 1u;
   }
-  __syncthreads();
-  const uint32_t epoch = *epoch_slot;
+  comm_warps_sync();
+  const uint32_t epoch = *word;
+  comm_warps_sync();
+  constexpr int UNITS = 2 * BM / COMM_UNIT_ROWS;  // per row block
   const long long row_bytes = (long long)args.n * 2;
   const long long block_bytes = 2LL * BM * row_bytes;
   const int num_rb = args.tiles_m;
+  const int owned = num_rb > fa.rank ? (num_rb - fa.rank + n - 1) / n : 0;
   const uint32_t ready_target = epoch * (uint32_t)(n * args.tiles_n * 2 * EPI_WARPS);
   bool ok = true;
-  for (int k = comm_idx; ok; k += num_comm) {
+  for (;;) {
+    if (tid == 0) *word = atomicAdd(fa.ctl + 2, 1u);
+    comm_warps_sync();
+    const int w = (int)*word;
+    comm_warps_sync();
+    if (w >= UNITS * owned) break;
+    const int k = w / UNITS, sub = w % UNITS;
     const int rb = fa.rank + n * k;
-    if (rb >= num_rb) break;
     if (tid == 0 && !wait_flag_ge(fa.flags[fa.rank] + rb, ready_target)) *abort_flag = 1;
-    __syncthreads();
+    comm_warps_sync();
     if (*abort_flag) { ok = false; break; }
-    const int rows = min(2 * BM, args.m - rb * 2 * BM);
+    const int rows = max(0, min(COMM_UNIT_ROWS, args.m - rb * 2 * BM - sub * COMM_UNIT_ROWS));
     const long long nvec = (rows * row_bytes) >> 4;
-    const long long out_base = (long long)rb * block_bytes;
-    for (long long v0 = tid; v0 < nvec; v0 += (long long)NUM_THREADS * COMM_UNROLL) {
-      float acc[COMM_UNROLL][8];
-#pragma unroll
-      for (int u = 0; u < COMM_UNROLL; ++u)
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
-      for (int s = 0; s < n; ++s) {
-        const uint8_t* src = fa.stage + ((long long)s * fa.blocks_per_rank + k) * block_bytes;
-        uint4 x[COMM_UNROLL];
-#pragma unroll
-        for (int u = 0; u < COMM_UNROLL; ++u) {
-          const long long v = v0 + (long long)u * NUM_THREADS;
-          x[u] = v < nvec ? ld_cv_v4(src + v * 16) : make_uint4(0u, 0u, 0u, 0u);
-        }
-#pragma unroll
-        for (int u = 0; u < COMM_UNROLL; ++u) {
-          const uint32_t w[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            acc[u][2 * e] += __uint_as_float(w[e] << 16);
-            acc[u][2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < COMM_UNROLL; ++u) {
-        const long long v = v0 + (long long)u * NUM_THREADS;
-        if (v < nvec) {
-          uint4 o;
-          o.x = pack_bf16x2(acc[u][0], acc[u][1]);
-          o.y = pack_bf16x2(acc[u][2], acc[u][3]);
-          o.z = pack_bf16x2(acc[u][4], acc[u][5]);
-          o.w = pack_bf16x2(acc[u][6], acc[u][7]);
-          for (int p = 0; p < n; ++p) st_v4(fa.out[p] + out_base + v * 16, o);
-        }
-      }
+    const long long sub_off = (long long)sub * COMM_UNIT_ROWS * row_bytes;
+    const uint8_t* src0 = fa.stage + (long long)k * block_bytes + sub_off;
+    const long long src_stride = (long long)fa.blocks_per_rank * block_bytes;
+    const long long out_off = (long long)rb * block_bytes + sub_off;
+    switch (n) {
+      case 2: reduce_block<2>(src0, src_stride, fa.out, out_off, nvec, n, tid); break;
+      case 4: reduce_block<4>(src0, src_stride, fa.out, out_off, nvec, n, tid); break;
+      case 8: reduce_block<8>(src0, src_stride, fa.out, out_off, nvec, n, tid); break;
+      default: reduce_block<1>(src0, src_stride, fa.out, out_off, nvec, n, tid); break;
     }
     // every thread's stores are ordered before the flag update made on its behalf
     __threadfence_system();
-    __syncthreads();
+    comm_warps_sync();
     if (tid == 0)
       for (int p = 0; p < n; ++p) red_release_sys_add(fa.flags[p] + FLAG_DONE, 1u);
   }
   if (tid == 0) {
     if (!ok) {
       if (args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
-    } else if (atomicAdd(fa.ctl + 1, 1u) == (uint32_t)(num_comm - 1)) {
-      // last comm CTA of this launch: the output is whole once every row block
+    } else if (atomicAdd(fa.ctl + 1, 1u) == gridDim.x - 1) {
+      // last CTA of this launch: the output is whole once every half row block
       // has been written here, and only then may the next launch start
-      if (wait_flag_ge(fa.flags[fa.rank] + FLAG_DONE, epoch * (uint32_t)num_rb)) {
+      if (wait_flag_ge(fa.flags[fa.rank] + FLAG_DONE, epoch * (uint32_t)(UNITS * num_rb))) {
         fa.ctl[1] = 0u;
+        fa.ctl[2] = 0u;
         __threadfence();
         fa.ctl[0] = epoch;
       } else if (args.status) {
@@ -565,13 +637,6 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const bool leader = rank == 0;
 
-  if (FUSED && (int)(blockIdx.x >> 1) >= fa->gemm_clusters) {
-    // comm cluster: no MMA work, no TMEM, no cluster barriers
-    allreduce_comm_cta(smem, args, *fa, (int)blockIdx.x - 2 * fa->gemm_clusters,
-                       (int)gridDim.x - 2 * fa->gemm_clusters);
-    return;
-  }
-
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES2; ++s) {
       mbar_init(full_bar(s), 1);   // leader's: its producer's expect_tx arrival
@@ -601,7 +666,7 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
   const long long tiles_per_batch = (long long)args.tiles_m * args.tiles_n;  // 256x256 tiles
   const long long num_tiles = tiles_per_batch * args.batch;
   const long long cluster_id = blockIdx.x >> 1;
-  const long long num_clusters = FUSED ? (long long)fa->gemm_clusters : (long long)(gridDim.x >> 1);
+  const long long num_clusters = gridDim.x >> 1;
 
   if (warp == 0) {
     // ------------------------------------------------ TMA producer (both CTAs)
@@ -682,6 +747,9 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
       }
       if (!ok && args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
     }
+  } else if (FUSED && warp >= 2 + EPI_WARPS) {
+    // ------------------------------------------------ comm warps (fused kernel only)
+    allreduce_comm_warps(smem, args, *fa);
   } else {
     // ------------------------------------------------ epilogue (both CTAs)
     const int q = warp & 3;
@@ -692,7 +760,9 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
     bool ok = true;
     long long local = 0;
     int store_idx = 0;
+    int pending_rb = -1;  // fused: row block of the tile whose arrival is not yet signalled
     for (long long t = cluster_id; t < num_tiles && ok; t += num_clusters, ++local) {
+      const int tile_first_store = store_idx;
       const int buf = (int)(local & 1);
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
       const int b = (int)(t / tiles_per_batch);
@@ -771,14 +841,22 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(tmem_empty_bar(buf), 0));
       if (FUSED && lane == 0) {
-        // this warp's part of the tile has arrived at its owner (complete, not
-        // merely read out of the staging buffers): count it there
-        tma_store_wait_all();
-        __threadfence_system();
-        red_release_sys_add(fa->flags[rb % fa->nranks] + rb, 1u);
+        // Tell the owner of the PREVIOUS tile's row block that this warp's part of
+        // it has arrived (complete, not merely read out of the staging buffers):
+        // waiting for all but this tile's store groups costs nothing, while
+        // waiting for this tile's own would stall the epilogue for a round trip
+        // over NVLink per tile.
+        const int mine = store_idx - tile_first_store;
+        if (pending_rb >= 0) {
+          bulk_wait_upto(mine);
+          red_release_sys_add(fa->flags[pending_rb % fa->nranks] + pending_rb, 1u);
+        }
+        pending_rb = rb;
       }
     }
     if (lane == 0) tma_store_wait_all();
+    if (FUSED && lane == 0 && pending_rb >= 0)
+      red_release_sys_add(fa->flags[pending_rb % fa->nranks] + pending_rb, 1u);
     if (!ok && lane == 0 && args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
   }
 
@@ -801,7 +879,7 @@ einsum_gemm_tcgen05_2cta(const __grid_constant__ CUtensorMap map_a,
   pair_gemm_body<false>(map_a, map_b, map_c, args, nullptr);
 }
 
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS_FUSED, 1)
 einsum_gemm_allreduce_2cta(const __grid_constant__ CUtensorMap map_a,
                            const __grid_constant__ CUtensorMap map_b, const GemmArgs args,
                            const __grid_constant__ FusedArgs fa) {
@@ -1008,6 +1086,36 @@ int gemm_tcgen05_launch(const mtfc_gemm_desc* d, const void* a, const void* b, v
 
 int gemm_allreduce_flag_bytes() { return (FLAG_DONE + 1) * 4; }
 
+// Resident 2-CTA clusters for the fused kernel (its blocks are larger); cached per device.
+int max_fused_clusters() {
+  static int cached[64];
+  static bool known[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (!known[dev]) {
+    int n = 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (unsigned)sm_count(), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS_FUSED, 1, 1);
+    cfg.dynamicSmemBytes = SMEM2_ALLOC;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaFuncSetAttribute(einsum_gemm_allreduce_2cta, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SMEM2_ALLOC) != cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&n, einsum_gemm_allreduce_2cta, &cfg) != cudaSuccess)
+      n = 0;
+    (void)cudaGetLastError();
+    cached[dev] = n;
+    known[dev] = true;
+  }
+  return cached[dev];
+}
+
 long long gemm_allreduce_stage_bytes(long long m, long long n, int nranks) {
   if (m < 1 || n < 1 || nranks < 1) return 0;
   const long long num_rb = (m + 2 * BM - 1) / (2 * BM);
@@ -1017,10 +1125,10 @@ long long gemm_allreduce_stage_bytes(long long m, long long n, int nranks) {
 
 // GEMM with the allreduce of its bf16 [m, n] row-major output folded in (see
 // the kernel comment).  `stage`, `out` and `flags` hold every rank's buffer
-// address as seen from this process; `ctl` is this rank's private 8 bytes.
+// address as seen from this process; `ctl` is this rank's private 16 bytes.
 int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
                           void* const* stage, void* const* out, void* const* flags, void* ctl,
-                          int rank, int nranks, int comm_clusters, cudaStream_t stream) {
+                          int rank, int nranks, cudaStream_t stream) {
   if (nranks < 2 || nranks > MAX_RANKS || rank < 0 || rank >= nranks)
     return fail(MTFC_ERR_SHAPE, "gemm_allreduce: %d ranks (2..%d supported), rank %d", nranks,
                 MAX_RANKS, rank);
@@ -1036,10 +1144,8 @@ int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
       return fail(MTFC_ERR_SHAPE, "gemm_allreduce: buffer of rank %d missing or not 16-byte aligned", p);
   if (!gemm_tcgen05_eligible(d, a, b, stage[rank]))
     return fail(MTFC_ERR_UNSUPPORTED, "gemm_allreduce: operands not eligible for the tcgen05 path");
-  const int pair_clusters = max_pair_clusters();
-  if (pair_clusters < 2) return fail(MTFC_ERR_CUDA, "gemm_allreduce: no room for 2-CTA clusters");
-  if (comm_clusters < 1) comm_clusters = 1;
-  if (comm_clusters > pair_clusters - 1) comm_clusters = pair_clusters - 1;
+  const int pair_clusters = max_fused_clusters();
+  if (pair_clusters < 1) return fail(MTFC_ERR_CUDA, "gemm_allreduce: no room for 2-CTA clusters");
   const int a_major = classify(d->m, d->k, d->a_m, d->a_k, 1, 0);
   const int b_major = classify(d->n, d->k, d->b_n, d->b_k, 1, 0);
   if (a_major < 0 || b_major < 0) return fail(MTFC_ERR_SHAPE, "operand layout not TMA-able");
@@ -1093,21 +1199,11 @@ int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
   fa.rank = rank;
   fa.nranks = nranks;
   const long long num_tiles = (long long)args.tiles_m * args.tiles_n;
-  long long gemm_clusters = pair_clusters - comm_clusters;
-  if (num_tiles < gemm_clusters) gemm_clusters = num_tiles;
-  fa.gemm_clusters = (int)gemm_clusters;
-
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  MTFC_CUDA(cudaGetDevice(&dev));
-  if (dev < 64 && !attr_set[dev]) {
-    MTFC_CUDA(cudaFuncSetAttribute(einsum_gemm_allreduce_2cta,
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_ALLOC));
-    attr_set[dev] = true;
-  }
+  // every cluster must be resident at once: the comm warps wait on other CTAs' products
+  const long long clusters = num_tiles < pair_clusters ? num_tiles : pair_clusters;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(2 * (gemm_clusters + comm_clusters)), 1, 1);
-  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS_FUSED, 1, 1);
   cfg.dynamicSmemBytes = SMEM2_ALLOC;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

@@ -24,6 +24,8 @@ CudaMeshImpl binds it to DeviceOps and CUDA devices.
 
 from __future__ import annotations
 
+import os
+
 import numpy as np
 
 from mesh_b200 import mtf
@@ -516,9 +518,9 @@ class CudaMeshImpl(SlicedMeshImpl):
   OVERLAP_MIN_ROWS = 2048
   # GEMM and allreduce in one kernel over peer memory (mtfc_gemm_allreduce);
   # falls back to the chunked GEMM + NCCL sequence when the einsum is not a
-  # single bf16 GEMM or peer memory cannot be set up.
-  FUSED_ALLREDUCE = False
-  FUSED_COMM_CLUSTERS = 8
+  # single bf16 GEMM or peer memory cannot be set up.  MTFC_FUSED_ALLREDUCE=0/1
+  # in the environment overrides the default.
+  FUSED_ALLREDUCE = os.environ.get("MTFC_FUSED_ALLREDUCE", "0") == "1"
   FUSED_MIN_BYTES = 1 << 20
 
   def einsum_allreduce(self, equation, inputs, mesh_axes):
@@ -592,7 +594,7 @@ class CudaMeshImpl(SlicedMeshImpl):
       nat.check(lib.mtfc_gemm_allreduce(
           ctypes.byref(desc), ctypes.c_void_p(a_ptr), ctypes.c_void_p(b_ptr), ws.stage_ptrs,
           ws.out_ptrs, ws.flag_ptrs, ctypes.c_void_p(ws.ctl.data_ptr()), ws.rank, ws.nranks,
-          self.FUSED_COMM_CLUSTERS, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+          ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
       state["ran"] = True
       # the workspace is reused by the next contraction of this size: hand back a copy
       flat = ws.out_tensor[:nbytes].view(torch.bfloat16).clone()
@@ -629,7 +631,7 @@ class CudaMeshImpl(SlicedMeshImpl):
       out_t, out_h = alloc(nbytes)
       flag_t, flag_h = alloc(int(lib.mtfc_gemm_allreduce_flag_bytes()))
       flag_t.zero_()
-      ctl = torch.zeros(2, dtype=torch.int32, device=dev)
+      ctl = torch.zeros(4, dtype=torch.int32, device=dev)
       torch.cuda.synchronize()
       dist.barrier(group=pg)
 

@@ -120,7 +120,7 @@ def _worker(rank, world, port, out_dir):
     ws = [w for w in getattr(fused, "_peer_ws", {}).values()]
     assert ws and all(w is not None for w in ws), "the fused einsum+allreduce path did not run"
     assert used < 1 + fused.OVERLAP_CHUNKS + 4   # one launch for the contraction, not one per chunk
-    assert nat_mod.device_status() == 0
+    nat_mod.device_status()   # raises if a bounded wait ran out
     for o in ffn_big(fused, replay=True):
       assert rel_err(o, ref_big) < 2e-2
     # every rank holds the same bits
