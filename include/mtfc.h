@@ -101,9 +101,11 @@ int mtfc_gemm_uses_tensor_cores(const mtfc_gemm_desc* desc, const void* a,
  * allreduce itself: placement_mesh_impl.py:358-391).  One kernel launch per rank.
  * Row blocks of 256 output rows are owned round-robin; every rank's epilogue
  * stores its partial tiles into the owner's staging buffer (peer memory), and
- * four extra warps in every CTA add the nranks copies of the owned blocks (fp32,
- * rank order, one rounding to bf16) and write the sums into every rank's `out`
- * buffer while the MMA pipeline is still multiplying the later blocks.  All ranks
+ * four extra warps in every CTA add the nranks copies of the owned blocks (packed
+ * bf16 additions as a balanced tree over the ranks for 2, 4 or 8 ranks - the
+ * correctly rounded sum for 2; fp32 accumulation with one rounding otherwise) and
+ * write the sums into every rank's `out` buffer while the MMA pipeline is still
+ * multiplying the later blocks.  Every rank receives the same bits.  All ranks
  * of the group must call it in the same order with the same shapes.
  *
  * desc: batch 1, bf16 in, bf16 out, c_m == n, c_n == 1, n % 8 == 0, no epilogue.

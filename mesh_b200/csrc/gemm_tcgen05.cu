@@ -308,16 +308,26 @@ einsum_gemm_tcgen05(const __grid_constant__ CUtensorMap map_a,
 // which is what lifts the single-CTA kernel's shared-memory bandwidth ceiling.
 // No load uses multicast: each CTA fetches its own halves with plain TMA loads
 // that report to the leader's mbarrier.
-constexpr int STAGES2 = 6;
 constexpr int B2_STAGE_BYTES = (BN / 2) * BK * 2;  // 16 KiB: this CTA's half of B
-constexpr int SMEM2_A = 0;
-constexpr int SMEM2_B = SMEM2_A + STAGES2 * A_STAGE_BYTES;
-constexpr int SMEM2_EPI = SMEM2_B + STAGES2 * B2_STAGE_BYTES;
-constexpr int SMEM2_BAR = SMEM2_EPI + EPI_BYTES;
-constexpr int NUM_BARS2 = 2 * STAGES2 + 4;
-constexpr int SMEM2_MISC = SMEM2_BAR + NUM_BARS2 * 8;
-constexpr int SMEM2_USED = SMEM2_MISC + 16;
-constexpr int SMEM2_ALLOC = SMEM2_USED + 1024;
+// Shared-memory plan of the pair kernel.  The fused GEMM+allreduce variant trades
+// one pipeline stage for two more staging buffers per epilogue warp: half of its
+// output tiles are stored into a peer GPU's memory, and such a store holds its
+// staging buffer for a NVLink round trip.
+template <bool FUSED>
+struct PairCfg {
+  static constexpr int STAGES = FUSED ? 5 : 6;
+  static constexpr int EPI_BUFS = FUSED ? 4 : 2;  // staging buffers per epilogue warp
+  static constexpr int A = 0;
+  static constexpr int B = A + STAGES * A_STAGE_BYTES;
+  static constexpr int EPI = B + STAGES * B2_STAGE_BYTES;
+  static constexpr int BAR = EPI + EPI_WARPS * EPI_BUFS * EPI_BUF_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int MISC = BAR + NUM_BARS * 8;
+  static constexpr int USED = MISC + 16;
+  static constexpr int ALLOC = USED + 1024;
+};
+constexpr int SMEM2_ALLOC = PairCfg<false>::ALLOC;
+constexpr int SMEM2F_ALLOC = PairCfg<true>::ALLOC;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -382,8 +392,8 @@ __device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_des
 // of the exchange rides on stores the epilogue issues anyway.  Every CTA carries
 // four extra "comm" warps that take no part in the product: once all ranks have
 // delivered a row block this rank owns, the comm warps of one CTA add the nranks
-// partial copies of a slice of it (local reads, fp32, in rank order, one rounding
-// to bf16) and write the sum into every rank's output buffer (plain 16-byte
+// partial copies of a slice of it (local reads; see reduce_block for the
+// arithmetic) and write the sum into every rank's output buffer (plain 16-byte
 // stores, local and peer).  The loop is bound by memory latency, so spreading it
 // over all SMs (beside the MMA pipeline, which leaves the load/store units idle)
 // buys the bytes in flight that a few dedicated CTAs cannot have.  Clusters walk
@@ -473,22 +483,38 @@ __device__ __forceinline__ void add_bf16x8(float (&acc)[8], const uint4& x) {
   }
 }
 
+__device__ __forceinline__ uint32_t add_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint4 add_bf16x8_packed(const uint4& a, const uint4& b) {
+  return make_uint4(add_bf16x2(a.x, b.x), add_bf16x2(a.y, b.y), add_bf16x2(a.z, b.z),
+                    add_bf16x2(a.w, b.w));
+}
+
 // Sum of the n copies of part of a row block (src0 + s * src_stride, s < n),
-// nvec 16-byte vectors, written to every rank's output at out_off.  NR = n when
-// n is 2, 4 or 8: the loads of all copies of COMM_LOADS / NR vectors are in
-// flight together; NR = 1 is the general form, one copy at a time.
+// nvec 16-byte vectors, written to every rank's output at out_off.
+// NR = n when n is 2, 4 or 8: the loads of all copies of COMM_LOADS / NR vectors
+// are in flight together, and the sum is a balanced tree of packed bf16 additions
+// (for two ranks that is the correctly rounded sum; for four and eight, log2(n)
+// roundings, where a ring allreduce in bf16 has n - 1): four instructions per
+// 16 bytes and level, so that the warps doing this beside the MMA pipeline take
+// few issue slots.  NR = 1 is the general form: one copy at a time, accumulated
+// in fp32 and rounded once.
 template <int NR>
 __device__ __forceinline__ void reduce_block(const uint8_t* src0, long long src_stride,
                                              uint8_t* const* out, long long out_off,
                                              long long nvec, int n, int tid) {
   constexpr int U = NR == 1 ? COMM_UNROLL : COMM_LOADS / NR;
   for (long long v0 = tid; v0 < nvec; v0 += (long long)COMM_THREADS * U) {
-    float acc[U][8];
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+    uint4 res[U];
     if (NR == 1) {
+      float acc[U][8];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
       for (int s = 0; s < n; ++s) {
         uint4 x[U];
 #pragma unroll
@@ -498,6 +524,13 @@ __device__ __forceinline__ void reduce_block(const uint8_t* src0, long long src_
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) add_bf16x8(acc[u], x[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        res[u].x = pack_bf16x2(acc[u][0], acc[u][1]);
+        res[u].y = pack_bf16x2(acc[u][2], acc[u][3]);
+        res[u].z = pack_bf16x2(acc[u][4], acc[u][5]);
+        res[u].w = pack_bf16x2(acc[u][6], acc[u][7]);
       }
     } else {
       uint4 x[NR][U];
@@ -509,21 +542,19 @@ __device__ __forceinline__ void reduce_block(const uint8_t* src0, long long src_
           x[s][u] = v < nvec ? ld_cg_v4(src0 + s * src_stride + v * 16) : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
-      for (int s = 0; s < NR; ++s)   // rank order, the same on every owner
+      for (int width = NR / 2; width >= 1; width /= 2)   // ranks (0+1)+(2+3) ..., the same on every owner
 #pragma unroll
-        for (int u = 0; u < U; ++u) add_bf16x8(acc[u], x[s][u]);
+        for (int s = 0; s < width; ++s)
+#pragma unroll
+          for (int u = 0; u < U; ++u) x[s][u] = add_bf16x8_packed(x[2 * s][u], x[2 * s + 1][u]);
+#pragma unroll
+      for (int u = 0; u < U; ++u) res[u] = x[0][u];
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const long long v = v0 + (long long)u * COMM_THREADS;
-      if (v < nvec) {
-        uint4 o;
-        o.x = pack_bf16x2(acc[u][0], acc[u][1]);
-        o.y = pack_bf16x2(acc[u][2], acc[u][3]);
-        o.z = pack_bf16x2(acc[u][4], acc[u][5]);
-        o.w = pack_bf16x2(acc[u][6], acc[u][7]);
-        for (int p = 0; p < n; ++p) st_v4(out[p] + out_off + v * 16, o);
-      }
+      if (v < nvec)
+        for (int p = 0; p < n; ++p) st_v4(out[p] + out_off + v * 16, res[u]);
     }
   }
 }
@@ -539,8 +570,8 @@ __device__ __forceinline__ void comm_warps_sync() {
 // ones not hidden behind the product - spread over all SMs.
 __device__ void allreduce_comm_warps(uint8_t* smem, const GemmArgs& args, const FusedArgs& fa) {
   const int n = fa.nranks;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SMEM2_MISC + 12);
-  volatile uint32_t* word = reinterpret_cast<volatile uint32_t*>(smem + SMEM2_MISC + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + PairCfg<true>::MISC + 12);
+  volatile uint32_t* word = reinterpret_cast<volatile uint32_t*>(smem + PairCfg<true>::MISC + 8);
   const int tid = (int)threadIdx.x - NUM_THREADS;
   if (tid == 0) {
     *abort_flag = 0;
@@ -579,11 +610,13 @@ __device__ void allreduce_comm_warps(uint8_t* smem, const GemmArgs& args, const 
       case 8: reduce_block<8>(src0, src_stride, fa.out, out_off, nvec, n, tid); break;
       default: reduce_block<1>(src0, src_stride, fa.out, out_off, nvec, n, tid); break;
     }
-    // every thread's stores are ordered before the flag update made on its behalf
-    __threadfence_system();
+    // the barrier orders every thread's stores before thread 0's release, which
+    // is cumulative: one system-scope release per slice instead of 128 fences
     comm_warps_sync();
-    if (tid == 0)
+    if (tid == 0) {
+      __threadfence_system();
       for (int p = 0; p < n; ++p) red_release_sys_add(fa.flags[p] + FLAG_DONE, 1u);
+    }
   }
   if (tid == 0) {
     if (!ok) {
@@ -620,17 +653,19 @@ template <bool FUSED>
 __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const CUtensorMap& map_b,
                                                const CUtensorMap& map_c, const GemmArgs& args,
                                                const FusedArgs* fa) {
+  using Cfg = PairCfg<FUSED>;
+  constexpr int STAGES2 = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t bar_base = smem_base + SMEM2_BAR;
+  const uint32_t bar_base = smem_base + Cfg::BAR;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES2 + s); };
   auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * STAGES2 + b); };
   auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES2 + 2 + b); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + SMEM2_MISC);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SMEM2_MISC + 4);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Cfg::MISC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::MISC + 4);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -651,7 +686,7 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_base + SMEM2_MISC),
+                     smem_base + Cfg::MISC),
                  "r"(TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
@@ -685,8 +720,8 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
           if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
           if (leader) mbar_expect_tx(full_bar(stage), 2 * (A_STAGE_BYTES + B2_STAGE_BYTES));
           const uint32_t lead_full = map_to_cta(full_bar(stage), 0);
-          const uint32_t sa = smem_base + SMEM2_A + stage * A_STAGE_BYTES;
-          const uint32_t sb = smem_base + SMEM2_B + stage * B2_STAGE_BYTES;
+          const uint32_t sa = smem_base + Cfg::A + stage * A_STAGE_BYTES;
+          const uint32_t sb = smem_base + Cfg::B + stage * B2_STAGE_BYTES;
           const int k0 = kb * BK;
           if (args.a_mn_major) {
 #pragma unroll
@@ -728,8 +763,8 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_base + SMEM2_A + stage * A_STAGE_BYTES;
-          const uint32_t sb = smem_base + SMEM2_B + stage * B2_STAGE_BYTES;
+          const uint32_t sa = smem_base + Cfg::A + stage * A_STAGE_BYTES;
+          const uint32_t sb = smem_base + Cfg::B + stage * B2_STAGE_BYTES;
 #pragma unroll
           for (int ks = 0; ks < BK / UMMA_K; ++ks) {
             const uint64_t da = make_smem_desc(sa + ks * a_kstep, a_lbo, 1024);
@@ -754,8 +789,8 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
     // ------------------------------------------------ epilogue (both CTAs)
     const int q = warp & 3;
     const int ew = warp - 2;
-    uint8_t* stage_buf = smem + SMEM2_EPI + ew * 2 * EPI_BUF_BYTES;
-    const uint32_t stage_u32 = smem_base + SMEM2_EPI + ew * 2 * EPI_BUF_BYTES;
+    uint8_t* stage_buf = smem + Cfg::EPI + ew * Cfg::EPI_BUFS * EPI_BUF_BYTES;
+    const uint32_t stage_u32 = smem_base + Cfg::EPI + ew * Cfg::EPI_BUFS * EPI_BUF_BYTES;
     const int cols_per_store = args.out_f32 ? 32 : 64;
     bool ok = true;
     long long local = 0;
@@ -784,8 +819,8 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
       const bool rows_live = (m0 + q * 32) < args.m;
       for (int c0 = 0; c0 < BN; c0 += cols_per_store) {
         if (n0 + c0 >= args.n || !rows_live) break;
-        const int sbuf = store_idx & 1;
-        if (lane == 0) tma_store_wait_read<1>();
+        const int sbuf = store_idx % Cfg::EPI_BUFS;
+        if (lane == 0) tma_store_wait_read<Cfg::EPI_BUFS - 1>();
         __syncwarp();
         uint8_t* row = stage_buf + sbuf * EPI_BUF_BYTES + lane * 128;
         const int sw = lane & 7;
@@ -1097,7 +1132,7 @@ int max_fused_clusters() {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * (unsigned)sm_count(), 1, 1);
     cfg.blockDim = dim3(NUM_THREADS_FUSED, 1, 1);
-    cfg.dynamicSmemBytes = SMEM2_ALLOC;
+    cfg.dynamicSmemBytes = SMEM2F_ALLOC;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
@@ -1106,7 +1141,7 @@ int max_fused_clusters() {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (cudaFuncSetAttribute(einsum_gemm_allreduce_2cta, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             SMEM2_ALLOC) != cudaSuccess ||
+                             SMEM2F_ALLOC) != cudaSuccess ||
         cudaOccupancyMaxActiveClusters(&n, einsum_gemm_allreduce_2cta, &cfg) != cudaSuccess)
       n = 0;
     (void)cudaGetLastError();
@@ -1204,7 +1239,7 @@ int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
   cfg.blockDim = dim3(NUM_THREADS_FUSED, 1, 1);
-  cfg.dynamicSmemBytes = SMEM2_ALLOC;
+  cfg.dynamicSmemBytes = SMEM2F_ALLOC;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
