@@ -156,6 +156,18 @@ class Operation(object):
         type(self).__name__, ", ".join(x.to_string for x in self._inputs),
         ", ".join(x.to_string for x in self._outputs))
 
+  @property
+  def has_gradient(self):
+    """Whether gradients() differentiates through this operation
+    (mesh_tensorflow/ops.py:1569-1573): by default when every output is
+    floating point; operations without a gradient() override it."""
+    return all(t.dtype.is_floating for t in self._outputs)
+
+  def gradient(self, grad_ys):
+    """Gradients with respect to the inputs, one per input (None where there is
+    none), given the gradients of the outputs (None where none flows in)."""
+    raise NotImplementedError("Gradient not implemented for %s" % type(self).__name__)
+
   def lower(self, lowering):
     raise NotImplementedError("Lower not implemented")
 

@@ -181,9 +181,10 @@ class SlicewiseOperation(Operation):
   """Applies a per-slice function to same-shaped inputs (ops.py:1651-1723)."""
 
   def __init__(self, slice_fn, inputs, output_shape, output_dtype, splittable_dims,
-               name=None):
+               name=None, grad_function=None):
     super().__init__(inputs, name=name or "slicewise")
     self._slice_fn = slice_fn
+    self._grad_function = grad_function
     self._outputs = [Tensor(self, output_shape, output_dtype)]
     self._splittable_dims = [convert_to_dimension(d).name if not isinstance(d, str) else d
                              for d in splittable_dims]
@@ -201,16 +202,51 @@ class SlicewiseOperation(Operation):
                            *[lowering.tensors[x] for x in self.inputs])
     lowering.set_tensor_lowering(self.outputs[0], value)
 
+  @property
+  def has_gradient(self):
+    return self._grad_function is not None and super().has_gradient
 
-def cwise(slice_fn, xs, output_dtype=None, name=None):
+  def gradient(self, grad_ys):
+    """`grad_function(op, dy)` returns one gradient per input
+    (mesh_tensorflow/ops.py:1686-1693)."""
+    return self._grad_function(self, grad_ys[0])
+
+
+def cwise(slice_fn, xs, output_dtype=None, name=None, grad_function=None):
   """Component-wise op on same-shaped tensors; `slice_fn(ops, *slices)`."""
   return SlicewiseOperation(slice_fn, xs, xs[0].shape, output_dtype or xs[0].dtype,
-                            splittable_dims=xs[0].shape.dims, name=name or "cwise").outputs[0]
+                            splittable_dims=xs[0].shape.dims, name=name or "cwise",
+                            grad_function=grad_function).outputs[0]
+
+
+def _mask_times(dy, x, comparison):
+  """dy where `x <comparison> 0`, else 0 (one component-wise kernel sequence)."""
+  return cwise(lambda ops, g, v: ops.binary(
+      "multiply", g, ops.cast(ops.binary(comparison, v, 0), g.dtype)), [dy, x], name="mask_grad")
+
+
+# d/dx of each differentiable unary op, from x = op.inputs[0], y = op.outputs[0]
+# and dy (mesh_tensorflow/ops.py:1724-1962 give the same formulas through
+# tf.gradients of the slice function).
+_UNARY_GRADS = {
+    "identity": lambda op, dy: [dy],
+    "relu": lambda op, dy: [_mask_times(dy, op.inputs[0], "greater")],
+    "exp": lambda op, dy: [dy * op.outputs[0]],
+    "log": lambda op, dy: [dy / op.inputs[0]],
+    "negative": lambda op, dy: [negative(dy)],
+    "reciprocal": lambda op, dy: [negative(dy * square(op.outputs[0]))],
+    "sqrt": lambda op, dy: [dy * 0.5 / op.outputs[0]],
+    "rsqrt": lambda op, dy: [dy * -0.5 * op.outputs[0] * square(op.outputs[0])],
+    "square": lambda op, dy: [dy * op.inputs[0] * 2.0],
+    "tanh": lambda op, dy: [dy * (1.0 - square(op.outputs[0]))],
+    "sigmoid": lambda op, dy: [dy * op.outputs[0] * (1.0 - op.outputs[0])],
+}
 
 
 def _unary(name):
   def api(x, name=name):
-    return cwise(lambda ops, xs: ops.unary(name, xs), [x], name=name)
+    return cwise(lambda ops, xs: ops.unary(name, xs), [x], name=name,
+                 grad_function=_UNARY_GRADS.get(name))
   api.__name__ = name
   return api
 
@@ -228,13 +264,19 @@ sigmoid = _unary("sigmoid")
 sign = _unary("sign")
 logical_not = _unary("logical_not")
 identity = _unary("identity")
-stop_gradient = identity
+
+
+def stop_gradient(x, name="stop_gradient"):
+  """Identity that gradients() does not cross (mesh_tensorflow/ops.py:1973-1986)."""
+  return cwise(lambda ops, xs: ops.unary("identity", xs), [x], name=name)
 
 
 def cast(x, dtype, name="cast"):
   if dtype == x.dtype:
     return x
-  return cwise(lambda ops, xs: ops.cast(xs, dtype), [x], output_dtype=dtype, name=name)
+  back = x.dtype
+  return cwise(lambda ops, xs: ops.cast(xs, dtype), [x], output_dtype=dtype, name=name,
+               grad_function=(lambda op, dy: [cast(dy, back)]) if back.is_floating else None)
 
 
 def to_float(x, name="to_float"):
@@ -263,6 +305,9 @@ class ScalarMultiplyOperation(Operation):
         self.outputs[0],
         impl.slicewise(lambda xs: ops.binary("multiply", xs, c), lowering.tensors[self.inputs[0]]))
 
+  def gradient(self, grad_ys):
+    return [grad_ys[0] * self._scalar]
+
 
 class ScalarAddOperation(Operation):
 
@@ -277,6 +322,9 @@ class ScalarAddOperation(Operation):
     lowering.set_tensor_lowering(
         self.outputs[0],
         impl.slicewise(lambda xs: ops.binary("add", xs, c), lowering.tensors[self.inputs[0]]))
+
+  def gradient(self, grad_ys):
+    return [grad_ys[0]]
 
 
 # --------------------------------------------------------------------- binary
@@ -336,12 +384,44 @@ class BinaryOpWithBroadcasting(Operation):
       y = impl.slicewise(fn, lx1, lx2)
     lowering.set_tensor_lowering(out, y)
 
+  @property
+  def has_gradient(self):
+    return self._op_name in _BINARY_GRADS and super().has_gradient
+
+  def gradient(self, grad_ys):
+    """Per-operand gradients, summed over the dims an operand was broadcast
+    along (mesh_tensorflow/ops.py:2086-2199)."""
+    x1, x2 = self.inputs
+    g1, g2 = _BINARY_GRADS[self._op_name](x1, x2, self.outputs[0], grad_ys[0])
+    return [None if g is None else reduce_sum(g, output_shape=x.shape)
+            for g, x in ((g1, x1), (g2, x2))]
+
 
 def binary_op_with_broadcasting(op_name, x1, x2, output_shape=None, output_dtype=None):
   x1, x2 = binary_arguments_to_tensors(x1, x2)
   output_shape = _infer_binary_broadcast_shape(x1.shape, x2.shape, output_shape)
   return BinaryOpWithBroadcasting(op_name, x1, x2, output_shape,
                                   output_dtype or x1.dtype).outputs[0]
+
+
+def _select_grad(comparison):
+  """Gradients of maximum / minimum: dy goes to the operand that was selected
+  (ties to the first)."""
+  def fn(x1, x2, y, dy):
+    del y
+    first = cast(binary_op_with_broadcasting(comparison, x1, x2, output_dtype=G.bool_), dy.dtype)
+    return dy * first, dy * (1.0 - first)
+  return fn
+
+
+_BINARY_GRADS = {
+    "add": lambda x1, x2, y, dy: (dy, dy),
+    "sub": lambda x1, x2, y, dy: (dy, negative(dy)),
+    "multiply": lambda x1, x2, y, dy: (dy * x2, dy * x1),
+    "divide": lambda x1, x2, y, dy: (dy / x2, negative(dy * y / x2)),
+    "maximum": _select_grad("greater_equal"),
+    "minimum": _select_grad("less_equal"),
+}
 
 
 def _compare(op_name):
@@ -453,6 +533,18 @@ class ReduceOperation(Operation):
         y = impl.allreduce(y, reduced_mesh_axes, self._reduction)
         add_counter_fn()
     lowering.set_tensor_lowering(out, y)
+
+  def gradient(self, grad_ys):
+    """SUM: dy broadcast back; MAX / MIN: dy to the positions that hold the
+    extremum (mesh_tensorflow/ops.py:2340-2362 and 2388-2400)."""
+    x, y, dy = self.inputs[0], self.outputs[0], grad_ys[0]
+    if self._reduction == "SUM":
+      return [broadcast(dy, x.shape)]
+    if self._reduction in ("MAX", "MIN"):
+      hit = cast(binary_op_with_broadcasting("equal", x, y, output_shape=x.shape,
+                                             output_dtype=G.bool_), x.dtype)
+      return [multiply(dy, hit, output_shape=x.shape)]
+    raise NotImplementedError("gradient of reduction %s" % self._reduction)
 
 
 def _reduction_output_shape(x, output_shape, reduced_dim):
@@ -595,6 +687,18 @@ class EinsumOperation(Operation):
     lowering.add_counter("einsum", impl.laid_out_size(computation_shape))
     lowering.add_counter("einsum_unique", computation_shape.size)
 
+  def gradient(self, grad_ys):
+    """d/dx_i = einsum(dy, the other inputs) onto x_i's shape
+    (mesh_tensorflow/ops.py:2846-2854); a fused activation is undone first."""
+    dy = grad_ys[0]
+    if self._activation == "relu":
+      dy = _mask_times(dy, self.outputs[0], "greater")
+    elif self._activation is not None:
+      raise NotImplementedError("gradient through fused activation %s" % self._activation)
+    xs = self.inputs
+    return [einsum([dy] + [xs[j] for j in range(len(xs)) if j != i], output_shape=xs[i].shape)
+            for i in range(len(xs))]
+
 
 def einsum(xs, output_shape=None, reduced_dims=None, name=None, activation=None):
   """Einstein summation; exactly one of output_shape / reduced_dims may be given
@@ -629,6 +733,9 @@ class BroadcastOperation(Operation):
     lowering.set_tensor_lowering(
         out, impl.broadcast_impl(lowering.tensors[x], x.shape, out.shape))
 
+  def gradient(self, grad_ys):
+    return [reduce_sum(grad_ys[0], output_shape=self.inputs[0].shape)]
+
 
 def broadcast(x, new_shape):
   new_shape = convert_to_shape(new_shape)
@@ -650,6 +757,9 @@ class ReshapeOperation(Operation):
   def __init__(self, x, new_shape, name=None):
     super().__init__([x], name=name or "reshape")
     self._outputs = [Tensor(self, new_shape, x.dtype)]
+
+  def gradient(self, grad_ys):
+    return [reshape(grad_ys[0], self.inputs[0].shape)]
 
   def lower(self, lowering):
     old_shape = self.inputs[0].shape
@@ -746,6 +856,20 @@ class TopKOperation(Operation):
     self._reduced_dim = reduced_dim
     self._k_dim = k_dim
 
+  @property
+  def has_gradient(self):
+    return self.outputs[0].dtype.is_floating
+
+  def gradient(self, grad_ys):
+    """The values' gradient scattered back through one-hot indices; the indices
+    carry none (mesh_tensorflow/ops.py:4916-4920)."""
+    dy = grad_ys[0]
+    if dy is None:
+      return [None]
+    x = self.inputs[0]
+    hot = one_hot(self.outputs[1], self._reduced_dim, dtype=x.dtype)
+    return [einsum([dy, hot], output_shape=x.shape)]
+
   def lower(self, lowering):
     impl = lowering.mesh_impl(self)
     ops = impl.slice_ops
@@ -830,6 +954,42 @@ class StackOperation(Operation):
     fn = lambda *xs: ops.concat([ops.expand_dims(x, axis) for x in xs], axis)
     lowering.set_tensor_lowering(
         self.outputs[0], impl.slicewise(fn, *[lowering.tensors[x] for x in self.inputs]))
+
+  def gradient(self, grad_ys):
+    """Each input receives its own layer of dy (mesh_tensorflow/ops.py:2616-2618)."""
+    return [UnstackOperation(grad_ys[0], self._axis, i).outputs[0]
+            for i in range(len(self.inputs))]
+
+
+class UnstackOperation(Operation):
+  """Layer `index` of an unsplit dim, the dim dropped (one output of
+  mesh_tensorflow/ops.py:2633-2670)."""
+
+  def __init__(self, x, axis, index, name=None):
+    super().__init__([x], name=name or "unstack")
+    self._axis, self._index = axis, index
+    dims = x.shape.dims
+    self._outputs = [Tensor(self, Shape(dims[:axis] + dims[axis + 1:]), x.dtype)]
+
+  def gradient(self, grad_ys):
+    dim = self.inputs[0].shape.dims[self._axis]
+    layers = [grad_ys[0] if i == self._index else zeros_like(grad_ys[0]) for i in range(dim.size)]
+    return [stack(layers, dim.name, self._axis)]
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    if impl.tensor_dimension_to_mesh_axis(self.inputs[0].shape.dims[self._axis]) is not None:
+      raise ValueError("can't unstack along a split axis")
+    ops, axis, index = impl.slice_ops, self._axis, self._index
+
+    def fn(xs):
+      shape = list(ops.shape(xs))
+      begin = [0] * len(shape)
+      begin[axis] = index
+      size = list(shape)
+      size[axis] = 1
+      return ops.reshape(ops.slice(xs, begin, size), shape[:axis] + shape[axis + 1:])
+    lowering.set_tensor_lowering(self.outputs[0], impl.slicewise(fn, lowering.tensors[self.inputs[0]]))
 
 
 def stack(xs, dim_name, axis=0, name=None):
@@ -1039,3 +1199,34 @@ Tensor.__truediv__ = lambda self, other: divide(self, other)
 Tensor.__rtruediv__ = lambda self, other: divide(other, self)
 Tensor.__floordiv__ = lambda self, other: _floordiv(self, other)
 Tensor.__mod__ = lambda self, other: _mod(self, other)
+
+
+# ------------------------------------------------------------------ gradients
+def gradients(ys, xs, grad_ys=None, operations=None):
+  """Symbolic d(sum ys)/d(xs): walks the operations backwards, asks each for
+  its input gradients and sums what arrives at a tensor
+  (mesh_tensorflow/ops.py:6493-6586).  Returns one tensor (or None) per x."""
+  if not ys:
+    return [None] * len(xs)
+  graph = ys[0].graph
+  operations = list(graph.operations if operations is None else operations)
+  if not grad_ys:
+    grad_ys = [constant(y.mesh, 1.0, y.shape, y.dtype) for y in ys]
+  # tensors that depend on some x through differentiable operations
+  downstream = set(xs)
+  for op in operations:
+    if op.has_gradient and set(op.inputs) & downstream:
+      downstream |= set(op.outputs)
+  tensor_to_gradient = dict(zip(ys, grad_ys))
+  for op in reversed(operations):
+    grad_outputs = [tensor_to_gradient.get(out) for out in op.outputs]
+    if (not op.has_gradient or all(g is None for g in grad_outputs)
+        or not set(op.inputs) & downstream):
+      continue
+    for inp, grad in zip(op.inputs, op.gradient(grad_outputs)):
+      if inp in downstream and grad is not None:
+        if inp in tensor_to_gradient:
+          tensor_to_gradient[inp] = add(tensor_to_gradient[inp], grad)
+        else:
+          tensor_to_gradient[inp] = grad
+  return [tensor_to_gradient.get(x) for x in xs]

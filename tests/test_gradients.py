@@ -1,0 +1,80 @@
+"""mtf.gradients on the CPU oracle backend: analytic gradients against central
+finite differences, on meshes that split batch and contracted dims (the
+gradient einsums then carry their own allreduces), and the operation-level
+rules of mesh_tensorflow/ops.py:6493-6586 (no gradient through integer
+outputs, stop_gradient, None for unreachable inputs)."""
+
+import numpy as np
+import pytest
+
+from mesh_b200 import mtf
+from oracle.numpy_mesh_impl import NumpyMeshImpl
+from helpers import rng
+
+
+def _lower(graph, mesh, outs, mesh_shape, layout):
+  low = mtf.Lowering(graph, {mesh: NumpyMeshImpl(mesh_shape, layout)})
+  return [np.asarray(low.export_to_tf_tensor(o), dtype=np.float64) for o in outs]
+
+
+def _ffn_loss(arrays):
+  x, wi, wo, b = arrays
+  g = mtf.Graph()
+  m = mtf.Mesh(g, "m")
+  X = mtf.import_tf_tensor(m, x, "batch:4,d_model:8", dtype=mtf.float32)
+  WI = mtf.import_tf_tensor(m, wi, "d_model:8,d_ff:16", dtype=mtf.float32)
+  WO = mtf.import_tf_tensor(m, wo, "d_ff:16,d_model:8", dtype=mtf.float32)
+  B = mtf.import_tf_tensor(m, b, "d_model:8", dtype=mtf.float32)
+  h = mtf.relu(mtf.einsum([X, WI], output_shape="batch:4,d_ff:16"))
+  y = mtf.einsum([h, WO], output_shape="batch:4,d_model:8") + B      # broadcast add
+  p = mtf.softmax(y, y.shape.dims[1])
+  top, _ = mtf.top_k(y, y.shape.dims[1], mtf.Dimension("k", 2))
+  loss = (mtf.reduce_sum(mtf.square(p) * mtf.tanh(y)) + mtf.reduce_sum(mtf.reduce_max(y, reduced_dim=y.shape.dims[1]))
+          + mtf.reduce_sum(top) * 0.5 + mtf.reduce_sum(mtf.maximum(y, B)) - mtf.reduce_sum(mtf.sigmoid(y) / (mtf.exp(B) + 1.0)))
+  return g, m, [X, WI, WO, B], loss
+
+
+@pytest.mark.parametrize("mesh_shape,layout", [
+    ("all:1", ""), ("a:2,b:2", "batch:a;d_ff:b"), ("a:4", "d_model:a")])
+def test_gradients_match_finite_differences(mesh_shape, layout):
+  r = rng(11)
+  arrays = [r.standard_normal((4, 8)).astype(np.float32),
+            (r.standard_normal((8, 16)) / 3).astype(np.float32),
+            (r.standard_normal((16, 8)) / 4).astype(np.float32),
+            r.standard_normal((8,)).astype(np.float32)]
+  g, m, ins, loss = _ffn_loss(arrays)
+  grads = mtf.gradients([loss], ins)
+  vals = _lower(g, m, [loss] + grads, mesh_shape, layout)
+
+  def loss_at(which, idx, delta):
+    a = [v.copy() for v in arrays]
+    a[which][idx] += delta
+    g2, m2, _, l2 = _ffn_loss(a)
+    return float(_lower(g2, m2, [l2], "all:1", "")[0])
+  eps = 2e-3
+  for which, arr in enumerate(arrays):
+    assert vals[1 + which].shape == arr.shape
+    for _ in range(4):
+      idx = tuple(int(r.integers(0, s)) for s in arr.shape)
+      fd = (loss_at(which, idx, eps) - loss_at(which, idx, -eps)) / (2 * eps)
+      assert abs(vals[1 + which][idx] - fd) < 2e-3 + 2e-2 * abs(fd), (which, idx)
+
+
+def test_gradient_rules():
+  g = mtf.Graph()
+  m = mtf.Mesh(g, "m")
+  x = mtf.import_tf_tensor(m, np.arange(6, dtype=np.float32).reshape(2, 3), "a:2,b:3", dtype=mtf.float32)
+  w = mtf.import_tf_tensor(m, np.ones((3,), np.float32), "b:3", dtype=mtf.float32)
+  unused = mtf.import_tf_tensor(m, np.ones((3,), np.float32), "b:3", dtype=mtf.float32)
+  y = mtf.reduce_sum(mtf.stop_gradient(x) * w) + mtf.reduce_sum(mtf.reshape(x, "c:6") * 2.0)
+  dx, dw, du = mtf.gradients([y], [x, w, unused])
+  assert du is None
+  vx, vw = _lower(g, m, [dx, dw], "all:1", "")
+  np.testing.assert_allclose(vx, np.full((2, 3), 2.0))          # only the reshape branch
+  np.testing.assert_allclose(vw, np.arange(6).reshape(2, 3).sum(0))
+  idx = mtf.argmax(x, x.shape.dims[1])
+  assert not idx.operation.has_gradient or idx.dtype.is_integer
+  ds, = mtf.gradients([mtf.reduce_sum(mtf.stack([x, x * 3.0], "s"))], [x])
+  np.testing.assert_allclose(_lower(g, m, [ds], "all:1", "")[0], np.full((2, 3), 4.0))
+  with pytest.raises(NotImplementedError):
+    mtf.gradients([mtf.reduce_sum(mtf.shift(x, 1, x.shape.dims[1], False))], [x])
