@@ -1,6 +1,6 @@
 """Per-configuration measurements beside bench.py's headline line.
 
-  python -m mesh_b200.bench_configs --config moe|einsum_fp32|attention|collectives [--gpus N]
+  python -m mesh_b200.bench_configs --config moe|einsum_fp32|attention|collectives|ffn_train [--gpus N]
 
 Each configuration prints JSON lines (one per measured quantity) with the
 algorithmic bytes or flops it was divided by, so roofline fractions can be
@@ -173,6 +173,51 @@ def config_moe(args):
     _leave(dist_module=None)
 
 
+def config_ffn_train(args):
+  """Forward and backward of the dense FFN (x[64,1024,1024], wi[1024,4096],
+  wo[4096,1024], bf16) on one GPU: y, then dx, dwi, dwo from a given dy through
+  mtf.gradients - three GEMM pairs with permuted operand roles and the ReLU
+  mask, lowered onto the same kernels and replayed as a CUDA graph."""
+  peaks = _peaks()
+  torch.cuda.set_device(0)
+  impl = CudaMeshImpl("all:1", "", [0])
+  ops = impl.slice_ops
+  b, l, d, f = 64, 1024, 1024, 4096
+  r = np.random.Generator(np.random.PCG64(1238))
+
+  def laid(shape, scale):
+    t = torch.from_numpy(r.standard_normal(shape, dtype=np.float32) * np.float32(scale)).to(torch.bfloat16)
+    return impl.LaidOutTensor([ops.from_host(t, mtf.bfloat16)])
+  lx, ldy = laid((b, l, d), 1.0), laid((b, l, d), 1.0)
+  lwi, lwo = laid((d, f), d ** -0.5), laid((f, d), f ** -0.5)
+  g = mtf.Graph()
+  mesh = mtf.Mesh(g, "mesh")
+  act = "batch:%d,length:%d,d_model:%d" % (b, l, d)
+  X = mtf.import_laid_out_tensor(mesh, lx, act, mtf.bfloat16)
+  DY = mtf.import_laid_out_tensor(mesh, ldy, act, mtf.bfloat16)
+  WI = mtf.import_laid_out_tensor(mesh, lwi, "d_model:%d,d_ff:%d" % (d, f), mtf.bfloat16)
+  WO = mtf.import_laid_out_tensor(mesh, lwo, "d_ff:%d,d_model:%d" % (f, d), mtf.bfloat16)
+  y = mtf.layers.dense_relu_dense(X, mtf.Dimension("d_ff", f), wi=WI, wo=WO)
+  grads = mtf.gradients([y], [X, WI, WO], grad_ys=[DY])
+
+  def step():
+    low = mtf.Lowering(g, {mesh: impl})
+    return [low.tensors[t].to_laid_out_tensor() for t in [y] + grads]
+  before = nat.launch_count()
+  step()
+  launches = nat.launch_count() - before
+  impl.synchronize()
+  run = step
+  if not args.eager:
+    _, run = impl.capture(step)
+  ms = _time(run, iters=args.iters, warmup=3)
+  flops = 3 * 2.0 * 2.0 * b * l * d * f     # forward + two gradient GEMMs per forward GEMM
+  _emit(config="ffn_train", quantity="dense_relu_dense forward + backward (dx, dwi, dwo)", ms=ms,
+        tflops=flops / (ms * 1e-3) / 1e12, frac_of_peak=flops / (ms * 1e-3) / 1e12 / peaks["tflops"],
+        peak_tflops=peaks["tflops"], peak_source=peaks["source"], libmtfc_launches_per_step=launches,
+        stepping="eager" if args.eager else "cuda-graph replay")
+
+
 def config_einsum_fp32(args):
   """x[4096,1024] . w[1024,4096] in fp32 (one GPU: the whole problem)."""
   torch.cuda.set_device(0)
@@ -295,7 +340,7 @@ def config_collectives(args):
 
 def main():
   ap = argparse.ArgumentParser()
-  ap.add_argument("--config", required=True, choices=["moe", "einsum_fp32", "attention", "collectives"])
+  ap.add_argument("--config", required=True, choices=["moe", "einsum_fp32", "attention", "collectives", "ffn_train"])
   ap.add_argument("--gpus", type=int, default=1)
   ap.add_argument("--iters", type=int, default=10)
   ap.add_argument("--eager", action="store_true")
@@ -305,6 +350,7 @@ def main():
   if not torch.cuda.is_available():
     sys.exit("needs a CUDA device")
   {"moe": config_moe, "einsum_fp32": config_einsum_fp32, "attention": config_attention,
+   "ffn_train": config_ffn_train,
    "collectives": config_collectives}[args.config](args)
 
 
