@@ -187,6 +187,7 @@ int mtfc_split_bf16x3(const float* src, int64_t s_batch, int64_t s_row, int64_t 
 #define MTFC_BINARY_NOT_EQUAL 13
 #define MTFC_BINARY_LOGICAL_AND 14
 #define MTFC_BINARY_LOGICAL_OR 15
+#define MTFC_BINARY_SELECT_POSITIVE 16 /* a where b > 0, else 0: the ReLU gradient in one pass */
 
 #define MTFC_REDUCE_SUM 0
 #define MTFC_REDUCE_MAX 1

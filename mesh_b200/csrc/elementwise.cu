@@ -108,6 +108,7 @@ __device__ __forceinline__ float binary_f(int op, float a, float b) {
     case MTFC_BINARY_NOT_EQUAL: return a != b;
     case MTFC_BINARY_LOGICAL_AND: return (a != 0.f) && (b != 0.f);
     case MTFC_BINARY_LOGICAL_OR: return (a != 0.f) || (b != 0.f);
+    case MTFC_BINARY_SELECT_POSITIVE: return b > 0.f ? a : 0.f;
     default: return 0.f;
   }
 }
@@ -133,6 +134,7 @@ __device__ __forceinline__ int binary_i(int op, int a, int b) {
     case MTFC_BINARY_NOT_EQUAL: return a != b;
     case MTFC_BINARY_LOGICAL_AND: return (a != 0) && (b != 0);
     case MTFC_BINARY_LOGICAL_OR: return (a != 0) || (b != 0);
+    case MTFC_BINARY_SELECT_POSITIVE: return b > 0 ? a : 0;
     default: return 0;
   }
 }

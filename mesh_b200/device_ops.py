@@ -33,7 +33,7 @@ _UNARY = {"identity": 0, "relu": 1, "exp": 2, "log": 3, "negative": 4, "reciproc
 _BINARY = {"add": 0, "sub": 1, "multiply": 2, "divide": 3, "maximum": 4, "minimum": 5,
            "floordiv": 6, "mod": 7, "less": 8, "greater": 9, "less_equal": 10,
            "greater_equal": 11, "equal": 12, "not_equal": 13, "logical_and": 14,
-           "logical_or": 15}
+           "logical_or": 15, "select_positive": 16}
 _COMPARISONS = frozenset(["less", "greater", "less_equal", "greater_equal", "equal",
                           "not_equal", "logical_and", "logical_or"])
 _REDUCE = {"SUM": 0, "MAX": 1, "MIN": 2}

@@ -220,9 +220,10 @@ def cwise(slice_fn, xs, output_dtype=None, name=None, grad_function=None):
 
 
 def _mask_times(dy, x, comparison):
-  """dy where `x <comparison> 0`, else 0 (one component-wise kernel sequence)."""
-  return cwise(lambda ops, g, v: ops.binary(
-      "multiply", g, ops.cast(ops.binary(comparison, v, 0), g.dtype)), [dy, x], name="mask_grad")
+  """dy where x > 0, else 0, in one pass over the two tensors (what
+  tf.nn.relu's gradient computes)."""
+  assert comparison == "greater"
+  return cwise(lambda ops, g, v: ops.binary("select_positive", g, v), [dy, x], name="relu_grad")
 
 
 # d/dx of each differentiable unary op, from x = op.inputs[0], y = op.outputs[0]

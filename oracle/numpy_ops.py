@@ -199,6 +199,8 @@ class NumpyOps(object):
         return Arr((av != 0) & (bv != 0), mtf.bool_)
       elif name == "logical_or":
         return Arr((av != 0) | (bv != 0), mtf.bool_)
+      elif name == "select_positive":
+        r = np.where(bv > 0, av, np.zeros_like(av))
       else:
         raise ValueError("unknown binary op %s" % name)
     return _finish(r, ref.dtype)

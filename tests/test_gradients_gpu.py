@@ -39,7 +39,17 @@ def test_ffn_backward(cuda_device, mesh_shape, layout, dtype, tol):
   n = mtf.convert_to_shape(mesh_shape).size if mesh_shape else 1
   got, low = _ffn_grads(CudaMeshImpl(mesh_shape or "all:1", layout, [0] * n), dtype)
   ref, low_ref = _ffn_grads(NumpyMeshImpl(mesh_shape or "all:1", layout), dtype)
-  for a, b_ in zip(got, ref):
+  # With d_model split, the pre-activation is an allreduce of bf16 partial sums:
+  # the two backends add them in different orders, a value next to zero can land
+  # on either side of it, and that flips single entries of the ReLU mask.  Each
+  # flip moves a gradient entry by about |dy . wo| |wi|, a few percent of the
+  # largest entry, and a row can collect several; the bulk of the entries must
+  # still agree to bf16 accuracy (the median check below).
+  flips = dtype == mtf.bfloat16 and "d_model" in layout
+  for name, a, b_ in zip(("y", "dx", "dwi", "dwo"), got, ref):
     assert a.shape == b_.shape
-    assert rel_err(a, b_) < tol
+    err = rel_err(a, b_)
+    assert err < (0.25 if flips else tol), (name, err)
+    scale = float(np.max(np.abs(b_)))
+    assert float(np.median(np.abs(np.asarray(a, np.float64) - b_))) < tol * scale / 4, name
   assert low.counter_totals() == low_ref.counter_totals()
