@@ -457,14 +457,18 @@ __device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
   return v;
 }
 // cp.async.bulk.wait_group with a run-time count: returns once at most `pending`
-// of this thread's newest bulk groups are still incomplete (0..4).
+// of this thread's newest bulk groups are still incomplete (0..8).
 __device__ __forceinline__ void bulk_wait_upto(int pending) {
   switch (pending) {
     case 0: asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); break;
     case 1: asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); break;
     case 2: asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); break;
     case 3: asm volatile("cp.async.bulk.wait_group 3;" ::: "memory"); break;
-    default: asm volatile("cp.async.bulk.wait_group 4;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.bulk.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.bulk.wait_group 5;" ::: "memory"); break;
+    case 6: asm volatile("cp.async.bulk.wait_group 6;" ::: "memory"); break;
+    case 7: asm volatile("cp.async.bulk.wait_group 7;" ::: "memory"); break;
+    default: asm volatile("cp.async.bulk.wait_group 8;" ::: "memory"); break;
   }
 }
 __device__ __forceinline__ void st_v4(void* p, const uint4& v) {
@@ -795,7 +799,9 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
     bool ok = true;
     long long local = 0;
     int store_idx = 0;
-    int pending_rb = -1;  // fused: row block of the tile whose arrival is not yet signalled
+    // fused: row blocks of the last two tiles, whose arrival is not yet signalled, and
+    // the number of store groups of the newer one
+    int pending_rb = -1, older_rb = -1, pending_stores = 0;
     for (long long t = cluster_id; t < num_tiles && ok; t += num_clusters, ++local) {
       const int tile_first_store = store_idx;
       const int buf = (int)(local & 1);
@@ -876,22 +882,27 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(tmem_empty_bar(buf), 0));
       if (FUSED && lane == 0) {
-        // Tell the owner of the PREVIOUS tile's row block that this warp's part of
-        // it has arrived (complete, not merely read out of the staging buffers):
-        // waiting for all but this tile's store groups costs nothing, while
-        // waiting for this tile's own would stall the epilogue for a round trip
-        // over NVLink per tile.
+        // Tell the owner of the row block of the tile TWO tiles back that this
+        // warp's part of it has arrived (complete, not merely read out of the
+        // staging buffers): its stores have had two tile times to land, so the
+        // wait for "all but the store groups of the last two tiles" returns at
+        // once, where waiting for this tile's own stores would stall the epilogue
+        // for a round trip over NVLink per tile.
         const int mine = store_idx - tile_first_store;
-        if (pending_rb >= 0) {
-          bulk_wait_upto(mine);
-          red_release_sys_add(fa->flags[pending_rb % fa->nranks] + pending_rb, 1u);
+        if (older_rb >= 0) {
+          bulk_wait_upto(mine + pending_stores);
+          red_release_sys_add(fa->flags[older_rb % fa->nranks] + older_rb, 1u);
         }
+        older_rb = pending_rb;
         pending_rb = rb;
+        pending_stores = mine;
       }
     }
     if (lane == 0) tma_store_wait_all();
-    if (FUSED && lane == 0 && pending_rb >= 0)
-      red_release_sys_add(fa->flags[pending_rb % fa->nranks] + pending_rb, 1u);
+    if (FUSED && lane == 0) {
+      if (older_rb >= 0) red_release_sys_add(fa->flags[older_rb % fa->nranks] + older_rb, 1u);
+      if (pending_rb >= 0) red_release_sys_add(fa->flags[pending_rb % fa->nranks] + pending_rb, 1u);
+    }
     if (!ok && lane == 0 && args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
   }
 
