@@ -78,3 +78,46 @@ def test_gradient_rules():
   np.testing.assert_allclose(_lower(g, m, [ds], "all:1", "")[0], np.full((2, 3), 4.0))
   with pytest.raises(NotImplementedError):
     mtf.gradients([mtf.reduce_sum(mtf.shift(x, 1, x.shape.dims[1], False))], [x])
+
+
+def _moe_total(arrays, mesh_shape, layout, grads):
+  x, wg, wi, wo = arrays
+  g = mtf.Graph()
+  m = mtf.Mesh(g, "m")
+  X = mtf.import_tf_tensor(m, x, "batch:4,length:16,d_model:8", dtype=mtf.float32)
+  WG = mtf.import_tf_tensor(m, wg, "d_model:8,expert_unsplit:4", dtype=mtf.float32)
+  WI = mtf.import_tf_tensor(m, wi, "experts:4,d_model:8,d_ff:16", dtype=mtf.float32)
+  WO = mtf.import_tf_tensor(m, wo, "experts:4,d_ff:16,d_model:8", dtype=mtf.float32)
+  hp = mtf.moe.HParams(moe_group_size=16, moe_second_policy_train="all",
+                       moe_use_fused_kernels=False, moe_capacity_factor_train=4.0)
+  out, loss = mtf.moe.transformer_moe_layer_v1(
+      X, mtf.Dimension("d_model", 8), hp, True, mesh_shape, layout, WG, WI, WO)
+  total = mtf.reduce_sum(mtf.square(out)) + loss * 10.0
+  outs = [total] + (mtf.gradients([total], [X, WG, WI, WO]) if grads else [])
+  return _lower(g, m, outs, mesh_shape, layout)
+
+
+def test_moe_layer_gradients_match_finite_differences():
+  """The op-by-op top-2 MoE layer differentiates end to end: through the gates
+  (softmax, renormalisation, the auxiliary loss) but not the integer routing
+  decisions, through the dispatch / combine einsums and the two reshapes that
+  lower to alltoalls (experts split over the mesh)."""
+  r = rng(13)
+  arrays = [r.standard_normal((4, 16, 8)).astype(np.float32),
+            (r.standard_normal((8, 4)) / 2).astype(np.float32),
+            (r.standard_normal((4, 8, 16)) / 3).astype(np.float32),
+            (r.standard_normal((4, 16, 8)) / 4).astype(np.float32)]
+  mesh_shape, layout = "all:2", "batch:all;experts:all"
+  vals = _moe_total(arrays, mesh_shape, layout, True)
+  eps = 1e-3
+  for which, arr in enumerate(arrays):
+    assert vals[1 + which].shape == arr.shape
+    for _ in range(3):
+      idx = tuple(int(r.integers(0, s)) for s in arr.shape)
+      a = [v.copy() for v in arrays]
+      a[which][idx] += eps
+      up = float(_moe_total(a, mesh_shape, layout, False)[0])
+      a[which][idx] -= 2 * eps
+      down = float(_moe_total(a, mesh_shape, layout, False)[0])
+      fd = (up - down) / (2 * eps)
+      assert abs(vals[1 + which][idx] - fd) < 2e-2 + 2e-2 * abs(fd), (which, idx)
