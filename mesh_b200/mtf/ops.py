@@ -126,6 +126,48 @@ class Variable(Operation):
     lowering.set_tensor_lowering(self.outputs[0], laid_out_variable.laid_out_tensor)
 
 
+class Assign(Operation):
+  """Replaces the slices of variables by new values (mesh_tensorflow/ops.py:4090-4148).
+  Lowering it after the variables' own operations updates their laid-out
+  slices in place of the imported ones; `copy_to_master=True` also writes the
+  assembled result back to each variable's master copy."""
+
+  def __init__(self, variables, new_values, copy_to_master=True, name=None):
+    super().__init__(list(new_values), variables[0].mesh, name=name or "assign")
+    for var, val in zip(variables, new_values):
+      if var.outputs[0].shape != val.shape:
+        raise ValueError("shape mismatch in assign: %s vs %s" % (var.outputs[0].shape, val.shape))
+    self._variables = list(variables)
+    self._copy_to_master = copy_to_master
+    self._outputs = []
+
+  @property
+  def has_gradient(self):
+    return False
+
+  def lower(self, lowering):
+    for var, val in zip(self._variables, self.inputs):
+      if var not in lowering.variables:
+        raise ValueError("variable %s is assigned before it is lowered" % var.name)
+      impl = lowering.mesh_impl(var)
+      ops = impl.slice_ops
+      dtype = var.outputs[0].dtype
+      new = lowering.tensors[val].to_laid_out_tensor()
+      laid_out_variable = lowering.variables[var]
+      laid_out_variable.assign_to_slices(
+          lambda v, old, value: ops.cast(value, dtype), new.all_slices)
+      if self._copy_to_master:
+        laid_out_variable.copy_slices_to_master()
+
+
+def assign(variable, new_value, copy_to_master=True):
+  """variable <- new_value; `variable` is a Variable or its tensor."""
+  var = variable.operation if isinstance(variable, Tensor) else variable
+  if not isinstance(var, Variable):
+    raise ValueError("assign needs a Variable, got %s" % (var,))
+  return Assign([var], [new_value], copy_to_master=copy_to_master)
+
+
 def get_variable(mesh, name, shape, dtype=G.float32, initial_value=None):
   """Creates a Variable and returns its tensor; `.operation` is the Variable."""
   shape = convert_to_shape(shape)
