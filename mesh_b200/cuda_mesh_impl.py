@@ -518,9 +518,9 @@ class CudaMeshImpl(SlicedMeshImpl):
   OVERLAP_MIN_ROWS = 2048
   # GEMM and allreduce in one kernel over peer memory (mtfc_gemm_allreduce);
   # falls back to the chunked GEMM + NCCL sequence when the einsum is not a
-  # single bf16 GEMM or peer memory cannot be set up.  MTFC_FUSED_ALLREDUCE=0/1
-  # in the environment overrides the default.
-  FUSED_ALLREDUCE = os.environ.get("MTFC_FUSED_ALLREDUCE", "0") == "1"
+  # single bf16 GEMM, the result is small, or peer memory cannot be set up.
+  # MTFC_FUSED_ALLREDUCE=0 in the environment switches it off.
+  FUSED_ALLREDUCE = os.environ.get("MTFC_FUSED_ALLREDUCE", "1") == "1"
   FUSED_MIN_BYTES = 1 << 20
 
   def einsum_allreduce(self, equation, inputs, mesh_axes):
