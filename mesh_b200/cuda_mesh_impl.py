@@ -522,6 +522,9 @@ class CudaMeshImpl(SlicedMeshImpl):
   # MTFC_FUSED_ALLREDUCE=0 in the environment switches it off.
   FUSED_ALLREDUCE = os.environ.get("MTFC_FUSED_ALLREDUCE", "1") == "1"
   FUSED_MIN_BYTES = 1 << 20
+  # above this the exchange dominates and NCCL moves the bytes faster (measured:
+  # a 256 MiB attention output projection on 2 GPUs, 4.25 ms fused against 3.86 ms)
+  FUSED_MAX_BYTES = 128 << 20
 
   def einsum_allreduce(self, equation, inputs, mesh_axes):
     """Contraction whose SUM allreduce over `mesh_axes` starts chunk by chunk.
@@ -586,7 +589,7 @@ class CudaMeshImpl(SlicedMeshImpl):
 
     def hook(desc, a_ptr, b_ptr, stored_shape):
       nbytes = int(desc.m) * int(desc.n) * 2
-      if desc.n % 8 != 0 or nbytes < self.FUSED_MIN_BYTES:
+      if desc.n % 8 != 0 or nbytes < self.FUSED_MIN_BYTES or nbytes > self.FUSED_MAX_BYTES:
         return None
       ws = self._peer_workspace(pg, members, pnum, int(desc.m), int(desc.n))
       if ws is None:
