@@ -55,6 +55,11 @@ def _volume(shape):
   return n
 
 
+class HookDeclined(Exception):
+  """einsum(..., gemm_hook=...) did not come down to a launch the hook took;
+  nothing has been launched."""
+
+
 class DeviceArray(object):
   """A strided view of a flat device buffer with an mtf dtype."""
   __slots__ = ("buf", "shape", "strides", "offset", "dtype")
@@ -419,9 +424,11 @@ class DeviceOps(object):
     the contraction comes down to ONE bf16 -> bf16 GEMM without batch or
     epilogue (desc describes a dense row-major [m, n] output): it may run the
     product itself (e.g. fused with an allreduce) and return the array of
-    `stored_shape` that holds the result, or return None to decline.  An
-    einsum that needs packing, a pre-reduction or another kernel never reaches
-    the hook (the hook itself knows whether it ran).
+    `stored_shape` that holds the result, or return None to decline.  With a
+    hook, the einsum either runs through it or raises HookDeclined before
+    anything is launched (a contraction that needs packing, a pre-reduction or
+    another kernel never reaches the hook), so the caller can fall back
+    without having paid for a product.
     """
     if gemm_hook is not None:
       return self._einsum_impl(equation, xs, epilogue, out_dtype, None, gemm_hook)
@@ -434,6 +441,8 @@ class DeviceOps(object):
 
   def _einsum_impl(self, equation, xs, epilogue, out_dtype, out_buf, gemm_hook=None):
     terms, out_term = self._parse(equation, len(xs))
+    if gemm_hook is not None and len(xs) != 2:
+      raise HookDeclined()
     if len(xs) == 1:
       return self.einsum_naive(equation, *xs)
     if len(xs) > 2:
@@ -448,6 +457,8 @@ class DeviceOps(object):
     # dims that occur in one operand only and not in the output are summed first
     for which, (t, other) in enumerate(((ta, tb), (tb, ta))):
       lone = [l for l in t if l not in other and l not in out_term]
+      if lone and gemm_hook is not None:
+        raise HookDeclined()
       if lone:
         kept = "".join(l for l in t if l not in lone)
         reduced = self.einsum_naive(t + "->" + kept, a if which == 0 else b)
@@ -464,6 +475,8 @@ class DeviceOps(object):
     n_dims = [l for l in out_term if l in tb and l not in ta]
     k_dims = [l for l in ta if l in tb and l not in out_term]
     if not k_dims or not a.dtype.is_floating:
+      if gemm_hook is not None:
+        raise HookDeclined()
       return self.einsum_naive(ta + "," + tb + "->" + out_term, a, b)
     sa, sb = dict(zip(ta, a.strides)), dict(zip(tb, b.strides))
 
@@ -496,6 +509,8 @@ class DeviceOps(object):
           break
     store = batch + m_dims + n_dims
     view_perm = [store.index(l) for l in out_term]
+    if plan is None and gemm_hook is not None:
+      raise HookDeclined()
     if plan is None:
       # pack to [batch, M, K] x [batch, K, N] first
       pa = self.contiguous(self.transpose(a, [ta.index(l) for l in batch + m_dims + k_dims]))
@@ -504,6 +519,10 @@ class DeviceOps(object):
                         + "->" + "".join(store), pa, pb, epilogue=epilogue, out_dtype=out_dtype)
       return self.transpose(res, view_perm)
     (nb, a_b), (_, b_b), (m, a_m), (n, b_n), (k, a_k), (_, b_k) = plan
+    if gemm_hook is not None and not (
+        nb == 1 and epilogue == nat.EPILOGUE_NONE and a.dtype.name == "bfloat16"
+        and b.dtype.name == "bfloat16" and out_dtype.name == "bfloat16"):
+      raise HookDeclined()
     if (out_buf is not None and view_perm == list(range(len(store))) and out_buf.is_contiguous
         and out_buf.dtype == out_dtype):
       out = out_buf
@@ -542,13 +561,11 @@ class DeviceOps(object):
     d.out_dtype = _CODE[out_dtype.name]
     d.epilogue = epilogue
     d.force_path = 0
-    if (gemm_hook is not None and nb == 1 and epilogue == nat.EPILOGUE_NONE
-        and a.dtype.name == "bfloat16" and b.dtype.name == "bfloat16"
-        and out_dtype.name == "bfloat16"):
+    if gemm_hook is not None:
       hooked = gemm_hook(d, a.ptr, b.ptr, [sizes[l] for l in store])
-      if hooked is not None:
-        res = hooked if view_perm == list(range(len(store))) else self.transpose(hooked, view_perm)
-        return res
+      if hooked is None:
+        raise HookDeclined()
+      return hooked if view_perm == list(range(len(store))) else self.transpose(hooked, view_perm)
     self._call(self._lib.mtfc_gemm, ctypes.byref(d), ctypes.c_void_p(a.ptr),
                ctypes.c_void_p(b.ptr), ctypes.c_void_p(out.ptr), self._stream())
     return result
