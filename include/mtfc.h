@@ -119,6 +119,12 @@ int mtfc_gemm_uses_tensor_cores(const mtfc_gemm_desc* desc, const void* a,
  * which the buffers must be re-created.
  */
 int mtfc_gemm_allreduce_flag_bytes(void);
+/* Limit, in milliseconds at a nominal 2 GHz, of each wait on another rank inside
+ * later mtfc_gemm_allreduce launches of this process; ms <= 0 restores the
+ * default (~3 s).  A job whose ranks can be further apart than that when they
+ * reach the launch (first-use set-up on one rank, a long host pause) should raise
+ * it; a test that wants to see the time-out path lowers it. */
+int mtfc_gemm_allreduce_set_wait_ms(int ms);
 int64_t mtfc_gemm_allreduce_stage_bytes(int64_t m, int64_t n, int nranks);
 int mtfc_gemm_allreduce(const mtfc_gemm_desc* desc, const void* a, const void* b,
                         void* const* stage_ptrs, void* const* out_ptrs,
@@ -288,6 +294,33 @@ int mtfc_moe_top2_gating(const float* logits, int32_t parts, int64_t groups, int
                          const float* noise, int32_t* idx1, int32_t* idx2, int32_t* pos1,
                          int32_t* pos2, float* gate1, float* gate2, float* raw_gates,
                          float* loss_per_group, void* stream);
+
+/* The same routing as mtfc_moe_split_gate_weights + mtfc_gemm +
+ * mtfc_moe_top2_gating for bf16 activations, with the activations read once:
+ * one tcgen05 kernel forms the gate logits of 128 tokens at a time in TMEM
+ * (x . [hi | mid | lo] of the fp32 gate kernel) and finishes softmax, top-2
+ * and gate renormalisation in registers, one thread per token; a per-group
+ * scan kernel then assigns positions and applies the second-expert policy and
+ * the capacity (moe.py:1380-1496).
+ *   mtfc_moe_gate_fused_supported: 1 when d_model `m` is a multiple of 8 and
+ *     2 <= experts <= 64, else 0 (use the three-call form then).
+ *   mtfc_moe_gate_padded_experts: EP, experts rounded up to 16, 32 or 64.
+ *   mtfc_moe_gate_prepare: fp32 gate kernel [m, experts] -> bf16 [3*EP, m].
+ *   mtfc_moe_gate_scratch_bytes: size of the caller-owned `scratch` (per-tile
+ *     column sums of the raw gates, from which the loss is formed).
+ *   mtfc_moe_gate_top2: x [groups*group_size, m] bf16; outputs as
+ *     mtfc_moe_top2_gating; `slot_table` (optional) receives what
+ *     mtfc_moe_slot_table would compute from the outputs. */
+int mtfc_moe_gate_fused_supported(int64_t m, int32_t experts);
+int32_t mtfc_moe_gate_padded_experts(int32_t experts);
+int64_t mtfc_moe_gate_scratch_bytes(int64_t groups, int32_t group_size, int32_t experts);
+int mtfc_moe_gate_prepare(const float* w, int64_t m, int32_t experts, void* w3t_bf16, void* stream);
+int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups, int32_t group_size,
+                       int64_t m, int32_t experts, int32_t capacity, int32_t policy,
+                       float threshold, const float* noise, int32_t* idx1, int32_t* idx2,
+                       int32_t* pos1, int32_t* pos2, float* gate1, float* gate2, float* raw_gates,
+                       float* loss_per_group, int32_t* slot_table, int32_t round_gates_to_bf16,
+                       void* scratch, int64_t scratch_bytes, void* stream);
 
 /* table[g, e, c] = token routed to slot c of expert e in group g, or -1.
  * With round_gates_to_bf16 a token whose gate rounds to 0 in bfloat16 is not

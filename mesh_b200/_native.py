@@ -71,6 +71,7 @@ def _declare(lib):
       "mtfc_gemm": [ctypes.POINTER(GemmDesc), vp, vp, vp, vp],
       "mtfc_gemm_uses_tensor_cores": [ctypes.POINTER(GemmDesc), vp, vp, vp],
       "mtfc_gemm_allreduce_flag_bytes": [],
+      "mtfc_gemm_allreduce_set_wait_ms": [ctypes.c_int],
       "mtfc_gemm_allreduce_stage_bytes": [i64, i64, i32],
       "mtfc_gemm_allreduce": [ctypes.POINTER(GemmDesc), vp, vp, ctypes.POINTER(vp), ctypes.POINTER(vp),
                               ctypes.POINTER(vp), vp, i32, i32, vp],
@@ -91,6 +92,12 @@ def _declare(lib):
       "mtfc_moe_split_gate_weights": [vp, i64, i32, vp, vp],
       "mtfc_moe_top2_gating": [vp, i32, i64, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp,
                                vp, vp, vp],
+      "mtfc_moe_gate_fused_supported": [i64, i32],
+      "mtfc_moe_gate_padded_experts": [i32],
+      "mtfc_moe_gate_scratch_bytes": [i64, i32, i32],
+      "mtfc_moe_gate_prepare": [vp, i64, i32, vp, vp],
+      "mtfc_moe_gate_top2": [vp, vp, i64, i32, i64, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp,
+                             vp, vp, vp, i32, vp, i64, vp],
       "mtfc_moe_slot_table": [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, vp, vp],
       "mtfc_moe_dispatch": [vp, vp, vp, i64, i64, i32, i32, i32, i64, vp],
       "mtfc_moe_dispatch_noalloc": [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64,
@@ -99,7 +106,8 @@ def _declare(lib):
   }
   for name, argtypes in signatures.items():
     fn = getattr(lib, name)
-    fn.restype = i64 if name == "mtfc_gemm_allreduce_stage_bytes" else ctypes.c_int
+    fn.restype = i64 if name in ("mtfc_gemm_allreduce_stage_bytes",
+                                 "mtfc_moe_gate_scratch_bytes") else ctypes.c_int
     fn.argtypes = argtypes
 
 

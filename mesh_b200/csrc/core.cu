@@ -59,6 +59,7 @@ int gemm_tcgen05_launch(const mtfc_gemm_desc* d, const void* a, const void* b, v
 int gemm_simt_launch(const mtfc_gemm_desc* d, const void* a, const void* b, void* c,
                      cudaStream_t stream);
 int gemm_allreduce_flag_bytes();
+void gemm_allreduce_set_wait_ms(int ms);
 long long gemm_allreduce_stage_bytes(long long m, long long n, int nranks);
 int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
                           void* const* stage, void* const* out, void* const* flags, void* ctl,
@@ -126,6 +127,11 @@ int mtfc_gemm(const mtfc_gemm_desc* d, const void* a, const void* b, void* c, vo
 }
 
 int mtfc_gemm_allreduce_flag_bytes(void) { return gemm_allreduce_flag_bytes(); }
+
+int mtfc_gemm_allreduce_set_wait_ms(int ms) {
+  gemm_allreduce_set_wait_ms(ms);
+  return MTFC_OK;
+}
 
 int64_t mtfc_gemm_allreduce_stage_bytes(int64_t m, int64_t n, int nranks) {
   return gemm_allreduce_stage_bytes(m, n, nranks);

@@ -413,7 +413,7 @@ constexpr int MAX_RANKS = 8;
 constexpr int FLAG_DONE = 4096;  // row-block counters live in [0, FLAG_DONE)
 constexpr int COMM_UNROLL = 8;   // 16-byte vectors per thread in flight, general rank count
 constexpr int COMM_LOADS = 32;   // 16-byte loads per thread in flight for 2, 4 or 8 ranks
-constexpr long long PEER_WAIT_CYCLES = 6000000000LL;  // ~3 s
+constexpr long long PEER_WAIT_CYCLES_DEFAULT = 6000000000LL;  // ~3 s
 constexpr int COMM_UNIT_ROWS = 32;
 constexpr int COMM_WARPS = 4;
 constexpr int COMM_THREADS = 32 * COMM_WARPS;
@@ -427,6 +427,7 @@ struct FusedArgs {
   uint32_t* ctl;
   int rank, nranks;
   int blocks_per_rank;
+  long long wait_cycles;  // how long a wait for another rank may last
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -438,11 +439,11 @@ __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // Waits (bounded) until *p has reached `target` (wrap-safe comparison).
-__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target) {
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target, long long limit) {
   const long long t0 = clock64();
   for (;;) {
     if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
-    if (clock64() - t0 > PEER_WAIT_CYCLES) return false;
+    if (clock64() - t0 > limit) return false;
     __nanosleep(128);
   }
 }
@@ -599,7 +600,7 @@ __device__ void allreduce_comm_warps(uint8_t* smem, const GemmArgs& args, const 
     if (w >= UNITS * owned) break;
     const int k = w / UNITS, sub = w % UNITS;
     const int rb = fa.rank + n * k;
-    if (tid == 0 && !wait_flag_ge(fa.flags[fa.rank] + rb, ready_target)) *abort_flag = 1;
+    if (tid == 0 && !wait_flag_ge(fa.flags[fa.rank] + rb, ready_target, fa.wait_cycles)) *abort_flag = 1;
     comm_warps_sync();
     if (*abort_flag) { ok = false; break; }
     const int rows = max(0, min(COMM_UNIT_ROWS, args.m - rb * 2 * BM - sub * COMM_UNIT_ROWS));
@@ -628,7 +629,8 @@ __device__ void allreduce_comm_warps(uint8_t* smem, const GemmArgs& args, const 
     } else if (atomicAdd(fa.ctl + 1, 1u) == gridDim.x - 1) {
       // last CTA of this launch: the output is whole once every half row block
       // has been written here, and only then may the next launch start
-      if (wait_flag_ge(fa.flags[fa.rank] + FLAG_DONE, epoch * (uint32_t)(UNITS * num_rb))) {
+      if (wait_flag_ge(fa.flags[fa.rank] + FLAG_DONE, epoch * (uint32_t)(UNITS * num_rb),
+                       fa.wait_cycles)) {
         fa.ctl[1] = 0u;
         fa.ctl[2] = 0u;
         __threadfence();
@@ -1132,6 +1134,14 @@ int gemm_tcgen05_launch(const mtfc_gemm_desc* d, const void* a, const void* b, v
 
 int gemm_allreduce_flag_bytes() { return (FLAG_DONE + 1) * 4; }
 
+static long long g_peer_wait_cycles = PEER_WAIT_CYCLES_DEFAULT;
+
+// Limit of every wait on another rank inside the fused kernel, in milliseconds
+// at a nominal 2 GHz clock; <= 0 restores the default of about 3 s.
+void gemm_allreduce_set_wait_ms(int ms) {
+  g_peer_wait_cycles = ms > 0 ? (long long)ms * 2000000LL : PEER_WAIT_CYCLES_DEFAULT;
+}
+
 // Resident 2-CTA clusters for the fused kernel (its blocks are larger); cached per device.
 int max_fused_clusters() {
   static int cached[64];
@@ -1244,6 +1254,7 @@ int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
   fa.ctl = static_cast<uint32_t*>(ctl);
   fa.rank = rank;
   fa.nranks = nranks;
+  fa.wait_cycles = g_peer_wait_cycles;
   const long long num_tiles = (long long)args.tiles_m * args.tiles_n;
   // every cluster must be resident at once: the comm warps wait on other CTAs' products
   const long long clusters = num_tiles < pair_clusters ? num_tiles : pair_clusters;

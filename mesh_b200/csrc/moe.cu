@@ -266,10 +266,12 @@ __global__ void __launch_bounds__(256)
 slot_table_kernel(const int* __restrict__ idx1, const int* __restrict__ idx2,
                   const int* __restrict__ pos1, const int* __restrict__ pos2,
                   const float* __restrict__ gate1, const float* __restrict__ gate2, int S, int E,
-                  int C, int round_bf16, int* __restrict__ table) {
-  extern __shared__ int slots[];
+                  int C, int round_bf16, int in_smem, int* __restrict__ table) {
+  extern __shared__ int slots_smem[];
   const int g = blockIdx.x;
   const int n = E * C;
+  // built in shared memory when the group's table fits there, else in place
+  int* slots = in_smem ? slots_smem : table + (long long)g * n;
   for (int i = threadIdx.x; i < n; i += blockDim.x) slots[i] = -1;
   __syncthreads();
   const long long tok0 = (long long)g * S;
@@ -286,7 +288,8 @@ slot_table_kernel(const int* __restrict__ idx1, const int* __restrict__ idx2,
     if (k2) slots[e2 * C + p2] = s;
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) table[(long long)g * n + i] = slots[i];
+  if (in_smem)
+    for (int i = threadIdx.x; i < n; i += blockDim.x) table[(long long)g * n + i] = slots[i];
 }
 
 // out rows are [E][G][C] (slice layout [O=1 folded into G]); one warp per row.
@@ -524,12 +527,15 @@ int mtfc_moe_slot_table(const int32_t* idx1, const int32_t* idx2, const int32_t*
     return fail(MTFC_ERR_SHAPE, "slot_table: null argument");
   if (groups < 0 || group_size < 1 || experts < 1 || capacity < 1)
     return fail(MTFC_ERR_SHAPE, "slot_table: bad extents");
-  const size_t smem = (size_t)experts * capacity * sizeof(int);
-  if (smem > 48 * 1024) return fail(MTFC_ERR_SHAPE, "slot_table: experts*capacity=%d too large", experts * capacity);
+  if (groups > INT32_MAX || (long long)experts * capacity > INT32_MAX)
+    return fail(MTFC_ERR_SHAPE, "slot_table: extents too large");
+  const size_t table_bytes = (size_t)experts * capacity * sizeof(int);
+  const int in_smem = table_bytes <= 48 * 1024;
   if (groups == 0) return MTFC_OK;
-  slot_table_kernel<<<(unsigned)groups, 256, smem, static_cast<cudaStream_t>(stream)>>>(
+  slot_table_kernel<<<(unsigned)groups, 256, in_smem ? table_bytes : 0,
+                      static_cast<cudaStream_t>(stream)>>>(
       idx1, idx2, pos1, pos2, gate1, gate2, group_size, experts, capacity, round_gates_to_bf16,
-      table);
+      in_smem, table);
   MTFC_LAUNCH_CHECK("slot_table_kernel");
   count_launch(1);
   return MTFC_OK;
@@ -543,6 +549,8 @@ int mtfc_moe_dispatch(const void* x, const int32_t* table, void* out, int64_t ou
     return fail(MTFC_ERR_SHAPE, "dispatch: row of %lld bytes is not a multiple of 16", (long long)row_bytes);
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) % 16 != 0)
     return fail(MTFC_ERR_SHAPE, "dispatch: buffers must be 16-byte aligned");
+  if (outer < 0 || groups_per_outer < 0 || group_size < 1 || experts < 1 || capacity < 1)
+    return fail(MTFC_ERR_SHAPE, "dispatch: bad extents");
   const long long groups = outer * groups_per_outer;
   const long long rows = groups * experts * capacity;
   if (rows == 0) return MTFC_OK;
@@ -619,7 +627,7 @@ int mtfc_moe_dispatch_noalloc(const void* x, const int32_t* idx1, const int32_t*
   // left over from an earlier call is ever read.
   slot_table_kernel<<<(unsigned)groups, 256, (size_t)experts * capacity * sizeof(int), s>>>(
       idx1, idx2, pos1, pos2, gate1, gate2, group_size, experts, capacity, round_gates_to_bf16,
-      table);
+      1, table);
   MTFC_LAUNCH_CHECK("slot_table_kernel");
   dispatch_rows_kernel<<<grid_for(entries * 32, 256), 256, 0, s>>>(
       static_cast<const uint4*>(x), table, static_cast<uint4*>(out), groups, group_size, experts,

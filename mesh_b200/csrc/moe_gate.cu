@@ -1,0 +1,681 @@
+// K2/K3, single pass over the activations: gate logits, softmax, top-2 and
+// renormalised gates in one tcgen05 kernel, then positions / capacity in a
+// small per-group scan kernel.
+//
+// Replaces, for bf16 activations, the sequence "gate-logit GEMM -> logits in
+// HBM -> top2_gating_kernel" for `_top_2_gating`
+// (mesh_tensorflow/transformer/moe.py:1380-1513): the activations are read
+// once (2 bytes x d_model per token), nothing but 16 bytes of routing per
+// token is written, and the softmax / top-2 arithmetic runs with one thread
+// per token on values held in registers.
+//
+//   gate_top2_fused   persistent, one CTA per SM, 192 threads:
+//       warp 0     TMA producer: x tile (128 tokens x 64) + gate-kernel tile
+//                  (3*EP rows x 64) per K block into a ring of swizzled stages
+//       warp 1     tcgen05.mma 128 x 3EP x 16 into one of two TMEM accumulators
+//       warps 2-5  epilogue: thread i owns token row i of the tile: reads the
+//                  3*EP accumulator columns (hi | mid | lo parts of the fp32
+//                  gate kernel, so the bf16 products add up to fp32 accuracy),
+//                  frees the accumulator, then softmax in the exp(x - logsumexp)
+//                  form, top-1, masked top-2 (ties: lowest index), gates
+//                  renormalised with reciprocal-then-multiply.  Column sums of
+//                  the raw gates (for the load-balancing loss) leave the CTA as
+//                  one partial row per tile, added in a fixed order.
+//       Tiles never straddle a group: tile (g, c) covers tokens [128c, 128c+128)
+//       of group g and ignores rows past the group's end.
+//   top2_positions    one CTA per group: position-in-expert of both choices by
+//                  warp match/popc ranks plus a cross-warp scan, second-expert
+//                  policy, capacity masks, loss; optionally the (expert, slot)
+//                  -> token table the dispatch kernel reads.
+//
+// Every mbarrier wait is bounded (tcgen05_ptx.cuh); on expiry the kernel raises
+// the status word, frees its TMEM and returns.
+
+#include "tcgen05_ptx.cuh"
+
+namespace mtfc {
+namespace {
+
+constexpr int TILE_TOKENS = 128;
+constexpr int GBK = 64;  // bf16 per K block = one 128-byte swizzle row
+constexpr int G_UMMA_K = 16;
+constexpr int X_STAGE_BYTES = TILE_TOKENS * GBK * 2;  // 16 KiB
+constexpr int MAX_STAGES = 8;
+constexpr int G_THREADS = 192;
+constexpr int G_EPI_WARPS = 4;
+constexpr int G_TMEM_COLS = 512;
+constexpr int G_ACC_STRIDE = 256;  // TMEM columns between the two accumulators
+constexpr int kMaxGateExperts = 64;
+
+struct GateFusedArgs {
+  int group_size, experts, m;
+  int tiles_per_group;
+  long long num_tiles;
+  int stages;
+  int* idx1;
+  int* idx2;
+  float* gate1;
+  float* gate2;
+  float* raw_gates;  // [tokens, experts] or null
+  float* tile_sums;  // [num_tiles, EP]: column sums of the raw gates per tile
+  int* status;
+};
+
+__device__ __forceinline__ void tc_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void epi_warps_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(32 * G_EPI_WARPS) : "memory");
+}
+
+// fp32 gate kernel [m, E] -> bf16 [3*EP, m]: row p*EP + e holds part p (hi, mid,
+// lo) of column e; rows of experts in [E, EP) are zero.
+__global__ void split_gate_weights_kmajor_kernel(const float* __restrict__ w, long long m, int e,
+                                                 int ep, __nv_bfloat16* __restrict__ out) {
+  const long long n = m * ep;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
+    const int col = (int)(i / m);        // expert (padded)
+    const long long row = i - col * m;   // d_model index: consecutive threads, consecutive rows
+    __nv_bfloat16 hi = __float2bfloat16_rn(0.f), mid = hi, lo = hi;
+    if (col < e) {
+      const float v = w[row * e + col];
+      hi = __float2bfloat16_rn(v);
+      const float r1 = v - __bfloat162float(hi);
+      mid = __float2bfloat16_rn(r1);
+      const float r2 = r1 - __bfloat162float(mid);
+      lo = __float2bfloat16_rn(r2);
+    }
+    out[(long long)col * m + row] = hi;
+    out[(long long)(ep + col) * m + row] = mid;
+    out[(long long)(2 * ep + col) * m + row] = lo;
+  }
+}
+
+template <int EP>
+__global__ void __launch_bounds__(G_THREADS, 1)
+gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                const GateFusedArgs a) {
+  constexpr int N = 3 * EP;
+  constexpr int W_STAGE_BYTES = N * GBK * 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  const int ST = a.stages;
+  const uint32_t off_w = (uint32_t)ST * X_STAGE_BYTES;
+  const uint32_t off_sums = off_w + (uint32_t)ST * W_STAGE_BYTES;
+  const uint32_t off_bar = off_sums + 2 * G_EPI_WARPS * EP * 4;
+  const uint32_t off_misc = off_bar + (2 * MAX_STAGES + 4) * 8;
+  const uint32_t bar_base = smem_base + off_bar;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
+  auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * MAX_STAGES + b); };
+  auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * MAX_STAGES + 2 + b); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + off_misc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + off_misc + 4);
+  float* warp_sums = reinterpret_cast<float*>(smem + off_sums);  // [2][G_EPI_WARPS][EP]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < ST; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tmem_full_bar(b), 1);
+      mbar_init(tmem_empty_bar(b), G_EPI_WARPS);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_base + off_misc),
+                 "r"(G_TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int num_kb = (a.m + GBK - 1) / GBK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < a.num_tiles && ok; t += gridDim.x) {
+        const long long g = t / a.tiles_per_group;
+        const int c = (int)(t - g * a.tiles_per_group);
+        const long long row0 = g * a.group_size + (long long)c * TILE_TOKENS;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(full_bar(stage), X_STAGE_BYTES + W_STAGE_BYTES);
+          tma_load_3d(smem_base + stage * X_STAGE_BYTES, &map_x, full_bar(stage), kb * GBK,
+                      (int)row0, 0);
+          tma_load_3d(smem_base + off_w + stage * W_STAGE_BYTES, &map_w, full_bar(stage), kb * GBK,
+                      0, 0);
+          if (++stage == ST) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok && a.status) atomicExch(a.status, MTFC_ERR_TIMEOUT);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // kind::f16 instruction descriptor: fp32 accumulator, bf16 operands, both K-major
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) |
+                             ((uint32_t)(TILE_TOKENS >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      long long local = 0;
+      for (long long t = blockIdx.x; t < a.num_tiles && ok; t += gridDim.x, ++local) {
+        const int buf = (int)(local & 1);
+        const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+        if (!mbar_wait(tmem_empty_bar(buf), acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * G_ACC_STRIDE);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sx = smem_base + stage * X_STAGE_BYTES;
+          const uint32_t sw = smem_base + off_w + stage * W_STAGE_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < GBK / G_UMMA_K; ++ks) {
+            const uint64_t da = make_smem_desc(sx + ks * G_UMMA_K * 2, 16, 1024);
+            const uint64_t db = make_smem_desc(sw + ks * G_UMMA_K * 2, 16, 1024);
+            tc_mma_bf16(d_tmem, da, db, idesc, (kb | ks) != 0 ? 1u : 0u);
+          }
+          tc_commit(empty_bar(stage));
+          if (++stage == ST) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(tmem_full_bar(buf));
+      }
+      if (!ok && a.status) atomicExch(a.status, MTFC_ERR_TIMEOUT);
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;   // TMEM lane quarter this warp may read
+    const int ew = warp - 2;  // 0..3
+    const int E = a.experts;
+    bool ok = true;
+    long long local = 0;
+    for (long long t = blockIdx.x; t < a.num_tiles && ok; t += gridDim.x, ++local) {
+      const int buf = (int)(local & 1);
+      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+      const long long g = t / a.tiles_per_group;
+      const int c = (int)(t - g * a.tiles_per_group);
+      const int s_in_group = c * TILE_TOKENS + q * 32 + lane;
+      const bool live = s_in_group < a.group_size;
+      const long long tok = g * a.group_size + s_in_group;
+      ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), acc_phase, abort_flag));
+      if (!ok) {
+        // a warp that gave up still counts at this tile's column-sum barrier, so
+        // that warps which got through the wait are not left standing there
+        asm volatile("bar.arrive 1, %0;" ::"n"(32 * G_EPI_WARPS) : "memory");
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * G_ACC_STRIDE);
+      float r[EP];
+#pragma unroll
+      for (int ch = 0; ch < EP / 16; ++ch) {
+        uint32_t hi[16], mid[16], lo[16];
+        tc_ld_32x16(t_row + ch * 16, hi);
+        tc_ld_32x16(t_row + EP + ch * 16, mid);
+        tc_ld_32x16(t_row + 2 * EP + ch * 16, lo);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          r[ch * 16 + j] = (__uint_as_float(hi[j]) + __uint_as_float(mid[j])) + __uint_as_float(lo[j]);
+      }
+      // the accumulator is in registers: hand it back before the arithmetic
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
+
+      float mx = r[0];
+#pragma unroll
+      for (int e = 1; e < EP; ++e)
+        if (e < E) mx = fmaxf(mx, r[e]);
+      float sum = 0.f;
+#pragma unroll
+      for (int e = 0; e < EP; ++e)
+        if (e < E) sum += expf(r[e] - mx);
+      const float lse = logf(sum) + mx;
+      int i1 = 0, i2 = 0;
+      float b1 = -1.f, b2 = -1.f;
+#pragma unroll
+      for (int e = 0; e < EP; ++e) {
+        const float p = e < E ? expf(r[e] - lse) : 0.f;
+        r[e] = p;
+        if (e < E && p > b1) { b1 = p; i1 = e; }
+      }
+#pragma unroll
+      for (int e = 0; e < EP; ++e) {
+        const float p = (e == i1) ? 0.f : r[e];
+        if (e < E && p > b2) { b2 = p; i2 = e; }
+      }
+      const float recip = 1.0f / ((b1 + b2) + 1e-9f);
+      if (live) {
+        a.idx1[tok] = i1;
+        a.idx2[tok] = i2;
+        a.gate1[tok] = b1 * recip;
+        a.gate2[tok] = b2 * recip;
+        if (a.raw_gates) {
+          float* dst = a.raw_gates + tok * E;
+#pragma unroll
+          for (int e = 0; e < EP; ++e)
+            if (e < E) dst[e] = r[e];
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < EP; ++e) r[e] = 0.f;   // rows past the group's end add nothing
+      }
+      // column sums over the warp's 32 rows: reduce-scatter over the lanes (a
+      // fixed tree), after which lane l holds the sums of EP/32 (or, for EP = 16,
+      // half a) column
+#pragma unroll
+      for (int k = 0; k < 5; ++k) {
+        const int off = 16 >> k;
+        const int before = (EP >> k) > 1 ? (EP >> k) : 1;   // values per lane entering the step
+        if (before > 1) {
+          const int half = before >> 1;
+          const bool upper = (lane & off) != 0;
+#pragma unroll
+          for (int i = 0; i < EP / 2; ++i) {
+            if (i < half) {
+              const float send = upper ? r[i] : r[i + half];
+              const float keep = upper ? r[i + half] : r[i];
+              r[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+            }
+          }
+        } else {
+          r[0] += __shfl_xor_sync(0xffffffffu, r[0], off);
+        }
+      }
+      float* mine = warp_sums + ((local & 1) * G_EPI_WARPS + ew) * EP;
+      if (EP >= 32) {
+#pragma unroll
+        for (int i = 0; i < EP / 32; ++i) mine[lane * (EP / 32) + i] = r[i];
+      } else if ((lane & 1) == 0) {
+        mine[lane >> 1] = r[0];
+      }
+      epi_warps_sync();
+      const int tid = ew * 32 + lane;
+      if (tid < EP) {
+        const float* ws = warp_sums + (local & 1) * G_EPI_WARPS * EP;
+        // rows in token order: warps 2..5 hold lane quarters 2, 3, 0, 1
+        const float s = ((ws[2 * EP + tid] + ws[3 * EP + tid]) + ws[0 * EP + tid]) + ws[1 * EP + tid];
+        a.tile_sums[t * EP + tid] = s;
+      }
+    }
+    if (!ok && lane == 0 && a.status) atomicExch(a.status, MTFC_ERR_TIMEOUT);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(G_TMEM_COLS)
+                 : "memory");
+  }
+}
+
+__device__ __forceinline__ bool gate_nonzero_bf16(float g) {
+  return __bfloat162float(__float2bfloat16_rn(g)) != 0.0f;
+}
+
+struct PositionArgs {
+  int group_size, experts, capacity, policy;
+  float threshold;
+  const float* noise;
+  const int* idx1;
+  const int* idx2;
+  int* pos1;
+  int* pos2;
+  float* gate1;  // in: renormalised gates; out: zeroed where dropped
+  float* gate2;
+  const float* tile_sums;  // [groups, tiles_per_group, ep]
+  int tiles_per_group, ep;
+  float* loss_per_group;
+  int* table;  // [groups, experts, capacity] or null
+  int table_in_smem;
+  int round_bf16;
+};
+
+// One CTA of T threads per group, tokens T at a time in index order.  Shared
+// memory: base1[E], base2[E], cnt1[E], wcnt[T/32][E], slots[E*C] (if a table is
+// written).
+__global__ void __launch_bounds__(1024)
+top2_positions_kernel(PositionArgs a) {
+  extern __shared__ int ismem[];
+  const int E = a.experts, S = a.group_size, C = a.capacity;
+  const int T = blockDim.x, W = T >> 5;
+  int* base1 = ismem;
+  int* base2 = base1 + E;
+  int* cnt1 = base2 + E;
+  int* wcnt = cnt1 + E;
+  const int g = blockIdx.x;
+  // the group's slot table is built in shared memory when it fits there, else in place
+  int* slots = a.table_in_smem ? wcnt + W * E : a.table + (long long)g * E * C;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const unsigned lt_mask = (1u << lane) - 1u;
+  const long long tok0 = (long long)g * S;
+  const bool single = S <= T;   // the whole group sits in registers between the passes
+
+  for (int e = tid; e < E; e += T) { base1[e] = 0; base2[e] = 0; }
+  if (a.table)
+    for (int i = tid; i < E * C; i += T) slots[i] = -1;
+  __syncthreads();
+
+  int keep_i1 = -1, keep_p1 = 0;
+  // ---- pass 1: first-choice positions ----
+  for (int c0 = 0; c0 < S; c0 += T) {
+    for (int i = tid; i < W * E; i += T) wcnt[i] = 0;
+    __syncthreads();
+    const bool live = c0 + tid < S;
+    const long long t = tok0 + c0 + tid;
+    int i1 = -1 - lane;   // dead lanes never match a live expert index
+    if (live) i1 = a.idx1[t];
+    const unsigned same = __match_any_sync(0xffffffffu, i1);
+    const int rank = __popc(same & lt_mask);
+    if (live && rank == 0) wcnt[warp * E + i1] = __popc(same);
+    __syncthreads();
+    for (int e = tid; e < E; e += T) {
+      int run = base1[e];
+      for (int w = 0; w < W; ++w) {
+        const int c = wcnt[w * E + e];
+        wcnt[w * E + e] = run;
+        run += c;
+      }
+      base1[e] = run;
+    }
+    __syncthreads();
+    if (live) {
+      const int p1 = wcnt[warp * E + i1] + rank;
+      a.pos1[t] = p1;
+      if (single) { keep_i1 = i1; keep_p1 = p1; }
+    }
+    __syncthreads();
+  }
+
+  // ---- loss (pre-capacity counts) and kept first-choice counts ----
+  for (int e = tid; e < E; e += T) cnt1[e] = min(base1[e], C);
+  if (warp == 0) {
+    float part = 0.f;
+    const float inv_s = 1.0f / (float)S;
+    for (int e = lane; e < E; e += 32) {
+      float proxy = 0.f;
+      const float* ts = a.tile_sums + ((long long)g * a.tiles_per_group) * a.ep + e;
+      for (int k = 0; k < a.tiles_per_group; ++k) proxy += ts[(long long)k * a.ep];
+      part += (proxy * inv_s) * ((float)base1[e] * inv_s);
+    }
+    for (int s = 16; s > 0; s >>= 1) part += __shfl_xor_sync(0xffffffffu, part, s);
+    if (lane == 0) a.loss_per_group[g] = part * (1.0f / (float)E) * (float)(E * E);
+  }
+  __syncthreads();
+
+  // ---- pass 2: second-choice policy, positions, capacity masks ----
+  for (int c0 = 0; c0 < S; c0 += T) {
+    for (int i = tid; i < W * E; i += T) wcnt[i] = 0;
+    __syncthreads();
+    const bool live = c0 + tid < S;
+    const long long t = tok0 + c0 + tid;
+    int i2 = -1 - lane, cand = 0, i1 = 0, p1 = 0;
+    float g1 = 0.f, g2 = 0.f;
+    bool m2 = false;
+    if (live) {
+      g1 = a.gate1[t];
+      g2 = a.gate2[t];
+      cand = a.idx2[t];
+      if (single) { i1 = keep_i1; p1 = keep_p1; } else { i1 = a.idx1[t]; p1 = a.pos1[t]; }
+      switch (a.policy) {
+        case MTFC_MOE_POLICY_ALL: m2 = true; break;
+        case MTFC_MOE_POLICY_NONE: m2 = false; break;
+        case MTFC_MOE_POLICY_THRESHOLD: m2 = g2 > a.threshold; break;
+        case MTFC_MOE_POLICY_RANDOM:
+          m2 = a.noise[t] < g2 * (1.0f / fmaxf(a.threshold, 1e-9f));
+          break;
+        default: m2 = true;
+      }
+      if (m2) i2 = cand;
+    }
+    const unsigned same = __match_any_sync(0xffffffffu, i2);
+    const int rank = __popc(same & lt_mask);
+    if (live && m2 && rank == 0) wcnt[warp * E + i2] = __popc(same);
+    __syncthreads();
+    for (int e = tid; e < E; e += T) {
+      int run = base2[e];
+      for (int w = 0; w < W; ++w) {
+        const int c = wcnt[w * E + e];
+        wcnt[w * E + e] = run;
+        run += c;
+      }
+      base2[e] = run;
+    }
+    __syncthreads();
+    if (live) {
+      int p2 = 0;
+      if (m2) p2 = wcnt[warp * E + i2] + rank + cnt1[i2];
+      const bool keep1 = p1 < C;
+      const bool keep2 = m2 && p2 < C;
+      g1 = keep1 ? g1 : 0.f;
+      g2 = keep2 ? g2 : 0.f;
+      a.pos2[t] = p2;
+      a.gate1[t] = g1;
+      a.gate2[t] = g2;
+      if (a.table) {
+        const int s = c0 + tid;
+        if (keep1 && (a.round_bf16 ? gate_nonzero_bf16(g1) : g1 != 0.f)) slots[i1 * C + p1] = s;
+        if (keep2 && (a.round_bf16 ? gate_nonzero_bf16(g2) : g2 != 0.f)) slots[cand * C + p2] = s;
+      }
+    }
+    __syncthreads();
+  }
+  if (a.table && a.table_in_smem)
+    for (int i = tid; i < E * C; i += T) a.table[(long long)g * E * C + i] = slots[i];
+}
+
+typedef CUresult (*GateEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                 const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+GateEncodeFn gate_encode_fn() {
+  static GateEncodeFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<GateEncodeFn>(p);
+  }
+  return fn;
+}
+
+// [rows, m] bf16 row-major as a 3-D map {m, rows, 1} with a {64, box_rows, 1} box.
+int gate_encode(CUtensorMap* map, const void* base, long long m, long long rows, int box_rows,
+                const char* what) {
+  GateEncodeFn fn = gate_encode_fn();
+  if (!fn) return fail(MTFC_ERR_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
+  cuuint64_t dims[3] = {(cuuint64_t)m, (cuuint64_t)rows, 1};
+  cuuint64_t strides[2] = {(cuuint64_t)(m * 2), (cuuint64_t)(m * 2 * rows)};
+  cuuint32_t box[3] = {(cuuint32_t)GBK, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(MTFC_ERR_SHAPE, "tensor map for %s rejected (CUresult %d): m=%lld rows=%lld", what,
+                (int)r, m, rows);
+  return MTFC_OK;
+}
+
+int padded_experts(int experts) { return experts <= 16 ? 16 : (experts <= 32 ? 32 : 64); }
+
+int gate_stages(int ep) {
+  const int per_stage = X_STAGE_BYTES + 3 * ep * GBK * 2;
+  int st = (200 * 1024) / per_stage;
+  return st > MAX_STAGES ? MAX_STAGES : st;
+}
+
+size_t gate_fused_smem(int ep) {
+  return (size_t)gate_stages(ep) * (X_STAGE_BYTES + 3 * ep * GBK * 2) + 2 * G_EPI_WARPS * ep * 4 +
+         (2 * MAX_STAGES + 4) * 8 + 16 + 1024;
+}
+
+template <int EP>
+int launch_gate_fused(const CUtensorMap& mx, const CUtensorMap& mw, const GateFusedArgs& a,
+                      cudaStream_t s) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  MTFC_CUDA(cudaGetDevice(&dev));
+  const size_t smem = gate_fused_smem(EP);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    MTFC_CUDA(cudaFuncSetAttribute(gate_top2_fused<EP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)smem));
+    attr_set[dev] = true;
+  }
+  const int sms = sm_count();
+  const unsigned grid = (unsigned)(a.num_tiles < sms ? a.num_tiles : sms);
+  gate_top2_fused<EP><<<grid, G_THREADS, smem, s>>>(mx, mw, a);
+  MTFC_LAUNCH_CHECK("gate_top2_fused");
+  return MTFC_OK;
+}
+
+}  // namespace
+}  // namespace mtfc
+
+using namespace mtfc;
+
+extern "C" {
+
+int mtfc_moe_gate_fused_supported(int64_t m, int32_t experts) {
+  return (m >= 8 && m % 8 == 0 && experts >= 2 && experts <= kMaxGateExperts) ? 1 : 0;
+}
+
+int32_t mtfc_moe_gate_padded_experts(int32_t experts) { return padded_experts(experts); }
+
+int64_t mtfc_moe_gate_scratch_bytes(int64_t groups, int32_t group_size, int32_t experts) {
+  if (groups < 0 || group_size < 1 || experts < 1) return 0;
+  const int64_t tpg = (group_size + TILE_TOKENS - 1) / TILE_TOKENS;
+  return groups * tpg * padded_experts(experts) * 4;
+}
+
+int mtfc_moe_gate_prepare(const float* w, int64_t m, int32_t experts, void* w3t_bf16, void* stream) {
+  if (!w || !w3t_bf16 || m < 1 || experts < 1 || experts > kMaxGateExperts)
+    return fail(MTFC_ERR_SHAPE, "gate_prepare: bad arguments");
+  const int ep = padded_experts(experts);
+  split_gate_weights_kmajor_kernel<<<grid_for(m * ep, 256), 256, 0,
+                                     static_cast<cudaStream_t>(stream)>>>(
+      w, m, experts, ep, static_cast<__nv_bfloat16*>(w3t_bf16));
+  MTFC_LAUNCH_CHECK("split_gate_weights_kmajor_kernel");
+  count_launch(1);
+  return MTFC_OK;
+}
+
+int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups, int32_t group_size,
+                       int64_t m, int32_t experts, int32_t capacity, int32_t policy,
+                       float threshold, const float* noise, int32_t* idx1, int32_t* idx2,
+                       int32_t* pos1, int32_t* pos2, float* gate1, float* gate2, float* raw_gates,
+                       float* loss_per_group, int32_t* slot_table, int32_t round_gates_to_bf16,
+                       void* scratch, int64_t scratch_bytes, void* stream) {
+  if (!x_bf16 || !w3t_bf16 || !idx1 || !idx2 || !pos1 || !pos2 || !gate1 || !gate2 ||
+      !loss_per_group || !scratch)
+    return fail(MTFC_ERR_SHAPE, "gate_top2: null argument");
+  if (groups < 0 || group_size < 1 || capacity < 0)
+    return fail(MTFC_ERR_SHAPE, "gate_top2: bad extents");
+  if (!mtfc_moe_gate_fused_supported(m, experts))
+    return fail(MTFC_ERR_UNSUPPORTED,
+                "gate_top2: needs d_model a multiple of 8 and 2..%d experts (got %lld, %d)",
+                kMaxGateExperts, (long long)m, experts);
+  if (policy == MTFC_MOE_POLICY_RANDOM && !noise)
+    return fail(MTFC_ERR_SHAPE, "gate_top2: policy random needs the noise tensor");
+  if (policy < MTFC_MOE_POLICY_ALL || policy > MTFC_MOE_POLICY_RANDOM)
+    return fail(MTFC_ERR_SHAPE, "gate_top2: unknown policy %d", policy);
+  if ((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(w3t_bf16)) % 16 != 0)
+    return fail(MTFC_ERR_SHAPE, "gate_top2: buffers must be 16-byte aligned");
+  if (groups == 0) return MTFC_OK;
+  const long long tokens = groups * group_size;
+  if (groups > INT32_MAX || tokens > INT32_MAX)
+    return fail(MTFC_ERR_SHAPE, "gate_top2: too many tokens");
+  if (scratch_bytes < mtfc_moe_gate_scratch_bytes(groups, group_size, experts))
+    return fail(MTFC_ERR_SHAPE, "gate_top2: scratch of %lld bytes is too small", (long long)scratch_bytes);
+  if ((long long)experts * capacity > INT32_MAX)
+    return fail(MTFC_ERR_SHAPE, "gate_top2: experts*capacity too large");
+  const int ep = padded_experts(experts);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  CUtensorMap map_x, map_w;
+  int rc = gate_encode(&map_x, x_bf16, m, tokens, TILE_TOKENS, "gate activations");
+  if (rc != MTFC_OK) return rc;
+  rc = gate_encode(&map_w, w3t_bf16, m, 3 * ep, 3 * ep, "gate kernel");
+  if (rc != MTFC_OK) return rc;
+  GateFusedArgs a;
+  a.group_size = group_size;
+  a.experts = experts;
+  a.m = (int)m;
+  a.tiles_per_group = (group_size + TILE_TOKENS - 1) / TILE_TOKENS;
+  a.num_tiles = groups * a.tiles_per_group;
+  a.stages = gate_stages(ep);
+  a.idx1 = idx1; a.idx2 = idx2; a.gate1 = gate1; a.gate2 = gate2;
+  a.raw_gates = raw_gates;
+  a.tile_sums = static_cast<float*>(scratch);
+  a.status = device_status_word();
+  switch (ep) {
+    case 16: rc = launch_gate_fused<16>(map_x, map_w, a, s); break;
+    case 32: rc = launch_gate_fused<32>(map_x, map_w, a, s); break;
+    default: rc = launch_gate_fused<64>(map_x, map_w, a, s); break;
+  }
+  if (rc != MTFC_OK) return rc;
+
+  PositionArgs p;
+  p.group_size = group_size; p.experts = experts; p.capacity = capacity; p.policy = policy;
+  p.threshold = threshold; p.noise = noise;
+  p.idx1 = idx1; p.idx2 = idx2; p.pos1 = pos1; p.pos2 = pos2; p.gate1 = gate1; p.gate2 = gate2;
+  p.tile_sums = a.tile_sums; p.tiles_per_group = a.tiles_per_group; p.ep = ep;
+  p.loss_per_group = loss_per_group;
+  p.table = slot_table;
+  p.round_bf16 = round_gates_to_bf16;
+  int threads = 1024;
+  while (threads > 32 && threads / 2 >= group_size) threads >>= 1;
+  const size_t base_smem = (size_t)(3 * experts + (threads / 32) * experts) * sizeof(int);
+  const size_t table_smem = (size_t)experts * capacity * sizeof(int);
+  p.table_in_smem = slot_table && base_smem + table_smem <= 96 * 1024;
+  const size_t smem = base_smem + (p.table_in_smem ? table_smem : 0);
+  if (smem > 48 * 1024) {
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    MTFC_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+      MTFC_CUDA(cudaFuncSetAttribute(top2_positions_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+      attr_set[dev] = true;
+    }
+  }
+  top2_positions_kernel<<<(unsigned)groups, threads, smem, s>>>(p);
+  MTFC_LAUNCH_CHECK("top2_positions_kernel");
+  count_launch(2);
+  return MTFC_OK;
+}
+
+}  // extern "C"

@@ -41,6 +41,8 @@ class SlicedMeshImpl(mtf.MeshImpl):
   `_from_torch(t, shape, dtype, pnum)` used by the distributed collectives.
   """
 
+  allreduce_accepts_donation = True
+
   def __init__(self, shape, layout, local_pnums, distributed):
     super().__init__(shape, layout)
     self._local_pnums = list(local_pnums)
@@ -181,14 +183,19 @@ class SlicedMeshImpl(mtf.MeshImpl):
     return _combine_host(self, host, x.shape)
 
   # ------------------------------------------------------------ collectives
-  def allreduce(self, x, mesh_axes, reduction_fn_string):
+  def allreduce(self, x, mesh_axes, reduction_fn_string, donate=False):
+    """Grouped SUM / MAX / MIN (placement_mesh_impl.py:200-212).  Mesh axes of
+    size one have single-member groups and are dropped.  `donate=True` says
+    the caller holds no other reference to `x`, so its buffers may be reduced
+    in place."""
+    if reduction_fn_string not in ("SUM", "MAX", "MIN"):
+      raise ValueError("unknown reduction %s" % reduction_fn_string)
+    mesh_axes = [a for a in mesh_axes if self.shape[a].size > 1]
     if not mesh_axes:
       return x
     x = x.to_laid_out_tensor()
-    if reduction_fn_string not in ("SUM", "MAX", "MIN"):
-      raise ValueError("unknown reduction %s" % reduction_fn_string)
     if self._distributed:
-      return self._dist_allreduce(x, mesh_axes, reduction_fn_string)
+      return self._dist_allreduce(x, mesh_axes, reduction_fn_string, donate)
     name = {"SUM": "add", "MAX": "maximum", "MIN": "minimum"}[reduction_fn_string]
 
     def collective(slices, pnums):
@@ -302,13 +309,20 @@ class SlicedMeshImpl(mtf.MeshImpl):
   def _from_torch(self, t, shape, dtype, pnum):
     raise NotImplementedError
 
-  def _dist_allreduce(self, x, mesh_axes, name):
+  def _owns_storage(self, s, t):
+    """True when the flat tensor `t` made from slice `s` may be overwritten
+    without touching memory another slice can see."""
+    return False
+
+  def _dist_allreduce(self, x, mesh_axes, name, donate=False):
     import torch.distributed as dist
     pg, _ = self._group(mesh_axes)
     op = {"SUM": dist.ReduceOp.SUM, "MAX": dist.ReduceOp.MAX, "MIN": dist.ReduceOp.MIN}[name]
     pnum = self._local_pnums[0]
     s = x.tensor_list[0]
-    t = self._as_torch(s).clone()
+    t = self._as_torch(s)
+    if not (donate and self._owns_storage(s, t)):
+      t = t.clone()   # collectives return fresh tensors; the input stays intact
     dist.all_reduce(t, op=op, group=pg)
     return self.LaidOutTensor([self._from_torch(t, s.shape, s.dtype, pnum)])
 
@@ -497,11 +511,69 @@ class CudaMeshImpl(SlicedMeshImpl):
     dev = self._devices[pnum]
     if s.device == dev:
       return s
-    ops = self._ops_for(pnum)
+    # pack on the SOURCE device (a strided view is gathered by a kernel that
+    # dereferences source-device pointers), then let the copy engine move the
+    # packed bytes: torch's cross-device copy enables peer access and orders
+    # the copy after the producer's stream
+    self._ops.device = s.device
     packed = self._ops.contiguous(s)
     flat = packed.buf[packed.offset:packed.offset + max(1, packed.size)].to(dev)
-    del ops
+    self._ops.device = dev
     return self._device_array(flat, s.shape, s.dtype)
+
+  # A host tensor whose slice is replicated over some mesh axes is uploaded in
+  # parts: each replica sends 1/k of the slice over its own host link and an
+  # allgather over NVLink (an order of magnitude faster than the host link)
+  # completes it on every replica.  Slices below this size are uploaded whole.
+  SHARED_UPLOAD_MIN_BYTES = 1 << 20
+
+  def _replica_group(self, tensor_shape):
+    """(process group, members, my position) over the mesh axes the tensor's
+    layout leaves unused, or None when the slice has no other replica."""
+    layout = self.tensor_layout(tensor_shape)
+    used = set(a for a in layout.tensor_axis_to_mesh_axis if a is not None)
+    free = [a for a in range(self.ndims) if a not in used and self.shape[a].size > 1]
+    if not free:
+      return None
+    pg, members = self._group(free)
+    return pg, members, members.index(self._local_pnums[0])
+
+  def import_tf_tensor(self, x, tf_x):
+    import torch
+    if self._distributed and isinstance(tf_x, torch.Tensor):
+      shared = self._import_shared(x, tf_x)
+      if shared is not None:
+        return shared
+    return super().import_tf_tensor(x, tf_x)
+
+  def _import_shared(self, x, value):
+    import torch
+    import torch.distributed as dist
+    from mesh_b200.device_ops import _TORCH
+    if value.dtype != _TORCH[x.dtype.name]:
+      return None
+    group = self._replica_group(x.shape)
+    if group is None:
+      return None
+    pg, members, me = group
+    k = len(members)
+    pnum = self._local_pnums[0]
+    slice_shape = self.slice_shape(x.shape)
+    begin = self.slice_begin(x.shape, pnum)
+    part = value[tuple(slice(b, b + s) for b, s in zip(begin, slice_shape))]
+    n = part.numel()
+    if not part.is_contiguous() or n % k != 0 or n * part.element_size() < self.SHARED_UPLOAD_MIN_BYTES:
+      return None
+    ops = self._ops_for(pnum)
+    ops._activate()
+    flat = part.reshape(-1)
+    chunk = n // k
+    buf = torch.empty(n, dtype=value.dtype, device=ops.device)
+    mine = buf[me * chunk:(me + 1) * chunk]
+    mine.copy_(flat[me * chunk:(me + 1) * chunk], non_blocking=True)
+    dist.all_gather_into_tensor(buf, mine, group=pg)
+    self.last_upload_bytes = chunk * part.element_size()
+    return self.LaidOutTensor([self._device_array(buf, slice_shape, x.dtype)])
 
   def einsum(self, equation, *slices, epilogue=None):
     """Per-slice contraction hook (ops.py:1331-1340) on the GEMM kernels;
@@ -525,6 +597,9 @@ class CudaMeshImpl(SlicedMeshImpl):
   # above this the exchange dominates and NCCL moves the bytes faster (measured:
   # a 256 MiB attention output projection on 2 GPUs, 4.25 ms fused against 3.86 ms)
   FUSED_MAX_BYTES = 128 << 20
+  # largest group the fused kernel is used for (groups of 2 and 4 have run on
+  # hardware; MTFC_FUSED_ALLREDUCE_MAX_RANKS=8 opens groups of eight)
+  FUSED_MAX_RANKS = int(os.environ.get("MTFC_FUSED_ALLREDUCE_MAX_RANKS", "4"))
 
   def einsum_allreduce(self, equation, inputs, mesh_axes):
     """Contraction whose SUM allreduce over `mesh_axes` starts chunk by chunk.
@@ -536,7 +611,8 @@ class CudaMeshImpl(SlicedMeshImpl):
     GEMM.  Returns an object with to_laid_out_tensor(), or None when the plain
     einsum-then-allreduce sequence should be used.
     """
-    if not self._distributed:
+    mesh_axes = [a for a in mesh_axes if self.shape[a].size > 1]
+    if not self._distributed or not mesh_axes:
       return None
     import torch.distributed as dist
     inputs = convert_args_to_laid_out_tensors(inputs)
@@ -559,7 +635,8 @@ class CudaMeshImpl(SlicedMeshImpl):
     pg, members = self._group(mesh_axes)
     sizes = dict(zip(ta, a.shape))
     sizes.update(zip(tb, b.shape))
-    if self.FUSED_ALLREDUCE and 2 <= len(members) <= 8 and a.dtype.name == "bfloat16":
+    if (self.FUSED_ALLREDUCE and 2 <= len(members) <= self.FUSED_MAX_RANKS
+        and a.dtype.name == "bfloat16"):
       fused = self._einsum_allreduce_fused(ops, equation, a, b, pg, members, pnum)
       if fused is not None:
         return _PendingAllreduce(self, fused, [])
@@ -666,14 +743,37 @@ class CudaMeshImpl(SlicedMeshImpl):
   def _from_torch(self, t, shape, dtype, pnum):
     return self._device_array(t, shape, dtype)
 
-  def export_to_host_tensors(self, laid_out_x, out=None):
+  def _owns_storage(self, s, t):
+    # a slice that spans its whole buffer shares it with no other view
+    return s.offset == 0 and s.is_contiguous and s.buf.numel() == max(1, s.size) \
+        and t.data_ptr() == s.buf.data_ptr()
+
+  def export_to_host_tensors(self, laid_out_x, out=None, tensor=None):
     """Copies this process's slices to host torch tensors in their own dtype.
 
     `out`, a list of (pinned) CPU tensors, one per local slice, makes the
     copies asynchronous on the current stream; call synchronize() before
     reading them.  The cheap sibling of export_to_tf_tensor for callers that
-    consume slices rather than the assembled full tensor."""
+    consume slices rather than the assembled full tensor.
+
+    With `tensor` (the mtf.Tensor the slices belong to) in a one-process-per-GPU
+    job, a slice that other processes hold replicas of is downloaded in parts:
+    replica j of k copies only elements [j*n/k, (j+1)*n/k) of the flattened
+    slice into the same region of its `out` buffer, so every byte of the tensor
+    crosses a host link once.  Returns, in that case, [(out, begin, end)]."""
     laid_out_x = laid_out_x.to_laid_out_tensor()
+    if tensor is not None and self._distributed and out is not None:
+      group = self._replica_group(tensor.shape)
+      s = laid_out_x.all_slices[0]
+      if group is not None and s.size % len(group[1]) == 0:
+        _, members, me = group
+        ops = self._ops_for(self._local_pnums[0])
+        ops._activate()
+        packed = ops.contiguous(s)
+        chunk = s.size // len(members)
+        src = packed.buf[packed.offset + me * chunk:packed.offset + (me + 1) * chunk]
+        out[0].reshape(-1)[me * chunk:(me + 1) * chunk].copy_(src, non_blocking=True)
+        return [(out[0], me * chunk, (me + 1) * chunk)]
     result = []
     for i, (pnum, s) in enumerate(zip(self._local_pnums, laid_out_x.all_slices)):
       ops = self._ops_for(pnum)
@@ -701,12 +801,32 @@ class CudaMeshImpl(SlicedMeshImpl):
       with torch.cuda.graph(graph):
         result = fn()
       torch.cuda.synchronize()
+    if not hasattr(self, "_graphs"):
+      self._graphs = []
+    self._graphs.append(graph)
     return result, graph.replay
+
+  def release_graphs(self):
+    """Destroys every CUDA graph recorded through capture().  A recorded graph
+    that contains NCCL kernels holds a reference on their communicator, and the
+    communicator's teardown waits for those references: release the graphs
+    (after synchronising) before destroying the process group."""
+    import torch
+    torch.cuda.synchronize()
+    for graph in getattr(self, "_graphs", []):
+      graph.reset()
+    self._graphs = []
 
   def synchronize(self):
     """Waits for all enqueued work and raises if a kernel reported a timeout."""
     import torch
     from mesh_b200 import _native as nat
-    for dev in sorted(set(self._devices[p] for p in self._local_pnums), key=str):
-      with torch.cuda.device(dev):
-        nat.device_status()
+    try:
+      for dev in sorted(set(self._devices[p] for p in self._local_pnums), key=str):
+        with torch.cuda.device(dev):
+          nat.device_status()
+    except nat.MtfcError:
+      # a fused einsum+allreduce whose wait ran out leaves its flags and epoch
+      # counters out of step with the other ranks: never reuse those buffers
+      self._peer_ws = {}
+      raise

@@ -666,21 +666,84 @@ class DeviceOps(object):
     result = (i1, i2, p1, p2, g1, g2, loss)
     return result + (raw,) if want_raw else result
 
-  def moe_top2_gating(self, x, w, capacity, policy, threshold, noise, num_groups_total):
-    """Fused `_top_2_gating` on one slice: x [..., S, M], w [M, E]."""
-    logits, parts = self.moe_gate_logits(x, w)
-    return self.moe_top2_gating_from_logits(
-        logits, parts, x.shape[:-2], x.shape[-2], w.shape[1], capacity, policy, threshold, noise,
-        num_groups_total)
+  def moe_top2_gating(self, x, w, capacity, policy, threshold, noise, num_groups_total,
+                      want_table=False, want_raw=False):
+    """Fused `_top_2_gating` on one slice: x [..., S, M], w [M, E].
 
-  def moe_dispatch(self, x, i1, i2, p1, p2, g1, g2, num_experts, capacity):
+    Returns (index_1, index_2, position_1, position_2, gate_1, gate_2, loss)
+    plus, with `want_table`, the [groups, E, capacity] slot table that
+    moe_dispatch reads and, with `want_raw`, the softmax outputs.  bf16
+    activations take the single-pass tcgen05 kernel (x is read once); other
+    cases form the logits with a GEMM first."""
+    m, e = w.shape
+    lead, s = tuple(x.shape[:-2]), x.shape[-2]
+    if (x.dtype.name == "bfloat16" and x.size > 0
+        and self._lib.mtfc_moe_gate_fused_supported(m, e) == 1):
+      return self._moe_gate_fused(x, w, capacity, policy, threshold, noise, num_groups_total,
+                                  want_table, want_raw)
+    logits, parts = self.moe_gate_logits(x, w)
+    res = self.moe_top2_gating_from_logits(
+        logits, parts, lead, s, e, capacity, policy, threshold, noise, num_groups_total,
+        want_raw=want_raw)
+    if want_table:
+      table = self.moe_slot_table(*res[:6], e, capacity, x.dtype.name == "bfloat16")
+      res = res[:7] + (table,) + res[7:]
+    return res
+
+  def _moe_gate_fused(self, x, w, capacity, policy, threshold, noise, num_groups_total,
+                      want_table, want_raw):
+    m, e = w.shape
+    lead, s = tuple(x.shape[:-2]), x.shape[-2]
+    groups = _volume(lead)
+    x = self.contiguous(x)
+    w = self.contiguous(w)
+    ep = int(self._lib.mtfc_moe_gate_padded_experts(e))
+    w3t = self._empty([3 * ep, m], G.bfloat16)
+    self._call(self._lib.mtfc_moe_gate_prepare, ctypes.c_void_p(w.ptr), m, e,
+               ctypes.c_void_p(w3t.ptr), self._stream())
+    tok_shape = lead + (s,)
+    i1, i2, p1, p2 = [self._empty(tok_shape, G.int32) for _ in range(4)]
+    g1, g2 = self._empty(tok_shape, G.float32), self._empty(tok_shape, G.float32)
+    raw = self._empty(tok_shape + (e,), G.float32) if want_raw else None
+    table = self._empty(lead + (e, capacity), G.int32) if want_table else None
+    loss_per_group = self._empty([groups], G.float32)
+    nbytes = int(self._lib.mtfc_moe_gate_scratch_bytes(groups, s, e))
+    scratch = self._empty([max(1, nbytes // 4)], G.float32)
+    noise_ptr = ctypes.c_void_p(self.contiguous(noise).ptr) if noise is not None else ctypes.c_void_p(0)
+    self._call(self._lib.mtfc_moe_gate_top2, ctypes.c_void_p(x.ptr), ctypes.c_void_p(w3t.ptr),
+               groups, s, m, e, capacity, _POLICY[policy], ctypes.c_float(threshold), noise_ptr,
+               ctypes.c_void_p(i1.ptr), ctypes.c_void_p(i2.ptr), ctypes.c_void_p(p1.ptr),
+               ctypes.c_void_p(p2.ptr), ctypes.c_void_p(g1.ptr), ctypes.c_void_p(g2.ptr),
+               ctypes.c_void_p(raw.ptr if raw is not None else 0),
+               ctypes.c_void_p(loss_per_group.ptr),
+               ctypes.c_void_p(table.ptr if table is not None else 0), 1,
+               ctypes.c_void_p(scratch.ptr), nbytes, self._stream())
+    loss = self.binary("multiply", self.reduce("SUM", loss_per_group, [0]),
+                       1.0 / float(num_groups_total))
+    res = (i1, i2, p1, p2, g1, g2, loss)
+    if want_table:
+      res += (table,)
+    if want_raw:
+      res += (raw,)
+    return res
+
+  def moe_slot_table(self, i1, i2, p1, p2, g1, g2, num_experts, capacity, round_bf16):
+    """[groups..., E, capacity] int32: token held by each expert slot, -1 if none."""
+    lead, s = tuple(i1.shape[:-1]), i1.shape[-1]
+    args = [self.contiguous(t) for t in (i1, i2, p1, p2, g1, g2)]
+    table = self._empty(lead + (num_experts, capacity), G.int32)
+    self._call(self._lib.mtfc_moe_slot_table, *[ctypes.c_void_p(t.ptr) for t in args],
+               _volume(lead), s, num_experts, capacity, 1 if round_bf16 else 0,
+               ctypes.c_void_p(table.ptr), self._stream())
+    return table
+
+  def moe_dispatch(self, x, i1, i2, p1, p2, g1, g2, num_experts, capacity, table=None):
     o, g, s, m = x.shape
     x = self.contiguous(x)
-    args = [self.contiguous(t) for t in (i1, i2, p1, p2, g1, g2)]
-    table = self._empty([o * g, num_experts, capacity], G.int32)
-    self._call(self._lib.mtfc_moe_slot_table, *[ctypes.c_void_p(t.ptr) for t in args], o * g, s,
-               num_experts, capacity, 1 if x.dtype.name == "bfloat16" else 0,
-               ctypes.c_void_p(table.ptr), self._stream())
+    if table is None:
+      table = self.moe_slot_table(i1, i2, p1, p2, g1, g2, num_experts, capacity,
+                                  x.dtype.name == "bfloat16")
+    table = self.contiguous(table)
     out = self._empty([o, num_experts, g, capacity, m], x.dtype)
     self._call(self._lib.mtfc_moe_dispatch, ctypes.c_void_p(x.ptr), ctypes.c_void_p(table.ptr),
                ctypes.c_void_p(out.ptr), o, g, s, num_experts, capacity, m * x.dtype.itemsize,

@@ -10,7 +10,7 @@ from mesh_b200.mtf.layout import (LayoutRules, TensorLayout, convert_to_layout_r
                                   pnum_to_group, pnum_to_processor_coordinates,
                                   processor_coordinates_to_pnum, processor_groups,
                                   tensor_dim_to_mesh_dim_size)
-from mesh_b200.mtf.mesh_impl import (LazyAllreduceSum, MeshImpl, compatible_lazy_allreduce_sums,
+from mesh_b200.mtf.mesh_impl import (LazyAllreduceSum, LazyLaidOutTensor, MeshImpl, compatible_lazy_allreduce_sums,
                                      convert_args_to_laid_out_tensors, expand_dims_to)
 from mesh_b200.mtf.ops import *  # noqa: F401,F403
 from mesh_b200.mtf.ops import mtf_range as range  # noqa: A001

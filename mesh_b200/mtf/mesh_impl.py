@@ -41,20 +41,50 @@ class LazyAllreduceSum(object):
 
   def to_laid_out_tensor(self):
     if self._reduced is None:
-      self._reduced = self.mesh_impl.allreduce(self.laid_out_input, self.mesh_axes, "SUM")
+      # the unreduced input is reachable only through this object: a backend
+      # that can reduce in place is told so
+      if getattr(self.mesh_impl, "allreduce_accepts_donation", False):
+        self._reduced = self.mesh_impl.allreduce(self.laid_out_input, self.mesh_axes, "SUM",
+                                                 donate=True)
+      else:
+        self._reduced = self.mesh_impl.allreduce(self.laid_out_input, self.mesh_axes, "SUM")
+      self.laid_out_input = None
       if self.add_counter_fn:
         self.add_counter_fn()
     return self._reduced
 
   @property
   def slice_shape(self):
+    if self._reduced is not None:
+      return self._reduced.slice_shape
     return self.laid_out_input.slice_shape
+
+
+class LazyLaidOutTensor(object):
+  """A LaidOutTensor made by a function when it is first needed
+  (mesh_tensorflow/ops.py:3941-3958): `to_laid_out_tensor_fn()` runs on every
+  to_laid_out_tensor() call.  Importing one (import_laid_out_tensor) makes the
+  function run once per lowering, which is how a step's input is uploaded
+  from host memory at the time the step is lowered."""
+
+  def __init__(self, to_laid_out_tensor_fn, slice_shape):
+    self._to_laid_out_tensor_fn = to_laid_out_tensor_fn
+    self._slice_shape = list(slice_shape)
+
+  def to_laid_out_tensor(self):
+    return self._to_laid_out_tensor_fn()
+
+  @property
+  def slice_shape(self):
+    return self._slice_shape
 
 
 def compatible_lazy_allreduce_sums(xs):
   if not xs or not all(isinstance(x, LazyAllreduceSum) for x in xs):
     return False
   first = xs[0]
+  if any(x.laid_out_input is None for x in xs):
+    return False   # already reduced (and its input given up): use the reduced value
   return all(y.mesh_impl is first.mesh_impl and y.mesh_axes == first.mesh_axes
              for y in xs[1:])
 

@@ -167,10 +167,13 @@ class Top2GatingOperation(Operation):
     self._capacity = capacity
     self._policy = policy
     self._threshold = threshold
+    # output 7: the (expert, slot) -> token table of every group, which the
+    # gating kernel has at hand and the dispatch would otherwise rebuild
+    table_shape = Shape(inputs.shape.dims[:-2] + [experts_dim, Dimension("expert_capacity", capacity)])
     self._outputs = (
         [Tensor(self, token_shape, G.int32, index=i) for i in range(4)] +
         [Tensor(self, token_shape, G.float32, index=4), Tensor(self, token_shape, G.float32, index=5),
-         Tensor(self, Shape([]), G.float32, index=6)])
+         Tensor(self, Shape([]), G.float32, index=6), Tensor(self, table_shape, G.int32, index=7)])
 
   def lower(self, lowering):
     impl = lowering.mesh_impl(self)
@@ -184,10 +187,11 @@ class Top2GatingOperation(Operation):
 
     def fn(xs, ws, *noise):
       return ops.moe_top2_gating(xs, ws, capacity, policy, threshold,
-                                 noise[0] if noise else None, num_groups_total)
+                                 noise[0] if noise else None, num_groups_total, want_table=True)
     results = impl.slicewise(fn, *[lowering.tensors[t] for t in self.inputs])
     for out, value in zip(self.outputs[:6], results[:6]):
       lowering.set_tensor_lowering(out, value)
+    lowering.set_tensor_lowering(self.outputs[7], results[7])
     layout = impl.tensor_layout(Shape(x.shape.dims[:-2]))
     mesh_axes = [a for a in layout.tensor_axis_to_mesh_axis if a is not None]
     loss = results[6]
@@ -200,8 +204,9 @@ class MoeDispatchOperation(Operation):
   """expert_inputs[O,E,G,C,M]: row gather replacing the dispatch einsum
   `inputs[O,G,S,M] x dispatch[O,G,S,E,C]` (moe.py:443-447)."""
 
-  def __init__(self, inputs, routing, experts_dim, capacity_dim, name=None):
-    super().__init__([inputs] + list(routing), name=name or "moe_dispatch")
+  def __init__(self, inputs, routing, experts_dim, capacity_dim, slot_table=None, name=None):
+    extra = [slot_table] if slot_table is not None else []
+    super().__init__([inputs] + list(routing) + extra, name=name or "moe_dispatch")
     o, g, _, m = inputs.shape.dims
     self._num_experts = experts_dim.size
     self._capacity = capacity_dim.size
@@ -211,7 +216,8 @@ class MoeDispatchOperation(Operation):
     impl = lowering.mesh_impl(self)
     ops = impl.slice_ops
     e, c = self._num_experts, self._capacity
-    fn = lambda xs, i1, i2, p1, p2, g1, g2: ops.moe_dispatch(xs, i1, i2, p1, p2, g1, g2, e, c)
+    fn = lambda xs, i1, i2, p1, p2, g1, g2, *table: ops.moe_dispatch(
+        xs, i1, i2, p1, p2, g1, g2, e, c, *table)
     lowering.set_tensor_lowering(
         self.outputs[0], impl.slicewise(fn, *[lowering.tensors[t] for t in self.inputs]))
 
@@ -278,12 +284,12 @@ def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, lay
     policy, threshold = _second_policy(hparams, train)
     gating = Top2GatingOperation(inputs, gate_weights, experts_dim_unsplit, capacity, policy,
                                  threshold, second_noise=second_noise)
-    i1, i2, p1, p2, g1, g2, loss_sum = gating.outputs
+    i1, i2, p1, p2, g1, g2, loss_sum, slot_table = gating.outputs
     routing = [i1, i2, p1, p2, g1, g2]
     loss = mtf.cast(loss_sum, inputs.dtype)
     aux = dict(index_1=i1, index_2=i2, position_1=p1, position_2=p2, gate_1=g1, gate_2=g2)
-    expert_inputs = MoeDispatchOperation(inputs, routing, experts_dim_unsplit,
-                                         capacity_dim).outputs[0]
+    expert_inputs = MoeDispatchOperation(inputs, routing, experts_dim_unsplit, capacity_dim,
+                                         slot_table=slot_table).outputs[0]
   else:
     dispatch_tensor, combine_tensor, loss, aux = _top_2_gating(
         inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights,

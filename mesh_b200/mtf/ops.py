@@ -15,7 +15,7 @@ import numpy as np
 
 from mesh_b200.mtf import graph as G
 from mesh_b200.mtf.graph import Operation, Tensor
-from mesh_b200.mtf.mesh_impl import LazyAllreduceSum, expand_dims_to
+from mesh_b200.mtf.mesh_impl import LazyAllreduceSum, LazyLaidOutTensor, expand_dims_to
 from mesh_b200.mtf.shapes import (Dimension, Shape, convert_to_dimension,
                                   convert_to_shape, shape_union)
 
@@ -84,7 +84,10 @@ class ImportLaidOutTensorOperation(Operation):
     self._outputs = [Tensor(self, shape, dtype)]
 
   def lower(self, lowering):
-    lowering.set_tensor_lowering(self.outputs[0], self._laid_out_tensor)
+    value = self._laid_out_tensor
+    if isinstance(value, LazyLaidOutTensor):
+      value = value.to_laid_out_tensor()   # once per lowering, not once per consumer
+    lowering.set_tensor_lowering(self.outputs[0], value)
 
 
 def import_laid_out_tensor(mesh, laid_out_tensor, shape, dtype, name=None):

@@ -65,3 +65,31 @@ def time_ffn(batch, length, d_model, d_ff, mesh_shape, layout, steps, warmup, se
     if i >= warmup:
       times.append(dt)
   return float(np.median(times)), times
+
+
+def time_moe(x, wg, wi, wo, group_size, steps, warmup):
+  """Seconds per lowering (median of `steps`) of the reference's own op chain
+  for the top-2 MoE layer on the CPU backend: softmax, two top_1, triangular
+  cumsum, dense [G,S,E,C] dispatch / combine tensors and their dense einsums
+  (what transformer_moe_layer_v1, transformer/moe.py:191-525, costs the
+  reference).  x [groups, length, d_model]; wi [E, d_model, d_ff]; wo [E, d_ff, d_model]."""
+  b, l, m = x.shape
+  e, _, h = wi.shape
+  g = mtf.Graph()
+  mesh = mtf.Mesh(g, "mesh")
+  X = mtf.import_tf_tensor(mesh, x, "batch:%d,length:%d,d_model:%d" % (b, l, m), dtype=mtf.bfloat16)
+  WG = mtf.import_tf_tensor(mesh, wg, "d_model:%d,expert_unsplit:%d" % (m, e), dtype=mtf.float32)
+  WI = mtf.import_tf_tensor(mesh, wi, "experts:%d,d_model:%d,d_ff:%d" % (e, m, h), dtype=mtf.bfloat16)
+  WO = mtf.import_tf_tensor(mesh, wo, "experts:%d,d_ff:%d,d_model:%d" % (e, h, m), dtype=mtf.bfloat16)
+  hp = mtf.moe.HParams(moe_group_size=group_size, moe_second_policy_train="all",
+                       moe_use_fused_kernels=False)
+  out, _ = mtf.moe.transformer_moe_layer_v1(X, mtf.Dimension("d_model", m), hp, True, "", "", WG, WI, WO)
+  impl = NumpyMeshImpl("", "", fast=True)
+  times = []
+  for i in range(warmup + steps):
+    t0 = time.perf_counter()
+    mtf.Lowering(g, {mesh: impl}).tensors[out].to_laid_out_tensor()
+    dt = time.perf_counter() - t0
+    if i >= warmup:
+      times.append(dt)
+  return float(np.median(times)), times

@@ -96,6 +96,20 @@ def combine_weights(gate, bf16=True):
   return round_to_bf16(gate) if bf16 else np.asarray(gate, dtype=np.float32)
 
 
+def slot_table(i1, i2, p1, p2, g1, g2, num_experts, capacity, bf16=True):
+  """[G, E, C] int32: the token that occupies each expert slot, -1 for none."""
+  g_, s_ = i1.shape
+  table = np.full((g_, num_experts, capacity), -1, dtype=np.int32)
+  w1, w2 = combine_weights(g1, bf16), combine_weights(g2, bf16)
+  for g in range(g_):
+    for s in range(s_):
+      if w1[g, s] != 0 and p1[g, s] < capacity:
+        table[g, i1[g, s], p1[g, s]] = s
+      if w2[g, s] != 0 and p2[g, s] < capacity:
+        table[g, i2[g, s], p2[g, s]] = s
+  return table
+
+
 def dispatch(x, i1, i2, p1, p2, g1, g2, num_experts, capacity, bf16=True):
   """x [G,S,M] -> expert inputs [G,E,C,M]; a slot holds at most one token."""
   g_, s_, m_ = x.shape

@@ -24,7 +24,21 @@ from mesh_b200 import mtf
 
 
 def round_to_bf16(x):
-  """float32 -> nearest-even bfloat16, returned as float32."""
+  """float32 -> nearest-even bfloat16, returned as float32.
+
+  Arrays of a million elements or more go through torch's float32 -> bfloat16
+  conversion, which is the same round-to-nearest-even (tests/test_oracle.py
+  holds the two against each other bit for bit); the numpy form below is the
+  definition."""
+  if np.size(x) >= (1 << 20):
+    import torch
+    t = torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32))
+    return t.to(torch.bfloat16).to(torch.float32).numpy()
+  return round_to_bf16_numpy(x)
+
+
+def round_to_bf16_numpy(x):
+  """The definition: add 0x7FFF plus the lowest kept bit, truncate 16 bits."""
   shape = np.shape(x)
   x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
   u = x.view(np.uint32)
@@ -271,7 +285,8 @@ class NumpyOps(object):
     return _finish(out.astype(np.float32), v.dtype)
 
   # ---- fused MoE entry points: the scalar specification
-  def moe_top2_gating(self, x, w, capacity, policy, threshold, noise, num_groups_total):
+  def moe_top2_gating(self, x, w, capacity, policy, threshold, noise, num_groups_total,
+                      want_table=False, want_raw=False):
     from oracle import moe_spec
     lead = x.a.shape[:-2]
     s, m = x.a.shape[-2:]
@@ -284,9 +299,19 @@ class NumpyOps(object):
     outs += [Arr(r[k].reshape(tok), mtf.float32) for k in ("gate_1", "gate_2")]
     loss = np.float32(np.sum(r["loss_per_group"].astype(np.float64)) / num_groups_total)
     outs.append(Arr(np.asarray(loss, dtype=np.float32), mtf.float32))
+    if want_table:
+      e = w.a.shape[-1]
+      table = moe_spec.slot_table(*[r[k] for k in ("index_1", "index_2", "position_1", "position_2",
+                                                    "gate_1", "gate_2")], e, capacity,
+                                  bf16=(x.dtype == mtf.bfloat16))
+      outs.append(Arr(table.reshape(lead + (e, capacity)), mtf.int32))
+    if want_raw:
+      outs.append(Arr(r["raw_gates"].reshape(tok + (w.a.shape[-1],)), mtf.float32))
     return tuple(outs)
 
-  def moe_dispatch(self, x, i1, i2, p1, p2, g1, g2, num_experts, capacity):
+  def moe_dispatch(self, x, i1, i2, p1, p2, g1, g2, num_experts, capacity, table=None):
+    """`table`, when given, must be what the routing implies; the rows are
+    placed from the routing itself."""
     from oracle import moe_spec
     o, g, s, m = x.a.shape
     out = moe_spec.dispatch(x.a.reshape(o * g, s, m), i1.a.reshape(-1, s), i2.a.reshape(-1, s),

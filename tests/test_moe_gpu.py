@@ -85,6 +85,70 @@ def test_gate_logits_on_tensor_cores(dev_ops):
   assert rel_err(got, ref) < 1e-5
 
 
+@pytest.mark.parametrize("policy", ["all", "threshold", "random"])
+@pytest.mark.parametrize("groups,s,m,e,cap", [(3, 1024, 1024, 32, 40), (2, 300, 256, 8, 20),
+                                              (5, 64, 64, 4, 4), (1, 1024, 512, 64, 1024),
+                                              (2, 257, 72, 16, 3), (150, 128, 128, 32, 8)])
+def test_single_pass_gating_kernel(dev_ops, groups, s, m, e, cap, policy):
+  """mtfc_moe_gate_top2 (activations read once, logits in TMEM) against the
+  per-group specification fed float64 logits: indices, positions, keep masks and
+  the slot table exact on groups whose raw-gate margins exceed 1e-5."""
+  from oracle import moe_spec
+  from oracle.numpy_ops import round_to_bf16
+  r = rng(17)
+  x = round_to_bf16(r.standard_normal((groups, s, m)).astype(np.float32))
+  w = (r.standard_normal((m, e)) * 2 / np.sqrt(m)).astype(np.float32)
+  noise = r.random((groups, s)).astype(np.float32)
+  spec = moe_spec.top2_gating(x, w, cap, policy, 0.2, noise)
+  out = dev_ops.moe_top2_gating(dev_ops.from_host(x, mtf.bfloat16), dev_ops.from_host(w, mtf.float32),
+                                cap, policy, 0.2, dev_ops.from_host(noise, mtf.float32), groups,
+                                want_table=True, want_raw=True)
+  from mesh_b200 import _native as nat
+  nat.device_status()
+  names = ["index_1", "index_2", "position_1", "position_2", "gate_1", "gate_2"]
+  got = {k: dev_ops.to_host(v) for k, v in zip(names, out[:6])}
+  loss, table, raw = float(dev_ops.to_host(out[6])), dev_ops.to_host(out[7]), dev_ops.to_host(out[8])
+  assert rel_err(raw, spec["raw_gates"]) < 1e-5
+  safe = np.all(_safe_tokens(spec["raw_gates"], margin=1e-5), axis=-1)
+  if policy != "all":
+    # a gate within 1e-5 of the policy's cut may fall on either side of it
+    cut = 0.2 if policy == "threshold" else noise * 0.2
+    safe &= np.all(np.abs(_renormalised_second_gate(spec) - cut) > 1e-5, axis=-1)
+  assert safe.sum() >= 1, "margin filter removed every group"
+  for k in names[:4]:
+    np.testing.assert_array_equal(got[k][safe], spec[k][safe], err_msg=k)
+  for k in names[4:]:
+    np.testing.assert_array_equal(got[k][safe] != 0, spec[k][safe] != 0, err_msg=k + " keep mask")
+    assert np.max(np.abs(got[k][safe] - spec[k][safe])) < 1e-5
+  ref_table = moe_spec.slot_table(*[spec[k] for k in names], e, cap, bf16=True)
+  np.testing.assert_array_equal(table[safe], ref_table[safe])
+  ref_loss = float(np.mean(spec["loss_per_group"]))
+  assert abs(loss - ref_loss) <= 1e-5 * max(1.0, abs(ref_loss))
+
+
+def _renormalised_second_gate(spec):
+  """gate_2 before the capacity mask: raw second gate / (g1 + g2 + 1e-9)."""
+  raw = spec["raw_gates"]
+  top = np.sort(raw, axis=-1)[..., ::-1]
+  return top[..., 1] / (top[..., 0] + top[..., 1] + np.float32(1e-9))
+
+
+def test_single_pass_gating_matches_three_call_form(dev_ops):
+  """Same routing as split weights + logit GEMM + gating kernel."""
+  from oracle.numpy_ops import round_to_bf16
+  r = rng(18)
+  groups, s, m, e, cap = 4, 512, 256, 32, 24
+  x = dev_ops.from_host(round_to_bf16(r.standard_normal((groups, s, m)).astype(np.float32)), mtf.bfloat16)
+  w = dev_ops.from_host((r.standard_normal((m, e)) / np.sqrt(m)).astype(np.float32), mtf.float32)
+  a = dev_ops.moe_top2_gating(x, w, cap, "all", 0.2, None, groups)
+  logits, parts = dev_ops.moe_gate_logits(x, w)
+  b = dev_ops.moe_top2_gating_from_logits(logits, parts, (groups,), s, e, cap, "all", 0.2, None, groups)
+  for u, v in zip(a[:4], b[:4]):
+    np.testing.assert_array_equal(dev_ops.to_host(u), dev_ops.to_host(v))
+  for u, v in zip(a[4:7], b[4:7]):
+    assert np.max(np.abs(dev_ops.to_host(u) - dev_ops.to_host(v))) < 1e-6
+
+
 @pytest.mark.parametrize("dtype", [mtf.bfloat16, mtf.float32])
 def test_dispatch_and_combine(dev_ops, dtype):
   from oracle import moe_spec

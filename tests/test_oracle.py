@@ -297,3 +297,19 @@ def test_fused_attention_operation_matches_op_chain():
   assert "output/FusedAttentionOperation" not in low32.counter_totals()
   with pytest.raises(ValueError):
     _attention_layer("all:2", "memory_length:all", fused=True)
+
+
+def test_bf16_rounding_fast_path_equals_definition():
+  """round_to_bf16 uses torch for large arrays: the same bits as the numpy definition,
+  including ties, subnormals, infinities and values that round up to infinity."""
+  import torch
+  from oracle.numpy_ops import round_to_bf16_numpy
+  r = np.random.Generator(np.random.PCG64(3))
+  bits = r.integers(0, 2 ** 32, size=1 << 20, dtype=np.uint64).astype(np.uint32)
+  special = np.array([0x3F808000, 0x3F818000, 0x3F80FFFF, 0x7F7FFFFF, 0x7F800000, 0xFF800000,
+                      0x00000001, 0x00008000, 0x80008000, 0x0000FFFF], dtype=np.uint32)
+  x = np.concatenate([bits, special]).view(np.float32)
+  x = x[~np.isnan(x)]
+  a = round_to_bf16_numpy(x)
+  b = torch.from_numpy(x.copy()).to(torch.bfloat16).to(torch.float32).numpy()
+  np.testing.assert_array_equal(a.view(np.uint32), b.view(np.uint32))
