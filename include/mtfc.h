@@ -131,6 +131,20 @@ int mtfc_gemm_allreduce(const mtfc_gemm_desc* desc, const void* a, const void* b
                         void* const* flag_ptrs, void* ctl, int rank, int nranks,
                         void* stream);
 
+/* The same with the exchange done by the NVSwitch: `stage_multicast` and
+ * `out_multicast` are the multicast (NVLS) addresses of the staging and output
+ * buffers of the group - the same allocations as stage_ptrs / out_ptrs, bound to
+ * one multicast object each.  Every rank then keeps its partial product in its own
+ * staging buffer; the owner of a row block reads the fp32-accumulated sum of all
+ * ranks' copies with multimem.ld_reduce and writes it to all ranks' outputs with
+ * multimem.st, so each byte of the output crosses a GPU's links once in and once
+ * out, whatever the group size (1.5 to 1.75 times in each direction without).
+ * Either address null: identical to mtfc_gemm_allreduce. */
+int mtfc_gemm_allreduce_multimem(const mtfc_gemm_desc* desc, const void* a, const void* b,
+                                 void* const* stage_ptrs, void* const* out_ptrs,
+                                 void* const* flag_ptrs, void* ctl, int rank, int nranks,
+                                 const void* stage_multicast, void* out_multicast, void* stream);
+
 /* K1f on the tensor cores: fp32 [batch, rows, k] (element strides s_*) -> bf16
  * [batch, rows, 6k], every value split into three bf16 terms laid along K
  * (pattern 0 for the left operand, 1 for the right) so that one mtfc_gemm over
@@ -309,8 +323,10 @@ int mtfc_moe_top2_gating(const float* logits, int32_t parts, int64_t groups, int
  *   mtfc_moe_gate_scratch_bytes: size of the caller-owned `scratch` (per-tile
  *     column sums of the raw gates, from which the loss is formed).
  *   mtfc_moe_gate_top2: x [groups*group_size, m] bf16; outputs as
- *     mtfc_moe_top2_gating; `slot_table` (optional) receives what
- *     mtfc_moe_slot_table would compute from the outputs. */
+ *     mtfc_moe_top2_gating; `loss_mean` (optional) receives the sum of
+ *     loss_per_group divided by num_groups_total (the groups of all slices, so
+ *     that per-slice values add up to the mean over all groups); `slot_table`
+ *     (optional) receives what mtfc_moe_slot_table would compute from the outputs. */
 int mtfc_moe_gate_fused_supported(int64_t m, int32_t experts);
 int32_t mtfc_moe_gate_padded_experts(int32_t experts);
 int64_t mtfc_moe_gate_scratch_bytes(int64_t groups, int32_t group_size, int32_t experts);
@@ -319,8 +335,9 @@ int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups,
                        int64_t m, int32_t experts, int32_t capacity, int32_t policy,
                        float threshold, const float* noise, int32_t* idx1, int32_t* idx2,
                        int32_t* pos1, int32_t* pos2, float* gate1, float* gate2, float* raw_gates,
-                       float* loss_per_group, int32_t* slot_table, int32_t round_gates_to_bf16,
-                       void* scratch, int64_t scratch_bytes, void* stream);
+                       float* loss_per_group, float* loss_mean, int64_t num_groups_total,
+                       int32_t* slot_table, int32_t round_gates_to_bf16, void* scratch,
+                       int64_t scratch_bytes, void* stream);
 
 /* table[g, e, c] = token routed to slot c of expert e in group g, or -1.
  * With round_gates_to_bf16 a token whose gate rounds to 0 in bfloat16 is not
@@ -373,6 +390,25 @@ int mtfc_moe_combine(const void* y, int dtype, const int32_t* idx1, const int32_
                      const float* gate2, void* out, int64_t outer, int64_t groups_per_outer,
                      int32_t group_size, int32_t experts, int32_t capacity, int64_t row_elems,
                      void* stream);
+
+/* Backward pass of mtfc_moe_combine (the transposes of the combine einsum,
+ * moe.py:509-510, that mtf's einsum gradient would form densely, ops.py:2846-2854).
+ *   mtfc_moe_dispatch_weighted: d(expert outputs)[o, e, g, c, :] = w * x[o, g, s, :]
+ *     for the token s in slot (e, c) of `table`, w its gate for that choice rounded
+ *     to `dtype`; zero rows for empty slots.  x plays dout's role.
+ *   mtfc_moe_combine_gate_grad: dgate_k[o, g, s] = <dout[o, g, s, :], y[o, i_k, g, p_k, :]>
+ *     for kept choices, else 0; fp32 sums. */
+int mtfc_moe_dispatch_weighted(const void* x, int dtype, const int32_t* table, const int32_t* idx1,
+                               const int32_t* pos1, const float* gate1, const float* gate2,
+                               void* out, int64_t outer, int64_t groups_per_outer,
+                               int32_t group_size, int32_t experts, int32_t capacity,
+                               int64_t row_elems, void* stream);
+int mtfc_moe_combine_gate_grad(const void* y, const void* dout, int dtype, const int32_t* idx1,
+                               const int32_t* idx2, const int32_t* pos1, const int32_t* pos2,
+                               const float* gate1, const float* gate2, float* dgate1,
+                               float* dgate2, int64_t outer, int64_t groups_per_outer,
+                               int32_t group_size, int32_t experts, int32_t capacity,
+                               int64_t row_elems, void* stream);
 
 #ifdef __cplusplus
 }

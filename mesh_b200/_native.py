@@ -75,6 +75,8 @@ def _declare(lib):
       "mtfc_gemm_allreduce_stage_bytes": [i64, i64, i32],
       "mtfc_gemm_allreduce": [ctypes.POINTER(GemmDesc), vp, vp, ctypes.POINTER(vp), ctypes.POINTER(vp),
                               ctypes.POINTER(vp), vp, i32, i32, vp],
+      "mtfc_gemm_allreduce_multimem": [ctypes.POINTER(GemmDesc), vp, vp, ctypes.POINTER(vp),
+                                       ctypes.POINTER(vp), ctypes.POINTER(vp), vp, i32, i32, vp, vp, vp],
       "mtfc_split_bf16x3": [vp, i64, i64, i64, vp, i64, i64, i64, i32, vp],
       "mtfc_attention_set_variant": [i32],
       "mtfc_attention_supported": [i64, p_i64, p_i64, p_i64, p_i64],
@@ -97,11 +99,14 @@ def _declare(lib):
       "mtfc_moe_gate_scratch_bytes": [i64, i32, i32],
       "mtfc_moe_gate_prepare": [vp, i64, i32, vp, vp],
       "mtfc_moe_gate_top2": [vp, vp, i64, i32, i64, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp,
-                             vp, vp, vp, i32, vp, i64, vp],
+                             vp, vp, vp, i64, vp, i32, vp, i64, vp],
       "mtfc_moe_slot_table": [vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, vp, vp],
       "mtfc_moe_dispatch": [vp, vp, vp, i64, i64, i32, i32, i32, i64, vp],
       "mtfc_moe_dispatch_noalloc": [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64,
                                     i32, vp],
+      "mtfc_moe_dispatch_weighted": [vp, i32, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64, vp],
+      "mtfc_moe_combine_gate_grad": [vp, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32,
+                                     i32, i64, vp],
       "mtfc_moe_combine": [vp, i32, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64, vp],
   }
   for name, argtypes in signatures.items():

@@ -63,7 +63,8 @@ void gemm_allreduce_set_wait_ms(int ms);
 long long gemm_allreduce_stage_bytes(long long m, long long n, int nranks);
 int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
                           void* const* stage, void* const* out, void* const* flags, void* ctl,
-                          int rank, int nranks, cudaStream_t stream);
+                          int rank, int nranks, const void* mc_stage, void* mc_out,
+                          cudaStream_t stream);
 
 }  // namespace mtfc
 
@@ -137,16 +138,24 @@ int64_t mtfc_gemm_allreduce_stage_bytes(int64_t m, int64_t n, int nranks) {
   return gemm_allreduce_stage_bytes(m, n, nranks);
 }
 
-int mtfc_gemm_allreduce(const mtfc_gemm_desc* d, const void* a, const void* b,
-                        void* const* stage_ptrs, void* const* out_ptrs, void* const* flag_ptrs,
-                        void* ctl, int rank, int nranks, void* stream) {
+int mtfc_gemm_allreduce_multimem(const mtfc_gemm_desc* d, const void* a, const void* b,
+                                 void* const* stage_ptrs, void* const* out_ptrs,
+                                 void* const* flag_ptrs, void* ctl, int rank, int nranks,
+                                 const void* stage_multicast, void* out_multicast, void* stream) {
   if (!d || !a || !b) return fail(MTFC_ERR_SHAPE, "gemm_allreduce: null argument");
   if (d->batch < 1 || d->m < 1 || d->n < 1 || d->k < 1)
     return fail(MTFC_ERR_SHAPE, "gemm_allreduce: empty problem");
   int rc = gemm_allreduce_launch(d, a, b, stage_ptrs, out_ptrs, flag_ptrs, ctl, rank, nranks,
-                                 static_cast<cudaStream_t>(stream));
+                                 stage_multicast, out_multicast, static_cast<cudaStream_t>(stream));
   if (rc == MTFC_OK) count_launch(1);
   return rc;
+}
+
+int mtfc_gemm_allreduce(const mtfc_gemm_desc* d, const void* a, const void* b,
+                        void* const* stage_ptrs, void* const* out_ptrs, void* const* flag_ptrs,
+                        void* ctl, int rank, int nranks, void* stream) {
+  return mtfc_gemm_allreduce_multimem(d, a, b, stage_ptrs, out_ptrs, flag_ptrs, ctl, rank, nranks,
+                                      nullptr, nullptr, stream);
 }
 
 }  // extern "C"

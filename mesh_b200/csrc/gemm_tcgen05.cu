@@ -428,6 +428,15 @@ struct FusedArgs {
   int rank, nranks;
   int blocks_per_rank;
   long long wait_cycles;  // how long a wait for another rank may last
+  // Switch-reduced exchange (use_mc): every rank keeps its partial product in its own
+  // staging buffer at the output's own row offsets (part_map), and the owner of a row
+  // block reads the SUM of all ranks' copies through the staging buffers' multicast
+  // address (multimem.ld_reduce: NVSwitch adds the copies in fp32) and writes it to all
+  // ranks' outputs through the output buffers' multicast address (multimem.st).
+  int use_mc;
+  const uint8_t* mc_stage;
+  uint8_t* mc_out;
+  CUtensorMap part_map;
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -564,6 +573,44 @@ __device__ __forceinline__ void reduce_block(const uint8_t* src0, long long src_
   }
 }
 
+// Sum over all ranks of eight bf16 values at a multicast address, accumulated in fp32
+// inside the switch and rounded once.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+// 16 bytes to the same offset of every rank's buffer.
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+               "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
+// The switch-reduced form of reduce_block: nvec 16-byte vectors starting at byte
+// offset `off` of the (symmetric) staging and output buffers.
+__device__ __forceinline__ void reduce_block_multimem(const uint8_t* mc_src, uint8_t* mc_dst,
+                                                      long long off, long long nvec, int tid) {
+  constexpr int U = COMM_UNROLL;
+  for (long long v0 = tid; v0 < nvec; v0 += (long long)COMM_THREADS * U) {
+    uint4 x[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + (long long)u * COMM_THREADS;
+      if (v < nvec) x[u] = multimem_ld_reduce_bf16x8(mc_src + off + v * 16);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + (long long)u * COMM_THREADS;
+      if (v < nvec) multimem_st_v4(mc_dst + off + v * 16, x[u]);
+    }
+  }
+}
+
 __device__ __forceinline__ void comm_warps_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(COMM_THREADS) : "memory");
 }
@@ -609,6 +656,9 @@ __device__ void allreduce_comm_warps(uint8_t* smem, const GemmArgs& args, const 
     const uint8_t* src0 = fa.stage + (long long)k * block_bytes + sub_off;
     const long long src_stride = (long long)fa.blocks_per_rank * block_bytes;
     const long long out_off = (long long)rb * block_bytes + sub_off;
+    if (fa.use_mc) {
+      reduce_block_multimem(fa.mc_stage, fa.mc_out, out_off, nvec, tid);
+    } else
     switch (n) {
       case 2: reduce_block<2>(src0, src_stride, fa.out, out_off, nvec, n, tid); break;
       case 4: reduce_block<4>(src0, src_stride, fa.out, out_off, nvec, n, tid); break;
@@ -817,8 +867,12 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
       const CUtensorMap* dst_map = &map_c;
       int dst_row = m0 + q * 32;
       if (FUSED) {
-        dst_map = &fa->stage_map[rb % fa->nranks];
-        dst_row = (fa->rank * fa->blocks_per_rank + rb / fa->nranks) * (2 * BM) + (int)rank * BM + q * 32;
+        if (fa->use_mc) {
+          dst_map = &fa->part_map;   // own staging buffer, at the output's row offsets
+        } else {
+          dst_map = &fa->stage_map[rb % fa->nranks];
+          dst_row = (fa->rank * fa->blocks_per_rank + rb / fa->nranks) * (2 * BM) + (int)rank * BM + q * 32;
+        }
       }
       ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), acc_phase, abort_flag));
       if (!ok) break;
@@ -1184,7 +1238,8 @@ long long gemm_allreduce_stage_bytes(long long m, long long n, int nranks) {
 // address as seen from this process; `ctl` is this rank's private 16 bytes.
 int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
                           void* const* stage, void* const* out, void* const* flags, void* ctl,
-                          int rank, int nranks, cudaStream_t stream) {
+                          int rank, int nranks, const void* mc_stage, void* mc_out,
+                          cudaStream_t stream) {
   if (nranks < 2 || nranks > MAX_RANKS || rank < 0 || rank >= nranks)
     return fail(MTFC_ERR_SHAPE, "gemm_allreduce: %d ranks (2..%d supported), rank %d", nranks,
                 MAX_RANKS, rank);
@@ -1249,6 +1304,16 @@ int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
     if (rc != MTFC_OK) return rc;
     fa.out[p] = static_cast<uint8_t*>(out[p]);
     fa.flags[p] = static_cast<uint32_t*>(flags[p]);
+  }
+  fa.use_mc = (mc_stage && mc_out) ? 1 : 0;
+  if (fa.use_mc) {
+    if (!aligned16(mc_stage) || !aligned16(mc_out))
+      return fail(MTFC_ERR_SHAPE, "gemm_allreduce: multicast addresses must be 16-byte aligned");
+    fa.mc_stage = static_cast<const uint8_t*>(mc_stage);
+    fa.mc_out = static_cast<uint8_t*>(mc_out);
+    rc = encode_map(&fa.part_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, stage[rank], d->n,
+                    (long long)args.tiles_m * 2 * BM, 1, d->n, 0, 64, 32, "partial-product buffer");
+    if (rc != MTFC_OK) return rc;
   }
   fa.stage = static_cast<const uint8_t*>(stage[rank]);
   fa.ctl = static_cast<uint32_t*>(ctl);

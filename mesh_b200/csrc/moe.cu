@@ -423,6 +423,126 @@ combine_rows_f32_kernel(const float4* __restrict__ y, const int* __restrict__ id
   }
 }
 
+// Backward of combine with respect to the expert outputs: slot (e, g, c) of dy
+// receives w * dout[token of the slot], w being the gate (rounded to the data
+// type, as in the forward pass) of the choice that put the token there.  Same
+// traversal as dispatch_rows; empty slots get zero rows.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+dispatch_rows_weighted_kernel(const uint4* __restrict__ x, const int* __restrict__ table,
+                              const int* __restrict__ idx1, const int* __restrict__ pos1,
+                              const float* __restrict__ gate1, const float* __restrict__ gate2,
+                              uint4* __restrict__ out, long long groups, int S, int E, int C,
+                              int vec_per_row, long long og_stride_groups) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const long long rows = groups * E * C;
+  for (long long r = warp; r < rows; r += nwarps) {
+    const int c = (int)(r % C);
+    long long rest = r / C;
+    const long long gi = rest % og_stride_groups;
+    rest /= og_stride_groups;
+    const int e = (int)(rest % E);
+    const long long o = rest / E;
+    const long long g = o * og_stride_groups + gi;
+    const int s = table[(g * E + e) * C + c];
+    uint4* dst = out + r * vec_per_row;
+    if (s >= 0) {
+      const long long t = g * S + s;
+      const bool first = idx1[t] == e && pos1[t] == c && gate1[t] != 0.f;
+      float w = first ? gate1[t] : gate2[t];
+      if (BF16) w = __bfloat162float(__float2bfloat16_rn(w));
+      const uint4* src = x + t * vec_per_row;
+      for (int v = lane; v < vec_per_row; v += 32) {
+        if (BF16) {
+          float f[8];
+          unpack8(src[v], f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] *= w;
+          dst[v] = pack8(f);
+        } else {
+          float4 f = reinterpret_cast<const float4*>(src)[v];
+          f.x *= w; f.y *= w; f.z *= w; f.w *= w;
+          reinterpret_cast<float4*>(dst)[v] = f;
+        }
+      }
+    } else {
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (int v = lane; v < vec_per_row; v += 32) dst[v] = z;
+    }
+  }
+}
+
+// Backward of combine with respect to the gates: dgate_k[t] = <dout[t, :], y[slot_k(t), :]>
+// for the kept choices, 0 for the dropped ones.  One warp per token, fp32 sums.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+combine_gate_grad_kernel(const uint4* __restrict__ y, const uint4* __restrict__ dout,
+                         const int* __restrict__ idx1, const int* __restrict__ idx2,
+                         const int* __restrict__ pos1, const int* __restrict__ pos2,
+                         const float* __restrict__ gate1, const float* __restrict__ gate2,
+                         float* __restrict__ dgate1, float* __restrict__ dgate2, long long groups,
+                         int S, int E, int C, int vec_per_row, long long og_stride_groups) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const long long tokens = groups * S;
+  for (long long t = warp; t < tokens; t += nwarps) {
+    const long long g = t / S;
+    const long long o = g / og_stride_groups, gi = g % og_stride_groups;
+    float w1 = gate1[t], w2 = gate2[t];
+    if (BF16) {
+      w1 = __bfloat162float(__float2bfloat16_rn(w1));
+      w2 = __bfloat162float(__float2bfloat16_rn(w2));
+    }
+    const int p1 = pos1[t], p2 = pos2[t];
+    const int e1 = idx1[t], e2 = idx2[t];
+    const bool k1 = w1 != 0.f && p1 >= 0 && p1 < C && e1 >= 0 && e1 < E;
+    const bool k2 = w2 != 0.f && p2 >= 0 && p2 < C && e2 >= 0 && e2 < E;
+    const uint4* r1 = y + (((o * E + e1) * og_stride_groups + gi) * C + p1) * vec_per_row;
+    const uint4* r2 = y + (((o * E + e2) * og_stride_groups + gi) * C + p2) * vec_per_row;
+    const uint4* d = dout + t * vec_per_row;
+    float a1 = 0.f, a2 = 0.f;
+    for (int v = lane; v < vec_per_row; v += 32) {
+      if (BF16) {
+        float dv[8];
+        unpack8(d[v], dv);
+        if (k1) {
+          float f[8];
+          unpack8(r1[v], f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) a1 = fmaf(dv[i], f[i], a1);
+        }
+        if (k2) {
+          float f[8];
+          unpack8(r2[v], f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) a2 = fmaf(dv[i], f[i], a2);
+        }
+      } else {
+        const float4 dv = reinterpret_cast<const float4*>(d)[v];
+        if (k1) {
+          const float4 f = reinterpret_cast<const float4*>(r1)[v];
+          a1 += dv.x * f.x + dv.y * f.y + dv.z * f.z + dv.w * f.w;
+        }
+        if (k2) {
+          const float4 f = reinterpret_cast<const float4*>(r2)[v];
+          a2 += dv.x * f.x + dv.y * f.y + dv.z * f.z + dv.w * f.w;
+        }
+      }
+    }
+    for (int sft = 16; sft > 0; sft >>= 1) {
+      a1 += __shfl_xor_sync(0xffffffffu, a1, sft);
+      a2 += __shfl_xor_sync(0xffffffffu, a2, sft);
+    }
+    if (lane == 0) {
+      dgate1[t] = k1 ? a1 : 0.f;
+      dgate2[t] = k2 ? a2 : 0.f;
+    }
+  }
+}
+
 // Slot-table scratch of mtfc_moe_dispatch_noalloc.  Lives in the library image:
 // every GPU that loads libmtfc holds these 4 MiB until the process exits.
 constexpr long long kNoAllocSlotCapacity = 1LL << 20;  // (group, expert, slot) entries
@@ -590,6 +710,77 @@ int mtfc_moe_combine(const void* y, int dtype, const int32_t* idx1, const int32_
         static_cast<const float4*>(y), idx1, idx2, pos1, pos2, gate1, gate2,
         static_cast<float4*>(out), groups, group_size, experts, capacity, vec, groups_per_outer);
   MTFC_LAUNCH_CHECK("combine_rows_kernel");
+  count_launch(1);
+  return MTFC_OK;
+}
+
+int mtfc_moe_dispatch_weighted(const void* x, int dtype, const int32_t* table, const int32_t* idx1,
+                               const int32_t* pos1, const float* gate1, const float* gate2,
+                               void* out, int64_t outer, int64_t groups_per_outer,
+                               int32_t group_size, int32_t experts, int32_t capacity,
+                               int64_t row_elems, void* stream) {
+  if (!x || !table || !idx1 || !pos1 || !gate1 || !gate2 || !out)
+    return fail(MTFC_ERR_SHAPE, "dispatch_weighted: null argument");
+  if (dtype != MTFC_BF16 && dtype != MTFC_F32)
+    return fail(MTFC_ERR_UNSUPPORTED, "dispatch_weighted: dtype %d", dtype);
+  if (outer < 0 || groups_per_outer < 0 || group_size < 1 || experts < 1 || capacity < 1)
+    return fail(MTFC_ERR_SHAPE, "dispatch_weighted: bad extents");
+  const long long esz = dtype == MTFC_BF16 ? 2 : 4;
+  if (row_elems < 1 || (row_elems * esz) % 16 != 0)
+    return fail(MTFC_ERR_SHAPE, "dispatch_weighted: row of %lld elements is not a multiple of 16 bytes",
+                (long long)row_elems);
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) % 16 != 0)
+    return fail(MTFC_ERR_SHAPE, "dispatch_weighted: buffers must be 16-byte aligned");
+  const long long groups = outer * groups_per_outer;
+  const long long rows = groups * experts * capacity;
+  if (rows == 0) return MTFC_OK;
+  const int vec = (int)(row_elems * esz / 16);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == MTFC_BF16)
+    dispatch_rows_weighted_kernel<true><<<grid_for(rows * 32, 256), 256, 0, s>>>(
+        static_cast<const uint4*>(x), table, idx1, pos1, gate1, gate2, static_cast<uint4*>(out),
+        groups, group_size, experts, capacity, vec, groups_per_outer);
+  else
+    dispatch_rows_weighted_kernel<false><<<grid_for(rows * 32, 256), 256, 0, s>>>(
+        static_cast<const uint4*>(x), table, idx1, pos1, gate1, gate2, static_cast<uint4*>(out),
+        groups, group_size, experts, capacity, vec, groups_per_outer);
+  MTFC_LAUNCH_CHECK("dispatch_rows_weighted_kernel");
+  count_launch(1);
+  return MTFC_OK;
+}
+
+int mtfc_moe_combine_gate_grad(const void* y, const void* dout, int dtype, const int32_t* idx1,
+                               const int32_t* idx2, const int32_t* pos1, const int32_t* pos2,
+                               const float* gate1, const float* gate2, float* dgate1,
+                               float* dgate2, int64_t outer, int64_t groups_per_outer,
+                               int32_t group_size, int32_t experts, int32_t capacity,
+                               int64_t row_elems, void* stream) {
+  if (!y || !dout || !idx1 || !idx2 || !pos1 || !pos2 || !gate1 || !gate2 || !dgate1 || !dgate2)
+    return fail(MTFC_ERR_SHAPE, "combine_gate_grad: null argument");
+  if (dtype != MTFC_BF16 && dtype != MTFC_F32)
+    return fail(MTFC_ERR_UNSUPPORTED, "combine_gate_grad: dtype %d", dtype);
+  if (outer < 0 || groups_per_outer < 0 || group_size < 1 || experts < 1 || capacity < 1)
+    return fail(MTFC_ERR_SHAPE, "combine_gate_grad: bad extents");
+  const long long esz = dtype == MTFC_BF16 ? 2 : 4;
+  if (row_elems < 1 || (row_elems * esz) % 16 != 0)
+    return fail(MTFC_ERR_SHAPE, "combine_gate_grad: row of %lld elements is not a multiple of 16 bytes",
+                (long long)row_elems);
+  if ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(dout)) % 16 != 0)
+    return fail(MTFC_ERR_SHAPE, "combine_gate_grad: buffers must be 16-byte aligned");
+  const long long groups = outer * groups_per_outer;
+  const long long tokens = groups * group_size;
+  if (tokens == 0) return MTFC_OK;
+  const int vec = (int)(row_elems * esz / 16);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == MTFC_BF16)
+    combine_gate_grad_kernel<true><<<grid_for(tokens * 32, 256), 256, 0, s>>>(
+        static_cast<const uint4*>(y), static_cast<const uint4*>(dout), idx1, idx2, pos1, pos2, gate1,
+        gate2, dgate1, dgate2, groups, group_size, experts, capacity, vec, groups_per_outer);
+  else
+    combine_gate_grad_kernel<false><<<grid_for(tokens * 32, 256), 256, 0, s>>>(
+        static_cast<const uint4*>(y), static_cast<const uint4*>(dout), idx1, idx2, pos1, pos2, gate1,
+        gate2, dgate1, dgate2, groups, group_size, experts, capacity, vec, groups_per_outer);
+  MTFC_LAUNCH_CHECK("combine_gate_grad_kernel");
   count_launch(1);
   return MTFC_OK;
 }

@@ -49,6 +49,7 @@ constexpr int kMaxGateExperts = 64;
 
 struct GateFusedArgs {
   int group_size, experts, m;
+  int tile_rows;  // tokens per tile: 128, or 64 when that fills the SMs more evenly
   int tiles_per_group;
   long long num_tiles;
   int stages;
@@ -58,6 +59,7 @@ struct GateFusedArgs {
   float* gate2;
   float* raw_gates;  // [tokens, experts] or null
   float* tile_sums;  // [num_tiles, EP]: column sums of the raw gates per tile
+  unsigned* groups_done;  // counter the positions kernel's CTAs take tickets from; zeroed here
   int* status;
 };
 
@@ -151,6 +153,7 @@ gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int num_kb = (a.m + GBK - 1) / GBK;
+  if (blockIdx.x == 0 && threadIdx.x == 0) *a.groups_done = 0u;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -160,10 +163,13 @@ gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       for (long long t = blockIdx.x; t < a.num_tiles && ok; t += gridDim.x) {
         const long long g = t / a.tiles_per_group;
         const int c = (int)(t - g * a.tiles_per_group);
-        const long long row0 = g * a.group_size + (long long)c * TILE_TOKENS;
+        const long long row0 = g * a.group_size + (long long)c * a.tile_rows;
+        // with 64-token tiles the box is half a stage: rows 64..127 of the stage keep
+        // whatever they held, and the accumulator rows they produce are never read
+        const uint32_t x_bytes = (uint32_t)a.tile_rows * GBK * 2;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(full_bar(stage), X_STAGE_BYTES + W_STAGE_BYTES);
+          mbar_expect_tx(full_bar(stage), x_bytes + W_STAGE_BYTES);
           tma_load_3d(smem_base + stage * X_STAGE_BYTES, &map_x, full_bar(stage), kb * GBK,
                       (int)row0, 0);
           tma_load_3d(smem_base + off_w + stage * W_STAGE_BYTES, &map_w, full_bar(stage), kb * GBK,
@@ -219,8 +225,9 @@ gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
       const long long g = t / a.tiles_per_group;
       const int c = (int)(t - g * a.tiles_per_group);
-      const int s_in_group = c * TILE_TOKENS + q * 32 + lane;
-      const bool live = s_in_group < a.group_size;
+      const int row = q * 32 + lane;
+      const int s_in_group = c * a.tile_rows + row;
+      const bool live = row < a.tile_rows && s_in_group < a.group_size;
       const long long tok = g * a.group_size + s_in_group;
       ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), acc_phase, abort_flag));
       if (!ok) {
@@ -354,6 +361,9 @@ struct PositionArgs {
   const float* tile_sums;  // [groups, tiles_per_group, ep]
   int tiles_per_group, ep;
   float* loss_per_group;
+  float* loss_mean;        // sum over groups / num_groups_total, or null
+  float inv_groups_total;
+  unsigned* groups_done;
   int* table;  // [groups, experts, capacity] or null
   int table_in_smem;
   int round_bf16;
@@ -490,6 +500,23 @@ top2_positions_kernel(PositionArgs a) {
   }
   if (a.table && a.table_in_smem)
     for (int i = tid; i < E * C; i += T) a.table[(long long)g * E * C + i] = slots[i];
+  // the CTA that finishes last adds the per-group losses, always in the same order
+  if (a.loss_mean && warp == 0) {
+    unsigned ticket = 0;
+    if (lane == 0) {
+      __threadfence();
+      ticket = atomicAdd(a.groups_done, 1u);
+    }
+    ticket = __shfl_sync(0xffffffffu, ticket, 0);
+    if (ticket == gridDim.x - 1) {
+      __threadfence();
+      float part = 0.f;
+      for (int i = lane; i < (int)gridDim.x; i += 32)
+        part += *reinterpret_cast<volatile const float*>(a.loss_per_group + i);
+      for (int s = 16; s > 0; s >>= 1) part += __shfl_xor_sync(0xffffffffu, part, s);
+      if (lane == 0) *a.loss_mean = part * a.inv_groups_total;
+    }
+  }
 }
 
 typedef CUresult (*GateEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -577,8 +604,8 @@ int32_t mtfc_moe_gate_padded_experts(int32_t experts) { return padded_experts(ex
 
 int64_t mtfc_moe_gate_scratch_bytes(int64_t groups, int32_t group_size, int32_t experts) {
   if (groups < 0 || group_size < 1 || experts < 1) return 0;
-  const int64_t tpg = (group_size + TILE_TOKENS - 1) / TILE_TOKENS;
-  return groups * tpg * padded_experts(experts) * 4;
+  const int64_t tpg = (group_size + 63) / 64;   // the smaller of the two tile sizes
+  return groups * tpg * padded_experts(experts) * 4 + 16;
 }
 
 int mtfc_moe_gate_prepare(const float* w, int64_t m, int32_t experts, void* w3t_bf16, void* stream) {
@@ -597,8 +624,9 @@ int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups,
                        int64_t m, int32_t experts, int32_t capacity, int32_t policy,
                        float threshold, const float* noise, int32_t* idx1, int32_t* idx2,
                        int32_t* pos1, int32_t* pos2, float* gate1, float* gate2, float* raw_gates,
-                       float* loss_per_group, int32_t* slot_table, int32_t round_gates_to_bf16,
-                       void* scratch, int64_t scratch_bytes, void* stream) {
+                       float* loss_per_group, float* loss_mean, int64_t num_groups_total,
+                       int32_t* slot_table, int32_t round_gates_to_bf16, void* scratch,
+                       int64_t scratch_bytes, void* stream) {
   if (!x_bf16 || !w3t_bf16 || !idx1 || !idx2 || !pos1 || !pos2 || !gate1 || !gate2 ||
       !loss_per_group || !scratch)
     return fail(MTFC_ERR_SHAPE, "gate_top2: null argument");
@@ -625,21 +653,27 @@ int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups,
   const int ep = padded_experts(experts);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-  CUtensorMap map_x, map_w;
-  int rc = gate_encode(&map_x, x_bf16, m, tokens, TILE_TOKENS, "gate activations");
-  if (rc != MTFC_OK) return rc;
-  rc = gate_encode(&map_w, w3t_bf16, m, 3 * ep, 3 * ep, "gate kernel");
-  if (rc != MTFC_OK) return rc;
   GateFusedArgs a;
   a.group_size = group_size;
   a.experts = experts;
   a.m = (int)m;
-  a.tiles_per_group = (group_size + TILE_TOKENS - 1) / TILE_TOKENS;
+  // 64-token tiles when they leave fewer SMs idle in the last round
+  const long long sms = sm_count();
+  const long long t128 = groups * ((group_size + 127) / 128), t64 = groups * ((group_size + 63) / 64);
+  a.tile_rows = ((t64 + sms - 1) / sms) * 64 < ((t128 + sms - 1) / sms) * 128 ? 64 : 128;
+  a.tiles_per_group = (group_size + a.tile_rows - 1) / a.tile_rows;
   a.num_tiles = groups * a.tiles_per_group;
   a.stages = gate_stages(ep);
+  CUtensorMap map_x, map_w;
+  int rc = gate_encode(&map_x, x_bf16, m, tokens, a.tile_rows, "gate activations");
+  if (rc != MTFC_OK) return rc;
+  rc = gate_encode(&map_w, w3t_bf16, m, 3 * ep, 3 * ep, "gate kernel");
+  if (rc != MTFC_OK) return rc;
   a.idx1 = idx1; a.idx2 = idx2; a.gate1 = gate1; a.gate2 = gate2;
   a.raw_gates = raw_gates;
   a.tile_sums = static_cast<float*>(scratch);
+  a.groups_done = reinterpret_cast<unsigned*>(
+      static_cast<uint8_t*>(scratch) + mtfc_moe_gate_scratch_bytes(groups, group_size, experts) - 16);
   a.status = device_status_word();
   switch (ep) {
     case 16: rc = launch_gate_fused<16>(map_x, map_w, a, s); break;
@@ -654,6 +688,9 @@ int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups,
   p.idx1 = idx1; p.idx2 = idx2; p.pos1 = pos1; p.pos2 = pos2; p.gate1 = gate1; p.gate2 = gate2;
   p.tile_sums = a.tile_sums; p.tiles_per_group = a.tiles_per_group; p.ep = ep;
   p.loss_per_group = loss_per_group;
+  p.loss_mean = loss_mean;
+  p.inv_groups_total = 1.0f / (float)(num_groups_total > 0 ? num_groups_total : groups);
+  p.groups_done = a.groups_done;
   p.table = slot_table;
   p.round_bf16 = round_gates_to_bf16;
   int threads = 1024;

@@ -402,7 +402,7 @@ class SlicedMeshImpl(mtf.MeshImpl):
 class _PeerWorkspace(object):
   """Buffers of one fused einsum+allreduce shape (see CudaMeshImpl._peer_workspace)."""
   __slots__ = ("tensors", "handles", "out_tensor", "ctl", "stage_ptrs", "out_ptrs", "flag_ptrs",
-               "rank", "nranks")
+               "rank", "nranks", "mc_stage", "mc_out")
 
 
 class _PendingAllreduce(object):
@@ -599,6 +599,9 @@ class CudaMeshImpl(SlicedMeshImpl):
   FUSED_MAX_BYTES = 128 << 20
   # largest group the fused kernel is used for (groups of 2 and 4 have run on
   # hardware; MTFC_FUSED_ALLREDUCE_MAX_RANKS=8 opens groups of eight)
+  # let the NVSwitch reduce and broadcast (multimem) when the buffers have multicast
+  # addresses; MTFC_FUSED_MULTIMEM=0 keeps the exchange on plain peer stores
+  FUSED_MULTIMEM = os.environ.get("MTFC_FUSED_MULTIMEM", "1") == "1"
   FUSED_MAX_RANKS = int(os.environ.get("MTFC_FUSED_ALLREDUCE_MAX_RANKS", "4"))
 
   def einsum_allreduce(self, equation, inputs, mesh_axes):
@@ -670,9 +673,10 @@ class CudaMeshImpl(SlicedMeshImpl):
       ws = self._peer_workspace(pg, members, pnum, int(desc.m), int(desc.n))
       if ws is None:
         return None
-      nat.check(lib.mtfc_gemm_allreduce(
+      nat.check(lib.mtfc_gemm_allreduce_multimem(
           ctypes.byref(desc), ctypes.c_void_p(a_ptr), ctypes.c_void_p(b_ptr), ws.stage_ptrs,
           ws.out_ptrs, ws.flag_ptrs, ctypes.c_void_p(ws.ctl.data_ptr()), ws.rank, ws.nranks,
+          ctypes.c_void_p(ws.mc_stage), ctypes.c_void_p(ws.mc_out),
           ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
       # the workspace is reused by the next contraction of this size: hand back a copy
       flat = ws.out_tensor[:nbytes].view(torch.bfloat16).clone()
@@ -726,6 +730,13 @@ class CudaMeshImpl(SlicedMeshImpl):
       ws.ctl = ctl
       ws.stage_ptrs, ws.out_ptrs, ws.flag_ptrs = ptr_array(part_h), ptr_array(out_h), ptr_array(flag_h)
       ws.rank, ws.nranks = members.index(pnum), len(members)
+      # NVSwitch multicast addresses of the two buffers (0 where the fabric has none):
+      # with both, the kernel lets the switch add and broadcast
+      ws.mc_stage = ws.mc_out = 0
+      if self.FUSED_MULTIMEM:
+        mc_s, mc_o = int(part_h.multicast_ptr or 0), int(out_h.multicast_ptr or 0)
+        if mc_s and mc_o:
+          ws.mc_stage, ws.mc_out = mc_s, mc_o
       if int(part_h.rank) != ws.rank or int(part_h.world_size) != ws.nranks:
         raise RuntimeError("symmetric-memory rank %d/%d does not match mesh group position %d/%d"
                            % (part_h.rank, part_h.world_size, ws.rank, ws.nranks))

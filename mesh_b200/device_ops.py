@@ -707,6 +707,7 @@ class DeviceOps(object):
     raw = self._empty(tok_shape + (e,), G.float32) if want_raw else None
     table = self._empty(lead + (e, capacity), G.int32) if want_table else None
     loss_per_group = self._empty([groups], G.float32)
+    loss = self._empty([], G.float32)
     nbytes = int(self._lib.mtfc_moe_gate_scratch_bytes(groups, s, e))
     scratch = self._empty([max(1, nbytes // 4)], G.float32)
     noise_ptr = ctypes.c_void_p(self.contiguous(noise).ptr) if noise is not None else ctypes.c_void_p(0)
@@ -715,11 +716,9 @@ class DeviceOps(object):
                ctypes.c_void_p(i1.ptr), ctypes.c_void_p(i2.ptr), ctypes.c_void_p(p1.ptr),
                ctypes.c_void_p(p2.ptr), ctypes.c_void_p(g1.ptr), ctypes.c_void_p(g2.ptr),
                ctypes.c_void_p(raw.ptr if raw is not None else 0),
-               ctypes.c_void_p(loss_per_group.ptr),
+               ctypes.c_void_p(loss_per_group.ptr), ctypes.c_void_p(loss.ptr), num_groups_total,
                ctypes.c_void_p(table.ptr if table is not None else 0), 1,
                ctypes.c_void_p(scratch.ptr), nbytes, self._stream())
-    loss = self.binary("multiply", self.reduce("SUM", loss_per_group, [0]),
-                       1.0 / float(num_groups_total))
     res = (i1, i2, p1, p2, g1, g2, loss)
     if want_table:
       res += (table,)
@@ -749,6 +748,36 @@ class DeviceOps(object):
                ctypes.c_void_p(out.ptr), o, g, s, num_experts, capacity, m * x.dtype.itemsize,
                self._stream())
     return out
+
+  def moe_dispatch_weighted(self, x, i1, i2, p1, p2, g1, g2, num_experts, capacity, table=None):
+    """Backward of moe_combine w.r.t. the expert outputs: like moe_dispatch, with
+    every row scaled by the gate of the choice that filled the slot."""
+    o, g, s, m = x.shape
+    x = self.contiguous(x)
+    if table is None:
+      table = self.moe_slot_table(i1, i2, p1, p2, g1, g2, num_experts, capacity,
+                                  x.dtype.name == "bfloat16")
+    table = self.contiguous(table)
+    a1, ap1, ag1, ag2 = [self.contiguous(t) for t in (i1, p1, g1, g2)]
+    out = self._empty([o, num_experts, g, capacity, m], x.dtype)
+    self._call(self._lib.mtfc_moe_dispatch_weighted, ctypes.c_void_p(x.ptr), _CODE[x.dtype.name],
+               ctypes.c_void_p(table.ptr), ctypes.c_void_p(a1.ptr), ctypes.c_void_p(ap1.ptr),
+               ctypes.c_void_p(ag1.ptr), ctypes.c_void_p(ag2.ptr), ctypes.c_void_p(out.ptr), o, g, s,
+               num_experts, capacity, m, self._stream())
+    return out
+
+  def moe_combine_gate_grad(self, y, dout, i1, i2, p1, p2, g1, g2):
+    """Backward of moe_combine w.r.t. the two gates: per token, the dot product
+    of its output gradient with the expert row each kept choice read."""
+    o, e, g, c, m = y.shape
+    s = i1.shape[-1]
+    y, dout = self.contiguous(y), self.contiguous(dout)
+    args = [self.contiguous(t) for t in (i1, i2, p1, p2, g1, g2)]
+    d1, d2 = self._empty([o, g, s], G.float32), self._empty([o, g, s], G.float32)
+    self._call(self._lib.mtfc_moe_combine_gate_grad, ctypes.c_void_p(y.ptr), ctypes.c_void_p(dout.ptr),
+               _CODE[y.dtype.name], *[ctypes.c_void_p(t.ptr) for t in args], ctypes.c_void_p(d1.ptr),
+               ctypes.c_void_p(d2.ptr), o, g, s, e, c, m, self._stream())
+    return d1, d2
 
   def moe_combine(self, y, i1, i2, p1, p2, g1, g2):
     o, e, g, c, m = y.shape

@@ -153,6 +153,21 @@ class FusedAttentionOperation(mtf.Operation):
     self._causal = causal
     self._outputs = [mtf.Tensor(self, Shape(q.shape.dims[:-1] + [v.shape.dims[-1]]), v.dtype)]
 
+  def gradient(self, grad_ys):
+    """Backward pass through the op-by-op chain (einsum, fp32 softmax, einsum),
+    which recomputes the attention weights: the fused kernel keeps no logits.
+    The chain materialises [..., length_q, length_kv] fp32 tensors."""
+    causal = self._causal
+
+    def chain(q, k, v):
+      mask = None
+      if causal:
+        q_pos = mtf.mtf_range(q.mesh, q.shape.dims[-2], G.float32)
+        k_pos = mtf.mtf_range(q.mesh, k.shape.dims[-2], G.float32)
+        mask = mtf.cast(mtf.less(q_pos, k_pos), G.float32) * -1e9
+      return [dot_product_attention(q, k, v, mask, fused=False)]
+    return mtf.gradients_by_recompute(self.inputs, chain, grad_ys)
+
   def lower(self, lowering):
     impl = lowering.mesh_impl(self)
     q, k, v = self.inputs

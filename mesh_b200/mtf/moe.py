@@ -175,6 +175,42 @@ class Top2GatingOperation(Operation):
         [Tensor(self, token_shape, G.float32, index=4), Tensor(self, token_shape, G.float32, index=5),
          Tensor(self, Shape([]), G.float32, index=6), Tensor(self, table_shape, G.int32, index=7)])
 
+  @property
+  def has_gradient(self):
+    return True   # through the two gates and the loss; indices and positions carry none
+
+  def gradient(self, grad_ys):
+    """d(gate_1, gate_2, loss) / d(inputs, gate_weights): the routing decisions
+    (indices, capacity masks) are constants, as in the reference, whose top_1
+    gradient is a one-hot scatter (ops.py:4916-4920) and whose masks come out of
+    comparisons; what remains is softmax -> picked gates -> renormalisation and
+    the loss's mean-gate factor (moe.py:1384-1424, 1485-1494), rebuilt here from
+    ordinary operations and differentiated."""
+    x, w = self.inputs[0], self.inputs[1]
+    i1, i2, _, _, g1_out, g2_out, _, _ = self.outputs
+    experts_dim = self._experts_dim
+    group_size_dim = x.shape.dims[-2]
+
+    def chain(x_, w_):
+      raw = layers.dense(mtf.to_float(x_), experts_dim, use_bias=False, kernel_weights=w_,
+                         name="gate_grad")
+      raw = mtf.softmax(raw, experts_dim)
+      m1 = mtf.one_hot(i1, experts_dim, dtype=raw.dtype)
+      m2 = mtf.one_hot(i2, experts_dim, dtype=raw.dtype)
+      g1 = mtf.reduce_sum(raw * m1, reduced_dim=experts_dim)
+      g2 = mtf.reduce_sum(raw * m2, reduced_dim=experts_dim)
+      denom = g1 + g2 + 1e-9
+      keep1 = mtf.to_float(mtf.not_equal(g1_out, 0.0))
+      keep2 = mtf.to_float(mtf.not_equal(g2_out, 0.0))
+      density_1 = mtf.reduce_mean(m1, reduced_dim=group_size_dim)
+      proxy = mtf.reduce_mean(raw, reduced_dim=group_size_dim)
+      loss = mtf.reduce_mean(proxy * density_1) * float(experts_dim.size * experts_dim.size)
+      return [g1 / denom * keep1, g2 / denom * keep2, loss]
+    dx, dw = mtf.gradients_by_recompute([x, w], chain, [grad_ys[4], grad_ys[5], grad_ys[6]])
+    if dx is not None and dx.dtype != x.dtype:
+      dx = mtf.cast(dx, x.dtype)
+    return [dx, dw] + [None] * (len(self.inputs) - 2)
+
   def lower(self, lowering):
     impl = lowering.mesh_impl(self)
     ops = impl.slice_ops
@@ -212,6 +248,18 @@ class MoeDispatchOperation(Operation):
     self._capacity = capacity_dim.size
     self._outputs = [Tensor(self, Shape([o, experts_dim, g, capacity_dim, m]), inputs.dtype)]
 
+  def gradient(self, grad_ys):
+    """dx[g, s] = the sum of the gradient rows of the slots the token was copied
+    to: a combine with unit gates.  The dispatch tensor itself comes from a cast
+    to bool (moe.py:1510-1511), so nothing flows to the gates from here."""
+    x = self.inputs[0]
+    i1, i2, p1, p2, g1, g2 = self.inputs[1:7]
+    # 1.0 where the gate, rounded to the activation type, is non-zero
+    unit = lambda g: mtf.cast(mtf.cast(mtf.cast(g, x.dtype), G.bool_), G.float32)
+    dx = MoeCombineOperation(grad_ys[0], [i1, i2, p1, p2, unit(g1), unit(g2)],
+                             x.shape.dims[2]).outputs[0]
+    return [dx] + [None] * (len(self.inputs) - 1)
+
   def lower(self, lowering):
     impl = lowering.mesh_impl(self)
     ops = impl.slice_ops
@@ -231,12 +279,67 @@ class MoeCombineOperation(Operation):
     o, _, g, _, m = expert_output.shape.dims
     self._outputs = [Tensor(self, Shape([o, g, group_size_dim, m]), expert_output.dtype)]
 
+  def gradient(self, grad_ys):
+    """Both transposes of the combine einsum: the expert-output gradient is a
+    gate-weighted dispatch of dout, the gate gradients are per-token row dots."""
+    y = self.inputs[0]
+    routing = self.inputs[1:7]
+    dy = MoeDispatchWeightedOperation(grad_ys[0], routing, y.shape.dims[1], y.shape.dims[3]).outputs[0]
+    dg1, dg2 = MoeCombineGateGradOperation(y, grad_ys[0], routing).outputs
+    return [dy, None, None, None, None, dg1, dg2]
+
   def lower(self, lowering):
     impl = lowering.mesh_impl(self)
     ops = impl.slice_ops
     fn = lambda ys, i1, i2, p1, p2, g1, g2: ops.moe_combine(ys, i1, i2, p1, p2, g1, g2)
     lowering.set_tensor_lowering(
         self.outputs[0], impl.slicewise(fn, *[lowering.tensors[t] for t in self.inputs]))
+
+
+class MoeDispatchWeightedOperation(Operation):
+  """d(expert_output)[O,E,G,C,M] of MoeCombineOperation: slot (e, c) receives
+  gate * dout[token in the slot] (the combine einsum's transpose, ops.py:2846-2854)."""
+
+  def __init__(self, dout, routing, experts_dim, capacity_dim, name=None):
+    super().__init__([dout] + list(routing), name=name or "moe_dispatch_weighted")
+    o, g, _, m = dout.shape.dims
+    self._num_experts = experts_dim.size
+    self._capacity = capacity_dim.size
+    self._outputs = [Tensor(self, Shape([o, experts_dim, g, capacity_dim, m]), dout.dtype)]
+
+  @property
+  def has_gradient(self):
+    return False
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    ops = impl.slice_ops
+    e, c = self._num_experts, self._capacity
+    fn = lambda xs, i1, i2, p1, p2, g1, g2: ops.moe_dispatch_weighted(xs, i1, i2, p1, p2, g1, g2, e, c)
+    lowering.set_tensor_lowering(
+        self.outputs[0], impl.slicewise(fn, *[lowering.tensors[t] for t in self.inputs]))
+
+
+class MoeCombineGateGradOperation(Operation):
+  """d(gate_1), d(gate_2) [O,G,S] of MoeCombineOperation: <dout[s], y[i_k, p_k]>."""
+
+  def __init__(self, expert_output, dout, routing, name=None):
+    super().__init__([expert_output, dout] + list(routing), name=name or "moe_combine_gate_grad")
+    token_shape = Shape(dout.shape.dims[:-1])
+    self._outputs = [Tensor(self, token_shape, G.float32, index=0),
+                     Tensor(self, token_shape, G.float32, index=1)]
+
+  @property
+  def has_gradient(self):
+    return False
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    ops = impl.slice_ops
+    fn = lambda ys, d, i1, i2, p1, p2, g1, g2: ops.moe_combine_gate_grad(ys, d, i1, i2, p1, p2, g1, g2)
+    d1, d2 = impl.slicewise(fn, *[lowering.tensors[t] for t in self.inputs])
+    lowering.set_tensor_lowering(self.outputs[0], d1)
+    lowering.set_tensor_lowering(self.outputs[1], d2)
 
 
 # ------------------------------------------------------------------ the layer
@@ -280,6 +383,8 @@ def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, lay
 
   aux = {}
   fused = hparams.moe_use_fused_kernels
+  if fused and hparams.moe_use_second_place_loss:
+    raise ValueError("moe_use_second_place_loss is not available with the fused kernels")
   if fused:
     policy, threshold = _second_policy(hparams, train)
     gating = Top2GatingOperation(inputs, gate_weights, experts_dim_unsplit, capacity, policy,

@@ -1276,3 +1276,67 @@ def gradients(ys, xs, grad_ys=None, operations=None):
         else:
           tensor_to_gradient[inp] = grad
   return [tensor_to_gradient.get(x) for x in xs]
+
+
+def gradients_by_recompute(inputs, build_fn, grad_ys):
+  """Gradients of a fused operation through an equivalent chain of ordinary
+  operations: `build_fn(*inputs)` adds that chain to the graph and returns its
+  outputs, which are differentiated against `grad_ys` (None entries are left
+  out).  The chain is only ever lowered if the gradient is; it recomputes the
+  forward values it needs (the approach of mesh_tensorflow/ops.py:6607-6720,
+  recompute_grad).  Returns one gradient (or None) per input."""
+  graph = inputs[0].graph
+  start = len(graph.operations)
+  ys = list(build_fn(*inputs))
+  pairs = [(y, g) for y, g in zip(ys, grad_ys) if g is not None]
+  if not pairs:
+    return [None] * len(inputs)
+  chain = graph.operations[start:]
+  return gradients([y for y, _ in pairs], list(inputs), grad_ys=[g for _, g in pairs],
+                   operations=chain)
+
+
+class RecomputeGradOperation(Operation):
+  """y = fn(*inputs) whose gradient re-runs fn instead of keeping what the
+  forward pass computed inside it (mesh_tensorflow/ops.py:6607-6720)."""
+
+  def __init__(self, fn, explicit_inputs, name=None):
+    forward = fn(*explicit_inputs)
+    self._single = isinstance(forward, Tensor)
+    self._forward = [forward] if self._single else list(forward)
+    super().__init__(list(explicit_inputs), name=name or "recompute_grad")
+    self._fn = fn
+    self._outputs = [Tensor(self, y.shape, y.dtype, index=i) for i, y in enumerate(self._forward)]
+
+  def lower(self, lowering):
+    for out, y in zip(self.outputs, self._forward):
+      lowering.set_tensor_lowering(out, lowering.tensors[y])
+
+  def gradient(self, grad_ys):
+    def chain(*xs):
+      ys = self._fn(*xs)
+      return [ys] if isinstance(ys, Tensor) else list(ys)
+    return gradients_by_recompute(self.inputs, chain, grad_ys)
+
+
+def recompute_grad(fn, explicit_inputs):
+  op = RecomputeGradOperation(fn, explicit_inputs)
+  return op.outputs[0] if op._single else op.outputs
+
+
+def anonymous_shape(shape):
+  shape = convert_to_shape(shape)
+  return Shape([Dimension("_anonymous_%i" % i, d.size) for i, d in enumerate(shape.dims)])
+
+
+def anonymize(x):
+  return reshape(x, anonymous_shape(x.shape))
+
+
+def import_fully_replicated(mesh, tf_tensor, shape, name=None, dtype=None):
+  """Imports under anonymous dim names (so that no layout rule applies and the
+  whole array is uploaded everywhere), then reshapes to `shape`, which slices
+  locally (mesh_tensorflow/ops.py:3935-3938)."""
+  shape = convert_to_shape(shape)
+  return reshape(import_tf_tensor(mesh, tf_tensor, anonymous_shape(shape), name, dtype=dtype), shape)
+

@@ -140,3 +140,35 @@ def combine(y, i1, i2, p1, p2, g1, g2, bf16=True):
         acc = acc + w2[g, s] * y[g, i2[g, s], p2[g, s]]
       out[g, s] = acc
   return out
+
+
+def dispatch_weighted(x, i1, i2, p1, p2, g1, g2, num_experts, capacity, bf16=True):
+  """Transpose of combine w.r.t. the expert outputs: slot (e, c) receives
+  w * x[s] for the token s that occupies it through either choice."""
+  g_, s_, m_ = x.shape
+  out = np.zeros((g_, num_experts, capacity, m_), dtype=np.float32)
+  w1, w2 = combine_weights(g1, bf16), combine_weights(g2, bf16)
+  for g in range(g_):
+    for s in range(s_):
+      if w1[g, s] != 0 and p1[g, s] < capacity:
+        out[g, i1[g, s], p1[g, s]] += w1[g, s] * x[g, s]
+      if w2[g, s] != 0 and p2[g, s] < capacity:
+        out[g, i2[g, s], p2[g, s]] += w2[g, s] * x[g, s]
+  return out
+
+
+def combine_gate_grad(y, dout, i1, i2, p1, p2, g1, g2, bf16=True):
+  """Gradient of combine w.r.t. the gates: <dout[s], y[i_k, p_k]> per kept choice."""
+  g_, e_, c_, m_ = y.shape
+  s_ = i1.shape[-1]
+  d1 = np.zeros((g_, s_), dtype=np.float32)
+  d2 = np.zeros((g_, s_), dtype=np.float32)
+  w1, w2 = combine_weights(g1, bf16), combine_weights(g2, bf16)
+  y64, d64 = y.astype(np.float64), dout.astype(np.float64)
+  for g in range(g_):
+    for s in range(s_):
+      if w1[g, s] != 0 and p1[g, s] < c_:
+        d1[g, s] = np.dot(d64[g, s], y64[g, i1[g, s], p1[g, s]])
+      if w2[g, s] != 0 and p2[g, s] < c_:
+        d2[g, s] = np.dot(d64[g, s], y64[g, i2[g, s], p2[g, s]])
+  return d1, d2

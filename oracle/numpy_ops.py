@@ -321,6 +321,27 @@ class NumpyOps(object):
     out = out.reshape(o, g, num_experts, capacity, m).transpose(0, 2, 1, 3, 4)
     return Arr(np.ascontiguousarray(out), x.dtype)
 
+  def moe_dispatch_weighted(self, x, i1, i2, p1, p2, g1, g2, num_experts, capacity, table=None):
+    from oracle import moe_spec
+    o, g, s, m = x.a.shape
+    out = moe_spec.dispatch_weighted(
+        x.a.reshape(o * g, s, m), i1.a.reshape(-1, s), i2.a.reshape(-1, s), p1.a.reshape(-1, s),
+        p2.a.reshape(-1, s), g1.a.reshape(-1, s), g2.a.reshape(-1, s), num_experts, capacity,
+        bf16=(x.dtype == mtf.bfloat16))
+    out = out.reshape(o, g, num_experts, capacity, m).transpose(0, 2, 1, 3, 4)
+    return _finish(np.ascontiguousarray(out), x.dtype)
+
+  def moe_combine_gate_grad(self, y, dout, i1, i2, p1, p2, g1, g2):
+    from oracle import moe_spec
+    o, e, g, c, m = y.a.shape
+    s = i1.a.shape[-1]
+    yg = np.ascontiguousarray(y.a.transpose(0, 2, 1, 3, 4)).reshape(o * g, e, c, m)
+    d1, d2 = moe_spec.combine_gate_grad(
+        yg, dout.a.reshape(o * g, s, m), i1.a.reshape(-1, s), i2.a.reshape(-1, s),
+        p1.a.reshape(-1, s), p2.a.reshape(-1, s), g1.a.reshape(-1, s), g2.a.reshape(-1, s),
+        bf16=(y.dtype == mtf.bfloat16))
+    return Arr(d1.reshape(o, g, s), mtf.float32), Arr(d2.reshape(o, g, s), mtf.float32)
+
   def moe_combine(self, y, i1, i2, p1, p2, g1, g2):
     from oracle import moe_spec
     o, e, g, c, m = y.a.shape

@@ -80,7 +80,7 @@ def test_gradient_rules():
     mtf.gradients([mtf.reduce_sum(mtf.shift(x, 1, x.shape.dims[1], False))], [x])
 
 
-def _moe_total(arrays, mesh_shape, layout, grads):
+def _moe_total(arrays, mesh_shape, layout, grads, fused=False):
   x, wg, wi, wo = arrays
   g = mtf.Graph()
   m = mtf.Mesh(g, "m")
@@ -89,7 +89,7 @@ def _moe_total(arrays, mesh_shape, layout, grads):
   WI = mtf.import_tf_tensor(m, wi, "experts:4,d_model:8,d_ff:16", dtype=mtf.float32)
   WO = mtf.import_tf_tensor(m, wo, "experts:4,d_ff:16,d_model:8", dtype=mtf.float32)
   hp = mtf.moe.HParams(moe_group_size=16, moe_second_policy_train="all",
-                       moe_use_fused_kernels=False, moe_capacity_factor_train=4.0)
+                       moe_use_fused_kernels=fused, moe_capacity_factor_train=1.5)
   out, loss = mtf.moe.transformer_moe_layer_v1(
       X, mtf.Dimension("d_model", 8), hp, True, mesh_shape, layout, WG, WI, WO)
   total = mtf.reduce_sum(mtf.square(out)) + loss * 10.0
@@ -121,6 +121,42 @@ def test_moe_layer_gradients_match_finite_differences():
       down = float(_moe_total(a, mesh_shape, layout, False)[0])
       fd = (up - down) / (2 * eps)
       assert abs(vals[1 + which][idx] - fd) < 2e-2 + 2e-2 * abs(fd), (which, idx)
+
+
+def test_fused_moe_gradients_equal_the_op_chain():
+  """The fused gating / dispatch / combine operations differentiate to the same
+  gradients as the reference's op chain (capacity tight enough to drop tokens),
+  on one processor and with groups and experts split."""
+  r = rng(14)
+  arrays = [r.standard_normal((4, 16, 8)).astype(np.float32),
+            (r.standard_normal((8, 4)) / 2).astype(np.float32),
+            (r.standard_normal((4, 8, 16)) / 3).astype(np.float32),
+            (r.standard_normal((4, 16, 8)) / 4).astype(np.float32)]
+  for mesh_shape, layout in (("all:1", ""), ("all:2", "batch:all;experts:all")):
+    ref = _moe_total(arrays, mesh_shape, layout, True, fused=False)
+    got = _moe_total(arrays, mesh_shape, layout, True, fused=True)
+    for a, b in zip(got, ref):
+      np.testing.assert_allclose(a, b, rtol=2e-4, atol=2e-5)
+
+
+def test_fused_attention_gradient_equals_the_op_chain():
+  r = rng(15)
+  b, h, l, d = 2, 2, 8, 4
+  vals = [r.standard_normal((b, h, l, d)).astype(np.float32) for _ in range(3)]
+  outs = []
+  for fused in (True, False):
+    g = mtf.Graph()
+    m = mtf.Mesh(g, "m")
+    q = mtf.import_tf_tensor(m, vals[0], "batch:2,heads:2,length:8,d_kv:4", dtype=mtf.float32)
+    k = mtf.import_tf_tensor(m, vals[1], "batch:2,heads:2,memory_length:8,d_kv:4", dtype=mtf.float32)
+    v = mtf.import_tf_tensor(m, vals[2], "batch:2,heads:2,memory_length:8,d_kv:4", dtype=mtf.float32)
+    pos = mtf.mtf_range(m, q.shape.dims[2], mtf.float32)
+    mask = mtf.layers.attention_mask_autoregressive(pos)
+    o = mtf.layers.dot_product_attention(q, k, v, mask, fused=fused)
+    loss = mtf.reduce_sum(mtf.square(o) * 0.5 + o)
+    outs.append(_lower(g, m, [loss] + mtf.gradients([loss], [q, k, v]), "all:2", "heads:all"))
+  for a, b in zip(*outs):
+    np.testing.assert_allclose(a, b, rtol=1e-5, atol=1e-6)
 
 
 @pytest.mark.parametrize("mesh_shape,layout", [("all:1", ""), ("a:2,b:2", "batch:a;d_ff:b")])

@@ -56,6 +56,45 @@ def test_golden_top_k_on_split_dim():
   np.testing.assert_array_equal(indices, v["expected_indices"])
 
 
+def golden_top_k_gradient(impl):
+  """The reference's pinned top-k gradient (ops_test.py:606-611, 636-640)."""
+  v = GOLDEN["top_k"]
+  g = mtf.Graph()
+  mesh = mtf.Mesh(g, "my_mesh")
+  x = mtf.import_fully_replicated(mesh, np.array(v["inputs"], dtype=np.float32), v["shape"])
+  d_values = mtf.import_tf_tensor(mesh, np.array(v["d_values"], dtype=np.float32), "b:2,k:2")
+  values, _ = mtf.top_k(x, x.shape.get_dim_by_name(v["reduced_dim"]), mtf.Dimension("k", v["k"]))
+  d_inputs, = mtf.gradients([values], [x], [d_values])
+  low = mtf.Lowering(g, {mesh: impl})
+  return low.export_to_tf_tensor(d_inputs), v["expected_d_inputs"]
+
+
+def golden_recompute_grad(impl):
+  """The reference's pinned recompute_grad case (ops_test.py:645-671)."""
+  v = GOLDEN["recompute_grad"]
+  g = mtf.Graph()
+  mesh = mtf.Mesh(g, "my_mesh")
+  x = mtf.import_fully_replicated(mesh, np.array(v["x"], dtype=np.float32), v["shape"])
+  dy = mtf.import_tf_tensor(mesh, np.array(v["dy"], dtype=np.float32), v["shape"])
+  y = mtf.recompute_grad(lambda t: t * t + t, [x])
+  dx, = mtf.gradients([y], [x], [dy])
+  low = mtf.Lowering(g, {mesh: impl})
+  return (low.export_to_tf_tensor(y), low.export_to_tf_tensor(dx)), (v["expected_y"], v["expected_dx"])
+
+
+def test_golden_top_k_gradient():
+  v = GOLDEN["top_k"]
+  got, expected = golden_top_k_gradient(NumpyMeshImpl(v["mesh"], v["layout"]))
+  np.testing.assert_array_equal(got, expected)
+
+
+def test_golden_recompute_grad():
+  v = GOLDEN["recompute_grad"]
+  got, expected = golden_recompute_grad(NumpyMeshImpl(v["mesh"], v["layout"]))
+  np.testing.assert_array_equal(got[0], expected[0])
+  np.testing.assert_array_equal(got[1], expected[1])
+
+
 def test_top_k_operation_large_k_on_split_dim():
   """k >= 5 takes the TopKOperation path: local top-k, allconcat, global top-k."""
   x = rng(1).standard_normal((4, 16)).astype(np.float32)
