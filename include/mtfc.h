@@ -125,25 +125,68 @@ int mtfc_gemm_allreduce_flag_bytes(void);
  * reach the launch (first-use set-up on one rank, a long host pause) should raise
  * it; a test that wants to see the time-out path lowers it. */
 int mtfc_gemm_allreduce_set_wait_ms(int ms);
+/* How the fused kernel is launched: 1 = cooperatively (the whole grid is
+ * guaranteed resident, which its waits between CTAs rely on), 0 = the driver
+ * refused a cooperative cluster launch and plain launches are used, -1 = not
+ * launched yet. */
+int mtfc_gemm_allreduce_cooperative(void);
 int64_t mtfc_gemm_allreduce_stage_bytes(int64_t m, int64_t n, int nranks);
 int mtfc_gemm_allreduce(const mtfc_gemm_desc* desc, const void* a, const void* b,
                         void* const* stage_ptrs, void* const* out_ptrs,
                         void* const* flag_ptrs, void* ctl, int rank, int nranks,
                         void* stream);
 
-/* The same with the exchange done by the NVSwitch: `stage_multicast` and
- * `out_multicast` are the multicast (NVLS) addresses of the staging and output
- * buffers of the group - the same allocations as stage_ptrs / out_ptrs, bound to
- * one multicast object each.  Every rank then keeps its partial product in its own
- * staging buffer; the owner of a row block reads the fp32-accumulated sum of all
- * ranks' copies with multimem.ld_reduce and writes it to all ranks' outputs with
- * multimem.st, so each byte of the output crosses a GPU's links once in and once
- * out, whatever the group size (1.5 to 1.75 times in each direction without).
- * Either address null: identical to mtfc_gemm_allreduce. */
-int mtfc_gemm_allreduce_multimem(const mtfc_gemm_desc* desc, const void* a, const void* b,
-                                 void* const* stage_ptrs, void* const* out_ptrs,
-                                 void* const* flag_ptrs, void* ctl, int rank, int nranks,
-                                 const void* stage_multicast, void* out_multicast, void* stream);
+/* The same with a choice of how the partial products travel:
+ *   MTFC_EXCHANGE_PUSH      as mtfc_gemm_allreduce: the epilogue stores each tile into
+ *                           the owner's staging buffer over NVLink.
+ *   MTFC_EXCHANGE_PULL      every rank keeps its partial product in its own staging
+ *                           buffer, so the GEMM's epilogue never waits on NVLink; the
+ *                           owner's reduction warps read the other ranks' copies with
+ *                           peer loads.  Same bytes on the links as PUSH.
+ *   MTFC_EXCHANGE_MULTIMEM  partial products local as for PULL; `stage_multicast` and
+ *                           `out_multicast` are the multicast (NVLS) addresses of the
+ *                           group's staging and output buffers - the same allocations
+ *                           as stage_ptrs / out_ptrs, each bound to one multicast
+ *                           object.  The owner of a row block reads the fp32-accumulated
+ *                           sum of all ranks' copies with multimem.ld_reduce (the switch
+ *                           adds) and writes it to all ranks with multimem.st: (1 + 1/n)
+ *                           times the output's bytes per direction per GPU, against
+ *                           2(n-1)/n for the other two - less from n = 4 up.
+ * The multicast addresses are ignored by the first two forms. */
+#define MTFC_EXCHANGE_PUSH 0
+#define MTFC_EXCHANGE_PULL 1
+#define MTFC_EXCHANGE_MULTIMEM 2
+int mtfc_gemm_allreduce_ex(const mtfc_gemm_desc* desc, const void* a, const void* b,
+                           void* const* stage_ptrs, void* const* out_ptrs, void* const* flag_ptrs,
+                           void* ctl, int rank, int nranks, int exchange,
+                           const void* stage_multicast, void* out_multicast, void* stream);
+
+/* Pipelined form of "local einsum, then allreduce" (ops.py:2867-2873,
+ * placement_mesh_impl.py:200-212): the GEMM runs un-chunked and counts finished
+ * row blocks; a second stream moves the partial sums with the copy engines,
+ * which overlap the GEMM fully, and reduces them with small kernels.
+ *   mtfc_gemm_with_progress: mtfc_gemm on the CTA-pair tensor-core kernel (bf16,
+ *     batch 1, m >= 256) that also increments progress[rb] once per epilogue warp
+ *     and tile of 256-row block rb when the tile's rows are in memory:
+ *     8 * ceil(n / 256) increments per launch complete a row block.  The array is
+ *     never reset; consumers count launches.
+ *   mtfc_wait_counters: a one-CTA kernel that returns when counters[0..count) have
+ *     all reached (launches of this waiter so far, kept in *epoch_counter) *
+ *     per_epoch.  The wait is bounded (mtfc_pipeline_set_wait_ms, default ~3 s);
+ *     when it runs out MTFC_ERR_TIMEOUT is recorded for mtfc_device_status and
+ *     the kernel returns.
+ *   mtfc_signal_peers: adds 1 (release, system scope) to peer_counters[i][index]
+ *     for i < n <= 8 - after everything enqueued earlier on the stream.
+ *   mtfc_add_n_bf16: dst = sum of n <= 8 bf16 arrays, fp32 accumulation in source
+ *     order, one rounding; elements a multiple of 8, 16-byte aligned buffers. */
+int mtfc_gemm_with_progress(const mtfc_gemm_desc* desc, const void* a, const void* b, void* c,
+                            uint32_t* progress, void* stream);
+int mtfc_pipeline_set_wait_ms(int ms);
+int mtfc_wait_counters(const uint32_t* counters, int32_t count, uint32_t per_epoch,
+                       uint32_t* epoch_counter, void* stream);
+int mtfc_signal_peers(void* const* peer_counters, int32_t n, int64_t index, void* stream);
+int mtfc_add_n_bf16(const void* const* sources, int32_t n, void* dst, int64_t elements,
+                    void* stream);
 
 /* K1f on the tensor cores: fp32 [batch, rows, k] (element strides s_*) -> bf16
  * [batch, rows, 6k], every value split into three bf16 terms laid along K
@@ -409,6 +452,45 @@ int mtfc_moe_combine_gate_grad(const void* y, const void* dout, int dtype, const
                                float* dgate2, int64_t outer, int64_t groups_per_outer,
                                int32_t group_size, int32_t experts, int32_t capacity,
                                int64_t row_elems, void* stream);
+
+/* ---- K8: row kernels of the rest of a transformer block ------------------- */
+/* y[r, :] = (x[r, :] - mean) * rsqrt(var + epsilon) * scale + bias over rows of
+ * `cols` contiguous elements (centered: layer_norm, layers.py:950-979), or
+ * x * rsqrt(mean(x^2) + epsilon) * scale (centered = 0: RMS norm,
+ * transformer/transformer.py:493-516).  scale / bias: [cols] or null.  fp32
+ * statistics, one rounding at the store. */
+int mtfc_norm_rows(const void* x, const void* scale, const void* bias, void* y, int dtype,
+                   int64_t rows, int64_t cols, float epsilon, int32_t centered, void* stream);
+
+/* Counter-based random fill standing for tf.random.uniform / tf.random.normal
+ * inside MeshImpl.random (placement_mesh_impl.py:307-325): element i is word i % 4
+ * of Philox4x32-10 block i / 4 under key `seed`, so a slice's values depend only
+ * on the seed (which the mesh implementation derives from the slice's offset:
+ * replicas get equal values).  normal = 0: uniform in [a, b) from the word's top
+ * 24 bits; normal = 1: mean a, standard deviation b by Box-Muller. */
+int mtfc_random(void* out, int dtype, int64_t n, int32_t normal, uint64_t seed, float a, float b,
+                void* stream);
+
+/* out[r, :] = table[indices[r] - first_row, :] if 0 <= indices[r] - first_row <
+ * table_rows, else zeros: the row gather behind mtf.gather / layers.embedding
+ * (ops.py:5231-5251, a one-hot einsum in the reference).  first_row is the
+ * offset of this slice of the table when the gathered dim is split over the
+ * mesh; the slices' results then add up to the full gather. */
+int mtfc_gather_rows(const void* table, const int32_t* indices, void* out, int64_t rows,
+                     int64_t table_rows, int32_t first_row, int64_t row_bytes, void* stream);
+
+/* Softmax cross-entropy with hard targets over rows of `cols` logits that are the
+ * columns [first_col, first_col + cols) of the vocabulary (layers.py:1062-1117,
+ * reduce_logsumexp ops.py:5493-5520).  mtfc_xent_stats: per row the slice's max,
+ * sum of exp(x - max) and the target's logit (0 when the target lies in another
+ * slice).  Over slices: M = max of maxes, Z = sum of sums * exp(max - M),
+ * log_z = log Z + M, loss = log_z - sum of picked + z_loss * log_z^2.
+ * mtfc_xent_grad: dlogits = dloss * ((1 + 2 z_loss log_z) softmax - onehot(target)). */
+int mtfc_xent_stats(const void* logits, int dtype, const int32_t* targets, int64_t rows, int64_t cols,
+                    int32_t first_col, float* row_max, float* row_sum, float* picked, void* stream);
+int mtfc_xent_grad(const void* logits, int dtype, const int32_t* targets, const float* log_z,
+                   const float* dloss, float z_loss, int64_t rows, int64_t cols, int32_t first_col,
+                   void* dlogits, void* stream);
 
 #ifdef __cplusplus
 }

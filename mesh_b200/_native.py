@@ -22,6 +22,8 @@ F32 = 0
 BF16 = 1
 I32 = 2
 
+EXCHANGE_PUSH, EXCHANGE_PULL, EXCHANGE_MULTIMEM = 0, 1, 2
+
 EPILOGUE_NONE = 0
 EPILOGUE_RELU = 1
 
@@ -72,11 +74,17 @@ def _declare(lib):
       "mtfc_gemm_uses_tensor_cores": [ctypes.POINTER(GemmDesc), vp, vp, vp],
       "mtfc_gemm_allreduce_flag_bytes": [],
       "mtfc_gemm_allreduce_set_wait_ms": [ctypes.c_int],
+      "mtfc_gemm_allreduce_cooperative": [],
       "mtfc_gemm_allreduce_stage_bytes": [i64, i64, i32],
       "mtfc_gemm_allreduce": [ctypes.POINTER(GemmDesc), vp, vp, ctypes.POINTER(vp), ctypes.POINTER(vp),
                               ctypes.POINTER(vp), vp, i32, i32, vp],
-      "mtfc_gemm_allreduce_multimem": [ctypes.POINTER(GemmDesc), vp, vp, ctypes.POINTER(vp),
-                                       ctypes.POINTER(vp), ctypes.POINTER(vp), vp, i32, i32, vp, vp, vp],
+      "mtfc_gemm_allreduce_ex": [ctypes.POINTER(GemmDesc), vp, vp, ctypes.POINTER(vp),
+                                 ctypes.POINTER(vp), ctypes.POINTER(vp), vp, i32, i32, i32, vp, vp, vp],
+      "mtfc_gemm_with_progress": [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp],
+      "mtfc_pipeline_set_wait_ms": [ctypes.c_int],
+      "mtfc_wait_counters": [vp, i32, ctypes.c_uint32, vp, vp],
+      "mtfc_signal_peers": [ctypes.POINTER(vp), i32, i64, vp],
+      "mtfc_add_n_bf16": [ctypes.POINTER(vp), i32, vp, i64, vp],
       "mtfc_split_bf16x3": [vp, i64, i64, i64, vp, i64, i64, i64, i32, vp],
       "mtfc_attention_set_variant": [i32],
       "mtfc_attention_supported": [i64, p_i64, p_i64, p_i64, p_i64],
@@ -91,6 +99,11 @@ def _declare(lib):
       "mtfc_one_hot": [vp, i64, i32, f32, f32, vp, i32, vp],
       "mtfc_fill": [vp, i32, i64, f32, f32, vp],
       "mtfc_copy_strided": [vp, p_i64, vp, p_i64, i32, p_i64, i32, vp],
+      "mtfc_norm_rows": [vp, vp, vp, vp, i32, i64, i64, f32, i32, vp],
+      "mtfc_random": [vp, i32, i64, i32, ctypes.c_uint64, f32, f32, vp],
+      "mtfc_gather_rows": [vp, vp, vp, i64, i64, i32, i64, vp],
+      "mtfc_xent_stats": [vp, i32, vp, i64, i64, i32, vp, vp, vp, vp],
+      "mtfc_xent_grad": [vp, i32, vp, vp, vp, f32, i64, i64, i32, vp, vp],
       "mtfc_moe_split_gate_weights": [vp, i64, i32, vp, vp],
       "mtfc_moe_top2_gating": [vp, i32, i64, i32, i32, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp,
                                vp, vp, vp],

@@ -55,15 +55,16 @@ int sm_count() {
 
 bool gemm_tcgen05_eligible(const mtfc_gemm_desc* d, const void* a, const void* b, const void* c);
 int gemm_tcgen05_launch(const mtfc_gemm_desc* d, const void* a, const void* b, void* c,
-                        cudaStream_t stream, int cta_group);
+                        cudaStream_t stream, int cta_group, void* progress);
 int gemm_simt_launch(const mtfc_gemm_desc* d, const void* a, const void* b, void* c,
                      cudaStream_t stream);
 int gemm_allreduce_flag_bytes();
 void gemm_allreduce_set_wait_ms(int ms);
+int gemm_allreduce_cooperative();
 long long gemm_allreduce_stage_bytes(long long m, long long n, int nranks);
 int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
                           void* const* stage, void* const* out, void* const* flags, void* ctl,
-                          int rank, int nranks, const void* mc_stage, void* mc_out,
+                          int rank, int nranks, int exchange, const void* mc_stage, void* mc_out,
                           cudaStream_t stream);
 
 }  // namespace mtfc
@@ -119,7 +120,7 @@ int mtfc_gemm(const mtfc_gemm_desc* d, const void* a, const void* b, void* c, vo
     return fail(MTFC_ERR_SHAPE, "gemm: tensor-core path forced but the problem is not eligible");
   if (tc_ok && d->force_path != 2) {
     rc = gemm_tcgen05_launch(d, a, b, c, s,
-                             d->force_path == 3 ? 1 : (d->force_path == 4 ? 2 : 0));
+                             d->force_path == 3 ? 1 : (d->force_path == 4 ? 2 : 0), nullptr);
   } else {
     rc = gemm_simt_launch(d, a, b, c, s);
   }
@@ -127,7 +128,22 @@ int mtfc_gemm(const mtfc_gemm_desc* d, const void* a, const void* b, void* c, vo
   return rc;
 }
 
+int mtfc_gemm_with_progress(const mtfc_gemm_desc* d, const void* a, const void* b, void* c,
+                            uint32_t* progress, void* stream) {
+  int rc = validate_gemm(d, a, b, c);
+  if (rc != MTFC_OK) return rc;
+  if (!progress) return fail(MTFC_ERR_SHAPE, "gemm_with_progress: null progress array");
+  if (d->batch != 1 || d->m < 256 || d->n < 1 || d->k < 1 || !gemm_tcgen05_eligible(d, a, b, c))
+    return fail(MTFC_ERR_UNSUPPORTED,
+                "gemm_with_progress: needs one bf16 tensor-core GEMM of at least 256 rows");
+  rc = gemm_tcgen05_launch(d, a, b, c, static_cast<cudaStream_t>(stream), 2, progress);
+  if (rc == MTFC_OK) count_launch(1);
+  return rc;
+}
+
 int mtfc_gemm_allreduce_flag_bytes(void) { return gemm_allreduce_flag_bytes(); }
+
+int mtfc_gemm_allreduce_cooperative(void) { return gemm_allreduce_cooperative(); }
 
 int mtfc_gemm_allreduce_set_wait_ms(int ms) {
   gemm_allreduce_set_wait_ms(ms);
@@ -138,15 +154,16 @@ int64_t mtfc_gemm_allreduce_stage_bytes(int64_t m, int64_t n, int nranks) {
   return gemm_allreduce_stage_bytes(m, n, nranks);
 }
 
-int mtfc_gemm_allreduce_multimem(const mtfc_gemm_desc* d, const void* a, const void* b,
-                                 void* const* stage_ptrs, void* const* out_ptrs,
-                                 void* const* flag_ptrs, void* ctl, int rank, int nranks,
-                                 const void* stage_multicast, void* out_multicast, void* stream) {
+int mtfc_gemm_allreduce_ex(const mtfc_gemm_desc* d, const void* a, const void* b,
+                           void* const* stage_ptrs, void* const* out_ptrs, void* const* flag_ptrs,
+                           void* ctl, int rank, int nranks, int exchange,
+                           const void* stage_multicast, void* out_multicast, void* stream) {
   if (!d || !a || !b) return fail(MTFC_ERR_SHAPE, "gemm_allreduce: null argument");
   if (d->batch < 1 || d->m < 1 || d->n < 1 || d->k < 1)
     return fail(MTFC_ERR_SHAPE, "gemm_allreduce: empty problem");
   int rc = gemm_allreduce_launch(d, a, b, stage_ptrs, out_ptrs, flag_ptrs, ctl, rank, nranks,
-                                 stage_multicast, out_multicast, static_cast<cudaStream_t>(stream));
+                                 exchange, stage_multicast, out_multicast,
+                                 static_cast<cudaStream_t>(stream));
   if (rc == MTFC_OK) count_launch(1);
   return rc;
 }
@@ -154,8 +171,8 @@ int mtfc_gemm_allreduce_multimem(const mtfc_gemm_desc* d, const void* a, const v
 int mtfc_gemm_allreduce(const mtfc_gemm_desc* d, const void* a, const void* b,
                         void* const* stage_ptrs, void* const* out_ptrs, void* const* flag_ptrs,
                         void* ctl, int rank, int nranks, void* stream) {
-  return mtfc_gemm_allreduce_multimem(d, a, b, stage_ptrs, out_ptrs, flag_ptrs, ctl, rank, nranks,
-                                      nullptr, nullptr, stream);
+  return mtfc_gemm_allreduce_ex(d, a, b, stage_ptrs, out_ptrs, flag_ptrs, ctl, rank, nranks,
+                                MTFC_EXCHANGE_PUSH, nullptr, nullptr, stream);
 }
 
 }  // extern "C"

@@ -58,6 +58,11 @@ struct GemmArgs {
   int relu;
   int out_f32;
   int* status;
+  // pair kernel only, optional: progress[rb] is incremented once per epilogue warp
+  // and tile of 256-row block rb when that tile's rows have landed in memory
+  // (tiles_n * 8 increments complete a row block), for a consumer on another
+  // stream that starts on row blocks while later ones are still being multiplied
+  uint32_t* progress;
 };
 
 // Instruction descriptor for kind::f16: fp32 accumulator, bf16 A and B,
@@ -428,16 +433,25 @@ struct FusedArgs {
   int rank, nranks;
   int blocks_per_rank;
   long long wait_cycles;  // how long a wait for another rank may last
-  // Switch-reduced exchange (use_mc): every rank keeps its partial product in its own
-  // staging buffer at the output's own row offsets (part_map), and the owner of a row
-  // block reads the SUM of all ranks' copies through the staging buffers' multicast
-  // address (multimem.ld_reduce: NVSwitch adds the copies in fp32) and writes it to all
-  // ranks' outputs through the output buffers' multicast address (multimem.st).
-  int use_mc;
+  // Exchange form.
+  //   EXCHANGE_PUSH: the epilogue stores each partial tile into the owner's staging
+  //     buffer (remote TMA stores); the owner adds local copies.
+  //   EXCHANGE_PULL: every rank keeps its partial product in its OWN staging buffer at
+  //     the output's row offsets (part_map), so the epilogue never waits on NVLink; the
+  //     owner's comm warps read the other ranks' copies with plain peer loads.
+  //   EXCHANGE_MULTIMEM: partial products local as for PULL; the owner reads the SUM of
+  //     all ranks' copies through the staging buffers' multicast address
+  //     (multimem.ld_reduce: NVSwitch adds the copies in fp32) and writes it to all ranks'
+  //     outputs through the output buffers' multicast address (multimem.st).
+  int exchange;
+  const uint8_t* stage_all[MAX_RANKS];
   const uint8_t* mc_stage;
   uint8_t* mc_out;
   CUtensorMap part_map;
 };
+constexpr int EXCHANGE_PUSH = 0;
+constexpr int EXCHANGE_PULL = 1;
+constexpr int EXCHANGE_MULTIMEM = 2;
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
@@ -507,7 +521,7 @@ __device__ __forceinline__ uint4 add_bf16x8_packed(const uint4& a, const uint4& 
                     add_bf16x2(a.w, b.w));
 }
 
-// Sum of the n copies of part of a row block (src0 + s * src_stride, s < n),
+// Sum of the n copies of part of a row block (src[s], s < n; local or peer memory),
 // nvec 16-byte vectors, written to every rank's output at out_off.
 // NR = n when n is 2, 4 or 8: the loads of all copies of COMM_LOADS / NR vectors
 // are in flight together, and the sum is a balanced tree of packed bf16 additions
@@ -517,9 +531,8 @@ __device__ __forceinline__ uint4 add_bf16x8_packed(const uint4& a, const uint4& 
 // few issue slots.  NR = 1 is the general form: one copy at a time, accumulated
 // in fp32 and rounded once.
 template <int NR>
-__device__ __forceinline__ void reduce_block(const uint8_t* src0, long long src_stride,
-                                             uint8_t* const* out, long long out_off,
-                                             long long nvec, int n, int tid) {
+__device__ __forceinline__ void reduce_block(const uint8_t* const* src, uint8_t* const* out,
+                                             long long out_off, long long nvec, int n, int tid) {
   constexpr int U = NR == 1 ? COMM_UNROLL : COMM_LOADS / NR;
   for (long long v0 = tid; v0 < nvec; v0 += (long long)COMM_THREADS * U) {
     uint4 res[U];
@@ -534,7 +547,7 @@ __device__ __forceinline__ void reduce_block(const uint8_t* src0, long long src_
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const long long v = v0 + (long long)u * COMM_THREADS;
-          x[u] = v < nvec ? ld_cg_v4(src0 + s * src_stride + v * 16) : make_uint4(0u, 0u, 0u, 0u);
+          x[u] = v < nvec ? ld_cg_v4(src[s] + v * 16) : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) add_bf16x8(acc[u], x[u]);
@@ -553,7 +566,7 @@ __device__ __forceinline__ void reduce_block(const uint8_t* src0, long long src_
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const long long v = v0 + (long long)u * COMM_THREADS;
-          x[s][u] = v < nvec ? ld_cg_v4(src0 + s * src_stride + v * 16) : make_uint4(0u, 0u, 0u, 0u);
+          x[s][u] = v < nvec ? ld_cg_v4(src[s] + v * 16) : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
       for (int width = NR / 2; width >= 1; width /= 2)   // ranks (0+1)+(2+3) ..., the same on every owner
@@ -653,23 +666,30 @@ __device__ void allreduce_comm_warps(uint8_t* smem, const GemmArgs& args, const 
     const int rows = max(0, min(COMM_UNIT_ROWS, args.m - rb * 2 * BM - sub * COMM_UNIT_ROWS));
     const long long nvec = (rows * row_bytes) >> 4;
     const long long sub_off = (long long)sub * COMM_UNIT_ROWS * row_bytes;
-    const uint8_t* src0 = fa.stage + (long long)k * block_bytes + sub_off;
-    const long long src_stride = (long long)fa.blocks_per_rank * block_bytes;
     const long long out_off = (long long)rb * block_bytes + sub_off;
-    if (fa.use_mc) {
+    if (fa.exchange == EXCHANGE_MULTIMEM) {
       reduce_block_multimem(fa.mc_stage, fa.mc_out, out_off, nvec, tid);
-    } else
-    switch (n) {
-      case 2: reduce_block<2>(src0, src_stride, fa.out, out_off, nvec, n, tid); break;
-      case 4: reduce_block<4>(src0, src_stride, fa.out, out_off, nvec, n, tid); break;
-      case 8: reduce_block<8>(src0, src_stride, fa.out, out_off, nvec, n, tid); break;
-      default: reduce_block<1>(src0, src_stride, fa.out, out_off, nvec, n, tid); break;
+    } else {
+      const uint8_t* src[MAX_RANKS];
+      if (fa.exchange == EXCHANGE_PULL) {
+        // rank s's partial of this row block sits in ITS staging buffer at the output's offset
+        for (int s = 0; s < n; ++s) src[s] = fa.stage_all[s] + out_off;
+      } else {
+        // all ranks' partials were stored into this rank's staging buffer, slot [source][k]
+        const long long src_stride = (long long)fa.blocks_per_rank * block_bytes;
+        for (int s = 0; s < n; ++s) src[s] = fa.stage + (long long)k * block_bytes + sub_off + s * src_stride;
+      }
+      switch (n) {
+        case 2: reduce_block<2>(src, fa.out, out_off, nvec, n, tid); break;
+        case 4: reduce_block<4>(src, fa.out, out_off, nvec, n, tid); break;
+        case 8: reduce_block<8>(src, fa.out, out_off, nvec, n, tid); break;
+        default: reduce_block<1>(src, fa.out, out_off, nvec, n, tid); break;
+      }
     }
     // the barrier orders every thread's stores before thread 0's release, which
-    // is cumulative: one system-scope release per slice instead of 128 fences
+    // is cumulative: one system-scope release per slice, no separate fence
     comm_warps_sync();
     if (tid == 0) {
-      __threadfence_system();
       for (int p = 0; p < n; ++p) red_release_sys_add(fa.flags[p] + FLAG_DONE, 1u);
     }
   }
@@ -867,7 +887,7 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
       const CUtensorMap* dst_map = &map_c;
       int dst_row = m0 + q * 32;
       if (FUSED) {
-        if (fa->use_mc) {
+        if (fa->exchange != EXCHANGE_PUSH) {
           dst_map = &fa->part_map;   // own staging buffer, at the output's row offsets
         } else {
           dst_map = &fa->stage_map[rb % fa->nranks];
@@ -937,7 +957,7 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(tmem_empty_bar(buf), 0));
-      if (FUSED && lane == 0) {
+      if ((FUSED || args.progress) && lane == 0) {
         // Tell the owner of the row block of the tile TWO tiles back that this
         // warp's part of it has arrived (complete, not merely read out of the
         // staging buffers): its stores have had two tile times to land, so the
@@ -947,7 +967,8 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
         const int mine = store_idx - tile_first_store;
         if (older_rb >= 0) {
           bulk_wait_upto(mine + pending_stores);
-          red_release_sys_add(fa->flags[older_rb % fa->nranks] + older_rb, 1u);
+          red_release_sys_add(FUSED ? fa->flags[older_rb % fa->nranks] + older_rb
+                                    : args.progress + older_rb, 1u);
         }
         older_rb = pending_rb;
         pending_rb = rb;
@@ -955,9 +976,12 @@ __device__ __forceinline__ void pair_gemm_body(const CUtensorMap& map_a, const C
       }
     }
     if (lane == 0) tma_store_wait_all();
-    if (FUSED && lane == 0) {
-      if (older_rb >= 0) red_release_sys_add(fa->flags[older_rb % fa->nranks] + older_rb, 1u);
-      if (pending_rb >= 0) red_release_sys_add(fa->flags[pending_rb % fa->nranks] + pending_rb, 1u);
+    if ((FUSED || args.progress) && lane == 0) {
+      if (older_rb >= 0)
+        red_release_sys_add(FUSED ? fa->flags[older_rb % fa->nranks] + older_rb : args.progress + older_rb, 1u);
+      if (pending_rb >= 0)
+        red_release_sys_add(FUSED ? fa->flags[pending_rb % fa->nranks] + pending_rb
+                                  : args.progress + pending_rb, 1u);
     }
     if (!ok && lane == 0 && args.status) atomicExch(args.status, MTFC_ERR_TIMEOUT);
   }
@@ -1100,7 +1124,7 @@ int max_pair_clusters() {
 
 // cta_group: 0 = choose, 1 = single-CTA kernel, 2 = CTA-pair kernel.
 int gemm_tcgen05_launch(const mtfc_gemm_desc* d, const void* a, const void* b, void* c,
-                        cudaStream_t stream, int cta_group) {
+                        cudaStream_t stream, int cta_group, void* progress) {
   int pair_clusters = 0;
   if (cta_group != 1) pair_clusters = max_pair_clusters();
   // The pair kernel works on 256-row tiles: worth it once M fills them.
@@ -1151,6 +1175,9 @@ int gemm_tcgen05_launch(const mtfc_gemm_desc* d, const void* a, const void* b, v
   args.relu = d->epilogue == MTFC_EPILOGUE_RELU;
   args.out_f32 = out_f32 ? 1 : 0;
   args.status = device_status_word();
+  args.progress = static_cast<uint32_t*>(progress);
+  if (progress && !(use_pair && d->batch == 1))
+    return fail(MTFC_ERR_UNSUPPORTED, "gemm: progress counters need the CTA-pair kernel and batch 1");
 
   const long long num_tiles = (long long)args.tiles_m * args.tiles_n * args.batch;
   if (use_pair) {
@@ -1189,6 +1216,7 @@ int gemm_tcgen05_launch(const mtfc_gemm_desc* d, const void* a, const void* b, v
 int gemm_allreduce_flag_bytes() { return (FLAG_DONE + 1) * 4; }
 
 static long long g_peer_wait_cycles = PEER_WAIT_CYCLES_DEFAULT;
+static int g_cooperative_ok = 1, g_cooperative_launched = 0;
 
 // Limit of every wait on another rank inside the fused kernel, in milliseconds
 // at a nominal 2 GHz clock; <= 0 restores the default of about 3 s.
@@ -1238,7 +1266,7 @@ long long gemm_allreduce_stage_bytes(long long m, long long n, int nranks) {
 // address as seen from this process; `ctl` is this rank's private 16 bytes.
 int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
                           void* const* stage, void* const* out, void* const* flags, void* ctl,
-                          int rank, int nranks, const void* mc_stage, void* mc_out,
+                          int rank, int nranks, int exchange, const void* mc_stage, void* mc_out,
                           cudaStream_t stream) {
   if (nranks < 2 || nranks > MAX_RANKS || rank < 0 || rank >= nranks)
     return fail(MTFC_ERR_SHAPE, "gemm_allreduce: %d ranks (2..%d supported), rank %d", nranks,
@@ -1291,6 +1319,7 @@ int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
   args.relu = 0;
   args.out_f32 = 0;
   args.status = device_status_word();
+  args.progress = nullptr;
   if (args.tiles_m > FLAG_DONE)
     return fail(MTFC_ERR_UNSUPPORTED, "gemm_allreduce: more than %d row blocks", FLAG_DONE);
 
@@ -1305,16 +1334,23 @@ int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
     fa.out[p] = static_cast<uint8_t*>(out[p]);
     fa.flags[p] = static_cast<uint32_t*>(flags[p]);
   }
-  fa.use_mc = (mc_stage && mc_out) ? 1 : 0;
-  if (fa.use_mc) {
+  if (exchange < EXCHANGE_PUSH || exchange > EXCHANGE_MULTIMEM)
+    return fail(MTFC_ERR_SHAPE, "gemm_allreduce: unknown exchange form %d", exchange);
+  if (exchange == EXCHANGE_MULTIMEM && (!mc_stage || !mc_out))
+    return fail(MTFC_ERR_SHAPE, "gemm_allreduce: the multimem exchange needs both multicast addresses");
+  fa.exchange = exchange;
+  if (exchange == EXCHANGE_MULTIMEM) {
     if (!aligned16(mc_stage) || !aligned16(mc_out))
       return fail(MTFC_ERR_SHAPE, "gemm_allreduce: multicast addresses must be 16-byte aligned");
     fa.mc_stage = static_cast<const uint8_t*>(mc_stage);
     fa.mc_out = static_cast<uint8_t*>(mc_out);
+  }
+  if (exchange != EXCHANGE_PUSH) {
     rc = encode_map(&fa.part_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, stage[rank], d->n,
                     (long long)args.tiles_m * 2 * BM, 1, d->n, 0, 64, 32, "partial-product buffer");
     if (rc != MTFC_OK) return rc;
   }
+  for (int p = 0; p < nranks; ++p) fa.stage_all[p] = static_cast<const uint8_t*>(stage[p]);
   fa.stage = static_cast<const uint8_t*>(stage[rank]);
   fa.ctl = static_cast<uint32_t*>(ctl);
   fa.rank = rank;
@@ -1328,15 +1364,34 @@ int gemm_allreduce_launch(const mtfc_gemm_desc* d, const void* a, const void* b,
   cfg.blockDim = dim3(NUM_THREADS_FUSED, 1, 1);
   cfg.dynamicSmemBytes = SMEM2F_ALLOC;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // A cooperative launch starts only when the whole grid can be resident at once,
+  // which is what the comm warps' waits on other CTAs' products rely on; without it
+  // a kernel of another stream could keep some clusters off the GPU.  Where the
+  // driver refuses the attribute together with clusters, the plain launch (grid
+  // sized from the occupancy query above) is used from then on.
+  attr[1].id = cudaLaunchAttributeCooperative;
+  attr[1].val.cooperative = 1;
   cfg.attrs = attr;
+  g_cooperative_launched = 1;
+  if (g_cooperative_ok) {
+    cfg.numAttrs = 2;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, einsum_gemm_allreduce_2cta, map_a, map_b, args, fa);
+    if (e == cudaSuccess) return MTFC_OK;
+    (void)cudaGetLastError();
+    g_cooperative_ok = 0;
+  }
   cfg.numAttrs = 1;
   MTFC_CUDA(cudaLaunchKernelEx(&cfg, einsum_gemm_allreduce_2cta, map_a, map_b, args, fa));
   return MTFC_OK;
 }
+
+// 1: the fused kernel is launched cooperatively; 0: the driver refused that and
+// plain launches are used; -1: no launch has been made yet.
+int gemm_allreduce_cooperative() { return g_cooperative_launched ? g_cooperative_ok : -1; }
 
 }  // namespace mtfc

@@ -657,10 +657,11 @@ int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups,
   a.group_size = group_size;
   a.experts = experts;
   a.m = (int)m;
-  // 64-token tiles when they leave fewer SMs idle in the last round
-  const long long sms = sm_count();
-  const long long t128 = groups * ((group_size + 127) / 128), t64 = groups * ((group_size + 63) / 64);
-  a.tile_rows = ((t64 + sms - 1) / sms) * 64 < ((t128 + sms - 1) / sms) * 128 ? 64 : 128;
+  // 64-token tiles only when 128-token tiles would leave SMs without any tile: a
+  // half-height tile halves the bytes a CTA keeps in flight, which costs more than
+  // an uneven last round does
+  const long long t128 = groups * ((group_size + 127) / 128);
+  a.tile_rows = t128 < sm_count() ? 64 : 128;
   a.tiles_per_group = (group_size + a.tile_rows - 1) / a.tile_rows;
   a.num_tiles = groups * a.tiles_per_group;
   a.stages = gate_stages(ep);

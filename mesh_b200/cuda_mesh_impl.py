@@ -117,7 +117,7 @@ class SlicedMeshImpl(mtf.MeshImpl):
     def copy_slices_to_master(self):
       tensor = self._variable.outputs[0]
       self._variable.assign_to_master(
-          self._mesh_impl.export_to_tf_tensor(tensor, self._laid_out_tensor))
+          self._mesh_impl.export_to_tf_tensor(tensor, self._laid_out_tensor), from_slices=self)
 
   # ------------------------------------------------------------ basics
   @property
@@ -150,8 +150,35 @@ class SlicedMeshImpl(mtf.MeshImpl):
     return self.LaidOutTensor(list(self._local_pnums))
 
   def random(self, shape, tf_fn, kwargs):
-    raise NotImplementedError(
-        "random ops are not lowered; pass the noise tensor in as an imported input")
+    """A random tensor, slice by slice (placement_mesh_impl.py:307-325).
+
+    `tf_fn` is "uniform" (kwargs minval, maxval) or "normal" (mean, stddev), or a
+    callable `tf_fn(ops, slice_shape, seed=..., **kwargs)` returning a slice.
+    As in the reference, every slice's seed is derived from the operation's seed
+    and the slice's offset in the tensor, so processors that hold the same part
+    of the tensor draw the same values.  Unlike the reference, whose operation
+    seed is Python's unseeded random.random(), the seed here is `kwargs["seed"]`
+    (the RandomOperation passes one derived from its name): runs repeat."""
+    import hashlib
+    kwargs = dict(kwargs)
+    op_seed = kwargs.pop("seed", 0)
+    dtype = kwargs.pop("dtype", mtf.float32)
+    slice_shape = self.slice_shape(shape)
+
+    def my_fn(pnum):
+      ops = self._ops_for(pnum)
+      text = "%s,%s" % (op_seed, self.slice_begin(shape, pnum))
+      seed = int.from_bytes(hashlib.sha256(text.encode()).digest()[:8], "little")
+      if callable(tf_fn):
+        return tf_fn(ops, slice_shape, seed=seed, dtype=dtype, **kwargs)
+      if tf_fn == "uniform":
+        return ops.random(slice_shape, "uniform", seed, dtype,
+                          float(kwargs.get("minval", 0.0)), float(kwargs.get("maxval", 1.0)))
+      if tf_fn == "normal":
+        return ops.random(slice_shape, "normal", seed, dtype,
+                          float(kwargs.get("mean", 0.0)), float(kwargs.get("stddev", 1.0)))
+      raise ValueError("unknown random function %r" % (tf_fn,))
+    return self.slicewise(my_fn, self.laid_out_pnum())
 
   # ------------------------------------------------------------ import/export
   def import_tf_tensor(self, x, tf_x):
@@ -198,12 +225,10 @@ class SlicedMeshImpl(mtf.MeshImpl):
       return self._dist_allreduce(x, mesh_axes, reduction_fn_string, donate)
     name = {"SUM": "add", "MAX": "maximum", "MIN": "minimum"}[reduction_fn_string]
 
-    def collective(slices, pnums):
+    def chain(ops, local):
       # (x0 + ... + x_lc) + (x_rc + ... + x_{n-1}), as the reference's
       # single-shard chain (placement_mesh_impl.py:378-397)
-      n = len(slices)
-      ops = self._ops_for(pnums[0])
-      local = [self._move(s, pnums[0]) for s in slices]
+      n = len(local)
       left_center = n // 2 - 1 if n % 2 == 0 else n // 2
       left = local[0]
       for i in range(1, left_center + 1):
@@ -211,7 +236,30 @@ class SlicedMeshImpl(mtf.MeshImpl):
       right = local[n - 1]
       for i in reversed(range(left_center + 1, n - 1)):
         right = ops.binary(name, local[i], right)
-      total = ops.binary(name, left, right) if n > 1 else left
+      return ops.binary(name, left, right) if n > 1 else left
+
+    def collective(slices, pnums):
+      n = len(slices)
+      ops = self._ops_for(pnums[0])
+      local = [self._move(s, pnums[0]) for s in slices]
+      size = 1
+      for d in local[0].shape:
+        size *= d
+      if n > 1 and size >= 1024 and size % n == 0:
+        # the reference's sharded ring (placement_mesh_impl.py:407-455): the flat slice
+        # is cut in n shards and shard s is reduced over the member list rotated right
+        # by s, so the association order differs from shard to shard
+        flat = [ops.reshape(t, [size]) for t in local]
+        shard = size // n
+        parts = []
+        for sh in range(n):
+          members = [ops.slice(t, [sh * shard], [shard]) for t in flat]
+          k = sh % n
+          rotated = members[-k:] + members[:-k] if k else members
+          parts.append(chain(ops, rotated))
+        total = ops.reshape(ops.concat(parts, 0), local[0].shape)
+      else:
+        total = chain(ops, local)
       return [self._move(total, p) for p in pnums]
     return self._local_groups(x, mesh_axes, collective)
 
@@ -402,7 +450,15 @@ class SlicedMeshImpl(mtf.MeshImpl):
 class _PeerWorkspace(object):
   """Buffers of one fused einsum+allreduce shape (see CudaMeshImpl._peer_workspace)."""
   __slots__ = ("tensors", "handles", "out_tensor", "ctl", "stage_ptrs", "out_ptrs", "flag_ptrs",
-               "rank", "nranks", "mc_stage", "mc_out")
+               "rank", "nranks", "mc_stage", "mc_out", "exchange")
+
+
+class _PipelineWorkspace(object):
+  """Buffers, counters and the communication stream of one pipelined
+  einsum+allreduce shape (see CudaMeshImpl._einsum_allreduce_pipelined)."""
+  __slots__ = ("part", "recv", "out", "flags", "progress", "epochs", "handles", "peer_recv",
+               "peer_out", "peer_flag_ptrs", "stream", "rank", "nranks", "chunks", "blocks_per_chunk",
+               "part_rows", "tiles_n")
 
 
 class _PendingAllreduce(object):
@@ -599,9 +655,8 @@ class CudaMeshImpl(SlicedMeshImpl):
   FUSED_MAX_BYTES = 128 << 20
   # largest group the fused kernel is used for (groups of 2 and 4 have run on
   # hardware; MTFC_FUSED_ALLREDUCE_MAX_RANKS=8 opens groups of eight)
-  # let the NVSwitch reduce and broadcast (multimem) when the buffers have multicast
-  # addresses; MTFC_FUSED_MULTIMEM=0 keeps the exchange on plain peer stores
-  FUSED_MULTIMEM = os.environ.get("MTFC_FUSED_MULTIMEM", "1") == "1"
+  # exchange form of the fused kernel: auto | push | pull | multimem
+  FUSED_EXCHANGE = os.environ.get("MTFC_FUSED_EXCHANGE", "auto")
   FUSED_MAX_RANKS = int(os.environ.get("MTFC_FUSED_ALLREDUCE_MAX_RANKS", "4"))
 
   def einsum_allreduce(self, equation, inputs, mesh_axes):
@@ -638,6 +693,10 @@ class CudaMeshImpl(SlicedMeshImpl):
     pg, members = self._group(mesh_axes)
     sizes = dict(zip(ta, a.shape))
     sizes.update(zip(tb, b.shape))
+    if self.PIPELINED_ALLREDUCE and 2 <= len(members) <= 8 and a.dtype.name == "bfloat16":
+      piped = self._einsum_allreduce_pipelined(ops, equation, a, b, pg, members, pnum)
+      if piped is not None:
+        return _PendingAllreduce(self, piped, [])
     if (self.FUSED_ALLREDUCE and 2 <= len(members) <= self.FUSED_MAX_RANKS
         and a.dtype.name == "bfloat16"):
       fused = self._einsum_allreduce_fused(ops, equation, a, b, pg, members, pnum)
@@ -657,6 +716,152 @@ class CudaMeshImpl(SlicedMeshImpl):
                                    op=dist.ReduceOp.SUM, group=pg, async_op=True))
     return _PendingAllreduce(self, out, works)
 
+  # GEMM on the compute stream, exchange by the copy engines on a second stream
+  # (mtfc_gemm_with_progress and friends); MTFC_PIPELINED_ALLREDUCE=0 switches it off,
+  # the single-kernel form (FUSED_ALLREDUCE) is then tried
+  PIPELINED_ALLREDUCE = os.environ.get("MTFC_PIPELINED_ALLREDUCE", "1") == "1"
+  PIPELINE_MIN_BYTES = 4 << 20
+  PIPELINE_MAX_CHUNKS = 8
+
+  def _einsum_allreduce_pipelined(self, ops, equation, a, b, pg, members, pnum):
+    """The einsum and its SUM allreduce over `members` with the exchange on the copy
+    engines, or None when the contraction does not qualify (nothing launched then).
+
+    The product is ONE launch of the CTA-pair GEMM into a local buffer of partial
+    sums; it counts finished 256-row blocks.  On a second stream, chunk by chunk of
+    row blocks: wait for the chunk's blocks (a small polling kernel), push the part
+    of the chunk each other rank owns into that rank's receive buffer (peer copies:
+    copy engines, which take nothing from the SMs and overlap the GEMM fully), tell
+    the peers, wait for their parts, add the n copies of the own part (fp32
+    accumulation, one rounding), push the sum into every rank's output buffer, tell
+    the peers.  The chunk's exchange overlaps the multiplication of the later
+    chunks; after the last GEMM tile only the last chunk's exchange remains.  Per
+    direction and GPU 2 (n-1)/n times the output crosses NVLink, as in a ring
+    allreduce.  Every rank receives the same bits (each part is summed once, by its
+    owner).  All waits are bounded."""
+    import ctypes
+    import torch
+    from mesh_b200 import _native as nat
+    from mesh_b200.device_ops import HookDeclined
+    lib = nat.lib()
+    n_ranks = len(members)
+
+    def hook(desc, a_ptr, b_ptr, stored_shape):
+      m, n = int(desc.m), int(desc.n)
+      nbytes = m * n * 2
+      if m % 256 != 0 or n % 8 != 0 or nbytes < self.PIPELINE_MIN_BYTES or (m // 256) % n_ranks != 0:
+        return None
+      ws = self._pipeline_workspace(pg, members, pnum, m, n)
+      if ws is None:
+        return None
+      main = torch.cuda.current_stream()
+      comm = ws.stream
+      fork = torch.cuda.Event()
+      fork.record(main)
+      result = torch.empty(m * n, dtype=torch.bfloat16, device=ws.part.device)
+      c_desc = nat.GemmDesc()
+      ctypes.memmove(ctypes.byref(c_desc), ctypes.byref(desc), ctypes.sizeof(nat.GemmDesc))
+      nat.check(lib.mtfc_gemm_with_progress(
+          ctypes.byref(c_desc), ctypes.c_void_p(a_ptr), ctypes.c_void_p(b_ptr),
+          ctypes.c_void_p(ws.part.data_ptr()), ctypes.c_void_p(ws.progress.data_ptr()),
+          ctypes.c_void_p(main.cuda_stream)))
+      me, C, bpc, prow = ws.rank, ws.chunks, ws.blocks_per_chunk, ws.part_rows
+      others = [r for r in range(n_ranks) if r != me]
+      part2d = ws.part.view(m, n)
+      out2d = ws.out.view(m, n)
+      comm.wait_event(fork)
+      with torch.cuda.stream(comm):
+        cs = ctypes.c_void_p(comm.cuda_stream)
+        flags_ptr, epochs_ptr = ws.flags.data_ptr(), ws.epochs.data_ptr()
+        for c in range(C):
+          row0 = c * bpc * 256
+          nat.check(lib.mtfc_wait_counters(ctypes.c_void_p(ws.progress.data_ptr() + 4 * c * bpc), bpc,
+                                           8 * ws.tiles_n, ctypes.c_void_p(epochs_ptr + 4 * (C + 1 + c)), cs))
+          for r in others:     # reduce-scatter: my partial of rank r's part goes to rank r
+            ws.peer_recv[r][me, c].copy_(part2d[row0 + r * prow:row0 + (r + 1) * prow], non_blocking=True)
+          nat.check(lib.mtfc_signal_peers(ws.peer_flag_ptrs, len(others), c, cs))
+          nat.check(lib.mtfc_wait_counters(ctypes.c_void_p(flags_ptr + 4 * c), 1, n_ranks - 1,
+                                           ctypes.c_void_p(epochs_ptr + 4 * c), cs))
+          mine = slice(row0 + me * prow, row0 + (me + 1) * prow)
+          srcs = (ctypes.c_void_p * n_ranks)(*[
+              ctypes.c_void_p(part2d[mine].data_ptr() if r == me else ws.recv[r, c].data_ptr())
+              for r in range(n_ranks)])
+          nat.check(lib.mtfc_add_n_bf16(srcs, n_ranks, ctypes.c_void_p(out2d[mine].data_ptr()),
+                                        prow * n, cs))
+          for r in others:     # allgather: my sum goes to every rank's output
+            ws.peer_out[r][mine].copy_(out2d[mine], non_blocking=True)
+          nat.check(lib.mtfc_signal_peers(ws.peer_flag_ptrs, len(others), C + c, cs))
+        nat.check(lib.mtfc_wait_counters(ctypes.c_void_p(flags_ptr + 4 * C), C, n_ranks - 1,
+                                         ctypes.c_void_p(epochs_ptr + 4 * C), cs))
+        # the buffers serve the next contraction of this shape: hand back a copy
+        result.copy_(ws.out, non_blocking=True)
+      main.wait_stream(comm)
+      return self._device_array(result, stored_shape, a.dtype)
+    try:
+      return ops.einsum(equation, a, b, gemm_hook=hook)
+    except HookDeclined:
+      return None
+
+  def _pipeline_workspace(self, pg, members, pnum, m, n):
+    """Receive / output / counter buffers (peer-mapped) and the local partial-sum
+    buffer for an [m, n] bf16 GEMM allreduced over `members`; created collectively on
+    first use.  None when symmetric memory is unavailable."""
+    import ctypes
+    import torch
+    import torch.distributed as dist
+    key = (tuple(members), m, n)
+    if not hasattr(self, "_pipe_ws"):
+      self._pipe_ws = {}
+    if key in self._pipe_ws:
+      return self._pipe_ws[key]
+    ws = None
+    try:
+      import torch.distributed._symmetric_memory as symm
+      dev = torch.device("cuda", torch.cuda.current_device())
+      n_ranks = len(members)
+      me = members.index(pnum)
+      num_rb = m // 256
+      per_rank = num_rb // n_ranks
+      chunks = max(c for c in range(1, self.PIPELINE_MAX_CHUNKS + 1) if per_rank % c == 0)
+      bpc = num_rb // chunks
+      prow = bpc * 256 // n_ranks
+
+      def alloc(count, dtype):
+        t = symm.empty(count, dtype=dtype, device=dev)
+        return t, symm.rendezvous(t, pg)
+      recv_t, recv_h = alloc(m * n, torch.bfloat16)       # [source rank, chunk, part rows, n]
+      out_t, out_h = alloc(m * n, torch.bfloat16)
+      flag_t, flag_h = alloc(2 * chunks, torch.int32)
+      flag_t.zero_()
+      if int(recv_h.rank) != me or int(recv_h.world_size) != n_ranks:
+        raise RuntimeError("symmetric-memory rank %d/%d does not match mesh group position %d/%d"
+                           % (recv_h.rank, recv_h.world_size, me, n_ranks))
+      ws = _PipelineWorkspace()
+      ws.part = torch.empty(m * n, dtype=torch.bfloat16, device=dev)
+      ws.recv = recv_t.view(n_ranks, chunks, prow, n)
+      ws.out = out_t
+      ws.flags = flag_t
+      ws.progress = torch.zeros(num_rb, dtype=torch.int32, device=dev)
+      ws.epochs = torch.zeros(2 * chunks + 2, dtype=torch.int32, device=dev)
+      ws.handles = (recv_h, out_h, flag_h)
+      ws.peer_recv = {r: recv_h.get_buffer(r, (n_ranks, chunks, prow, n), torch.bfloat16)
+                      for r in range(n_ranks) if r != me}
+      ws.peer_out = {r: out_h.get_buffer(r, (m, n), torch.bfloat16) for r in range(n_ranks) if r != me}
+      peers = [int(flag_h.buffer_ptrs[r]) for r in range(n_ranks) if r != me]
+      ws.peer_flag_ptrs = (ctypes.c_void_p * len(peers))(*[ctypes.c_void_p(p) for p in peers])
+      ws.stream = torch.cuda.Stream(device=dev)
+      ws.rank, ws.nranks = me, n_ranks
+      ws.chunks, ws.blocks_per_chunk, ws.part_rows = chunks, bpc, prow
+      ws.tiles_n = (n + 255) // 256
+      torch.cuda.synchronize()
+      dist.barrier(group=pg)
+    except Exception as e:  # pylint: disable=broad-except
+      import warnings
+      warnings.warn("peer memory for the pipelined einsum+allreduce unavailable (%r)" % (e,))
+      ws = None
+    self._pipe_ws[key] = ws
+    return ws
+
   def _einsum_allreduce_fused(self, ops, equation, a, b, pg, members, pnum):
     """The einsum and its allreduce over `members` as one kernel launch per
     rank, or None when the contraction is not a single bf16 GEMM (then nothing
@@ -673,10 +878,10 @@ class CudaMeshImpl(SlicedMeshImpl):
       ws = self._peer_workspace(pg, members, pnum, int(desc.m), int(desc.n))
       if ws is None:
         return None
-      nat.check(lib.mtfc_gemm_allreduce_multimem(
+      nat.check(lib.mtfc_gemm_allreduce_ex(
           ctypes.byref(desc), ctypes.c_void_p(a_ptr), ctypes.c_void_p(b_ptr), ws.stage_ptrs,
           ws.out_ptrs, ws.flag_ptrs, ctypes.c_void_p(ws.ctl.data_ptr()), ws.rank, ws.nranks,
-          ctypes.c_void_p(ws.mc_stage), ctypes.c_void_p(ws.mc_out),
+          ws.exchange, ctypes.c_void_p(ws.mc_stage), ctypes.c_void_p(ws.mc_out),
           ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
       # the workspace is reused by the next contraction of this size: hand back a copy
       flat = ws.out_tensor[:nbytes].view(torch.bfloat16).clone()
@@ -730,13 +935,22 @@ class CudaMeshImpl(SlicedMeshImpl):
       ws.ctl = ctl
       ws.stage_ptrs, ws.out_ptrs, ws.flag_ptrs = ptr_array(part_h), ptr_array(out_h), ptr_array(flag_h)
       ws.rank, ws.nranks = members.index(pnum), len(members)
-      # NVSwitch multicast addresses of the two buffers (0 where the fabric has none):
-      # with both, the kernel lets the switch add and broadcast
+      # How the partial products travel (see mtfc_gemm_allreduce_ex).  "auto": through
+      # the switch's multicast addresses (multimem) for groups of four and more where
+      # the fabric offers them - fewer bytes per link from four ranks up - else by
+      # peer loads from the owners' side ("pull"), which keeps NVLink out of the
+      # GEMM's epilogue.
       ws.mc_stage = ws.mc_out = 0
-      if self.FUSED_MULTIMEM:
-        mc_s, mc_o = int(part_h.multicast_ptr or 0), int(out_h.multicast_ptr or 0)
-        if mc_s and mc_o:
-          ws.mc_stage, ws.mc_out = mc_s, mc_o
+      mc_s, mc_o = int(part_h.multicast_ptr or 0), int(out_h.multicast_ptr or 0)
+      form = self.FUSED_EXCHANGE
+      if form == "auto":
+        form = "multimem" if (len(members) >= 4 and mc_s and mc_o) else "pull"
+      if form == "multimem" and not (mc_s and mc_o):
+        form = "pull"
+      if form == "multimem":
+        ws.mc_stage, ws.mc_out = mc_s, mc_o
+      ws.exchange = {"push": nat.EXCHANGE_PUSH, "pull": nat.EXCHANGE_PULL,
+                     "multimem": nat.EXCHANGE_MULTIMEM}[form]
       if int(part_h.rank) != ws.rank or int(part_h.world_size) != ws.nranks:
         raise RuntimeError("symmetric-memory rank %d/%d does not match mesh group position %d/%d"
                            % (part_h.rank, part_h.world_size, ws.rank, ws.nranks))
@@ -840,4 +1054,5 @@ class CudaMeshImpl(SlicedMeshImpl):
       # a fused einsum+allreduce whose wait ran out leaves its flags and epoch
       # counters out of step with the other ranks: never reuse those buffers
       self._peer_ws = {}
+      self._pipe_ws = {}
       raise

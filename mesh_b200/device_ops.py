@@ -273,6 +273,14 @@ class DeviceOps(object):
                ctypes.c_float(0.0), ctypes.c_float(1.0), self._stream())
     return out
 
+  def random(self, shape, kind, seed, dtype, a, b):
+    """Philox-keyed fill: kind "uniform" in [a, b) or "normal" with mean a, stddev b."""
+    out = self._empty(shape, dtype)
+    self._call(self._lib.mtfc_random, ctypes.c_void_p(out.ptr), _CODE[dtype.name], out.size,
+               1 if kind == "normal" else 0, ctypes.c_uint64(seed & 0xFFFFFFFFFFFFFFFF),
+               ctypes.c_float(a), ctypes.c_float(b), self._stream())
+    return out
+
   # ---------------------------------------------------------------- maps
   def _unary_code(self, code, x, out_dtype):
     x = self.contiguous(x)
@@ -626,6 +634,56 @@ class DeviceOps(object):
         self.reduce("SUM", self.unary("exp", shifted), [nd - 1]), nd - 1)), mx)
     w = self.cast(self.unary("exp", self.binary("sub", logits, lse)), v.dtype)
     return self.einsum("%sxy,%sye->%sxe" % (letters, letters, letters), w, v)
+
+  # ---------------------------------------------------------------- block rows
+  def norm_rows(self, x, scale, bias, epsilon, centered):
+    """Layer norm (centered) or RMS norm over the last axis; scale / bias [cols] or None."""
+    x = self.contiguous(x)
+    cols = x.shape[-1]
+    rows = x.size // max(1, cols)
+    out = self._empty(x.shape, x.dtype)
+    sp = ctypes.c_void_p(self.contiguous(scale).ptr) if scale is not None else ctypes.c_void_p(0)
+    bp = ctypes.c_void_p(self.contiguous(bias).ptr) if bias is not None else ctypes.c_void_p(0)
+    self._call(self._lib.mtfc_norm_rows, ctypes.c_void_p(x.ptr), sp, bp, ctypes.c_void_p(out.ptr),
+               _CODE[x.dtype.name], rows, cols, ctypes.c_float(epsilon), 1 if centered else 0,
+               self._stream())
+    return out
+
+  def gather_rows(self, table, indices, first_row):
+    """out[..., :] = table[indices[...] - first_row, :] (zeros outside the table):
+    table [rows, *rest], indices any shape -> indices.shape + rest."""
+    table, indices = self.contiguous(table), self.contiguous(indices)
+    rest = tuple(table.shape[1:])
+    row_bytes = _volume(rest) * table.dtype.itemsize
+    out = self._empty(tuple(indices.shape) + rest, table.dtype)
+    if row_bytes % 16 != 0:
+      raise ValueError("gather_rows: rows of %d bytes are not a multiple of 16" % row_bytes)
+    self._call(self._lib.mtfc_gather_rows, ctypes.c_void_p(table.ptr), ctypes.c_void_p(indices.ptr),
+               ctypes.c_void_p(out.ptr), indices.size, table.shape[0], first_row, row_bytes,
+               self._stream())
+    return out
+
+  def xent_stats(self, logits, targets, first_col):
+    """Per row of the last axis: (max, sum exp(x - max), logit of the target or 0)."""
+    logits, targets = self.contiguous(logits), self.contiguous(targets)
+    cols = logits.shape[-1]
+    lead = tuple(logits.shape[:-1])
+    outs = [self._empty(lead, G.float32) for _ in range(3)]
+    self._call(self._lib.mtfc_xent_stats, ctypes.c_void_p(logits.ptr), _CODE[logits.dtype.name],
+               ctypes.c_void_p(targets.ptr), _volume(lead), cols, first_col,
+               *[ctypes.c_void_p(o.ptr) for o in outs], self._stream())
+    return tuple(outs)
+
+  def xent_grad(self, logits, targets, log_z, dloss, z_loss, first_col):
+    logits, targets = self.contiguous(logits), self.contiguous(targets)
+    log_z, dloss = self.contiguous(log_z), self.contiguous(dloss)
+    cols = logits.shape[-1]
+    out = self._empty(logits.shape, logits.dtype)
+    self._call(self._lib.mtfc_xent_grad, ctypes.c_void_p(logits.ptr), _CODE[logits.dtype.name],
+               ctypes.c_void_p(targets.ptr), ctypes.c_void_p(log_z.ptr), ctypes.c_void_p(dloss.ptr),
+               ctypes.c_float(z_loss), logits.size // max(1, cols), cols, first_col,
+               ctypes.c_void_p(out.ptr), self._stream())
+    return out
 
   # ---------------------------------------------------------------- fused MoE
   def moe_gate_logits(self, x, w):

@@ -16,4 +16,4 @@ from mesh_b200.mtf.ops import *  # noqa: F401,F403
 from mesh_b200.mtf.ops import mtf_range as range  # noqa: A001
 from mesh_b200.mtf.shapes import (Dimension, Shape, convert_to_dimension, convert_to_shape,
                                   list_product, parse_pairs, shape_union)
-from mesh_b200.mtf import layers, moe  # noqa: E402
+from mesh_b200.mtf import layers, moe, optimize  # noqa: E402

@@ -206,6 +206,19 @@ class Lowering(object):
 
   export = export_to_tf_tensor
 
+  def copy_slices_to_masters(self, variables=None):
+    """Device slices -> host masters for every lowered variable (or the given
+    ones), mesh_tensorflow/ops.py:730-737."""
+    for var, laid_out_variable in self.variables.items():
+      if variables is None or var in variables:
+        laid_out_variable.copy_slices_to_master()
+
+  def copy_masters_to_slices(self, variables=None):
+    """Host masters -> device slices (mesh_tensorflow/ops.py:739-745)."""
+    for var, laid_out_variable in self.variables.items():
+      if variables is None or var in variables:
+        laid_out_variable.copy_master_to_slices()
+
   def lowered_operation(self, op):
     return self.operations[op]
 

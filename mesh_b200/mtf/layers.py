@@ -121,6 +121,260 @@ def dense_relu_dense(x, hidden_channels, is_training=False, dropout=0.0, weights
                weights=weights, name="wo")
 
 
+# ------------------------------------------------------- norms, embedding, loss
+class NormOperation(mtf.Operation):
+  """Layer norm (`centered`) or RMS norm over `dim` as one operation.
+
+  When `dim` is the last dim of x and not split over the mesh, a slice's rows
+  are normalised by one kernel (fp32 statistics, one rounding at the store);
+  otherwise the statistics are formed with slice reductions and an allreduce
+  over the mesh axis `dim` is split over, in the reference's order of
+  operations (layers.py:968-979, transformer/transformer.py:516)."""
+
+  def __init__(self, x, scale, bias, dim, epsilon, centered, name=None):
+    inputs = [x] + [t for t in (scale, bias) if t is not None]
+    super().__init__(inputs, name=name or ("layer_norm" if centered else "rms_norm"))
+    self._dim, self._epsilon, self._centered = dim, epsilon, centered
+    self._has_scale, self._has_bias = scale is not None, bias is not None
+    self._outputs = [mtf.Tensor(self, x.shape, x.dtype)]
+
+  def _unpack(self, tensors):
+    it = iter(tensors[1:])
+    return tensors[0], (next(it) if self._has_scale else None), (next(it) if self._has_bias else None)
+
+  def gradient(self, grad_ys):
+    dim, eps, centered = self._dim, self._epsilon, self._centered
+
+    def chain(*tensors):
+      x, scale, bias = self._unpack(list(tensors))
+      return [_norm_chain(x, dim, eps, centered, scale, bias)]
+    return mtf.gradients_by_recompute(self.inputs, chain, grad_ys)
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    ops = impl.slice_ops
+    x = self.inputs[0]
+    dim, eps, centered = self._dim, self._epsilon, self._centered
+    axis = x.shape.dims.index(dim)
+    mesh_axis = impl.tensor_dimension_to_mesh_axis(dim)
+    lowered = [lowering.tensors[t] for t in self.inputs]
+    has_scale, has_bias = self._has_scale, self._has_bias
+
+    def split_args(args):
+      it = iter(args[1:])
+      return args[0], (next(it) if has_scale else None), (next(it) if has_bias else None)
+    if mesh_axis is None and axis == x.shape.ndims - 1:
+      def fn(*args):
+        xs, sc, bi = split_args(args)
+        return ops.norm_rows(xs, sc, bi, eps, centered)
+      lowering.set_tensor_lowering(self.outputs[0], impl.slicewise(fn, *lowered))
+      return
+    # general layout: partial sums per slice, completed over the mesh axis
+    nd = x.shape.ndims
+    inv = 1.0 / float(dim.size)
+
+    def mean_over_dim(values):
+      part = impl.slicewise(lambda v: ops.expand_dims(ops.reduce("SUM", v, [axis]), axis), values)
+      if mesh_axis is not None:
+        part = impl.allreduce(part, [mesh_axis], "SUM")
+      return impl.slicewise(lambda v: ops.binary("multiply", v, inv), part)
+    xs = lowered[0]
+    if centered:
+      mean = mean_over_dim(xs)
+      xs = impl.slicewise(lambda v, m: ops.binary("sub", v, m), xs, mean)
+    var = mean_over_dim(impl.slicewise(lambda v: ops.unary("square", v), xs))
+
+    def finish(v, variance, *rest):
+      _, sc, bi = split_args((None,) + rest)
+      out = ops.binary("multiply", v, ops.unary("rsqrt", ops.binary("add", variance, eps)))
+      shape = [1] * nd
+      if sc is not None:
+        shape[axis] = ops.shape(sc)[0]
+        out = ops.binary("multiply", out, ops.reshape(sc, shape))
+      if bi is not None:
+        shape[axis] = ops.shape(bi)[0]
+        out = ops.binary("add", out, ops.reshape(bi, shape))
+      return out
+    lowering.set_tensor_lowering(self.outputs[0], impl.slicewise(finish, xs, var, *lowered[1:]))
+
+
+def _norm_chain(x, dim, epsilon, centered, scale, bias):
+  """The reference's op chains (layers.py:968-979; transformer.py:516)."""
+  reduced_shape = x.shape - dim
+  if centered:
+    mean = mtf.reduce_mean(x, output_shape=reduced_shape)
+    variance = mtf.reduce_mean(mtf.square(x - mean), output_shape=reduced_shape)
+    y = (x - mean) * mtf.rsqrt(variance + epsilon)
+  else:
+    variance = mtf.reduce_mean(mtf.square(x), output_shape=reduced_shape)
+    y = x * mtf.rsqrt(variance + epsilon)
+  if scale is not None:
+    y = y * scale
+  if bias is not None:
+    y = y + bias
+  return y
+
+
+def layer_norm(x, dim, epsilon=1e-6, scale=None, bias=None, fused=True, name="layer_norm"):
+  """Layer normalisation over `dim` (mesh_tensorflow/layers.py:950-979): scale and
+  bias are tensors of shape [dim] (the reference creates them as variables
+  initialised to ones / zeros; None leaves the factor / offset out).  fused=False
+  builds the reference's op chain instead of the single operation."""
+  if not fused:
+    return _norm_chain(x, dim, epsilon, True, scale, bias)
+  return NormOperation(x, scale, bias, dim, epsilon, True, name=name).outputs[0]
+
+
+def rms_norm(x, dim, epsilon=1e-6, scale=None, fused=True, name="rms_norm"):
+  """x * rsqrt(mean(x^2) + epsilon) * scale (transformer/transformer.py:493-516)."""
+  if not fused:
+    return _norm_chain(x, dim, epsilon, False, scale, None)
+  return NormOperation(x, scale, None, dim, epsilon, False, name=name).outputs[0]
+
+
+def embedding_weights(mesh, vocab_dim, output_dim, dtype, weights, ensemble_dim=None, name="embedding"):
+  """[ensemble dims,] vocab x output table ~ N(0, 1) (mesh_tensorflow/layers.py:2049-2066)."""
+  ensemble = [] if not ensemble_dim else (ensemble_dim if isinstance(ensemble_dim, list) else [ensemble_dim])
+  return weights.normal(mesh, Shape(ensemble + [vocab_dim, output_dim]), 1.0, dtype, name=name)
+
+
+def embedding(indices, vocab_dim, output_dim, dtype, weights=None, table=None, name="embedding"):
+  """Embedding lookup (mesh_tensorflow/layers.py:2069-2073): a row gather of the
+  [vocab, output] table; `table` passes an existing one."""
+  if table is None:
+    table = embedding_weights(indices.mesh, vocab_dim, output_dim, dtype, weights, name=name)
+  return mtf.gather(table, indices, vocab_dim)
+
+
+class SoftmaxCrossEntropyOperation(mtf.Operation):
+  """Per-example softmax loss with hard targets as one pass over the logits.
+
+  Outputs: loss [logits.shape - vocab_dim] in the logits' dtype, and log_z in
+  float32 (kept for the backward pass).  Each slice of a mesh-split vocabulary
+  yields its row max, its sum of exp(x - max) and the target's logit if it holds
+  the target column; an allreduce MAX and two allreduce SUMs over the vocabulary's
+  mesh axis complete them - the collectives the reference's reduce_logsumexp
+  and reduce_sum(log_softmax * one_hot) perform (layers.py:1109-1116,
+  ops.py:5493-5520) on tensors a vocabulary-size smaller."""
+
+  def __init__(self, logits, targets, vocab_dim, z_loss, name=None):
+    super().__init__([logits, targets], name=name or "softmax_cross_entropy")
+    self._vocab_dim, self._z_loss = vocab_dim, z_loss
+    out_shape = logits.shape - vocab_dim
+    self._outputs = [mtf.Tensor(self, out_shape, logits.dtype, index=0),
+                     mtf.Tensor(self, out_shape, G.float32, index=1)]
+
+  def gradient(self, grad_ys):
+    logits, targets = self.inputs
+    if grad_ys[0] is None:
+      return [None, None]
+    dlogits = SoftmaxCrossEntropyGradOperation(
+        logits, targets, self.outputs[1], mtf.cast(grad_ys[0], G.float32), self._vocab_dim,
+        self._z_loss).outputs[0]
+    return [dlogits, None]
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    ops = impl.slice_ops
+    logits, targets = self.inputs
+    vocab, z = self._vocab_dim, self._z_loss
+    axis = logits.shape.dims.index(vocab)
+    nd = logits.shape.ndims
+    mesh_axis = impl.tensor_dimension_to_mesh_axis(vocab)
+    cols_here = impl.slice_shape(logits.shape)[axis]
+    # targets' dims in the order the logits have them (minus the vocabulary)
+    t_perm = [targets.shape.dims.index(d) for d in logits.shape.dims if d != vocab]
+
+    def stats(x, t, pcoord):
+      if axis != nd - 1:
+        x = ops.transpose(x, [i for i in range(nd) if i != axis] + [axis])
+      if t_perm != list(range(len(t_perm))):
+        t = ops.transpose(t, t_perm)
+      return ops.xent_stats(x, t, int(pcoord) * cols_here)
+    pcoord = impl.laid_out_pcoord(mesh_axis) if mesh_axis is not None else 0
+    m, s, picked = impl.slicewise(stats, lowering.tensors[logits], lowering.tensors[targets], pcoord)
+    if mesh_axis is not None:
+      gmax = impl.allreduce(m, [mesh_axis], "MAX")
+      s = impl.slicewise(lambda sv, mv, gv: ops.binary("multiply", sv, ops.unary("exp", ops.binary("sub", mv, gv))),
+                         s, m, gmax)
+      s = impl.allreduce(s, [mesh_axis], "SUM")
+      picked = impl.allreduce(picked, [mesh_axis], "SUM")
+      m = gmax
+    log_z = impl.slicewise(lambda sv, mv: ops.binary("add", ops.unary("log", sv), mv), s, m)
+
+    def loss_fn(lz, pk):
+      out = ops.binary("sub", lz, pk)
+      if z != 0:
+        out = ops.binary("add", out, ops.binary("multiply", ops.unary("square", lz), z))
+      return ops.cast(out, logits.dtype)
+    lowering.set_tensor_lowering(self.outputs[0], impl.slicewise(loss_fn, log_z, picked))
+    lowering.set_tensor_lowering(self.outputs[1], log_z)
+
+
+class SoftmaxCrossEntropyGradOperation(mtf.Operation):
+  """dlogits = dloss * ((1 + 2 z_loss log_z) softmax(logits) - one_hot(targets))."""
+
+  def __init__(self, logits, targets, log_z, dloss, vocab_dim, z_loss, name=None):
+    super().__init__([logits, targets, log_z, dloss], name=name or "softmax_cross_entropy_grad")
+    self._vocab_dim, self._z_loss = vocab_dim, z_loss
+    self._outputs = [mtf.Tensor(self, logits.shape, logits.dtype)]
+
+  @property
+  def has_gradient(self):
+    return False
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    ops = impl.slice_ops
+    logits = self.inputs[0]
+    vocab, z = self._vocab_dim, self._z_loss
+    axis = logits.shape.dims.index(vocab)
+    nd = logits.shape.ndims
+    if axis != nd - 1:
+      raise NotImplementedError("cross-entropy gradient needs the vocabulary as the last dim of the logits")
+    mesh_axis = impl.tensor_dimension_to_mesh_axis(vocab)
+    cols_here = impl.slice_shape(logits.shape)[axis]
+    pcoord = impl.laid_out_pcoord(mesh_axis) if mesh_axis is not None else 0
+    fn = lambda x, t, lz, dl, pc: ops.xent_grad(x, t, lz, dl, z, int(pc) * cols_here)
+    lowering.set_tensor_lowering(
+        self.outputs[0], impl.slicewise(fn, *[lowering.tensors[t] for t in self.inputs], pcoord))
+
+
+def softmax_cross_entropy_with_logits(logits, targets, vocab_dim, z_loss=0.0, fused=True):
+  """Per-example softmax loss (mesh_tensorflow/layers.py:1062-1117); hard targets
+  (integer dtype) take the single-pass operation unless fused=False, soft
+  targets the reference's op chain."""
+  if targets.dtype.is_integer:
+    if set(targets.shape.dims) != set(logits.shape.dims).difference([vocab_dim]):
+      raise ValueError(
+          "softmax_cross_entropy_with_logits with hard targets "
+          "dims in targets=%s should be dims in logits=%s other than "
+          "vocab_dim=%s" % (targets, logits, vocab_dim))
+    if fused and vocab_dim in logits.shape.dims:
+      return SoftmaxCrossEntropyOperation(logits, targets, vocab_dim, z_loss).outputs[0]
+    targets = mtf.one_hot(targets, vocab_dim, dtype=logits.dtype)
+  elif set(targets.shape.dims) != set(logits.shape.dims):
+    raise ValueError(
+        "softmax_cross_entropy_with_logits with soft targets "
+        "dims in targets=%s should be dims in logits=%s" % (targets, logits))
+  if vocab_dim not in logits.shape.dims:
+    raise ValueError("vocab_dim must be in logits.shape.dims")
+  log_z = mtf.reduce_logsumexp(logits, vocab_dim)
+  log_softmax = logits - log_z
+  loss = mtf.negative(mtf.reduce_sum(log_softmax * targets, reduced_dim=vocab_dim))
+  if z_loss != 0:
+    loss += z_loss * mtf.square(log_z)
+  return loss
+
+
+def multiplicative_jitter(x, epsilon=1e-2):
+  """x times uniform noise in [1 - epsilon, 1 + epsilon) (mesh_tensorflow/layers.py:1936-1952)."""
+  if epsilon == 0:
+    return x
+  return x * mtf.random_uniform(x.mesh, x.shape, minval=1.0 - epsilon, maxval=1.0 + epsilon,
+                                dtype=x.dtype)
+
+
 def rename_length_to_memory_length(x, length_name="length", memory_length_name="memory_length"):
   return mtf.rename_dimension(x, length_name, memory_length_name)
 

@@ -380,6 +380,9 @@ def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, lay
     gate_weights = mtf.reshape(gate_weights, Shape([gate_weights.shape.dims[0], experts_dim_unsplit]))
   if second_noise is not None:
     second_noise = mtf.reshape(second_noise, moe_input_dims[:-1])
+  elif _second_policy(hparams, train)[0] == "random":
+    # the uniform draw of moe.py:1461-1465, one value per token
+    second_noise = mtf.random_uniform(inputs.mesh, Shape(moe_input_dims[:-1]), dtype=G.float32)
 
   aux = {}
   fused = hparams.moe_use_fused_kernels

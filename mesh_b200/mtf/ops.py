@@ -16,7 +16,7 @@ import numpy as np
 from mesh_b200.mtf import graph as G
 from mesh_b200.mtf.graph import Operation, Tensor
 from mesh_b200.mtf.mesh_impl import LazyAllreduceSum, LazyLaidOutTensor, expand_dims_to
-from mesh_b200.mtf.shapes import (Dimension, Shape, convert_to_dimension,
+from mesh_b200.mtf.shapes import (Dimension, Shape, convert_to_dimension, list_product,
                                   convert_to_shape, shape_union)
 
 
@@ -98,25 +98,46 @@ def import_laid_out_tensor(mesh, laid_out_tensor, shape, dtype, name=None):
 
 
 class Variable(Operation):
-  """A tensor with a host-resident master copy (mesh_tensorflow/ops.py:3961-4070,
-  reduced to what a forward lowering needs): lowering lays the master out
-  through `mesh_impl.LaidOutVariable` and records it in `lowering.variables`,
-  so slices can be copied back to the master after the lowering."""
+  """A tensor with a host-resident master copy (mesh_tensorflow/ops.py:3961-4070).
 
-  def __init__(self, mesh, name, shape, dtype, initial_value):
+  Lowering lays the master out through `mesh_impl.LaidOutVariable` and records
+  it in `lowering.variables`.  The laid-out slices are kept per backend between
+  lowerings, so a training loop that lowers the same graph once per step keeps
+  its weights and optimizer slots on the devices: the master is uploaded again
+  only after the host changed it (assign_to_master, a restored checkpoint), and
+  slices travel back only on request (Assign(copy_to_master=True),
+  Lowering.copy_slices_to_masters)."""
+
+  def __init__(self, mesh, name, shape, dtype, initial_value, trainable=True):
     super().__init__([], mesh=mesh, name=name)
     shape = convert_to_shape(shape)
     value = np.asarray(initial_value)
     if list(value.shape) != shape.to_integer_list:
       raise ValueError("initial value %s does not match %s" % (value.shape, shape))
     self._master = value
+    self._master_version = 0
+    self._laid_out = {}      # id(backend) -> (LaidOutVariable, master version it holds)
+    self._trainable = trainable
     self._outputs = [Tensor(self, shape, dtype)]
+    if not hasattr(mesh.graph, "all_variables"):
+      mesh.graph.all_variables = []
+    mesh.graph.all_variables.append(self)
+
+  @property
+  def trainable(self):
+    return self._trainable
 
   def get_master(self):
     return self._master
 
-  def assign_to_master(self, value):
+  def assign_to_master(self, value, from_slices=None):
+    """New master value; `from_slices` names the LaidOutVariable the value was
+    read from, whose slices therefore stay current."""
     self._master = np.asarray(value)
+    self._master_version += 1
+    for key, (lv, _) in list(self._laid_out.items()):
+      if lv is from_slices:
+        self._laid_out[key] = (lv, self._master_version)
 
   @property
   def value(self):
@@ -124,7 +145,14 @@ class Variable(Operation):
 
   def lower(self, lowering):
     impl = lowering.mesh_impl(self)
-    laid_out_variable = impl.LaidOutVariable(self, impl)
+    held = self._laid_out.get(id(impl))
+    if held is None:
+      laid_out_variable = impl.LaidOutVariable(self, impl)
+    else:
+      laid_out_variable, version = held
+      if version != self._master_version:
+        laid_out_variable.copy_master_to_slices()
+    self._laid_out[id(impl)] = (laid_out_variable, self._master_version)
     lowering.variables[self] = laid_out_variable
     lowering.set_tensor_lowering(self.outputs[0], laid_out_variable.laid_out_tensor)
 
@@ -171,12 +199,52 @@ def assign(variable, new_value, copy_to_master=True):
   return Assign([var], [new_value], copy_to_master=copy_to_master)
 
 
-def get_variable(mesh, name, shape, dtype=G.float32, initial_value=None):
+def assign_add(variable, value, copy_to_master=True):
+  var = variable.operation if isinstance(variable, Tensor) else variable
+  return assign(var, var.outputs[0] + cast(value, var.outputs[0].dtype), copy_to_master=copy_to_master)
+
+
+def assign_sub(variable, value, copy_to_master=True):
+  var = variable.operation if isinstance(variable, Tensor) else variable
+  return assign(var, var.outputs[0] - cast(value, var.outputs[0].dtype), copy_to_master=copy_to_master)
+
+
+def get_variable(mesh, name, shape, dtype=G.float32, initial_value=None, trainable=True):
   """Creates a Variable and returns its tensor; `.operation` is the Variable."""
   shape = convert_to_shape(shape)
   if initial_value is None:
     initial_value = np.zeros(shape.to_integer_list, dtype=np.float32)
-  return Variable(mesh, name, shape, dtype, initial_value).outputs[0]
+  return Variable(mesh, name, shape, dtype, initial_value, trainable=trainable).outputs[0]
+
+
+def save_checkpoint(path, variables, lowering=None):
+  """Writes the masters of `variables` (Variable operations or their tensors) to
+  `path` as a numpy .npz archive keyed by variable name.  With `lowering`, the
+  device slices are copied to the masters first, as the reference's checkpoint
+  listener does before every save (mesh_tensorflow/ops.py:5740-5757).  The
+  reference's files are TensorFlow checkpoints; that container needs TensorFlow
+  and is not written here."""
+  ops_ = [v.operation if isinstance(v, Tensor) else v for v in variables]
+  if lowering is not None:
+    lowering.copy_slices_to_masters(ops_)
+  arrays = {v.name: np.asarray(v.get_master()) for v in ops_}
+  with open(path, "wb") as f:
+    np.savez(f, **arrays)
+
+
+def restore_checkpoint(path, variables):
+  """Reads masters back from a save_checkpoint archive; the next lowering lays
+  them out again (the reference's restore hook, ops.py:5760-5779)."""
+  ops_ = [v.operation if isinstance(v, Tensor) else v for v in variables]
+  with np.load(path) as data:
+    for v in ops_:
+      if v.name not in data:
+        raise KeyError("checkpoint %s has no variable %s" % (path, v.name))
+      value = data[v.name]
+      if list(value.shape) != v.outputs[0].shape.to_integer_list:
+        raise ValueError("checkpoint value of %s has shape %s, expected %s"
+                         % (v.name, value.shape, v.outputs[0].shape))
+      v.assign_to_master(value)
 
 
 def constant(mesh, value, shape=None, dtype=G.float32):
@@ -875,15 +943,25 @@ def rename_dimension(x, old_name, new_name):
   return reshape(x, x.shape.rename_dimension(old_name, new_name))
 
 
-def replace_dimensions(x, old_dim_or_dims, new_dim_or_dims):
-  """Replaces a run of consecutive dims by another run (ops.py:4609-4653)."""
+def replace_dimensions(tensor_or_shape, old_dim_or_dims, new_dim_or_dims):
+  """Replaces a run of consecutive dims of a Tensor (by reshape) or of a Shape
+  by another run (ops.py:4609-4653)."""
+  if isinstance(tensor_or_shape, Tensor):
+    return reshape(tensor_or_shape, replace_dimensions(
+        tensor_or_shape.shape, old_dim_or_dims, new_dim_or_dims))
+  if not isinstance(tensor_or_shape, Shape):
+    raise ValueError("tensor_or_shape must be a Tensor or Shape got %s" % (tensor_or_shape,))
   old = [old_dim_or_dims] if isinstance(old_dim_or_dims, Dimension) else list(old_dim_or_dims)
   new = [new_dim_or_dims] if isinstance(new_dim_or_dims, Dimension) else list(new_dim_or_dims)
-  dims = x.shape.dims
+  dims = tensor_or_shape.dims
+  if not old or not new or old[0] not in dims:
+    raise ValueError("old_dim_or_dims must be a subsequence of the input's dimensions"
+                     " old_dim_or_dims=%s input's dimensions=%s" % (old, dims))
   start = dims.index(old[0])
   if dims[start:start + len(old)] != old:
-    raise ValueError("old dims must be consecutive in %s: %s" % (x.shape, old))
-  return reshape(x, Shape(dims[:start] + new + dims[start + len(old):]))
+    raise ValueError("old_dim_or_dims must be a subsequence of the input's dimensions"
+                     " old_dim_or_dims=%s input's dimensions=%s" % (old, dims))
+  return Shape(dims[:start] + new + dims[start + len(old):])
 
 
 # ------------------------------------------------------------ top-k / one-hot
@@ -1083,14 +1161,71 @@ def one_hot(indices, output_dim, on_value=1.0, off_value=0.0, dtype=G.float32, n
                          name=name).outputs[0]
 
 
+class GatherOperation(Operation):
+  """weights[indices] along `dim`, the leading dim of `weights`, as a row gather.
+
+  The reference forms this product as einsum(one_hot(indices, dim), weights)
+  (ops.py:5231-5251); the values are the same, row copies being exact.  When
+  `dim` is split over a mesh axis each processor gathers the rows it holds and
+  leaves zeros for the others, and the slices are summed lazily over that axis,
+  exactly what the one-hot einsum's contraction of a split dim does.
+  """
+
+  def __init__(self, weights, indices, dim, name=None):
+    super().__init__([weights, indices], name=name or "gather")
+    self._dim = dim
+    self._outputs = [Tensor(self, Shape(indices.shape.dims + weights.shape.dims[1:]), weights.dtype)]
+
+  def gradient(self, grad_ys):
+    """The one-hot einsum's own gradient: d(weights) = one_hot(indices)^T . dy."""
+    weights, indices = self.inputs
+    hot = one_hot(indices, self._dim, dtype=weights.dtype)
+    return [einsum([hot, grad_ys[0]], output_shape=weights.shape), None]
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    ops = impl.slice_ops
+    weights, indices = self.inputs
+    mesh_axis = impl.tensor_dimension_to_mesh_axis(self._dim)
+    rows_here = impl.slice_shape(weights.shape)[0]
+    row_bytes = list_product(impl.slice_shape(weights.shape)[1:]) * weights.dtype.itemsize
+
+    def fn(w, idx, pcoord):
+      first = int(pcoord) * rows_here
+      if row_bytes % 16 == 0 and row_bytes > 0:
+        return ops.gather_rows(w, idx, first)
+      # rows too short for the vector kernel: the reference's own form, on slices
+      local = idx if first == 0 else ops.binary("sub", idx, first)
+      hot = ops.one_hot(local, rows_here, 1.0, 0.0, w.dtype)     # out of range: all off
+      nd = len(ops.shape(idx))
+      lead = "abcdefgh"[:nd]
+      rest = "ijklmnop"[:len(ops.shape(w)) - 1]
+      return ops.einsum("%sz,z%s->%s%s" % (lead, rest, lead, rest), hot, w)
+    pcoord = impl.laid_out_pcoord(mesh_axis) if mesh_axis is not None else 0
+    y = impl.slicewise(fn, lowering.tensors[weights], lowering.tensors[indices], pcoord)
+    if mesh_axis is not None:
+      y = LazyAllreduceSum(impl, y, [mesh_axis])
+    lowering.set_tensor_lowering(self.outputs[0], y)
+
+
 def gather(weights, indices, dim, output_shape=None):
-  """einsum(one_hot(indices, dim), weights) reducing `dim` (ops.py:5231-5251)."""
+  """weights indexed along `dim` by integer `indices` (ops.py:5231-5251).
+
+  The common case - `dim` leading in `weights`, no dim shared between `indices`
+  and the rest of `weights`, default output order - is a row gather
+  (GatherOperation); anything else is the reference's one-hot einsum."""
   dim = convert_to_dimension(dim)
   output_shape = convert_to_shape(output_shape)
   if not isinstance(indices, Tensor):
     indices = constant(weights.mesh, indices, dtype=G.int32)
   if weights.dtype.is_bool:
     return cast(gather(to_float(weights), indices, dim, output_shape), G.bool_)
+  rest = weights.shape.dims[1:]
+  natural = Shape(indices.shape.dims + rest)
+  if (weights.shape.ndims >= 2 and weights.shape.dims[0] == dim and indices.shape.ndims >= 1
+      and not set(indices.shape.dims) & set(weights.shape.dims)
+      and (output_shape is None or output_shape == natural)):
+    return GatherOperation(weights, indices, dim).outputs[0]
   return einsum([one_hot(indices, dim, dtype=weights.dtype), weights],
                 reduced_dims=[dim], output_shape=output_shape)
 
@@ -1339,4 +1474,104 @@ def import_fully_replicated(mesh, tf_tensor, shape, name=None, dtype=None):
   locally (mesh_tensorflow/ops.py:3935-3938)."""
   shape = convert_to_shape(shape)
   return reshape(import_tf_tensor(mesh, tf_tensor, anonymous_shape(shape), name, dtype=dtype), shape)
+
+
+class RandomOperation(Operation):
+  """A tensor of random values (mesh_tensorflow/ops.py:5782-5799); `tf_fn` is
+  "uniform" or "normal" (what tf.random.uniform / tf.random.normal are to the
+  reference).  The operation's seed defaults to a hash of its name, so the same
+  graph draws the same numbers in every lowering on every backend."""
+
+  def __init__(self, mesh, shape, tf_fn, **kwargs):
+    super().__init__([], mesh=mesh, name=kwargs.pop("name", None) or "random")
+    self._tf_fn = tf_fn
+    if kwargs.get("seed") is None:
+      import zlib
+      kwargs["seed"] = zlib.crc32(self.name.encode())
+    self._kwargs = kwargs
+    self._outputs = [Tensor(self, shape, kwargs.get("dtype", G.float32))]
+
+  @property
+  def has_gradient(self):
+    return False
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    lowering.set_tensor_lowering(
+        self.outputs[0], impl.random(self.outputs[0].shape, self._tf_fn, self._kwargs))
+
+
+def random_uniform(mesh, shape, **kwargs):
+  """Uniform in [minval, maxval) (ops.py:5802-5814)."""
+  return RandomOperation(mesh, convert_to_shape(shape), "uniform", **kwargs).outputs[0]
+
+
+def random_normal(mesh, shape, **kwargs):
+  """Normal with `mean` and `stddev` (ops.py:5817-5829)."""
+  return RandomOperation(mesh, convert_to_shape(shape), "normal", **kwargs).outputs[0]
+
+
+def dropout(x, is_training, keep_prob=None, rate=None, noise_shape=None, name=None):
+  """Zeroes elements with probability 1 - keep_prob and scales the rest by
+  1 / keep_prob for floating types (ops.py:5832-5871)."""
+  if (keep_prob is None) == (rate is None):
+    raise ValueError("exactly one of keep_prob and rate should be set")
+  if keep_prob is None:
+    keep_prob = 1.0 - rate
+  noise_shape = convert_to_shape(noise_shape)
+  if noise_shape is None:
+    noise_shape = x.shape
+  if keep_prob == 1.0 or not is_training:
+    return x
+  noise = cast(less(random_uniform(x.mesh, noise_shape, name=name,
+                                   dtype=(x.dtype if x.dtype.is_floating else G.float32)),
+                    keep_prob), x.dtype)
+  if x.dtype.is_floating:
+    noise = noise / keep_prob
+  return x * noise
+
+
+def serialize_training_step(features, model_fn, batch_dim, num_splits, variables):
+  """Splits the training batch into `num_splits` microbatches run one after the
+  other, with gradients and outputs accumulated (mesh_tensorflow/ops.py:6493-6586).
+
+  features: dict of Tensors, each with `batch_dim`; model_fn: feature dict ->
+  output dict containing "loss"; variables: the tensors to differentiate with
+  respect to (the reference takes graph.trainable_variables).  Returns
+  (grads, outputs): gradients summed over the microbatches, and outputs summed
+  (no batch dim) or re-assembled to the full batch (batch dim).
+
+  The reference runs the microbatches in an mtf.while_loop whose accumulators
+  may stay un-reduced; here the loop is unrolled in the graph, which has the
+  same effect: a gradient whose einsum contracts a mesh-split dim is a lazy
+  allreduce, sums of such lazies stay lazy (ops.py:1343-1382, 2079-2081), and
+  the one allreduce per variable runs after the last microbatch.  Microbatch m
+  holds the examples m, m + num_splits, ... as the reference's reshape to
+  [batch / num_splits, microbatch] implies.
+  """
+  if batch_dim.size % num_splits != 0:
+    raise ValueError("num_splits=%d must divide %s" % (num_splits, batch_dim))
+  microbatch_dim = Dimension("microbatch", num_splits)
+  smaller_batch_dim = Dimension(batch_dim.name, batch_dim.size // num_splits)
+
+  def select(t, microbatch_num):
+    return gather(replace_dimensions(t, batch_dim, [smaller_batch_dim, microbatch_dim]),
+                  microbatch_num, microbatch_dim)
+  combined_grads, combined_outputs = None, {}
+  for m in range(num_splits):
+    outputs = model_fn({k: select(v, m) for k, v in features.items()})
+    grads = gradients([outputs["loss"]], list(variables))
+    if None in grads:
+      raise ValueError("Found variable(s) with None gradient; check for variables "
+                       "disconnected from the loss")
+    for k, t in outputs.items():
+      if smaller_batch_dim in t.shape.dims:
+        # pad the microbatch's rows into the full batch; summing completes the concatenation
+        t = einsum([t, one_hot(constant(t.mesh, m, dtype=G.int32), microbatch_dim, dtype=t.dtype)],
+                   output_shape=replace_dimensions(t.shape, smaller_batch_dim,
+                                                   [smaller_batch_dim, microbatch_dim]))
+        t = replace_dimensions(t, [smaller_batch_dim, microbatch_dim], batch_dim)
+      combined_outputs[k] = t if k not in combined_outputs or m == 0 else add(combined_outputs[k], t)
+    combined_grads = grads if combined_grads is None else [add(a, b) for a, b in zip(combined_grads, grads)]
+  return combined_grads, combined_outputs
 

@@ -84,7 +84,7 @@ class NumpyMeshImpl(mtf.MeshImpl):
 
     def copy_slices_to_master(self):
       self._variable.assign_to_master(self._mesh_impl.export_to_tf_tensor(
-          self._variable.outputs[0], self._laid_out_tensor))
+          self._variable.outputs[0], self._laid_out_tensor), from_slices=self)
 
   @property
   def slice_ops(self):
@@ -105,6 +105,28 @@ class NumpyMeshImpl(mtf.MeshImpl):
 
   def laid_out_pnum(self):
     return self.LaidOutTensor(list(range(self.size)))
+
+  def random(self, shape, tf_fn, kwargs):
+    """placement_mesh_impl.py:307-325: one draw per slice, seeded from the
+    operation's seed and the slice's offset so that replicas agree."""
+    import hashlib
+    kwargs = dict(kwargs)
+    op_seed = kwargs.pop("seed", 0)
+    dtype = kwargs.pop("dtype", mtf.float32)
+    slice_shape = self.slice_shape(shape)
+    ops = self._ops
+
+    def my_fn(pnum):
+      text = "%s,%s" % (op_seed, self.slice_begin(shape, pnum))
+      seed = int.from_bytes(hashlib.sha256(text.encode()).digest()[:8], "little")
+      if callable(tf_fn):
+        return tf_fn(ops, slice_shape, seed=seed, dtype=dtype, **kwargs)
+      if tf_fn == "uniform":
+        return ops.random(slice_shape, "uniform", seed, dtype,
+                          float(kwargs.get("minval", 0.0)), float(kwargs.get("maxval", 1.0)))
+      return ops.random(slice_shape, "normal", seed, dtype,
+                        float(kwargs.get("mean", 0.0)), float(kwargs.get("stddev", 1.0)))
+    return self.slicewise(my_fn, self.laid_out_pnum())
 
   def import_tf_tensor(self, x, tf_x):
     full = self._ops.from_host(tf_x, x.dtype)

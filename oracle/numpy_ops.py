@@ -284,6 +284,76 @@ class NumpyOps(object):
     out = np.einsum("...xy,...ye->...xe", w.astype(np.float64), v.a.astype(np.float64))
     return _finish(out.astype(np.float32), v.dtype)
 
+  # ---- random fill: Philox4x32-10, the generator the device kernel restates
+  def random(self, shape, kind, seed, dtype, a, b):
+    n = int(np.prod(shape)) if len(shape) else 1
+    blocks = (n + 3) // 4
+    q = np.arange(blocks, dtype=np.uint64)
+    c = [(q & np.uint64(0xFFFFFFFF)).astype(np.uint64), (q >> np.uint64(32)).astype(np.uint64),
+         np.zeros(blocks, np.uint64), np.zeros(blocks, np.uint64)]
+    k0, k1 = np.uint64(seed & 0xFFFFFFFF), np.uint64((seed >> 32) & 0xFFFFFFFF)
+    mask = np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+      p0 = np.uint64(0xD2511F53) * c[0]
+      p1 = np.uint64(0xCD9E8D57) * c[2]
+      n0 = ((p1 >> np.uint64(32)) ^ c[1] ^ k0) & mask
+      n2 = ((p0 >> np.uint64(32)) ^ c[3] ^ k1) & mask
+      c = [n0, p1 & mask, n2, p0 & mask]
+      k0 = (k0 + np.uint64(0x9E3779B9)) & mask
+      k1 = (k1 + np.uint64(0xBB67AE85)) & mask
+    u = [(w >> np.uint64(8)).astype(np.float32) * np.float32(1.0 / 16777216.0) for w in c]
+    if kind == "normal":
+      vals = []
+      for h in range(2):
+        r = np.sqrt(np.float32(-2.0) * np.log(np.float32(1.0) - u[2 * h], dtype=np.float32), dtype=np.float32)
+        ang = np.float32(6.283185307179586) * u[2 * h + 1]
+        vals += [np.float32(a) + np.float32(b) * (r * np.cos(ang, dtype=np.float32)),
+                 np.float32(a) + np.float32(b) * (r * np.sin(ang, dtype=np.float32))]
+    else:
+      vals = [np.float32(a) + (np.float32(b) - np.float32(a)) * w for w in u]
+    flat = np.stack(vals, axis=1).reshape(-1)[:n]
+    return _finish(flat.reshape(shape), dtype)
+
+  # ---- row kernels of the rest of a transformer block: direct formulas
+  def norm_rows(self, x, scale, bias, epsilon, centered):
+    """layer_norm (layers.py:950-979) / rms norm (transformer.py:493-516) on the
+    last axis, in float64, rounded once."""
+    a = x.a.astype(np.float64)
+    if centered:
+      mean = a.mean(-1, keepdims=True)
+      var = ((a - mean) ** 2).mean(-1, keepdims=True)
+      out = (a - mean) / np.sqrt(var + epsilon)
+    else:
+      out = a / np.sqrt((a * a).mean(-1, keepdims=True) + epsilon)
+    if scale is not None:
+      out = out * scale.a.astype(np.float64)
+    if bias is not None:
+      out = out + bias.a.astype(np.float64)
+    return _finish(out.astype(np.float32), x.dtype)
+
+  def gather_rows(self, table, indices, first_row):
+    idx = indices.a.astype(np.int64) - first_row
+    ok = (idx >= 0) & (idx < table.a.shape[0])
+    out = table.a[np.where(ok, idx, 0)]
+    out = np.where(ok.reshape(ok.shape + (1,) * (table.a.ndim - 1)), out, 0)
+    return Arr(out.astype(table.a.dtype), table.dtype)
+
+  def xent_stats(self, logits, targets, first_col):
+    a = logits.a.astype(np.float64)
+    m = a.max(-1)
+    s = np.exp(a - m[..., None]).sum(-1)
+    c = targets.a.astype(np.int64) - first_col
+    ok = (c >= 0) & (c < a.shape[-1])
+    picked = np.where(ok, np.take_along_axis(a, np.where(ok, c, 0)[..., None], -1)[..., 0], 0.0)
+    return tuple(Arr(v.astype(np.float32), mtf.float32) for v in (m, s, picked))
+
+  def xent_grad(self, logits, targets, log_z, dloss, z_loss, first_col):
+    a = logits.a.astype(np.float64)
+    lz = log_z.a.astype(np.float64)[..., None]
+    hot = (np.arange(a.shape[-1]) + first_col) == targets.a[..., None]
+    out = dloss.a.astype(np.float64)[..., None] * ((1 + 2 * z_loss * lz) * np.exp(a - lz) - hot)
+    return _finish(out.astype(np.float32), logits.dtype)
+
   # ---- fused MoE entry points: the scalar specification
   def moe_top2_gating(self, x, w, capacity, policy, threshold, noise, num_groups_total,
                       want_table=False, want_raw=False):

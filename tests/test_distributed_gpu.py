@@ -106,30 +106,81 @@ def _worker(rank, world, port, out_dir):
         run()
         outs.append(ops.to_host(res.tensor_list[0]))
       return outs
-    fused = CudaMeshImpl(mesh_shape, "d_ff:all", list(range(world)))
-    fused.OVERLAP_MIN_ROWS = 1
-    fused.FUSED_ALLREDUCE = True
-    fused.FUSED_MIN_BYTES = 1
     ref_big = ffn_big(ora)
     nat_mod = __import__("mesh_b200._native", fromlist=["x"])
-    for _ in range(3):
-      before = nat_mod.launch_count()
-      got_big = ffn_big(fused)
-      used = nat_mod.launch_count() - before
-      assert rel_err(got_big, ref_big) < 2e-2
-    ws = [w for w in getattr(fused, "_peer_ws", {}).values()]
-    assert ws and all(w is not None for w in ws), "the fused einsum+allreduce path did not run"
-    assert used < 1 + fused.OVERLAP_CHUNKS + 4   # one launch for the contraction, not one per chunk
-    nat_mod.device_status()   # raises if a bounded wait ran out
-    for o in ffn_big(fused, replay=True):
-      assert rel_err(o, ref_big) < 2e-2
-    # every rank holds the same bits
     import torch
-    mine = torch.from_numpy(np.ascontiguousarray(got_big).view(np.int32).astype(np.int64)).cuda().sum().reshape(1)
+    exchange = []
+    # every exchange form: remote epilogue stores, peer loads by the owner, and the
+    # switch's multicast addresses (multimem) where the fabric offers them
+    for form in ("push", "pull", "multimem"):
+      fused = CudaMeshImpl(mesh_shape, "d_ff:all", list(range(world)))
+      fused.OVERLAP_MIN_ROWS = 1
+      fused.PIPELINED_ALLREDUCE = False
+      fused.FUSED_ALLREDUCE = True
+      fused.FUSED_MIN_BYTES = 1
+      fused.FUSED_EXCHANGE = form
+      for _ in range(3):
+        before = nat_mod.launch_count()
+        got_big = ffn_big(fused)
+        used = nat_mod.launch_count() - before
+        assert rel_err(got_big, ref_big) < 2e-2
+      ws = [w for w in getattr(fused, "_peer_ws", {}).values()]
+      assert ws and all(w is not None for w in ws), "the fused einsum+allreduce path did not run"
+      exchange.append({0: "push", 1: "pull", 2: "multimem"}[ws[0].exchange])
+      assert used < 1 + fused.OVERLAP_CHUNKS + 4   # one launch for the contraction, not one per chunk
+      nat_mod.device_status()   # raises if a bounded wait ran out
+      for o in ffn_big(fused, replay=True):
+        assert rel_err(o, ref_big) < 2e-2
+      # every rank holds the same bits
+      mine = torch.from_numpy(np.ascontiguousarray(got_big).view(np.int32).astype(np.int64)).cuda().sum().reshape(1)
+      hi, lo = mine.clone(), mine.clone()
+      dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+      dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+      assert int(hi.item()) == int(lo.item())
+      fused.release_graphs()
+
+    # the pipelined form: un-chunked GEMM with progress counters, exchange by the copy
+    # engines on a second stream; eager three times (the counters' epochs advance),
+    # then recorded once and replayed
+    def ffn_rows(backend, replay=False):
+      rr = rng(4)
+      g = mtf.Graph()
+      m = mtf.Mesh(g, "m")
+      x = rr.standard_normal((8, 256, 128)).astype(np.float32)
+      wi = (rr.standard_normal((128, 512)) / 11).astype(np.float32)
+      wo = (rr.standard_normal((512, 128)) / 22).astype(np.float32)
+      X = mtf.import_tf_tensor(m, x, "batch:8,length:256,d_model:128", dtype=mtf.bfloat16)
+      WI = mtf.import_tf_tensor(m, wi, "d_model:128,d_ff:512", dtype=mtf.bfloat16)
+      WO = mtf.import_tf_tensor(m, wo, "d_ff:512,d_model:128", dtype=mtf.bfloat16)
+      y = mtf.layers.dense_relu_dense(X, mtf.Dimension("d_ff", 512), wi=WI, wo=WO)
+      if not replay:
+        return mtf.Lowering(g, {m: backend}).export_to_tf_tensor(y)
+      res, run = backend.capture(lambda: mtf.Lowering(g, {m: backend}).tensors[y].to_laid_out_tensor())
+      outs = []
+      for _ in range(3):
+        run()
+        outs.append(ops.to_host(res.tensor_list[0]))
+      return outs
+    piped = CudaMeshImpl(mesh_shape, "d_ff:all", list(range(world)))
+    piped.OVERLAP_MIN_ROWS = 1
+    piped.PIPELINE_MIN_BYTES = 1
+    piped.FUSED_ALLREDUCE = False
+    ref_rows = ffn_rows(ora)
+    for _ in range(3):
+      got_rows = ffn_rows(piped)
+      assert rel_err(got_rows, ref_rows) < 2e-2
+    ws = [w for w in getattr(piped, "_pipe_ws", {}).values()]
+    assert ws and all(w is not None for w in ws), "the pipelined einsum+allreduce path did not run"
+    nat_mod.device_status()
+    for o in ffn_rows(piped, replay=True):
+      assert rel_err(o, ref_rows) < 2e-2
+    mine = torch.from_numpy(np.ascontiguousarray(got_rows).view(np.int32).astype(np.int64)).cuda().sum().reshape(1)
     hi, lo = mine.clone(), mine.clone()
     dist.all_reduce(hi, op=dist.ReduceOp.MAX)
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
-    assert int(hi.item()) == int(lo.item())
+    assert int(hi.item()) == int(lo.item())    # every rank holds the same bits
+    piped.release_graphs()
+    exchange.append("pipelined x%d chunks" % ws[0].chunks)
 
     layout = "batch:all;experts:all"
 
@@ -160,7 +211,8 @@ def _worker(rank, world, port, out_dir):
     assert rel_err(go.reshape(ri.shape + (-1,))[same], ro.reshape(ri.shape + (-1,))[same]) < 2e-2
     assert abs(gl - rl) < 2e-2 * abs(rl)
     impl.synchronize()
-    open(os.path.join(out_dir, "ok%d" % rank), "w").write("ok")
+    open(os.path.join(out_dir, "ok%d" % rank), "w").write("ok exchange=%s cooperative=%d"
+                                                       % (exchange, nat_mod.lib().mtfc_gemm_allreduce_cooperative()))
   finally:
     dist.destroy_process_group()
 
@@ -174,3 +226,4 @@ def test_one_process_per_gpu_over_nccl(tmp_path):
   world = 2 if world < 4 else 4
   mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
   assert sorted(os.listdir(str(tmp_path))) == ["ok%d" % r for r in range(world)]
+  print(open(os.path.join(str(tmp_path), "ok0")).read())

@@ -207,3 +207,44 @@ def test_sgd_step_on_variables(mesh_shape, layout):
   mtf.Lowering(gg, {mm: NumpyMeshImpl(mesh_shape, layout)})
   np.testing.assert_allclose(W2.operation.get_master(), w1, rtol=1e-4, atol=1e-5)
   np.testing.assert_allclose(V2.operation.get_master(), v0 - 0.01 * dv, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("mesh_shape,layout", [("all:1", ""), ("a:2,b:2", "batch:a;d_ff:b")])
+def test_serialize_training_step_accumulates_with_one_allreduce(mesh_shape, layout):
+  """Microbatched gradients equal the full-batch gradients, and each variable's
+  data-parallel allreduce runs once, after the last microbatch, not once per microbatch."""
+  r = rng(19)
+  x = r.standard_normal((8, 6)).astype(np.float32)
+  target = r.standard_normal((8, 3)).astype(np.float32)
+  w0 = (r.standard_normal((6, 10)) / 3).astype(np.float32)
+  v0 = (r.standard_normal((10, 3)) / 3).astype(np.float32)
+
+  def build(num_splits):
+    g = mtf.Graph()
+    m = mtf.Mesh(g, "m")
+    X = mtf.import_tf_tensor(m, x, "batch:8,d_model:6", dtype=mtf.float32)
+    T = mtf.import_tf_tensor(m, target, "batch:8,out:3", dtype=mtf.float32)
+    W = mtf.get_variable(m, "w", "d_model:6,d_ff:10", initial_value=w0)
+    V = mtf.get_variable(m, "v", "d_ff:10,out:3", initial_value=v0)
+
+    def model_fn(features):
+      h = mtf.relu(mtf.einsum([features["x"], W], output_shape=mtf.Shape([features["x"].shape.dims[0], W.shape.dims[1]])))
+      y = mtf.einsum([h, V], output_shape=mtf.Shape([h.shape.dims[0], V.shape.dims[1]]))
+      return {"loss": mtf.reduce_sum(mtf.square(y - features["t"])), "y": y}
+    if num_splits == 1:
+      out = model_fn({"x": X, "t": T})
+      grads = mtf.gradients([out["loss"]], [W, V])
+    else:
+      grads, out = mtf.serialize_training_step({"x": X, "t": T}, model_fn, X.shape.dims[0], num_splits, [W, V])
+    low = mtf.Lowering(g, {m: NumpyMeshImpl(mesh_shape, layout)})
+    vals = [np.asarray(low.export_to_tf_tensor(t), np.float64) for t in grads + [out["loss"], out["y"]]]
+    return vals, low.counter_totals()
+  full, c_full = build(1)
+  micro, c_micro = build(4)
+  for a, b in zip(micro, full):
+    np.testing.assert_allclose(a, b, rtol=1e-5, atol=1e-5)
+  if "batch" in layout:
+    key = [k for k in c_full if k.startswith("allreduce") and k.endswith("einsum_op")]
+    assert key
+    for k in key:   # same allreduce volume as the un-split step: the microbatch sums stayed lazy
+      assert c_micro.get(k, 0) == c_full[k], (k, c_micro.get(k), c_full[k])

@@ -198,3 +198,28 @@ def test_fp32_einsum_on_tensor_cores(both, eq, shapes):
   assert rel_err(got, ref) < 1e-5
   from mesh_b200 import _native as nat
   nat.device_status()
+
+
+@pytest.mark.parametrize("n,shape", [(4, (16, 128)), (3, (8, 96)), (4, (5, 7)), (2, (64, 64))])
+@pytest.mark.parametrize("dtype", [mtf.float32, mtf.bfloat16])
+def test_in_process_allreduce_follows_the_reference_association(cuda_device, n, shape, dtype):
+  """Grouped SUM over slices held by one process: the reference's ring allreduce
+  cuts slices of >= 1024 elements in n shards and reduces shard s over the member
+  list rotated by s (placement_mesh_impl.py:407-455); same order here, so the sums
+  carry the same bits as the oracle's."""
+  from mesh_b200.cuda_mesh_impl import CudaMeshImpl
+  from oracle.numpy_mesh_impl import NumpyMeshImpl
+  from oracle.numpy_ops import Arr, round_to_bf16
+  r = rng(33)
+  vals = [r.standard_normal(shape).astype(np.float32) for _ in range(n)]
+  if dtype == mtf.bfloat16:
+    vals = [round_to_bf16(v) for v in vals]
+  dev = CudaMeshImpl("all:%d" % n, "", [0] * n)
+  ora = NumpyMeshImpl("all:%d" % n, "")
+  xd = dev.LaidOutTensor([dev.slice_ops.from_host(v, dtype) for v in vals])
+  xo = ora.LaidOutTensor([Arr(v.copy(), dtype) for v in vals])
+  for name in ("SUM", "MAX"):
+    yd = dev.allreduce(xd, [0], name)
+    yo = ora.allreduce(xo, [0], name)
+    for a, b in zip(yd.tensor_list, yo.tensor_list):
+      np.testing.assert_array_equal(dev.slice_ops.to_host(a), b.a)

@@ -48,19 +48,28 @@ def _both_paths(dev, seed, outer, groups, s, e, cap, m):
                                 e, cap, m * 2, stream))
   # the entry point under test: inputs and output only
   got = torch.full((outer, e, groups, cap, m), -7.0, dtype=torch.bfloat16, device=dev)
+  torch.cuda.synchronize()
+  free_before = torch.cuda.mem_get_info(dev)[0]
+  torch_allocs_before = torch.cuda.memory_stats(dev).get("allocation.all.allocated", 0)
   nat.check(L.mtfc_moe_dispatch_noalloc(x.data_ptr(), *ptrs, got.data_ptr(), outer, groups, s, e,
                                         cap, m * 2, 1, stream))
   torch.cuda.synchronize()
-  return got.float().cpu().numpy(), ref.float().cpu().numpy()
+  noalloc_deltas = (free_before - torch.cuda.mem_get_info(dev)[0],
+                    torch.cuda.memory_stats(dev).get("allocation.all.allocated", 0) - torch_allocs_before)
+  return got.float().cpu().numpy(), ref.float().cpu().numpy(), noalloc_deltas
 
 
 def test_noalloc_dispatch_matches_two_call_form_twice_in_a_row(cuda_device):
   first = _both_paths(cuda_device, 41, outer=2, groups=6, s=256, e=16, cap=24, m=128)
   second = _both_paths(cuda_device, 42, outer=1, groups=3, s=96, e=8, cap=40, m=64)
-  for got, ref in (first, second):
+  for got, ref, _ in (first, second):
     assert got.shape == ref.shape
     np.testing.assert_array_equal(got, ref)
     assert np.abs(ref).max() > 0
+  # Nothing was allocated by the second call: the device's free memory and the count
+  # of allocations made through torch are what they were just before it.  (The first
+  # call on a device may load the kernels' module; that is set-up, not the steady state.)
+  assert second[2] == (0, 0), "the no-alloc entry point changed device memory: %s" % (second[2],)
   # 320 slots per group for 192 (token, choice) pairs: empty slots must be zero rows
   assert (np.abs(second[1]).max(axis=-1) == 0).any()
 
