@@ -332,6 +332,9 @@ int mtfc_copy_strided(const void* src, const int64_t* src_strides, void* dst,
 #define MTFC_MOE_POLICY_NONE 1      /* "none"                        */
 #define MTFC_MOE_POLICY_THRESHOLD 2 /* "threshold": gate_2 > thr     */
 #define MTFC_MOE_POLICY_RANDOM 3    /* "random": noise < gate_2/thr  */
+#define MTFC_MOE_POLICY_SWITCH 4    /* top-1 routing (_switch_gating, moe.py:1184-1309):
+                                       no second expert, gate_1 is the raw softmax
+                                       output (not renormalised), gate_2 = 0 */
 
 /* fp32 gate kernel [m, experts] -> bf16 [m, 3*experts] = [hi | mid | lo] with
  * hi + mid + lo == w to fp32 accuracy, so x(bf16) . w runs on the tensor cores

@@ -342,12 +342,15 @@ __global__ void random_kernel(T* __restrict__ out, long long n, uint32_t seed_lo
         const float r = sqrtf(-2.0f * logf(1.0f - u0));
         float sn, cs;
         sincosf(6.283185307179586f * u1, &sn, &cs);
-        v[2 * h] = a + b * (r * cs);
-        v[2 * h + 1] = a + b * (r * sn);
+        v[2 * h] = __fadd_rn(a, __fmul_rn(b, __fmul_rn(r, cs)));
+        v[2 * h + 1] = __fadd_rn(a, __fmul_rn(b, __fmul_rn(r, sn)));
       }
     } else {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) v[e] = a + (b - a) * ((float)(c[e] >> 8) * (1.0f / 16777216.0f));
+      // separately rounded multiply and add (no fused multiply-add), so that the
+      // values can be restated exactly with ordinary float32 arithmetic
+      for (int e = 0; e < 4; ++e)
+        v[e] = __fadd_rn(a, __fmul_rn(__fsub_rn(b, a), (float)(c[e] >> 8) * (1.0f / 16777216.0f)));
     }
 #pragma unroll
     for (int e = 0; e < 4; ++e)

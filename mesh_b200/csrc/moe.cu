@@ -144,8 +144,8 @@ top2_gating_kernel(GateArgs a) {
       }
       const float denom = (b1 + b2) + 1e-9f;
       const float recip = 1.0f / denom;
-      g1 = b1 * recip;
-      g2 = b2 * recip;
+      g1 = a.policy == MTFC_MOE_POLICY_SWITCH ? b1 : b1 * recip;
+      g2 = a.policy == MTFC_MOE_POLICY_SWITCH ? 0.f : b2 * recip;
       if (a.raw_gates) {
         float* dst = a.raw_gates + (tok0 + c0 + tid) * E;
         for (int e = 0; e < E; ++e) dst[e] = r[e];
@@ -226,6 +226,7 @@ top2_gating_kernel(GateArgs a) {
       switch (a.policy) {
         case MTFC_MOE_POLICY_ALL: m2 = true; break;
         case MTFC_MOE_POLICY_NONE: m2 = false; break;
+        case MTFC_MOE_POLICY_SWITCH: m2 = false; break;
         case MTFC_MOE_POLICY_THRESHOLD: m2 = g2 > a.threshold; break;
         case MTFC_MOE_POLICY_RANDOM:
           m2 = a.noise[t] < g2 * (1.0f / fmaxf(a.threshold, 1e-9f));
@@ -612,7 +613,7 @@ int mtfc_moe_top2_gating(const float* logits, int32_t parts, int64_t groups, int
     return fail(MTFC_ERR_SHAPE, "top2_gating: experts=%d outside [2, %d]", experts, kMaxExperts);
   if (policy == MTFC_MOE_POLICY_RANDOM && !noise)
     return fail(MTFC_ERR_SHAPE, "top2_gating: policy random needs the noise tensor");
-  if (policy < MTFC_MOE_POLICY_ALL || policy > MTFC_MOE_POLICY_RANDOM)
+  if (policy < MTFC_MOE_POLICY_ALL || policy > MTFC_MOE_POLICY_SWITCH)
     return fail(MTFC_ERR_SHAPE, "top2_gating: unknown policy %d", policy);
   if (groups == 0) return MTFC_OK;
   if (groups > INT32_MAX) return fail(MTFC_ERR_SHAPE, "top2_gating: too many groups");

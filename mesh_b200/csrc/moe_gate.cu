@@ -49,6 +49,7 @@ constexpr int kMaxGateExperts = 64;
 
 struct GateFusedArgs {
   int group_size, experts, m;
+  int renormalize;  // 0: gate_1 is the raw top-1 gate and gate_2 is 0 (top-1 routing)
   int tile_rows;  // tokens per tile: 128, or 64 when that fills the SMs more evenly
   int tiles_per_group;
   long long num_tiles;
@@ -59,6 +60,12 @@ struct GateFusedArgs {
   float* gate2;
   float* raw_gates;  // [tokens, experts] or null
   float* tile_sums;  // [num_tiles, EP]: column sums of the raw gates per tile
+  int* tile_counts;  // [num_tiles, 2, EP]: tokens of the tile choosing each expert 1st / 2nd
+  int* rank1;        // per token: tokens of its tile before it with the same first choice
+  int* rank2;        // the same for the second choice among tokens that pass the policy; -1 if not
+  int policy;
+  float threshold;
+  const float* noise;
   unsigned* groups_done;  // counter the positions kernel's CTAs take tickets from; zeroed here
   int* status;
 };
@@ -115,7 +122,8 @@ gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   const int ST = a.stages;
   const uint32_t off_w = (uint32_t)ST * X_STAGE_BYTES;
   const uint32_t off_sums = off_w + (uint32_t)ST * W_STAGE_BYTES;
-  const uint32_t off_bar = off_sums + 2 * G_EPI_WARPS * EP * 4;
+  const uint32_t off_cnt = off_sums + 2 * G_EPI_WARPS * EP * 4;
+  const uint32_t off_bar = off_cnt + 2 * 2 * G_EPI_WARPS * EP * 4;
   const uint32_t off_misc = off_bar + (2 * MAX_STAGES + 4) * 8;
   const uint32_t bar_base = smem_base + off_bar;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -125,6 +133,7 @@ gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + off_misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + off_misc + 4);
   float* warp_sums = reinterpret_cast<float*>(smem + off_sums);  // [2][G_EPI_WARPS][EP]
+  int* warp_cnt = reinterpret_cast<int*>(smem + off_cnt);        // [2][2 choices][G_EPI_WARPS][EP]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -278,11 +287,38 @@ gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         if (e < E && p > b2) { b2 = p; i2 = e; }
       }
       const float recip = 1.0f / ((b1 + b2) + 1e-9f);
+      const float g1n = a.renormalize ? b1 * recip : b1;
+      const float g2n = a.renormalize ? b2 * recip : 0.f;
+      // second-expert policy (moe.py:1446-1467), on the renormalised gate
+      bool m2 = false;
+      if (live) {
+        switch (a.policy) {
+          case MTFC_MOE_POLICY_ALL: m2 = true; break;
+          case MTFC_MOE_POLICY_THRESHOLD: m2 = g2n > a.threshold; break;
+          case MTFC_MOE_POLICY_RANDOM:
+            m2 = a.noise[tok] < g2n * (1.0f / fmaxf(a.threshold, 1e-9f));
+            break;
+          default: m2 = false;   // none, switch
+        }
+      }
+      // rank among the tile's earlier tokens with the same choice: inside the warp by
+      // match/popc, across the four warps through per-warp counts (added after the barrier)
+      int* cnt_a = warp_cnt + (((local & 1) * 2 + 0) * G_EPI_WARPS + ew) * EP;
+      int* cnt_b = warp_cnt + (((local & 1) * 2 + 1) * G_EPI_WARPS + ew) * EP;
+      for (int e = lane; e < EP; e += 32) { cnt_a[e] = 0; cnt_b[e] = 0; }
+      __syncwarp();
+      const unsigned lt_mask = (1u << lane) - 1u;
+      const unsigned same1 = __match_any_sync(0xffffffffu, live ? i1 : -1 - lane);
+      int rank1 = __popc(same1 & lt_mask);
+      if (live && rank1 == 0) cnt_a[i1] = __popc(same1);
+      const unsigned same2 = __match_any_sync(0xffffffffu, m2 ? i2 : -1 - lane);
+      int rank2 = __popc(same2 & lt_mask);
+      if (m2 && rank2 == 0) cnt_b[i2] = __popc(same2);
       if (live) {
         a.idx1[tok] = i1;
         a.idx2[tok] = i2;
-        a.gate1[tok] = b1 * recip;
-        a.gate2[tok] = b2 * recip;
+        a.gate1[tok] = g1n;
+        a.gate2[tok] = g2n;
         if (a.raw_gates) {
           float* dst = a.raw_gates + tok * E;
 #pragma unroll
@@ -323,12 +359,30 @@ gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         mine[lane >> 1] = r[0];
       }
       epi_warps_sync();
+      {
+        // warps earlier in token order: lane quarter q' < q sits in epilogue warp (q' + 2) & 3
+        const int* all_a = warp_cnt + ((local & 1) * 2 + 0) * G_EPI_WARPS * EP;
+        const int* all_b = warp_cnt + ((local & 1) * 2 + 1) * G_EPI_WARPS * EP;
+        for (int qq = 0; qq < q; ++qq) {
+          const int w = (qq + 2) & 3;
+          if (live) rank1 += all_a[w * EP + i1];
+          if (m2) rank2 += all_b[w * EP + i2];
+        }
+        if (live) {
+          a.rank1[tok] = rank1;
+          a.rank2[tok] = m2 ? rank2 : -1;
+        }
+      }
       const int tid = ew * 32 + lane;
       if (tid < EP) {
         const float* ws = warp_sums + (local & 1) * G_EPI_WARPS * EP;
         // rows in token order: warps 2..5 hold lane quarters 2, 3, 0, 1
         const float s = ((ws[2 * EP + tid] + ws[3 * EP + tid]) + ws[0 * EP + tid]) + ws[1 * EP + tid];
         a.tile_sums[t * EP + tid] = s;
+        const int* ca = warp_cnt + ((local & 1) * 2 + 0) * G_EPI_WARPS * EP + tid;
+        const int* cb = warp_cnt + ((local & 1) * 2 + 1) * G_EPI_WARPS * EP + tid;
+        a.tile_counts[(t * 2 + 0) * EP + tid] = ca[0] + ca[EP] + ca[2 * EP] + ca[3 * EP];
+        a.tile_counts[(t * 2 + 1) * EP + tid] = cb[0] + cb[EP] + cb[2 * EP] + cb[3 * EP];
       }
     }
     if (!ok && lane == 0 && a.status) atomicExch(a.status, MTFC_ERR_TIMEOUT);
@@ -349,17 +403,16 @@ __device__ __forceinline__ bool gate_nonzero_bf16(float g) {
 }
 
 struct PositionArgs {
-  int group_size, experts, capacity, policy;
-  float threshold;
-  const float* noise;
+  int group_size, experts, capacity;
   const int* idx1;
   const int* idx2;
-  int* pos1;
-  int* pos2;
+  int* pos1;     // in: rank inside the tile; out: position in the expert's buffer
+  int* pos2;     // in: rank inside the tile among policy-passing tokens, -1 if none; out: position
   float* gate1;  // in: renormalised gates; out: zeroed where dropped
   float* gate2;
-  const float* tile_sums;  // [groups, tiles_per_group, ep]
-  int tiles_per_group, ep;
+  const float* tile_sums;   // [groups, tiles_per_group, ep]
+  const int* tile_counts;   // [groups, tiles_per_group, 2, ep]
+  int tiles_per_group, tile_rows, ep;
   float* loss_per_group;
   float* loss_mean;        // sum over groups / num_groups_total, or null
   float inv_groups_total;
@@ -369,137 +422,83 @@ struct PositionArgs {
   int round_bf16;
 };
 
-// One CTA of T threads per group, tokens T at a time in index order.  Shared
-// memory: base1[E], base2[E], cnt1[E], wcnt[T/32][E], slots[E*C] (if a table is
-// written).
+// One CTA per group.  The fused kernel left, per token, its rank among the
+// earlier tokens of its tile with the same choice and, per tile, the number of
+// tokens choosing each expert; an exclusive scan of those counts over the
+// group's tiles (one thread per expert) gives every tile's base, and
+// position = base + rank.  Second choices start after the kept first choices
+// (moe.py:1488-1490).  Shared memory: base1[tiles][E], base2[tiles][E], tot1[E],
+// slots[E*C] (if a table is built there).
 __global__ void __launch_bounds__(1024)
 top2_positions_kernel(PositionArgs a) {
   extern __shared__ int ismem[];
   const int E = a.experts, S = a.group_size, C = a.capacity;
-  const int T = blockDim.x, W = T >> 5;
+  const int T = blockDim.x, K = a.tiles_per_group;
   int* base1 = ismem;
-  int* base2 = base1 + E;
-  int* cnt1 = base2 + E;
-  int* wcnt = cnt1 + E;
+  int* base2 = base1 + K * E;
+  int* tot1 = base2 + K * E;
   const int g = blockIdx.x;
-  // the group's slot table is built in shared memory when it fits there, else in place
-  int* slots = a.table_in_smem ? wcnt + W * E : a.table + (long long)g * E * C;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const unsigned lt_mask = (1u << lane) - 1u;
   const long long tok0 = (long long)g * S;
-  const bool single = S <= T;   // the whole group sits in registers between the passes
+  // the group's slot table is built in shared memory when it fits there, else in place
+  int* slots = a.table_in_smem ? tot1 + E : a.table + (long long)g * E * C;
 
-  for (int e = tid; e < E; e += T) { base1[e] = 0; base2[e] = 0; }
+  for (int e = tid; e < E; e += T) {
+    const int* tc = a.tile_counts + ((long long)g * K * 2) * a.ep + e;
+    int run = 0;
+    for (int k = 0; k < K; ++k) {
+      base1[k * E + e] = run;
+      run += tc[(long long)(2 * k) * a.ep];
+    }
+    tot1[e] = run;
+    int run2 = min(run, C);   // second choices queue behind the kept first choices
+    for (int k = 0; k < K; ++k) {
+      base2[k * E + e] = run2;
+      run2 += tc[(long long)(2 * k + 1) * a.ep];
+    }
+  }
   if (a.table)
     for (int i = tid; i < E * C; i += T) slots[i] = -1;
   __syncthreads();
 
-  int keep_i1 = -1, keep_p1 = 0;
-  // ---- pass 1: first-choice positions ----
-  for (int c0 = 0; c0 < S; c0 += T) {
-    for (int i = tid; i < W * E; i += T) wcnt[i] = 0;
-    __syncthreads();
-    const bool live = c0 + tid < S;
-    const long long t = tok0 + c0 + tid;
-    int i1 = -1 - lane;   // dead lanes never match a live expert index
-    if (live) i1 = a.idx1[t];
-    const unsigned same = __match_any_sync(0xffffffffu, i1);
-    const int rank = __popc(same & lt_mask);
-    if (live && rank == 0) wcnt[warp * E + i1] = __popc(same);
-    __syncthreads();
-    for (int e = tid; e < E; e += T) {
-      int run = base1[e];
-      for (int w = 0; w < W; ++w) {
-        const int c = wcnt[w * E + e];
-        wcnt[w * E + e] = run;
-        run += c;
-      }
-      base1[e] = run;
-    }
-    __syncthreads();
-    if (live) {
-      const int p1 = wcnt[warp * E + i1] + rank;
-      a.pos1[t] = p1;
-      if (single) { keep_i1 = i1; keep_p1 = p1; }
-    }
-    __syncthreads();
-  }
-
-  // ---- loss (pre-capacity counts) and kept first-choice counts ----
-  for (int e = tid; e < E; e += T) cnt1[e] = min(base1[e], C);
-  if (warp == 0) {
+  if (warp == 0) {   // load-balancing loss on the pre-capacity counts (moe.py:1420-1424)
     float part = 0.f;
     const float inv_s = 1.0f / (float)S;
     for (int e = lane; e < E; e += 32) {
       float proxy = 0.f;
-      const float* ts = a.tile_sums + ((long long)g * a.tiles_per_group) * a.ep + e;
-      for (int k = 0; k < a.tiles_per_group; ++k) proxy += ts[(long long)k * a.ep];
-      part += (proxy * inv_s) * ((float)base1[e] * inv_s);
+      const float* ts = a.tile_sums + ((long long)g * K) * a.ep + e;
+      for (int k = 0; k < K; ++k) proxy += ts[(long long)k * a.ep];
+      part += (proxy * inv_s) * ((float)tot1[e] * inv_s);
     }
     for (int s = 16; s > 0; s >>= 1) part += __shfl_xor_sync(0xffffffffu, part, s);
     if (lane == 0) a.loss_per_group[g] = part * (1.0f / (float)E) * (float)(E * E);
   }
-  __syncthreads();
 
-  // ---- pass 2: second-choice policy, positions, capacity masks ----
-  for (int c0 = 0; c0 < S; c0 += T) {
-    for (int i = tid; i < W * E; i += T) wcnt[i] = 0;
-    __syncthreads();
-    const bool live = c0 + tid < S;
-    const long long t = tok0 + c0 + tid;
-    int i2 = -1 - lane, cand = 0, i1 = 0, p1 = 0;
-    float g1 = 0.f, g2 = 0.f;
-    bool m2 = false;
-    if (live) {
-      g1 = a.gate1[t];
-      g2 = a.gate2[t];
-      cand = a.idx2[t];
-      if (single) { i1 = keep_i1; p1 = keep_p1; } else { i1 = a.idx1[t]; p1 = a.pos1[t]; }
-      switch (a.policy) {
-        case MTFC_MOE_POLICY_ALL: m2 = true; break;
-        case MTFC_MOE_POLICY_NONE: m2 = false; break;
-        case MTFC_MOE_POLICY_THRESHOLD: m2 = g2 > a.threshold; break;
-        case MTFC_MOE_POLICY_RANDOM:
-          m2 = a.noise[t] < g2 * (1.0f / fmaxf(a.threshold, 1e-9f));
-          break;
-        default: m2 = true;
-      }
-      if (m2) i2 = cand;
+  for (int s = tid; s < S; s += T) {
+    const long long t = tok0 + s;
+    const int k = s / a.tile_rows;
+    const int i1 = a.idx1[t], i2 = a.idx2[t];
+    const int r2 = a.pos2[t];
+    const bool m2 = r2 >= 0;
+    const int p1 = base1[k * E + i1] + a.pos1[t];
+    const int p2 = m2 ? base2[k * E + i2] + r2 : 0;
+    const bool keep1 = p1 < C;
+    const bool keep2 = m2 && p2 < C;
+    const float g1 = keep1 ? a.gate1[t] : 0.f;
+    const float g2 = keep2 ? a.gate2[t] : 0.f;
+    a.pos1[t] = p1;
+    a.pos2[t] = p2;
+    a.gate1[t] = g1;
+    a.gate2[t] = g2;
+    if (a.table) {
+      if (keep1 && (a.round_bf16 ? gate_nonzero_bf16(g1) : g1 != 0.f)) slots[i1 * C + p1] = s;
+      if (keep2 && (a.round_bf16 ? gate_nonzero_bf16(g2) : g2 != 0.f)) slots[i2 * C + p2] = s;
     }
-    const unsigned same = __match_any_sync(0xffffffffu, i2);
-    const int rank = __popc(same & lt_mask);
-    if (live && m2 && rank == 0) wcnt[warp * E + i2] = __popc(same);
-    __syncthreads();
-    for (int e = tid; e < E; e += T) {
-      int run = base2[e];
-      for (int w = 0; w < W; ++w) {
-        const int c = wcnt[w * E + e];
-        wcnt[w * E + e] = run;
-        run += c;
-      }
-      base2[e] = run;
-    }
-    __syncthreads();
-    if (live) {
-      int p2 = 0;
-      if (m2) p2 = wcnt[warp * E + i2] + rank + cnt1[i2];
-      const bool keep1 = p1 < C;
-      const bool keep2 = m2 && p2 < C;
-      g1 = keep1 ? g1 : 0.f;
-      g2 = keep2 ? g2 : 0.f;
-      a.pos2[t] = p2;
-      a.gate1[t] = g1;
-      a.gate2[t] = g2;
-      if (a.table) {
-        const int s = c0 + tid;
-        if (keep1 && (a.round_bf16 ? gate_nonzero_bf16(g1) : g1 != 0.f)) slots[i1 * C + p1] = s;
-        if (keep2 && (a.round_bf16 ? gate_nonzero_bf16(g2) : g2 != 0.f)) slots[cand * C + p2] = s;
-      }
-    }
-    __syncthreads();
   }
-  if (a.table && a.table_in_smem)
+  if (a.table && a.table_in_smem) {
+    __syncthreads();
     for (int i = tid; i < E * C; i += T) a.table[(long long)g * E * C + i] = slots[i];
+  }
   // the CTA that finishes last adds the per-group losses, always in the same order
   if (a.loss_mean && warp == 0) {
     unsigned ticket = 0;
@@ -567,7 +566,7 @@ int gate_stages(int ep) {
 
 size_t gate_fused_smem(int ep) {
   return (size_t)gate_stages(ep) * (X_STAGE_BYTES + 3 * ep * GBK * 2) + 2 * G_EPI_WARPS * ep * 4 +
-         (2 * MAX_STAGES + 4) * 8 + 16 + 1024;
+         2 * 2 * G_EPI_WARPS * ep * 4 + (2 * MAX_STAGES + 4) * 8 + 16 + 1024;
 }
 
 template <int EP>
@@ -605,7 +604,8 @@ int32_t mtfc_moe_gate_padded_experts(int32_t experts) { return padded_experts(ex
 int64_t mtfc_moe_gate_scratch_bytes(int64_t groups, int32_t group_size, int32_t experts) {
   if (groups < 0 || group_size < 1 || experts < 1) return 0;
   const int64_t tpg = (group_size + 63) / 64;   // the smaller of the two tile sizes
-  return groups * tpg * padded_experts(experts) * 4 + 16;
+  // per tile: column sums of the raw gates (float) and two rows of counts (int)
+  return groups * tpg * padded_experts(experts) * 4 * 3 + 16;
 }
 
 int mtfc_moe_gate_prepare(const float* w, int64_t m, int32_t experts, void* w3t_bf16, void* stream) {
@@ -638,7 +638,7 @@ int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups,
                 kMaxGateExperts, (long long)m, experts);
   if (policy == MTFC_MOE_POLICY_RANDOM && !noise)
     return fail(MTFC_ERR_SHAPE, "gate_top2: policy random needs the noise tensor");
-  if (policy < MTFC_MOE_POLICY_ALL || policy > MTFC_MOE_POLICY_RANDOM)
+  if (policy < MTFC_MOE_POLICY_ALL || policy > MTFC_MOE_POLICY_SWITCH)
     return fail(MTFC_ERR_SHAPE, "gate_top2: unknown policy %d", policy);
   if ((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(w3t_bf16)) % 16 != 0)
     return fail(MTFC_ERR_SHAPE, "gate_top2: buffers must be 16-byte aligned");
@@ -657,6 +657,7 @@ int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups,
   a.group_size = group_size;
   a.experts = experts;
   a.m = (int)m;
+  a.renormalize = policy != MTFC_MOE_POLICY_SWITCH;
   // 64-token tiles only when 128-token tiles would leave SMs without any tile: a
   // half-height tile halves the bytes a CTA keeps in flight, which costs more than
   // an uneven last round does
@@ -673,6 +674,15 @@ int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups,
   a.idx1 = idx1; a.idx2 = idx2; a.gate1 = gate1; a.gate2 = gate2;
   a.raw_gates = raw_gates;
   a.tile_sums = static_cast<float*>(scratch);
+  a.tile_counts = reinterpret_cast<int*>(a.tile_sums + a.num_tiles * ep);
+  a.rank1 = pos1;
+  a.rank2 = pos2;
+  a.policy = policy;
+  a.threshold = threshold;
+  a.noise = noise;
+  if ((long long)a.tiles_per_group * experts > 8192)
+    return fail(MTFC_ERR_UNSUPPORTED, "gate_top2: group of %d tokens with %d experts is too long "
+                "for the single-pass kernel; use the three-call form", group_size, experts);
   a.groups_done = reinterpret_cast<unsigned*>(
       static_cast<uint8_t*>(scratch) + mtfc_moe_gate_scratch_bytes(groups, group_size, experts) - 16);
   a.status = device_status_word();
@@ -684,10 +694,10 @@ int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups,
   if (rc != MTFC_OK) return rc;
 
   PositionArgs p;
-  p.group_size = group_size; p.experts = experts; p.capacity = capacity; p.policy = policy;
-  p.threshold = threshold; p.noise = noise;
+  p.group_size = group_size; p.experts = experts; p.capacity = capacity;
   p.idx1 = idx1; p.idx2 = idx2; p.pos1 = pos1; p.pos2 = pos2; p.gate1 = gate1; p.gate2 = gate2;
-  p.tile_sums = a.tile_sums; p.tiles_per_group = a.tiles_per_group; p.ep = ep;
+  p.tile_sums = a.tile_sums; p.tile_counts = a.tile_counts;
+  p.tiles_per_group = a.tiles_per_group; p.tile_rows = a.tile_rows; p.ep = ep;
   p.loss_per_group = loss_per_group;
   p.loss_mean = loss_mean;
   p.inv_groups_total = 1.0f / (float)(num_groups_total > 0 ? num_groups_total : groups);
@@ -696,7 +706,7 @@ int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups,
   p.round_bf16 = round_gates_to_bf16;
   int threads = 1024;
   while (threads > 32 && threads / 2 >= group_size) threads >>= 1;
-  const size_t base_smem = (size_t)(3 * experts + (threads / 32) * experts) * sizeof(int);
+  const size_t base_smem = (size_t)(2 * a.tiles_per_group * experts + experts) * sizeof(int);
   const size_t table_smem = (size_t)experts * capacity * sizeof(int);
   p.table_in_smem = slot_table && base_smem + table_smem <= 96 * 1024;
   const size_t smem = base_smem + (p.table_in_smem ? table_smem : 0);

@@ -717,9 +717,13 @@ class CudaMeshImpl(SlicedMeshImpl):
     return _PendingAllreduce(self, out, works)
 
   # GEMM on the compute stream, exchange by the copy engines on a second stream
-  # (mtfc_gemm_with_progress and friends); MTFC_PIPELINED_ALLREDUCE=0 switches it off,
-  # the single-kernel form (FUSED_ALLREDUCE) is then tried
-  PIPELINED_ALLREDUCE = os.environ.get("MTFC_PIPELINED_ALLREDUCE", "1") == "1"
+  # (mtfc_gemm_with_progress and friends).  Off by default: the copy engines do overlap
+  # the GEMM completely, but each chunk costs two cross-GPU handshakes and about eight
+  # dependent stream operations (~60 us measured per chunk at 2 GPUs), which at the
+  # benchmark's sizes (64-128 MiB outputs, 0.1-0.2 ms GEMMs) is slower than the
+  # single-kernel form; it pays for outputs of several hundred MiB.
+  # MTFC_PIPELINED_ALLREDUCE=1 switches it on.
+  PIPELINED_ALLREDUCE = os.environ.get("MTFC_PIPELINED_ALLREDUCE", "0") == "1"
   PIPELINE_MIN_BYTES = 4 << 20
   PIPELINE_MAX_CHUNKS = 8
 
@@ -935,16 +939,16 @@ class CudaMeshImpl(SlicedMeshImpl):
       ws.ctl = ctl
       ws.stage_ptrs, ws.out_ptrs, ws.flag_ptrs = ptr_array(part_h), ptr_array(out_h), ptr_array(flag_h)
       ws.rank, ws.nranks = members.index(pnum), len(members)
-      # How the partial products travel (see mtfc_gemm_allreduce_ex).  "auto": through
-      # the switch's multicast addresses (multimem) for groups of four and more where
-      # the fabric offers them - fewer bytes per link from four ranks up - else by
-      # peer loads from the owners' side ("pull"), which keeps NVLink out of the
-      # GEMM's epilogue.
+      # How the partial products travel (see mtfc_gemm_allreduce_ex).  "auto" is the
+      # form that measured fastest: remote epilogue stores ("push").  At 2 GPUs with a
+      # 128 MiB output: push 0.43 ms, pull 0.50, multimem 0.58 for a 0.20 ms GEMM (the
+      # switch-reduced form moves (1 + 1/n) x the output per direction, which only
+      # undercuts push's 2 (n-1)/n from four ranks up).
       ws.mc_stage = ws.mc_out = 0
       mc_s, mc_o = int(part_h.multicast_ptr or 0), int(out_h.multicast_ptr or 0)
       form = self.FUSED_EXCHANGE
       if form == "auto":
-        form = "multimem" if (len(members) >= 4 and mc_s and mc_o) else "pull"
+        form = "push"
       if form == "multimem" and not (mc_s and mc_o):
         form = "pull"
       if form == "multimem":

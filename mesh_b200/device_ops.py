@@ -37,7 +37,7 @@ _BINARY = {"add": 0, "sub": 1, "multiply": 2, "divide": 3, "maximum": 4, "minimu
 _COMPARISONS = frozenset(["less", "greater", "less_equal", "greater_equal", "equal",
                           "not_equal", "logical_and", "logical_or"])
 _REDUCE = {"SUM": 0, "MAX": 1, "MIN": 2}
-_POLICY = {"all": 0, "none": 1, "threshold": 2, "random": 3}
+_POLICY = {"all": 0, "none": 1, "threshold": 2, "random": 3, "switch": 4}
 
 
 def _contiguous_strides(shape):
@@ -735,7 +735,7 @@ class DeviceOps(object):
     cases form the logits with a GEMM first."""
     m, e = w.shape
     lead, s = tuple(x.shape[:-2]), x.shape[-2]
-    if (x.dtype.name == "bfloat16" and x.size > 0
+    if (x.dtype.name == "bfloat16" and x.size > 0 and ((s + 63) // 64) * e <= 8192
         and self._lib.mtfc_moe_gate_fused_supported(m, e) == 1):
       return self._moe_gate_fused(x, w, capacity, policy, threshold, noise, num_groups_total,
                                   want_table, want_raw)

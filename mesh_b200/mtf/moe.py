@@ -43,6 +43,11 @@ class HParams(object):
     self.moe_second_threshold_eval = 0.2
     self.moe_dropout_rate = 0.0
     self.moe_min_expert_capacity = 4
+    self.moe_switch_policy_train = "argmax"
+    self.moe_switch_policy_eval = "argmax"
+    self.moe_switch_dropout = 0.1
+    self.moe_switch_jitter = 1e-2
+    self.moe_z_loss = None
     self.moe_use_fused_kernels = True
     for k, v in kwargs.items():
       if not hasattr(self, k):
@@ -146,6 +151,48 @@ def _top_2_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate
   return dispatch_tensor, combine_tensor, loss, aux
 
 
+def _switch_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate_weights):
+  """Top-1 ("Switch") routing as the reference's op chain (moe.py:1184-1309):
+  softmax, top_1 with the raw gate kept as it is, first-come positions within the
+  expert's capacity, the same load-balancing loss as top-2 gating plus the
+  optional router z-loss.  Policies argmax, input_jitter and input_dropout;
+  "sample" needs a categorical sampler that is not lowered here."""
+  policy = hparams.moe_switch_policy_train if train else hparams.moe_switch_policy_eval
+  group_size_dim = inputs.shape.dims[-2]
+  gate_inputs = mtf.to_float(inputs)
+  if policy == "input_dropout":
+    gate_inputs = mtf.dropout(gate_inputs, is_training=train, keep_prob=1.0 - hparams.moe_switch_dropout)
+  elif train and policy == "input_jitter":
+    gate_inputs = layers.multiplicative_jitter(gate_inputs, hparams.moe_switch_jitter)
+  elif policy not in ("argmax", "input_jitter"):
+    raise ValueError("Unknown Switch gating policy %s" % policy)
+  gate_logits = layers.dense(gate_inputs, experts_dim, use_bias=False, kernel_weights=gate_weights,
+                             name="switch_gating")
+  raw_gates = mtf.softmax(gate_logits, experts_dim)
+  expert_gate, expert_index = mtf.top_1(raw_gates, experts_dim)
+  expert_mask = mtf.one_hot(expert_index, experts_dim, dtype=raw_gates.dtype)
+  density_1 = mtf.reduce_mean(expert_mask, reduced_dim=group_size_dim)
+  density_1_proxy = mtf.reduce_mean(raw_gates, reduced_dim=group_size_dim)
+  loss = mtf.reduce_mean(density_1_proxy * density_1) * float(experts_dim.size * experts_dim.size)
+  if train and hparams.moe_z_loss is not None:
+    log_z = mtf.reduce_logsumexp(gate_logits, experts_dim)
+    loss += mtf.reduce_mean(mtf.square(log_z)) * hparams.moe_z_loss
+  position_in_expert = mtf.cumsum(expert_mask, group_size_dim, exclusive=True) * expert_mask
+  expert_mask *= mtf.to_float(mtf.less(position_in_expert, float(expert_capacity_dim.size)))
+  expert_mask_flat = mtf.reduce_sum(expert_mask, reduced_dim=experts_dim)
+  position_flat = mtf.reduce_sum(position_in_expert, reduced_dim=experts_dim)
+  expert_gate *= expert_mask_flat
+  combine_tensor = (expert_gate * expert_mask_flat
+                    * mtf.one_hot(expert_index, experts_dim, dtype=raw_gates.dtype)
+                    * mtf.one_hot(mtf.to_int32(position_flat), expert_capacity_dim, dtype=raw_gates.dtype))
+  combine_tensor = mtf.cast(combine_tensor, inputs.dtype)
+  loss = mtf.cast(loss, inputs.dtype)
+  dispatch_tensor = mtf.cast(mtf.cast(combine_tensor, G.bool_), combine_tensor.dtype)
+  aux = dict(index_1=expert_index, position_1=mtf.to_int32(position_flat), gate_1=expert_gate,
+             raw_gates=raw_gates)
+  return dispatch_tensor, combine_tensor, loss, aux
+
+
 # -------------------------------------------------------------- fused gating
 class Top2GatingOperation(Operation):
   """Fused `_top_2_gating`: one kernel per slice instead of ~60 operations.
@@ -199,12 +246,14 @@ class Top2GatingOperation(Operation):
       m2 = mtf.one_hot(i2, experts_dim, dtype=raw.dtype)
       g1 = mtf.reduce_sum(raw * m1, reduced_dim=experts_dim)
       g2 = mtf.reduce_sum(raw * m2, reduced_dim=experts_dim)
-      denom = g1 + g2 + 1e-9
       keep1 = mtf.to_float(mtf.not_equal(g1_out, 0.0))
       keep2 = mtf.to_float(mtf.not_equal(g2_out, 0.0))
       density_1 = mtf.reduce_mean(m1, reduced_dim=group_size_dim)
       proxy = mtf.reduce_mean(raw, reduced_dim=group_size_dim)
       loss = mtf.reduce_mean(proxy * density_1) * float(experts_dim.size * experts_dim.size)
+      if self._policy == "switch":        # top-1 routing keeps the raw gate
+        return [g1 * keep1, g2 * 0.0, loss]
+      denom = g1 + g2 + 1e-9
       return [g1 / denom * keep1, g2 / denom * keep2, loss]
     dx, dw = mtf.gradients_by_recompute([x, w], chain, [grad_ys[4], grad_ys[5], grad_ys[6]])
     if dx is not None and dx.dtype != x.dtype:
@@ -374,22 +423,29 @@ def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, lay
   capacity_dim = Dimension("expert_capacity", capacity)
   experts_dim_unsplit = Dimension("expert_unsplit", experts_dim.size)
   batch_dim_unsplit = Dimension("batch_unsplit", num_groups_dim.size)
-  if hparams.moe_gating != "top_2":
-    raise ValueError("only top_2 gating is implemented, got %s" % hparams.moe_gating)
+  if hparams.moe_gating not in ("top_2", "switch"):
+    raise ValueError("unknown gating %s: top_2 and switch are implemented" % hparams.moe_gating)
   if gate_weights.shape.dims[-1].name != experts_dim_unsplit.name:
     gate_weights = mtf.reshape(gate_weights, Shape([gate_weights.shape.dims[0], experts_dim_unsplit]))
   if second_noise is not None:
     second_noise = mtf.reshape(second_noise, moe_input_dims[:-1])
-  elif _second_policy(hparams, train)[0] == "random":
+  elif hparams.moe_gating == "top_2" and _second_policy(hparams, train)[0] == "random":
     # the uniform draw of moe.py:1461-1465, one value per token
     second_noise = mtf.random_uniform(inputs.mesh, Shape(moe_input_dims[:-1]), dtype=G.float32)
 
   aux = {}
   fused = hparams.moe_use_fused_kernels
+  switch = hparams.moe_gating == "switch"
+  if switch:
+    # the single-pass kernel serves plain argmax routing; perturbed gate inputs and the
+    # router z-loss (which needs the logits) take the op chain
+    switch_policy = hparams.moe_switch_policy_train if train else hparams.moe_switch_policy_eval
+    plain = switch_policy == "argmax" or (switch_policy == "input_jitter" and not train)
+    fused = fused and plain and not (train and hparams.moe_z_loss is not None)
   if fused and hparams.moe_use_second_place_loss:
     raise ValueError("moe_use_second_place_loss is not available with the fused kernels")
   if fused:
-    policy, threshold = _second_policy(hparams, train)
+    policy, threshold = ("switch", 0.0) if switch else _second_policy(hparams, train)
     gating = Top2GatingOperation(inputs, gate_weights, experts_dim_unsplit, capacity, policy,
                                  threshold, second_noise=second_noise)
     i1, i2, p1, p2, g1, g2, loss_sum, slot_table = gating.outputs
@@ -399,9 +455,13 @@ def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, lay
     expert_inputs = MoeDispatchOperation(inputs, routing, experts_dim_unsplit, capacity_dim,
                                          slot_table=slot_table).outputs[0]
   else:
-    dispatch_tensor, combine_tensor, loss, aux = _top_2_gating(
-        inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights,
-        second_noise=second_noise)
+    if switch:
+      dispatch_tensor, combine_tensor, loss, aux = _switch_gating(
+          inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights)
+    else:
+      dispatch_tensor, combine_tensor, loss, aux = _top_2_gating(
+          inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights,
+          second_noise=second_noise)
     expert_inputs = mtf.einsum(
         [inputs, dispatch_tensor],
         Shape([outer_batch_dim, experts_dim_unsplit, num_groups_dim, capacity_dim, input_dim]))

@@ -1293,6 +1293,10 @@ class ShiftOperation(Operation):
     self._wrap = wrap
     self._outputs = [Tensor(self, x.shape, x.dtype)]
 
+  def gradient(self, grad_ys):
+    """The opposite shift (mesh_tensorflow/ops.py:3594-3596)."""
+    return [shift(grad_ys[0], -self._offset, self._dim, self._wrap)]
+
   def lower(self, lowering):
     impl = lowering.mesh_impl(self)
     ops = impl.slice_ops
@@ -1574,4 +1578,213 @@ def serialize_training_step(features, model_fn, batch_dim, num_splits, variables
       combined_outputs[k] = t if k not in combined_outputs or m == 0 else add(combined_outputs[k], t)
     combined_grads = grads if combined_grads is None else [add(a, b) for a, b in zip(combined_grads, grads)]
   return combined_grads, combined_outputs
+
+
+# ------------------------------------------------- concat / split / slice / pad
+def _resized(shape, dim_name, size):
+  return Shape([Dimension(d.name, size) if d.name == dim_name else d for d in shape.dims])
+
+
+def _dim_axis(x, dim_name, what):
+  names = [d.name for d in x.shape.dims]
+  if dim_name not in names:
+    raise ValueError("%s: %s has no dimension named %s" % (what, x.shape, dim_name))
+  return names.index(dim_name)
+
+
+def _not_split(lowering, op, dim_name, what):
+  if lowering.mesh_impl(op).tensor_dimension_to_mesh_axis(Dimension(dim_name, 0)) is not None:
+    raise ValueError("can't %s along split axis" % what)
+
+
+class ConcatOperation(Operation):
+  """tf.concat along a named dim (mesh_tensorflow/ops.py:2537-2583)."""
+
+  def __init__(self, xs, concat_dim_name, name=None):
+    super().__init__(xs, name=name or "concat")
+    self._concat_dim_name = concat_dim_name
+    self._axis = _dim_axis(xs[0], concat_dim_name, "concat")
+    if not all(_resized(x.shape, concat_dim_name, 0) == _resized(xs[0].shape, concat_dim_name, 0)
+               for x in xs):
+      raise ValueError("shapes are not compatible %s" % (xs,))
+    self._input_sizes = [x.shape.dims[self._axis].size for x in xs]
+    self._outputs = [Tensor(self, _resized(xs[0].shape, concat_dim_name, sum(self._input_sizes)),
+                            xs[0].dtype)]
+
+  def gradient(self, grad_ys):
+    return split(grad_ys[0], self.outputs[0].shape.dims[self._axis], self._input_sizes)
+
+  def lower(self, lowering):
+    _not_split(lowering, self, self._concat_dim_name, "concat")
+    impl = lowering.mesh_impl(self)
+    ops, axis = impl.slice_ops, self._axis
+    lowering.set_tensor_lowering(
+        self.outputs[0],
+        impl.slicewise(lambda *args: ops.concat(list(args), axis),
+                       *[lowering.tensors[x] for x in self.inputs]))
+
+
+def concat(xs, concat_dim_name, name=None):
+  """Concatenates along the dim named `concat_dim_name`, which must not be split."""
+  return ConcatOperation(xs, concat_dim_name, name).outputs[0]
+
+
+class SplitOperation(Operation):
+  """tf.split along a dim into given sizes (mesh_tensorflow/ops.py:2586-2648)."""
+
+  def __init__(self, x, split_dim, num_or_size_splits, name=None):
+    super().__init__([x], name=name or "split")
+    self._split_dim = split_dim
+    self._axis = x.shape.dims.index(split_dim)
+    if isinstance(num_or_size_splits, list):
+      self._output_sizes = list(num_or_size_splits)
+      if sum(self._output_sizes) != split_dim.size:
+        raise ValueError("Sizes do not add up %s %s" % (num_or_size_splits, split_dim))
+    else:
+      if split_dim.size % num_or_size_splits != 0:
+        raise ValueError("num_splits does not divide %s" % (split_dim,))
+      self._output_sizes = [split_dim.size // num_or_size_splits] * num_or_size_splits
+    self._outputs = [Tensor(self, _resized(x.shape, split_dim.name, size), x.dtype, index=i)
+                     for i, size in enumerate(self._output_sizes)]
+
+  def gradient(self, grad_ys):
+    grad_ys = [g if g is not None else zeros_like(o) for g, o in zip(grad_ys, self.outputs)]
+    return [concat(grad_ys, self._split_dim.name)]
+
+  def lower(self, lowering):
+    _not_split(lowering, self, self._split_dim.name, "split")
+    impl = lowering.mesh_impl(self)
+    ops, axis = impl.slice_ops, self._axis
+    sizes = self._output_sizes
+
+    def fn(xs):
+      shape = list(ops.shape(xs))
+      out, at = [], 0
+      for size in sizes:
+        begin = [0] * len(shape)
+        begin[axis] = at
+        extent = list(shape)
+        extent[axis] = size
+        out.append(ops.contiguous(ops.slice(xs, begin, extent)))
+        at += size
+      return tuple(out)
+    values = impl.slicewise(fn, lowering.tensors[self.inputs[0]])
+    for out, value in zip(self.outputs, values):
+      lowering.set_tensor_lowering(out, value)
+
+
+def split(x, split_dim, num_or_size_splits, name=None):
+  return SplitOperation(x, split_dim, num_or_size_splits, name=name).outputs
+
+
+class SliceOperation(Operation):
+  """tf.slice along one dim (mesh_tensorflow/ops.py:2758... mtf_slice 2723-2758)."""
+
+  def __init__(self, x, begin, size, slice_dim_name, name=None):
+    super().__init__([x], name=name or "slice")
+    self._axis = _dim_axis(x, slice_dim_name, "slice")
+    dim = x.shape.dims[self._axis]
+    if begin < 0 or size < 0 or begin + size > dim.size:
+      raise ValueError("slice [%d, %d) is outside %s" % (begin, begin + size, dim))
+    self._begin, self._size, self._slice_dim_name = begin, size, slice_dim_name
+    self._outputs = [Tensor(self, _resized(x.shape, slice_dim_name, size), x.dtype)]
+
+  def gradient(self, grad_ys):
+    total = self.inputs[0].shape.dims[self._axis].size
+    return [pad(grad_ys[0], [self._begin, total - self._size - self._begin], self._slice_dim_name)]
+
+  def lower(self, lowering):
+    _not_split(lowering, self, self._slice_dim_name, "slice")
+    impl = lowering.mesh_impl(self)
+    ops, axis, b, n = impl.slice_ops, self._axis, self._begin, self._size
+
+    def fn(xs):
+      shape = list(ops.shape(xs))
+      begin = [0] * len(shape)
+      begin[axis] = b
+      shape[axis] = n
+      return ops.contiguous(ops.slice(xs, begin, shape))
+    lowering.set_tensor_lowering(self.outputs[0], impl.slicewise(fn, lowering.tensors[self.inputs[0]]))
+
+
+def mtf_slice(x, begin, size, slice_dim_name, name=None):
+  """x[..., begin:begin+size, ...] along the named dim (must not be split)."""
+  return SliceOperation(x, begin, size, slice_dim_name, name=name).outputs[0]
+
+
+class PadOperation(Operation):
+  """tf.pad with zeros along one dim (mesh_tensorflow/ops.py:2651-2720)."""
+
+  def __init__(self, x, paddings, pad_dim_name, name=None):
+    super().__init__([x], name=name or "pad")
+    if len(paddings) != 2 or min(paddings) < 0:
+      raise ValueError("paddings must be [before, after], got %s" % (paddings,))
+    self._axis = _dim_axis(x, pad_dim_name, "pad")
+    self._paddings, self._pad_dim_name = list(paddings), pad_dim_name
+    size = x.shape.dims[self._axis].size + sum(paddings)
+    self._outputs = [Tensor(self, _resized(x.shape, pad_dim_name, size), x.dtype)]
+
+  def gradient(self, grad_ys):
+    size = self.inputs[0].shape.dims[self._axis].size
+    return [mtf_slice(grad_ys[0], self._paddings[0], size, self._pad_dim_name)]
+
+  def lower(self, lowering):
+    _not_split(lowering, self, self._pad_dim_name, "pad")
+    impl = lowering.mesh_impl(self)
+    ops, axis, (before, after) = impl.slice_ops, self._axis, self._paddings
+
+    def fn(xs):
+      shape = list(ops.shape(xs))
+      parts = []
+      for n in (before, None, after):
+        if n is None:
+          parts.append(xs)
+        elif n > 0:
+          z = list(shape)
+          z[axis] = n
+          parts.append(ops.fill(z, 0, ops.dtype(xs)))
+      return ops.concat(parts, axis) if len(parts) > 1 else xs
+    lowering.set_tensor_lowering(self.outputs[0], impl.slicewise(fn, lowering.tensors[self.inputs[0]]))
+
+
+def pad(x, paddings, dim_name, name=None):
+  """Zero padding [before, after] along the named dim (must not be split)."""
+  return PadOperation(x, paddings, dim_name, name=name).outputs[0]
+
+
+def halo_exchange(x, blocks_dim, block_size_dim, halo_size, wrap=False):
+  """Each block concatenated with the margins of its neighbours along `blocks_dim`
+  (mesh_tensorflow/ops.py:6381-6418): `block_size_dim` grows by 2 * halo_size.  With
+  `blocks_dim` split over a mesh axis the shifts are collective permutes between
+  neighbouring processors (MeshImpl.receive)."""
+  if halo_size == 0:
+    return x
+  block_size = block_size_dim.size
+  partial_size = halo_size % block_size
+  num_complete_blocks = halo_size // block_size
+  parts = [x]
+  for i in range(1, num_complete_blocks + 1):
+    parts = [shift(x, i, blocks_dim, wrap)] + parts + [shift(x, -i, blocks_dim, wrap)]
+  if partial_size > 0:
+    left_margin = mtf_slice(x, 0, partial_size, block_size_dim.name)
+    right_margin = mtf_slice(x, block_size - partial_size, partial_size, block_size_dim.name)
+    parts = ([shift(right_margin, num_complete_blocks + 1, blocks_dim, wrap)] + parts
+             + [shift(left_margin, -(num_complete_blocks + 1), blocks_dim, wrap)])
+  return concat(parts, block_size_dim.name)
+
+
+def left_halo_exchange(x, blocks_dim, block_size_dim, halo_size, wrap=False):
+  """As halo_exchange, margins from the left neighbours only (ops.py:6421-6452)."""
+  if halo_size == 0:
+    return x
+  block_size = block_size_dim.size
+  partial_size = halo_size % block_size
+  num_complete_blocks = halo_size // block_size
+  parts = [x]
+  for i in range(1, num_complete_blocks + 1):
+    parts = [shift(x, i, blocks_dim, wrap)] + parts
+  if partial_size > 0:
+    right_margin = mtf_slice(x, block_size - partial_size, partial_size, block_size_dim.name)
+    parts = [shift(right_margin, num_complete_blocks + 1, blocks_dim, wrap)] + parts
+  return concat(parts, block_size_dim.name)
 

@@ -39,10 +39,14 @@ def gating_from_raw(raw, capacity, policy="all", threshold=0.2, noise=None):
   raw2 = raw * (np.float32(1.0) + (-mask1.astype(np.float32)))
   i2 = np.argmax(raw2, axis=-1).astype(np.int32)
   g2 = np.take_along_axis(raw2, i2[..., None].astype(np.int64), axis=-1)[..., 0]
-  denom = (g1 + g2) + np.float32(1e-9)
-  recip = np.float32(1.0) / denom
-  g1 = g1 * recip
-  g2 = g2 * recip
+  if policy == "switch":
+    # top-1 routing (_switch_gating, moe.py:1184-1309): the raw gate, no second expert
+    g2 = np.zeros_like(g2)
+  else:
+    denom = (g1 + g2) + np.float32(1e-9)
+    recip = np.float32(1.0) / denom
+    g1 = g1 * recip
+    g2 = g2 * recip
 
   # load-balancing loss per group (moe.py:1420-1424), on pre-capacity masks
   density = np.sum(mask1.astype(np.float32), axis=1, dtype=np.float32) * np.float32(1.0 / s_)
@@ -52,7 +56,7 @@ def gating_from_raw(raw, capacity, policy="all", threshold=0.2, noise=None):
 
   if policy == "all":
     m2 = np.ones((g_, s_), dtype=bool)
-  elif policy == "none":
+  elif policy in ("none", "switch"):
     m2 = np.zeros((g_, s_), dtype=bool)
   elif policy == "threshold":
     m2 = g2 > np.float32(threshold)

@@ -175,3 +175,112 @@ def test_moe_random_policy_draws_its_own_noise():
     return [out, loss]
   (out, loss), _ = _lower(fn, "all:2", "batch:all;experts:all")
   assert out.shape == (4, 16, 8) and np.isfinite(out).all() and np.isfinite(loss)
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_switch_routing_layer(fused):
+  """Top-1 ("Switch") routing: the single-operation form and the reference's op chain
+  agree with each other and with a direct numpy restatement of the routing."""
+  r = rng(77)
+  b, l, d, f, e = 4, 32, 8, 16, 4
+  x = r.standard_normal((b, l, d)).astype(np.float32)
+  wg = r.standard_normal((d, e)).astype(np.float32)
+  wi = (r.standard_normal((e, d, f)) / 3).astype(np.float32)
+  wo = (r.standard_normal((e, f, d)) / 4).astype(np.float32)
+
+  def fn(mesh):
+    X = mtf.import_tf_tensor(mesh, x, "batch:4,length:32,d_model:8", dtype=mtf.float32)
+    WG = mtf.import_tf_tensor(mesh, wg, "d_model:8,expert_unsplit:4")
+    WI = mtf.import_tf_tensor(mesh, wi, "experts:4,d_model:8,d_ff:16")
+    WO = mtf.import_tf_tensor(mesh, wo, "experts:4,d_ff:16,d_model:8")
+    hp = mtf.moe.HParams(moe_group_size=32, moe_gating="switch", moe_use_fused_kernels=fused,
+                         moe_capacity_factor_train=1.0)
+    out, loss, aux = mtf.moe.transformer_moe_layer_v1(
+        X, mtf.Dimension("d_model", 8), hp, True, "all:2", "batch:all;experts:all", WG, WI, WO,
+        return_aux=True)
+    grads = mtf.gradients([mtf.reduce_sum(mtf.square(out)) + loss * 5.0], [X, WG, WI])
+    return [out, loss, aux["index_1"], aux["position_1"], aux["gate_1"]] + grads
+  got, _ = _lower(fn, "all:2", "batch:all;experts:all")
+  out, loss, i1, p1, g1 = got[:5]
+  # direct restatement: 4 groups of 32 tokens, capacity 32 * 1.0 / 4 = 8
+  logits = x.astype(np.float64) @ wg
+  raw = np.exp(logits - logits.max(-1, keepdims=True))
+  raw /= raw.sum(-1, keepdims=True)
+  idx = raw.argmax(-1)
+  np.testing.assert_array_equal(i1.reshape(b, l), idx)
+  ref_out = np.zeros((b, l, d))
+  for g in range(b):
+    seen = np.zeros(e, int)
+    for s in range(l):
+      ex = idx[g, s]
+      pos = seen[ex]
+      seen[ex] += 1
+      assert int(p1.reshape(b, l)[g, s]) == pos
+      if pos < 8:
+        h = np.maximum(x[g, s].astype(np.float64) @ wi[ex], 0)
+        ref_out[g, s] = raw[g, s, ex] * (h @ wo[ex])
+        np.testing.assert_allclose(g1.reshape(b, l)[g, s], raw[g, s, ex], rtol=1e-5)
+      else:
+        assert g1.reshape(b, l)[g, s] == 0
+  np.testing.assert_allclose(out, ref_out, rtol=1e-4, atol=1e-5)
+  dens = np.stack([np.bincount(idx[g], minlength=e) / l for g in range(b)])
+  ref_loss = (raw.mean(1) * dens).mean() * e * e * 1e-2
+  np.testing.assert_allclose(loss, ref_loss, rtol=1e-5)
+
+
+def test_switch_routing_fused_gradients_equal_the_chain():
+  r = rng(78)
+  x = r.standard_normal((4, 16, 8)).astype(np.float32)
+  wg = r.standard_normal((8, 4)).astype(np.float32)
+  wi = (r.standard_normal((4, 8, 16)) / 3).astype(np.float32)
+  wo = (r.standard_normal((4, 16, 8)) / 4).astype(np.float32)
+  res = []
+  for fused in (True, False):
+    def fn(mesh):
+      X = mtf.import_tf_tensor(mesh, x, "batch:4,length:16,d_model:8", dtype=mtf.float32)
+      WG = mtf.import_tf_tensor(mesh, wg, "d_model:8,expert_unsplit:4")
+      WI = mtf.import_tf_tensor(mesh, wi, "experts:4,d_model:8,d_ff:16")
+      WO = mtf.import_tf_tensor(mesh, wo, "experts:4,d_ff:16,d_model:8")
+      hp = mtf.moe.HParams(moe_group_size=16, moe_gating="switch", moe_use_fused_kernels=fused,
+                           moe_capacity_factor_train=1.5)
+      out, loss = mtf.moe.transformer_moe_layer_v1(X, mtf.Dimension("d_model", 8), hp, True, "all:1", "",
+                                                   WG, WI, WO)
+      total = mtf.reduce_sum(mtf.square(out)) + loss * 10.0
+      return [total] + mtf.gradients([total], [X, WG, WI, WO])
+    res.append(_lower(fn, "all:1", "")[0])
+  for a, b_ in zip(*res):
+    np.testing.assert_allclose(a, b_, rtol=2e-4, atol=2e-5)
+
+
+@pytest.mark.parametrize("mesh_shape,layout", [("all:1", ""), ("all:4", "blocks:all"), ("a:2,b:2", "batch:a;blocks:b")])
+@pytest.mark.parametrize("halo,wrap", [(1, False), (3, True), (5, False), (8, True)])
+def test_halo_exchange(mesh_shape, layout, halo, wrap):
+  """Blocks of a sequence extended by their neighbours' margins (whole neighbouring
+  blocks when the halo exceeds the block), with the block dim split over the mesh so
+  that the shifts are collective permutes; against direct numpy indexing."""
+  r = rng(79)
+  b, nb, bs, d = 2, 4, 4, 3
+  x = r.standard_normal((b, nb, bs, d)).astype(np.float32)
+
+  def fn(mesh):
+    X = mtf.import_tf_tensor(mesh, x, "batch:2,blocks:4,block_size:4,d:3", dtype=mtf.float32)
+    y = mtf.halo_exchange(X, X.shape.dims[1], X.shape.dims[2], halo, wrap=wrap)
+    yl = mtf.left_halo_exchange(X, X.shape.dims[1], X.shape.dims[2], halo, wrap=wrap)
+    dX, = mtf.gradients([mtf.reduce_sum(y * y) * 0.5], [X])
+    return [y, yl, dX]
+  (y, yl, dX), _ = _lower(fn, mesh_shape, layout)
+  flat = x.reshape(b, nb * bs, d)
+  n = nb * bs
+  ref = np.zeros((b, nb, bs + 2 * halo, d))
+  count = np.zeros((b, n, d))
+  for blk in range(nb):
+    for j in range(bs + 2 * halo):
+      pos = blk * bs - halo + j
+      if wrap:
+        pos %= n
+      if 0 <= pos < n:
+        ref[:, blk, j] = flat[:, pos]
+        count[:, pos] += 1
+  np.testing.assert_array_equal(y, ref)
+  np.testing.assert_array_equal(yl, ref[:, :, :bs + halo])
+  np.testing.assert_allclose(dX.reshape(b, n, d), flat * count, rtol=1e-6)

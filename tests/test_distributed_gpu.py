@@ -163,6 +163,7 @@ def _worker(rank, world, port, out_dir):
       return outs
     piped = CudaMeshImpl(mesh_shape, "d_ff:all", list(range(world)))
     piped.OVERLAP_MIN_ROWS = 1
+    piped.PIPELINED_ALLREDUCE = True
     piped.PIPELINE_MIN_BYTES = 1
     piped.FUSED_ALLREDUCE = False
     ref_rows = ffn_rows(ora)

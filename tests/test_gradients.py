@@ -76,8 +76,8 @@ def test_gradient_rules():
   assert not idx.operation.has_gradient or idx.dtype.is_integer
   ds, = mtf.gradients([mtf.reduce_sum(mtf.stack([x, x * 3.0], "s"))], [x])
   np.testing.assert_allclose(_lower(g, m, [ds], "all:1", "")[0], np.full((2, 3), 4.0))
-  with pytest.raises(NotImplementedError):
-    mtf.gradients([mtf.reduce_sum(mtf.shift(x, 1, x.shape.dims[1], False))], [x])
+  dsh, = mtf.gradients([mtf.reduce_sum(mtf.shift(x, 1, x.shape.dims[1], False) * w)], [x])
+  np.testing.assert_allclose(_lower(g, m, [dsh], "all:1", "")[0], [[1, 1, 0], [1, 1, 0]])
 
 
 def _moe_total(arrays, mesh_shape, layout, grads, fused=False):

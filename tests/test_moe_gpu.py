@@ -44,7 +44,7 @@ def _gating_case(dev_ops, groups, s, e, capacity, policy, threshold, seed):
   return spec, got
 
 
-@pytest.mark.parametrize("policy", ["all", "none", "threshold", "random"])
+@pytest.mark.parametrize("policy", ["all", "none", "threshold", "random", "switch"])
 @pytest.mark.parametrize("groups,s,e,cap", [(3, 1024, 32, 40), (2, 300, 8, 20), (5, 64, 4, 4),
                                             (1, 1024, 64, 1024), (2, 257, 16, 3)])
 def test_gating_bit_exact_given_logits(dev_ops, groups, s, e, cap, policy):
@@ -85,7 +85,7 @@ def test_gate_logits_on_tensor_cores(dev_ops):
   assert rel_err(got, ref) < 1e-5
 
 
-@pytest.mark.parametrize("policy", ["all", "threshold", "random"])
+@pytest.mark.parametrize("policy", ["all", "threshold", "random", "switch"])
 @pytest.mark.parametrize("groups,s,m,e,cap", [(3, 1024, 1024, 32, 40), (2, 300, 256, 8, 20),
                                               (5, 64, 64, 4, 4), (1, 1024, 512, 64, 1024),
                                               (2, 257, 72, 16, 3), (150, 128, 128, 32, 8)])
@@ -110,7 +110,7 @@ def test_single_pass_gating_kernel(dev_ops, groups, s, m, e, cap, policy):
   loss, table, raw = float(dev_ops.to_host(out[6])), dev_ops.to_host(out[7]), dev_ops.to_host(out[8])
   assert rel_err(raw, spec["raw_gates"]) < 1e-5
   safe = np.all(_safe_tokens(spec["raw_gates"], margin=1e-5), axis=-1)
-  if policy != "all":
+  if policy in ("threshold", "random"):
     # a gate within 1e-5 of the policy's cut may fall on either side of it
     cut = 0.2 if policy == "threshold" else noise * 0.2
     safe &= np.all(np.abs(_renormalised_second_gate(spec) - cut) > 1e-5, axis=-1)
