@@ -52,6 +52,7 @@ struct GateFusedArgs {
   int renormalize;  // 0: gate_1 is the raw top-1 gate and gate_2 is 0 (top-1 routing)
   int tile_rows;  // tokens per tile: 128, or 64 when that fills the SMs more evenly
   int tiles_per_group;
+  int big_per_group;  // tiles_per_group / R rounded up: passes a CTA makes over a group
   long long num_tiles;
   int stages;
   int* idx1;
@@ -85,10 +86,24 @@ __device__ __forceinline__ void epi_warps_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(32 * G_EPI_WARPS) : "memory");
 }
 
+// Programmatic dependent launch: the three kernels of one gating call follow one
+// another closely and each is short, so the next one is allowed onto the SMs while
+// its predecessor still runs (launch_dependents) and does its set-up there; it
+// touches global memory only after griddepcontrol.wait, which returns when the
+// predecessor grid has completed and its writes are visible.  Both instructions do
+// nothing in a kernel that was launched without the attribute.
+__device__ __forceinline__ void let_next_kernel_start() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void wait_for_previous_kernel() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // fp32 gate kernel [m, E] -> bf16 [3*EP, m]: row p*EP + e holds part p (hi, mid,
 // lo) of column e; rows of experts in [E, EP) are zero.
 __global__ void split_gate_weights_kmajor_kernel(const float* __restrict__ w, long long m, int e,
                                                  int ep, __nv_bfloat16* __restrict__ out) {
+  let_next_kernel_start();
   const long long n = m * ep;
   const long long step = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step) {
@@ -109,18 +124,22 @@ __global__ void split_gate_weights_kmajor_kernel(const float* __restrict__ w, lo
   }
 }
 
-template <int EP>
+// R tiles of 128 tokens per pass share every K block of the gate kernel in shared
+// memory (R = 2 needs 3 * EP <= 128 accumulator columns per tile).
+template <int EP, int R>
 __global__ void __launch_bounds__(G_THREADS, 1)
 gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                 const GateFusedArgs a) {
   constexpr int N = 3 * EP;
   constexpr int W_STAGE_BYTES = N * GBK * 2;
+  constexpr int XS_BYTES = R * X_STAGE_BYTES;   // activations per stage
+  static_assert(R == 1 || 3 * EP <= 128, "two tiles per pass need 3*EP <= 128 accumulator columns");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const uint32_t smem_base = smem_u32(smem);
   const int ST = a.stages;
-  const uint32_t off_w = (uint32_t)ST * X_STAGE_BYTES;
+  const uint32_t off_w = (uint32_t)ST * XS_BYTES;
   const uint32_t off_sums = off_w + (uint32_t)ST * W_STAGE_BYTES;
   const uint32_t off_cnt = off_sums + 2 * G_EPI_WARPS * EP * 4;
   const uint32_t off_bar = off_cnt + 2 * 2 * G_EPI_WARPS * EP * 4;
@@ -162,6 +181,9 @@ gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int num_kb = (a.m + GBK - 1) / GBK;
+  // barriers, TMEM and descriptors are in place: from here on global memory is touched
+  wait_for_previous_kernel();
+  let_next_kernel_start();
   if (blockIdx.x == 0 && threadIdx.x == 0) *a.groups_done = 0u;
 
   if (warp == 0) {
@@ -170,17 +192,19 @@ gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       for (long long t = blockIdx.x; t < a.num_tiles && ok; t += gridDim.x) {
-        const long long g = t / a.tiles_per_group;
-        const int c = (int)(t - g * a.tiles_per_group);
+        const long long g = t / a.big_per_group;
+        const int c = (int)(t - g * a.big_per_group) * R;
         const long long row0 = g * a.group_size + (long long)c * a.tile_rows;
         // with 64-token tiles the box is half a stage: rows 64..127 of the stage keep
         // whatever they held, and the accumulator rows they produce are never read
         const uint32_t x_bytes = (uint32_t)a.tile_rows * GBK * 2;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(full_bar(stage), x_bytes + W_STAGE_BYTES);
-          tma_load_3d(smem_base + stage * X_STAGE_BYTES, &map_x, full_bar(stage), kb * GBK,
-                      (int)row0, 0);
+          mbar_expect_tx(full_bar(stage), R * x_bytes + W_STAGE_BYTES);
+#pragma unroll
+          for (int h = 0; h < R; ++h)   // a second tile past the group's end is loaded and ignored
+            tma_load_3d(smem_base + stage * XS_BYTES + h * X_STAGE_BYTES, &map_x, full_bar(stage),
+                        kb * GBK, (int)(row0 + (long long)h * a.tile_rows), 0);
           tma_load_3d(smem_base + off_w + stage * W_STAGE_BYTES, &map_w, full_bar(stage), kb * GBK,
                       0, 0);
           if (++stage == ST) { stage = 0; phase ^= 1; }
@@ -206,13 +230,17 @@ gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sx = smem_base + stage * X_STAGE_BYTES;
+          const uint32_t sx = smem_base + stage * XS_BYTES;
           const uint32_t sw = smem_base + off_w + stage * W_STAGE_BYTES;
 #pragma unroll
           for (int ks = 0; ks < GBK / G_UMMA_K; ++ks) {
-            const uint64_t da = make_smem_desc(sx + ks * G_UMMA_K * 2, 16, 1024);
             const uint64_t db = make_smem_desc(sw + ks * G_UMMA_K * 2, 16, 1024);
-            tc_mma_bf16(d_tmem, da, db, idesc, (kb | ks) != 0 ? 1u : 0u);
+#pragma unroll
+            for (int h = 0; h < R; ++h) {
+              const uint64_t da = make_smem_desc(sx + h * X_STAGE_BYTES + ks * G_UMMA_K * 2, 16, 1024);
+              tc_mma_bf16(d_tmem + (uint32_t)(h * (G_ACC_STRIDE / 2)), da, db, idesc,
+                          (kb | ks) != 0 ? 1u : 0u);
+            }
           }
           tc_commit(empty_bar(stage));
           if (++stage == ST) { stage = 0; phase ^= 1; }
@@ -232,21 +260,26 @@ gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     for (long long t = blockIdx.x; t < a.num_tiles && ok; t += gridDim.x, ++local) {
       const int buf = (int)(local & 1);
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
-      const long long g = t / a.tiles_per_group;
-      const int c = (int)(t - g * a.tiles_per_group);
+      const long long g = t / a.big_per_group;
+      const int c0 = (int)(t - g * a.big_per_group) * R;
       const int row = q * 32 + lane;
-      const int s_in_group = c * a.tile_rows + row;
-      const bool live = row < a.tile_rows && s_in_group < a.group_size;
-      const long long tok = g * a.group_size + s_in_group;
       ok = __all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), acc_phase, abort_flag));
       if (!ok) {
-        // a warp that gave up still counts at this tile's column-sum barrier, so
+        // a warp that gave up still counts at the column-sum barriers of this pass, so
         // that warps which got through the wait are not left standing there
-        asm volatile("bar.arrive 1, %0;" ::"n"(32 * G_EPI_WARPS) : "memory");
+        for (int h = 0; h < R; ++h) asm volatile("bar.arrive 1, %0;" ::"n"(32 * G_EPI_WARPS) : "memory");
         break;
       }
       tc_fence_after();
-      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * G_ACC_STRIDE);
+#pragma unroll 1
+      for (int h = 0; h < R; ++h) {
+      const int c = c0 + h;                      // tile of the group this half is
+      const long long slot = local * R + h;      // picks the double-buffered scratch rows
+      const int s_in_group = c * a.tile_rows + row;
+      const bool live = row < a.tile_rows && s_in_group < a.group_size;
+      const long long tok = g * a.group_size + s_in_group;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) +
+                             (uint32_t)(buf * G_ACC_STRIDE + h * (G_ACC_STRIDE / 2));
       float r[EP];
 #pragma unroll
       for (int ch = 0; ch < EP / 16; ++ch) {
@@ -259,10 +292,12 @@ gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         for (int j = 0; j < 16; ++j)
           r[ch * 16 + j] = (__uint_as_float(hi[j]) + __uint_as_float(mid[j])) + __uint_as_float(lo[j]);
       }
-      // the accumulator is in registers: hand it back before the arithmetic
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
+      if (h == R - 1) {
+        // the accumulators are in registers: hand the buffer back before the arithmetic
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tmem_empty_bar(buf));
+      }
 
       float mx = r[0];
 #pragma unroll
@@ -303,8 +338,8 @@ gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       }
       // rank among the tile's earlier tokens with the same choice: inside the warp by
       // match/popc, across the four warps through per-warp counts (added after the barrier)
-      int* cnt_a = warp_cnt + (((local & 1) * 2 + 0) * G_EPI_WARPS + ew) * EP;
-      int* cnt_b = warp_cnt + (((local & 1) * 2 + 1) * G_EPI_WARPS + ew) * EP;
+      int* cnt_a = warp_cnt + (((slot & 1) * 2 + 0) * G_EPI_WARPS + ew) * EP;
+      int* cnt_b = warp_cnt + (((slot & 1) * 2 + 1) * G_EPI_WARPS + ew) * EP;
       for (int e = lane; e < EP; e += 32) { cnt_a[e] = 0; cnt_b[e] = 0; }
       __syncwarp();
       const unsigned lt_mask = (1u << lane) - 1u;
@@ -351,7 +386,7 @@ gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           r[0] += __shfl_xor_sync(0xffffffffu, r[0], off);
         }
       }
-      float* mine = warp_sums + ((local & 1) * G_EPI_WARPS + ew) * EP;
+      float* mine = warp_sums + ((slot & 1) * G_EPI_WARPS + ew) * EP;
       if (EP >= 32) {
 #pragma unroll
         for (int i = 0; i < EP / 32; ++i) mine[lane * (EP / 32) + i] = r[i];
@@ -361,8 +396,8 @@ gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       epi_warps_sync();
       {
         // warps earlier in token order: lane quarter q' < q sits in epilogue warp (q' + 2) & 3
-        const int* all_a = warp_cnt + ((local & 1) * 2 + 0) * G_EPI_WARPS * EP;
-        const int* all_b = warp_cnt + ((local & 1) * 2 + 1) * G_EPI_WARPS * EP;
+        const int* all_a = warp_cnt + ((slot & 1) * 2 + 0) * G_EPI_WARPS * EP;
+        const int* all_b = warp_cnt + ((slot & 1) * 2 + 1) * G_EPI_WARPS * EP;
         for (int qq = 0; qq < q; ++qq) {
           const int w = (qq + 2) & 3;
           if (live) rank1 += all_a[w * EP + i1];
@@ -374,16 +409,18 @@ gate_top2_fused(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
       }
       const int tid = ew * 32 + lane;
-      if (tid < EP) {
-        const float* ws = warp_sums + (local & 1) * G_EPI_WARPS * EP;
+      if (tid < EP && c < a.tiles_per_group) {   // a half past the group's end has no slot
+        const long long tile = g * a.tiles_per_group + c;
+        const float* ws = warp_sums + (slot & 1) * G_EPI_WARPS * EP;
         // rows in token order: warps 2..5 hold lane quarters 2, 3, 0, 1
         const float s = ((ws[2 * EP + tid] + ws[3 * EP + tid]) + ws[0 * EP + tid]) + ws[1 * EP + tid];
-        a.tile_sums[t * EP + tid] = s;
-        const int* ca = warp_cnt + ((local & 1) * 2 + 0) * G_EPI_WARPS * EP + tid;
-        const int* cb = warp_cnt + ((local & 1) * 2 + 1) * G_EPI_WARPS * EP + tid;
-        a.tile_counts[(t * 2 + 0) * EP + tid] = ca[0] + ca[EP] + ca[2 * EP] + ca[3 * EP];
-        a.tile_counts[(t * 2 + 1) * EP + tid] = cb[0] + cb[EP] + cb[2 * EP] + cb[3 * EP];
+        a.tile_sums[tile * EP + tid] = s;
+        const int* ca = warp_cnt + ((slot & 1) * 2 + 0) * G_EPI_WARPS * EP + tid;
+        const int* cb = warp_cnt + ((slot & 1) * 2 + 1) * G_EPI_WARPS * EP + tid;
+        a.tile_counts[(tile * 2 + 0) * EP + tid] = ca[0] + ca[EP] + ca[2 * EP] + ca[3 * EP];
+        a.tile_counts[(tile * 2 + 1) * EP + tid] = cb[0] + cb[EP] + cb[2 * EP] + cb[3 * EP];
       }
+      }   // halves
     }
     if (!ok && lane == 0 && a.status) atomicExch(a.status, MTFC_ERR_TIMEOUT);
   }
@@ -428,7 +465,7 @@ struct PositionArgs {
 // group's tiles (one thread per expert) gives every tile's base, and
 // position = base + rank.  Second choices start after the kept first choices
 // (moe.py:1488-1490).  Shared memory: base1[tiles][E], base2[tiles][E], tot1[E],
-// slots[E*C] (if a table is built there).
+// sums[tiles][E], slots[E*C] (if a table is built there).
 __global__ void __launch_bounds__(1024)
 top2_positions_kernel(PositionArgs a) {
   extern __shared__ int ismem[];
@@ -437,39 +474,50 @@ top2_positions_kernel(PositionArgs a) {
   int* base1 = ismem;
   int* base2 = base1 + K * E;
   int* tot1 = base2 + K * E;
+  float* sums = reinterpret_cast<float*>(tot1 + E);   // [K][E]
   const int g = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const long long tok0 = (long long)g * S;
   // the group's slot table is built in shared memory when it fits there, else in place
-  int* slots = a.table_in_smem ? tot1 + E : a.table + (long long)g * E * C;
+  int* slots = a.table_in_smem ? reinterpret_cast<int*>(sums + K * E) : a.table + (long long)g * E * C;
+  wait_for_previous_kernel();
 
+  // every tile's counts and column sums in one round of loads, then the scans run
+  // out of shared memory
+  for (int i = tid; i < K * E; i += T) {
+    const int k = i / E, e = i - k * E;
+    const long long tile = (long long)g * K + k;
+    base1[i] = a.tile_counts[(tile * 2 + 0) * a.ep + e];
+    base2[i] = a.tile_counts[(tile * 2 + 1) * a.ep + e];
+    sums[i] = a.tile_sums[tile * a.ep + e];
+  }
+  if (a.table)
+    for (int i = tid; i < E * C; i += T) slots[i] = -1;
+  __syncthreads();
   for (int e = tid; e < E; e += T) {
-    const int* tc = a.tile_counts + ((long long)g * K * 2) * a.ep + e;
     int run = 0;
     for (int k = 0; k < K; ++k) {
+      const int n = base1[k * E + e];
       base1[k * E + e] = run;
-      run += tc[(long long)(2 * k) * a.ep];
+      run += n;
     }
     tot1[e] = run;
     int run2 = min(run, C);   // second choices queue behind the kept first choices
     for (int k = 0; k < K; ++k) {
+      const int n = base2[k * E + e];
       base2[k * E + e] = run2;
-      run2 += tc[(long long)(2 * k + 1) * a.ep];
+      run2 += n;
     }
+    float proxy = 0.f;
+    for (int k = 0; k < K; ++k) proxy += sums[k * E + e];
+    sums[e] = proxy;   // row 0 now holds the group's column sums
   }
-  if (a.table)
-    for (int i = tid; i < E * C; i += T) slots[i] = -1;
   __syncthreads();
 
   if (warp == 0) {   // load-balancing loss on the pre-capacity counts (moe.py:1420-1424)
     float part = 0.f;
     const float inv_s = 1.0f / (float)S;
-    for (int e = lane; e < E; e += 32) {
-      float proxy = 0.f;
-      const float* ts = a.tile_sums + ((long long)g * K) * a.ep + e;
-      for (int k = 0; k < K; ++k) proxy += ts[(long long)k * a.ep];
-      part += (proxy * inv_s) * ((float)tot1[e] * inv_s);
-    }
+    for (int e = lane; e < E; e += 32) part += (sums[e] * inv_s) * ((float)tot1[e] * inv_s);
     for (int s = 16; s > 0; s >>= 1) part += __shfl_xor_sync(0xffffffffu, part, s);
     if (lane == 0) a.loss_per_group[g] = part * (1.0f / (float)E) * (float)(E * E);
   }
@@ -556,34 +604,64 @@ int gate_encode(CUtensorMap* map, const void* base, long long m, long long rows,
   return MTFC_OK;
 }
 
+// Launches `kernel` so that it may start while the previous kernel of the stream is
+// still running (the kernel itself waits before it touches global memory).  If the
+// attribute is refused the launch is repeated as an ordinary one.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_overlapping(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem,
+                               cudaStream_t s, Args&&... args) {
+  static bool refused = false;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = refused ? 0 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+  if (e != cudaSuccess && !refused) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(s, &cap);
+    if (cap != cudaStreamCaptureStatusNone) return e;   // a failed capture cannot be retried here
+    (void)cudaGetLastError();
+    refused = true;
+    cfg.numAttrs = 0;
+    e = cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+  }
+  return e;
+}
+
 int padded_experts(int experts) { return experts <= 16 ? 16 : (experts <= 32 ? 32 : 64); }
 
-int gate_stages(int ep) {
-  const int per_stage = X_STAGE_BYTES + 3 * ep * GBK * 2;
+int gate_stages(int ep, int r) {
+  const int per_stage = r * X_STAGE_BYTES + 3 * ep * GBK * 2;
   int st = (200 * 1024) / per_stage;
   return st > MAX_STAGES ? MAX_STAGES : st;
 }
 
-size_t gate_fused_smem(int ep) {
-  return (size_t)gate_stages(ep) * (X_STAGE_BYTES + 3 * ep * GBK * 2) + 2 * G_EPI_WARPS * ep * 4 +
+size_t gate_fused_smem(int ep, int r) {
+  return (size_t)gate_stages(ep, r) * (r * X_STAGE_BYTES + 3 * ep * GBK * 2) + 2 * G_EPI_WARPS * ep * 4 +
          2 * 2 * G_EPI_WARPS * ep * 4 + (2 * MAX_STAGES + 4) * 8 + 16 + 1024;
 }
 
-template <int EP>
+template <int EP, int R>
 int launch_gate_fused(const CUtensorMap& mx, const CUtensorMap& mw, const GateFusedArgs& a,
                       cudaStream_t s) {
   static bool attr_set[64] = {false};
   int dev = 0;
   MTFC_CUDA(cudaGetDevice(&dev));
-  const size_t smem = gate_fused_smem(EP);
+  const size_t smem = gate_fused_smem(EP, R);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    MTFC_CUDA(cudaFuncSetAttribute(gate_top2_fused<EP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    MTFC_CUDA(cudaFuncSetAttribute(gate_top2_fused<EP, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)smem));
     attr_set[dev] = true;
   }
   const int sms = sm_count();
   const unsigned grid = (unsigned)(a.num_tiles < sms ? a.num_tiles : sms);
-  gate_top2_fused<EP><<<grid, G_THREADS, smem, s>>>(mx, mw, a);
+  MTFC_CUDA(launch_overlapping(gate_top2_fused<EP, R>, grid, G_THREADS, smem, s, mx, mw, a));
   MTFC_LAUNCH_CHECK("gate_top2_fused");
   return MTFC_OK;
 }
@@ -664,8 +742,16 @@ int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups,
   const long long t128 = groups * ((group_size + 127) / 128);
   a.tile_rows = t128 < sm_count() ? 64 : 128;
   a.tiles_per_group = (group_size + a.tile_rows - 1) / a.tile_rows;
-  a.num_tiles = groups * a.tiles_per_group;
-  a.stages = gate_stages(ep);
+  // Tiles per pass over the gate kernel.  The kernel can take two (their accumulators
+  // fit side by side for up to 32 experts), which halves the gate kernel's L2 reads;
+  // on the 65536-token, 32-expert shape that measured slower (36.5 us against 32.1 us:
+  // the pass's two epilogues run one after the other and the last one is exposed), so
+  // every shape takes one.
+  const int r = 1;
+  a.big_per_group = (a.tiles_per_group + r - 1) / r;
+  a.num_tiles = groups * a.big_per_group;
+  a.stages = gate_stages(ep, r);
+
   CUtensorMap map_x, map_w;
   int rc = gate_encode(&map_x, x_bf16, m, tokens, a.tile_rows, "gate activations");
   if (rc != MTFC_OK) return rc;
@@ -674,7 +760,7 @@ int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups,
   a.idx1 = idx1; a.idx2 = idx2; a.gate1 = gate1; a.gate2 = gate2;
   a.raw_gates = raw_gates;
   a.tile_sums = static_cast<float*>(scratch);
-  a.tile_counts = reinterpret_cast<int*>(a.tile_sums + a.num_tiles * ep);
+  a.tile_counts = reinterpret_cast<int*>(a.tile_sums + groups * a.tiles_per_group * ep);
   a.rank1 = pos1;
   a.rank2 = pos2;
   a.policy = policy;
@@ -687,9 +773,9 @@ int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups,
       static_cast<uint8_t*>(scratch) + mtfc_moe_gate_scratch_bytes(groups, group_size, experts) - 16);
   a.status = device_status_word();
   switch (ep) {
-    case 16: rc = launch_gate_fused<16>(map_x, map_w, a, s); break;
-    case 32: rc = launch_gate_fused<32>(map_x, map_w, a, s); break;
-    default: rc = launch_gate_fused<64>(map_x, map_w, a, s); break;
+    case 16: rc = launch_gate_fused<16, 1>(map_x, map_w, a, s); break;
+    case 32: rc = launch_gate_fused<32, 1>(map_x, map_w, a, s); break;
+    default: rc = launch_gate_fused<64, 1>(map_x, map_w, a, s); break;
   }
   if (rc != MTFC_OK) return rc;
 
@@ -706,7 +792,7 @@ int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups,
   p.round_bf16 = round_gates_to_bf16;
   int threads = 1024;
   while (threads > 32 && threads / 2 >= group_size) threads >>= 1;
-  const size_t base_smem = (size_t)(2 * a.tiles_per_group * experts + experts) * sizeof(int);
+  const size_t base_smem = (size_t)(3 * a.tiles_per_group * experts + experts) * sizeof(int);
   const size_t table_smem = (size_t)experts * capacity * sizeof(int);
   p.table_in_smem = slot_table && base_smem + table_smem <= 96 * 1024;
   const size_t smem = base_smem + (p.table_in_smem ? table_smem : 0);
@@ -720,7 +806,7 @@ int mtfc_moe_gate_top2(const void* x_bf16, const void* w3t_bf16, int64_t groups,
       attr_set[dev] = true;
     }
   }
-  top2_positions_kernel<<<(unsigned)groups, threads, smem, s>>>(p);
+  MTFC_CUDA(launch_overlapping(top2_positions_kernel, (unsigned)groups, (unsigned)threads, smem, s, p));
   MTFC_LAUNCH_CHECK("top2_positions_kernel");
   count_launch(2);
   return MTFC_OK;

@@ -181,3 +181,49 @@ def _moe_worker(rank, world, port, out_dir):
 def test_moe_layer_with_alltoall_over_gloo(tmp_path):
   mp.spawn(_moe_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
   assert sorted(os.listdir(str(tmp_path))) == ["ok0", "ok1"]
+
+
+def test_move_packs_on_the_source_device():
+  """CudaMeshImpl._move with distinct device ordinals in one process: a strided slice
+  must be packed by a kernel launched on the device that holds it, and only then
+  copied across; no kernel may be given pointers of another device."""
+  from mesh_b200.cuda_mesh_impl import CudaMeshImpl
+
+  class FakeBuf(object):
+    def __init__(self, device):
+      self.device = device
+      self.moves = []
+
+    def __getitem__(self, _):
+      return self
+
+    def to(self, dev):
+      self.moves.append(dev)
+      return FakeBuf(dev)
+
+  class FakeSlice(object):
+    def __init__(self, device, contiguous):
+      self.buf, self.device = FakeBuf(device), device
+      self.shape, self.dtype, self.offset, self.size = (4, 4), "f", 0, 16
+      self.is_contiguous = contiguous
+
+  class FakeOps(object):
+    def __init__(self):
+      self.device = "cuda:0"
+      self.calls = []
+
+    def contiguous(self, s):
+      self.calls.append((self.device, s.device))      # (device the kernel runs on, data's device)
+      return FakeSlice(s.device, True)
+
+  impl = object.__new__(CudaMeshImpl)
+  impl._devices = ["cuda:0", "cuda:1"]
+  impl._ops = FakeOps()
+  impl._device_array = lambda buf, shape, dtype: ("array", buf.device, tuple(shape))
+  src = FakeSlice("cuda:1", contiguous=False)          # a strided view living on device 1
+  moved = impl._move(src, 0)                           # wanted on processor 0's device
+  assert impl._ops.calls == [("cuda:1", "cuda:1")]     # packed where the data is
+  assert moved == ("array", "cuda:0", (4, 4))
+  assert impl._ops.device == "cuda:0"                  # and the ops object ends on the destination
+  same = FakeSlice("cuda:0", contiguous=True)
+  assert impl._move(same, 0) is same                   # already there: untouched
