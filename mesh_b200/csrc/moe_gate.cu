@@ -482,6 +482,17 @@ top2_positions_kernel(PositionArgs a) {
   int* slots = a.table_in_smem ? reinterpret_cast<int*>(sums + K * E) : a.table + (long long)g * E * C;
   wait_for_previous_kernel();
 
+  // this thread's first token, requested now so that it arrives while the scans run
+  int i1_first = 0, i2_first = 0, r1_first = 0, r2_first = -1;
+  float g1_first = 0.f, g2_first = 0.f;
+  if (tid < S) {
+    i1_first = a.idx1[tok0 + tid];
+    i2_first = a.idx2[tok0 + tid];
+    r1_first = a.pos1[tok0 + tid];
+    r2_first = a.pos2[tok0 + tid];
+    g1_first = a.gate1[tok0 + tid];
+    g2_first = a.gate2[tok0 + tid];
+  }
   // every tile's counts and column sums in one round of loads, then the scans run
   // out of shared memory
   for (int i = tid; i < K * E; i += T) {
@@ -525,15 +536,17 @@ top2_positions_kernel(PositionArgs a) {
   for (int s = tid; s < S; s += T) {
     const long long t = tok0 + s;
     const int k = s / a.tile_rows;
-    const int i1 = a.idx1[t], i2 = a.idx2[t];
-    const int r2 = a.pos2[t];
+    // the first round's token was fetched before the scans
+    const bool pre = s == tid;
+    const int i1 = pre ? i1_first : a.idx1[t], i2 = pre ? i2_first : a.idx2[t];
+    const int r1 = pre ? r1_first : a.pos1[t], r2 = pre ? r2_first : a.pos2[t];
     const bool m2 = r2 >= 0;
-    const int p1 = base1[k * E + i1] + a.pos1[t];
+    const int p1 = base1[k * E + i1] + r1;
     const int p2 = m2 ? base2[k * E + i2] + r2 : 0;
     const bool keep1 = p1 < C;
     const bool keep2 = m2 && p2 < C;
-    const float g1 = keep1 ? a.gate1[t] : 0.f;
-    const float g2 = keep2 ? a.gate2[t] : 0.f;
+    const float g1 = keep1 ? (pre ? g1_first : a.gate1[t]) : 0.f;
+    const float g2 = keep2 ? (pre ? g2_first : a.gate2[t]) : 0.f;
     a.pos1[t] = p1;
     a.pos2[t] = p2;
     a.gate1[t] = g1;
