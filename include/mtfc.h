@@ -188,6 +188,33 @@ int mtfc_signal_peers(void* const* peer_counters, int32_t n, int64_t index, void
 int mtfc_add_n_bf16(const void* const* sources, int32_t n, void* dst, int64_t elements,
                     void* stream);
 
+/* MeshImpl.alltoall (placement_mesh_impl.py:228-242, 490-510) between the ranks
+ * of one mesh-axis group as one kernel over peer-mapped memory: every rank
+ * reads its slice in place and stores part r of it straight into rank r's
+ * output buffer where the concatenation puts it - no pack and no unpack pass.
+ * Every rank of the group makes the same call, with
+ *   src              its slice (16-byte aligned),
+ *   peer_out[i]      rank i's output buffer as mapped into this process,
+ *   peer_flags[i]    rank i's flag array (mtfc_alltoall_peer_flag_bytes bytes,
+ *                    zeroed once when allocated),
+ *   dims / strides   one part described as `ndims` <= 4 leading extents with their
+ *                    byte strides in the source slice and in the output, followed
+ *                    by a row of row_bytes that is contiguous in both,
+ *   src_part_stride  part r starts r * src_part_stride bytes into src,
+ *   dst_part_stride  the part received from rank s lands s * dst_part_stride
+ *                    bytes into the output,
+ *   ctl              two zero-initialised uint32 of this rank (launch count, ticket).
+ * All byte counts are multiples of 16.  The kernel waits for the peers' "buffer
+ * free" signal before it stores and for their "stored" signal before it ends;
+ * both waits are bounded (mtfc_alltoall_peer_set_wait_ms, default ~3 s) and raise
+ * MTFC_ERR_TIMEOUT for mtfc_device_status when they run out. */
+int64_t mtfc_alltoall_peer_flag_bytes(void);
+int mtfc_alltoall_peer_set_wait_ms(int ms);
+int mtfc_alltoall_peer(const void* src, void* const* peer_out, void* const* peer_flags,
+                       int32_t nranks, int32_t rank, int32_t ndims, const int64_t* dims,
+                       const int64_t* src_strides, const int64_t* dst_strides, int64_t row_bytes,
+                       int64_t src_part_stride, int64_t dst_part_stride, uint32_t* ctl, void* stream);
+
 /* K1f on the tensor cores: fp32 [batch, rows, k] (element strides s_*) -> bf16
  * [batch, rows, 6k], every value split into three bf16 terms laid along K
  * (pattern 0 for the left operand, 1 for the right) so that one mtfc_gemm over

@@ -85,6 +85,10 @@ def _declare(lib):
       "mtfc_wait_counters": [vp, i32, ctypes.c_uint32, vp, vp],
       "mtfc_signal_peers": [ctypes.POINTER(vp), i32, i64, vp],
       "mtfc_add_n_bf16": [ctypes.POINTER(vp), i32, vp, i64, vp],
+      "mtfc_alltoall_peer_flag_bytes": [],
+      "mtfc_alltoall_peer_set_wait_ms": [ctypes.c_int],
+      "mtfc_alltoall_peer": [vp, ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i32, i32, p_i64, p_i64,
+                             p_i64, i64, i64, i64, vp, vp],
       "mtfc_split_bf16x3": [vp, i64, i64, i64, vp, i64, i64, i64, i32, vp],
       "mtfc_attention_set_variant": [i32],
       "mtfc_attention_supported": [i64, p_i64, p_i64, p_i64, p_i64],
@@ -124,8 +128,8 @@ def _declare(lib):
   }
   for name, argtypes in signatures.items():
     fn = getattr(lib, name)
-    fn.restype = i64 if name in ("mtfc_gemm_allreduce_stage_bytes",
-                                 "mtfc_moe_gate_scratch_bytes") else ctypes.c_int
+    fn.restype = i64 if name in ("mtfc_gemm_allreduce_stage_bytes", "mtfc_moe_gate_scratch_bytes",
+                                 "mtfc_alltoall_peer_flag_bytes") else ctypes.c_int
     fn.argtypes = argtypes
 
 

@@ -1,6 +1,6 @@
 """Per-configuration measurements beside bench.py's headline number.
 
-  python -m mesh_b200.bench_configs --config moe|einsum_fp32|attention|collectives|ffn_train [--gpus N]
+  python -m mesh_b200.bench_configs --config moe|moe_train|einsum_fp32|attention|collectives|ffn_train [--gpus N]
 
 `measure_moe`, `measure_attention` and `measure_einsum_fp32` return records
 (dicts) that bench.py places in its JSON line; the command line above prints
@@ -558,6 +558,67 @@ def config_ffn_train(args):
         stepping="eager" if args.eager else "cuda-graph replay")
 
 
+def config_moe_train(args):
+  """Forward and backward of the top-2 MoE layer at the benchmark shape: the
+  output, then dx, d(gate kernel), dwi, dwo from a given d(output) through
+  mtf.gradients (gating, dispatch and combine gradients on their own kernels,
+  six expert GEMMs per step instead of two), replayed as a CUDA graph."""
+  n, rank, local_rank = _init(args)
+  c = MOE
+  B, L, M, E, H, S, C = (c[k] for k in "BLMEHSC")
+  pk = peaks()
+  mesh_shape, layout = "all:%d" % n, "batch:all;experts:all"
+  impl = CudaMeshImpl(mesh_shape, layout, list(range(n)) if n > 1 else [local_rank], distributed=n > 1)
+  ops = impl.slice_ops
+  b_loc, e_loc = B // n, E // n
+  x, wg, wi, wo = moe_inputs(rows=list(range(rank * b_loc, (rank + 1) * b_loc)),
+                             experts=range(rank * e_loc, (rank + 1) * e_loc))
+  to_bf16 = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(torch.bfloat16)
+  laid = lambda t, dt: impl.LaidOutTensor([ops.from_host(t, dt)])
+  lx, lwg = laid(to_bf16(x), mtf.bfloat16), laid(wg, mtf.float32)
+  ldy = laid(to_bf16(np.stack([_normal([MOE_SEED, 4, b], (L, M))
+                               for b in range(rank * b_loc, (rank + 1) * b_loc)])), mtf.bfloat16)
+  lwi, lwo = laid(to_bf16(np.stack(wi)), mtf.bfloat16), laid(to_bf16(np.stack(wo)), mtf.bfloat16)
+  del x, wi, wo
+  g = mtf.Graph()
+  mesh = mtf.Mesh(g, "mesh")
+  act = "batch:%d,length:%d,d_model:%d" % (B, L, M)
+  X = mtf.import_laid_out_tensor(mesh, lx, act, mtf.bfloat16)
+  DY = mtf.import_laid_out_tensor(mesh, ldy, act, mtf.bfloat16)
+  WG = mtf.import_laid_out_tensor(mesh, lwg, "d_model:%d,expert_unsplit:%d" % (M, E), mtf.float32)
+  WI = mtf.import_laid_out_tensor(mesh, lwi, "experts:%d,d_model:%d,d_ff:%d" % (E, M, H), mtf.bfloat16)
+  WO = mtf.import_laid_out_tensor(mesh, lwo, "experts:%d,d_ff:%d,d_model:%d" % (E, H, M), mtf.bfloat16)
+  hp = mtf.moe.HParams(moe_group_size=S, moe_second_policy_train="all")
+  out, loss = mtf.moe.transformer_moe_layer_v1(X, mtf.Dimension("d_model", M), hp, True, mesh_shape,
+                                               layout, WG, WI, WO)
+  grads = mtf.gradients([out], [X, WG, WI, WO], grad_ys=[DY])
+
+  def step():
+    low = mtf.Lowering(g, {mesh: impl})
+    return [low.tensors[t].to_laid_out_tensor() for t in [out] + grads]
+  before = nat.launch_count()
+  step()
+  launches = nat.launch_count() - before
+  impl.synchronize()
+  run = step
+  if not args.eager:
+    _, run = impl.capture(step)
+  ms, _ = time_steps(run, args.iters, 3, n)
+  impl.synchronize()
+  tokens = B * L
+  flops = 3 * 2.0 * (E * (tokens // S) * C) * M * H * 2.0
+  if rank == 0:
+    _emit(config="moe_train", quantity="top-2 MoE layer forward + backward (dx, dwg, dwi, dwo)",
+          mesh=mesh_shape, layout=layout, n_gpus=n, ms_per_step=ms, tokens_per_s=tokens / (ms * 1e-3),
+          expert_tflops=flops / (ms * 1e-3) / 1e12, expert_flops_per_step=flops,
+          frac_of_peak=flops / (ms * 1e-3) / 1e12 / (pk["tflops"] * n), peak_tflops=pk["tflops"],
+          peak_source=pk["source"], libmtfc_launches_per_step=launches,
+          stepping="eager" if args.eager else "cuda-graph replay")
+  impl.release_graphs()
+  if n > 1:
+    leave()
+
+
 def config_collectives(args):
   """allreduce / allconcat / alltoall bus bandwidth over one mesh axis.
   --mesh names the mesh (default all:N) and --axis the axis the collectives run
@@ -589,7 +650,7 @@ def config_collectives(args):
 
 def main():
   ap = argparse.ArgumentParser()
-  ap.add_argument("--config", required=True, choices=["moe", "einsum_fp32", "attention", "collectives", "ffn_train"])
+  ap.add_argument("--config", required=True, choices=["moe", "moe_train", "einsum_fp32", "attention", "collectives", "ffn_train"])
   ap.add_argument("--gpus", type=int, default=1)
   ap.add_argument("--iters", type=int, default=10)
   ap.add_argument("--eager", action="store_true")
@@ -601,7 +662,7 @@ def main():
   if not torch.cuda.is_available():
     sys.exit("needs a CUDA device")
   {"moe": config_moe, "einsum_fp32": config_einsum_fp32, "attention": config_attention,
-   "ffn_train": config_ffn_train,
+   "ffn_train": config_ffn_train, "moe_train": config_moe_train,
    "collectives": config_collectives}[args.config](args)
 
 

@@ -393,6 +393,10 @@ class SlicedMeshImpl(mtf.MeshImpl):
     merged[concat_axis] *= n
     return self.LaidOutTensor([ops.reshape(ops.transpose(gathered, perm), merged)])
 
+  def _peer_alltoall(self, s, pg, members, pnum, split_axis, concat_axis):
+    """Hook: an alltoall of slice `s` without pack / unpack passes, or None."""
+    return None
+
   def _dist_alltoall(self, x, mesh_axis, split_axis, concat_axis):
     import torch
     import torch.distributed as dist
@@ -401,6 +405,9 @@ class SlicedMeshImpl(mtf.MeshImpl):
     pnum = self._local_pnums[0]
     ops = self._ops_for(pnum)
     s = x.tensor_list[0]
+    fast = self._peer_alltoall(s, pg, members, pnum, split_axis, concat_axis)
+    if fast is not None:
+      return self.LaidOutTensor([fast])
     shape = list(s.shape)
     part = list(shape)
     part[split_axis] //= n
@@ -451,6 +458,45 @@ class _PeerWorkspace(object):
   """Buffers of one fused einsum+allreduce shape (see CudaMeshImpl._peer_workspace)."""
   __slots__ = ("tensors", "handles", "out_tensor", "ctl", "stage_ptrs", "out_ptrs", "flag_ptrs",
                "rank", "nranks", "mc_stage", "mc_out", "exchange")
+
+
+def alltoall_peer_plan(shape, itemsize, n, split_axis, concat_axis):
+  """How mtfc_alltoall_peer walks a contiguous slice of `shape` whose
+  `split_axis` is cut in n parts that are concatenated along `concat_axis`:
+  `(out_shape, lead, row_bytes, src_part_stride, dst_part_stride)`, where `lead`
+  lists (extent, source byte stride, output byte stride) of the dims of one part
+  in front of the row, the row being everything from the later of the two axes
+  on (contiguous in the source and in the output).  None when the rows are not
+  multiples of 16 bytes, shorter than 256 bytes, or more than four dims lead."""
+  shape = [int(d) for d in shape]
+  part = list(shape)
+  part[split_axis] //= n
+  out_shape = list(part)
+  out_shape[concat_axis] *= n
+
+  def strides(dims):
+    st, run = [], itemsize
+    for d in reversed(dims):
+      st.append(run)
+      run *= d
+    return st[::-1]
+  sstr, dstr = strides(shape), strides(out_shape)
+  ax = max(split_axis, concat_axis)
+  row_bytes = itemsize
+  for d in part[ax:]:
+    row_bytes *= d
+  if row_bytes % 16 != 0 or row_bytes < 256:
+    return None
+  lead = [(part[k], sstr[k], dstr[k]) for k in range(ax) if part[k] != 1]
+  if len(lead) > 4:
+    return None
+  return (out_shape, lead, row_bytes, part[split_axis] * sstr[split_axis],
+          part[concat_axis] * dstr[concat_axis])
+
+
+class _AlltoallWorkspace(object):
+  """Buffers of one peer-memory alltoall size (see CudaMeshImpl._alltoall_workspace)."""
+  __slots__ = ("tensors", "handles", "out_tensor", "ctl", "out_ptrs", "flag_ptrs")
 
 
 class _PipelineWorkspace(object):
@@ -896,6 +942,86 @@ class CudaMeshImpl(SlicedMeshImpl):
       return ops.einsum(equation, a, b, gemm_hook=hook)
     except HookDeclined:
       return None
+
+  # The alltoall as one kernel over peer-mapped memory (mtfc_alltoall_peer): every rank
+  # stores its parts straight into the peers' output buffers in the concatenated
+  # layout.  MTFC_PEER_ALLTOALL=0 selects the library alltoall with its pack and unpack
+  # passes, which also serves slices under 64 KiB, rows that are not multiples of 16
+  # bytes, and processes without peer mappings.
+  PEER_ALLTOALL = os.environ.get("MTFC_PEER_ALLTOALL", "1") == "1"
+  PEER_ALLTOALL_MIN_BYTES = 64 * 1024
+
+  def _alltoall_workspace(self, pg, members, pnum, nbytes):
+    """Peer-mapped output buffer of `nbytes` plus the flag array, per group and
+    size (created collectively on first use).  None when symmetric memory is
+    unavailable."""
+    import ctypes
+    import torch
+    import torch.distributed as dist
+    from mesh_b200 import _native as nat
+    key = (tuple(members), nbytes)
+    if not hasattr(self, "_a2a_ws"):
+      self._a2a_ws = {}
+    if key in self._a2a_ws:
+      return self._a2a_ws[key]
+    ws = None
+    try:
+      import torch.distributed._symmetric_memory as symm
+      dev = torch.device("cuda", torch.cuda.current_device())
+      out_t = symm.empty(nbytes, dtype=torch.uint8, device=dev)
+      out_h = symm.rendezvous(out_t, pg)
+      flag_t = symm.empty(int(nat.lib().mtfc_alltoall_peer_flag_bytes()), dtype=torch.uint8, device=dev)
+      flag_h = symm.rendezvous(flag_t, pg)
+      flag_t.zero_()
+      ctl = torch.zeros(2, dtype=torch.int32, device=dev)
+      torch.cuda.synchronize()
+      dist.barrier(group=pg)
+      if int(out_h.rank) != members.index(pnum) or int(out_h.world_size) != len(members):
+        raise RuntimeError("symmetric-memory rank %d/%d does not match mesh group position"
+                           % (out_h.rank, out_h.world_size))
+
+      def ptr_array(handle):
+        ptrs = list(handle.buffer_ptrs)
+        return (ctypes.c_void_p * len(ptrs))(*[ctypes.c_void_p(int(p)) for p in ptrs])
+      ws = _AlltoallWorkspace()
+      ws.tensors, ws.handles = (out_t, flag_t), (out_h, flag_h)
+      ws.out_tensor, ws.ctl = out_t, ctl
+      ws.out_ptrs, ws.flag_ptrs = ptr_array(out_h), ptr_array(flag_h)
+    except Exception as e:  # pylint: disable=broad-except
+      import warnings
+      warnings.warn("peer memory for the alltoall unavailable (%r); using NCCL" % (e,))
+      ws = None
+    self._a2a_ws[key] = ws
+    return ws
+
+  def _peer_alltoall(self, s, pg, members, pnum, split_axis, concat_axis):
+    """The peer-memory alltoall of slice `s`, or None when it does not apply."""
+    import ctypes
+    import torch
+    from mesh_b200 import _native as nat
+    from mesh_b200.device_ops import _TORCH
+    n = len(members)
+    nbytes = s.size * s.dtype.itemsize
+    if not self.PEER_ALLTOALL or n > 8 or nbytes < self.PEER_ALLTOALL_MIN_BYTES:
+      return None
+    plan = alltoall_peer_plan(s.shape, s.dtype.itemsize, n, split_axis, concat_axis)
+    if plan is None:
+      return None
+    out_shape, lead, row_bytes, src_part_stride, dst_part_stride = plan
+    ws = self._alltoall_workspace(pg, members, pnum, nbytes)
+    if ws is None:
+      return None
+    ops = self._ops_for(pnum)
+    src = ops.contiguous(s)
+    i64s = lambda vals: (ctypes.c_int64 * max(1, len(vals)))(*vals)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    nat.check(nat.lib().mtfc_alltoall_peer(
+        ctypes.c_void_p(src.ptr), ws.out_ptrs, ws.flag_ptrs, n, members.index(pnum), len(lead),
+        i64s([d for d, _, _ in lead]), i64s([a for _, a, _ in lead]), i64s([b for _, _, b in lead]),
+        row_bytes, src_part_stride, dst_part_stride, ctypes.c_void_p(ws.ctl.data_ptr()), stream))
+    shared = self._device_array(ws.out_tensor.view(_TORCH[s.dtype.name]), out_shape, s.dtype)
+    # the buffer is this group's for every alltoall of this size: hand back a copy
+    return _fresh_copy(ops, shared)
 
   def _peer_workspace(self, pg, members, pnum, m, n):
     """Peer-mapped staging / output / flag buffers for an [m, n] bf16 GEMM that

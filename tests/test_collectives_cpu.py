@@ -227,3 +227,52 @@ def test_move_packs_on_the_source_device():
   assert impl._ops.device == "cuda:0"                  # and the ops object ends on the destination
   same = FakeSlice("cuda:0", contiguous=True)
   assert impl._move(same, 0) is same                   # already there: untouched
+
+
+def _walk_like_the_kernel(slices, plan, itemsize):
+  """What mtfc_alltoall_peer stores, replayed over byte arrays: rank `me` copies, for
+  every destination, every row of its part from the source offset to the output offset."""
+  out_shape, lead, row_bytes, src_part_stride, dst_part_stride = plan
+  n = len(slices)
+  outs = [np.zeros(int(np.prod(out_shape)) * itemsize, np.uint8) for _ in range(n)]
+  for me, s in enumerate(slices):
+    src = np.ascontiguousarray(s).view(np.uint8).reshape(-1)
+    rows = int(np.prod([d for d, _, _ in lead])) if lead else 1
+    for dest in range(n):
+      for row in range(rows):
+        soff, doff, rest = dest * src_part_stride, me * dst_part_stride, row
+        for d, ss, ds in reversed(lead):
+          i, rest = rest % d, rest // d
+          soff += i * ss
+          doff += i * ds
+        outs[dest][doff:doff + row_bytes] = src[soff:soff + row_bytes]
+  return outs
+
+
+@pytest.mark.parametrize("shape,n", [((8, 16, 128), 2), ((8, 16, 128), 4), ((2, 8, 4, 6, 64), 2),
+                                      ((1, 32, 8, 40, 64), 8), ((16, 64), 4)])
+def test_alltoall_peer_plan_moves_every_part_to_its_place(shape, n):
+  """The (dims, strides, row) description handed to mtfc_alltoall_peer, replayed in
+  numpy for every rank, gives the oracle's alltoall for every (split, concat) pair."""
+  from mesh_b200.cuda_mesh_impl import alltoall_peer_plan
+  from oracle.numpy_mesh_impl import NumpyMeshImpl
+  from oracle.numpy_ops import Arr
+  r = rng(77)
+  slices = [r.standard_normal(shape).astype(np.float32) for _ in range(n)]
+  ora = NumpyMeshImpl("all:%d" % n, "")
+  x = ora.LaidOutTensor([Arr(v.copy(), mtf.float32) for v in slices])
+  planned = 0
+  for split_axis in range(len(shape)):
+    if shape[split_axis] % n:
+      continue
+    for concat_axis in range(len(shape)):
+      plan = alltoall_peer_plan(shape, 4, n, split_axis, concat_axis)
+      if plan is None:
+        continue
+      planned += 1
+      want = ora.alltoall(x, 0, split_axis, concat_axis).tensor_list
+      got = _walk_like_the_kernel(slices, plan, 4)
+      assert all(b % 16 == 0 for _, a, c in plan[1] for b in (a, c)) and plan[2] % 16 == 0
+      for dest in range(n):
+        np.testing.assert_array_equal(got[dest].view(np.float32).reshape(plan[0]), want[dest].a)
+  assert planned >= 1

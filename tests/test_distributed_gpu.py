@@ -60,6 +60,36 @@ def _worker(rank, world, port, out_dir):
     for offset, wrap in ((1, False), (-1, True)):
       check(ora.shift_by_n_processors(a, 0, offset, wrap), impl.shift_by_n_processors(b, 0, offset, wrap))
 
+    # the alltoall as one kernel over peer memory (mtfc_alltoall_peer): every (split,
+    # concat) pair, three calls in a row on the same buffers and flags, a bf16 tensor of
+    # the MoE layer's shape, and a recorded call replayed
+    nat_a2a = __import__("mesh_b200._native", fromlist=["x"])
+    peer = CudaMeshImpl(mesh_shape, "d_ff:all", list(range(world)))
+    peer.PEER_ALLTOALL_MIN_BYTES = 1
+    big = [r.standard_normal((8, 16, 128)).astype(np.float32) for _ in range(world)]
+    a2 = ora.LaidOutTensor([Arr(v.copy(), mtf.float32) for v in big])
+    b2 = peer.LaidOutTensor([ops.from_host(big[rank], mtf.float32)])
+    for sa in range(3):
+      for ca in range(3):
+        want = ora.alltoall(a2, 0, sa, ca)
+        for _ in range(3):
+          check(want, peer.alltoall(b2, 0, sa, ca))
+    from oracle.numpy_ops import round_to_bf16
+    routed = [round_to_bf16(r.standard_normal((2, 8, 4, 6, 64)).astype(np.float32)) for _ in range(world)]
+    a3 = ora.LaidOutTensor([Arr(v.copy(), mtf.bfloat16) for v in routed])
+    b3 = peer.LaidOutTensor([ops.from_host(routed[rank], mtf.bfloat16)])
+    check(ora.alltoall(a3, 0, 1, 2), peer.alltoall(b3, 0, 1, 2))
+    check(ora.alltoall(a3, 0, 2, 1), peer.alltoall(b3, 0, 2, 1))
+    used = list(getattr(peer, "_a2a_ws", {}).values())
+    assert len(used) >= 2 and all(w is not None for w in used), "the peer-memory alltoall did not run"
+    want = ora.alltoall(a2, 0, 1, 0)
+    res, run = peer.capture(lambda: peer.alltoall(b2, 0, 1, 0))
+    for _ in range(3):
+      run()
+      check(want, res)
+    nat_a2a.device_status()   # raises if a bounded wait ran out
+    peer.release_graphs()
+
     def ffn(backend):
       rr = rng(2)
       g = mtf.Graph()

@@ -1,4 +1,5 @@
-"""The bounded waits of the fused GEMM + allreduce kernel run out cleanly.
+"""The bounded waits of the kernels that wait on other ranks run out cleanly
+(the fused GEMM + allreduce, the peer-memory alltoall).
 
 One GPU plays rank 0 of a group of two whose second member never launches:
 all "peer" buffers are ordinary local allocations that nobody ever signals.
@@ -72,3 +73,57 @@ def test_peer_wait_runs_out_and_context_survives(cuda_device):
   nat.check(L.mtfc_gemm(ctypes.byref(d), At.data_ptr(), Bt.data_ptr(), C.data_ptr(), stream))
   nat.device_status()
   assert rel_err(C.float().cpu().numpy(), ref) < 2e-2
+
+
+def test_alltoall_peer_single_rank_and_wait_that_runs_out(cuda_device):
+  """mtfc_alltoall_peer alone on one GPU.  A group of one is a strided copy (its
+  own signals satisfy its waits); as rank 0 of a group of two whose peer never
+  launches, the "buffer free" wait runs out: nothing is stored, the status word
+  reads MTFC_ERR_TIMEOUT, the context stays usable."""
+  import torch
+  from mesh_b200 import _native as nat
+  L = nat.lib()
+  nat.device_status()
+  stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+  i64s = lambda vals: (ctypes.c_int64 * max(1, len(vals)))(*vals)
+  r = rng(62)
+  x = torch.from_numpy(r.standard_normal((6, 5, 64)).astype(np.float32)).to(cuda_device)
+  flag_bytes = int(L.mtfc_alltoall_peer_flag_bytes())
+
+  def run(nranks, out, rows_as_dims):
+    flags = [torch.zeros(flag_bytes, dtype=torch.uint8, device=cuda_device) for _ in range(nranks)]
+    outs = [out] + [torch.zeros_like(out) for _ in range(nranks - 1)]
+    ctl = torch.zeros(2, dtype=torch.int32, device=cuda_device)
+    arr = lambda ts: (ctypes.c_void_p * nranks)(*[ctypes.c_void_p(t.data_ptr()) for t in ts])
+    dims, ss, ds, row = rows_as_dims
+    nat.check(L.mtfc_alltoall_peer(x.data_ptr(), arr(outs), arr(flags), nranks, 0, len(dims), i64s(dims),
+                                   i64s(ss), i64s(ds), row, 0, 0, ctl.data_ptr(), stream))
+    return ctl
+
+  # one rank, twice on the same flags: [6, 5, 64] copied as 6 x 5 rows of 256 bytes into a
+  # buffer whose rows are 512 bytes apart
+  out = torch.full((6, 5, 128), -1.0, dtype=torch.float32, device=cuda_device)
+  layout = ([6, 5], [5 * 256, 256], [5 * 512, 512], 256)
+  ctl = run(1, out, layout)
+  nat.device_status()
+  np.testing.assert_array_equal(out[:, :, :64].cpu().numpy(), x.cpu().numpy())
+  assert (out[:, :, 64:] == -1.0).all()
+  assert ctl.cpu().tolist() == [1, 0]        # one launch completed, ticket back at zero
+
+  nat.check(L.mtfc_alltoall_peer_set_wait_ms(5))
+  try:
+    out2 = torch.full((6, 5, 128), -1.0, dtype=torch.float32, device=cuda_device)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    run(2, out2, layout)
+    t1.record()
+    with pytest.raises(nat.MtfcError) as err:
+      nat.device_status()
+    assert err.value.code == nat.ERR_TIMEOUT
+    assert t0.elapsed_time(t1) < 2000.0
+    assert (out2 == -1.0).all()              # the peer never freed its buffer: nothing was stored
+  finally:
+    nat.check(L.mtfc_alltoall_peer_set_wait_ms(0))
+  nat.device_status()
+  y = x * 2
+  assert torch.equal(y.cpu(), x.cpu() * 2)
