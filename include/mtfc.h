@@ -203,6 +203,10 @@ int mtfc_add_n_bf16(const void* const* sources, int32_t n, void* dst, int64_t el
  *   src_part_stride  part r starts r * src_part_stride bytes into src,
  *   dst_part_stride  the part received from rank s lands s * dst_part_stride
  *                    bytes into the output,
+ *   slot, slot_stride  every rank's buffer is a row of equal slots slot_stride bytes
+ *                    apart; this rank's result is wanted in slot `slot` of its own
+ *                    buffer (the peers learn the number through the hand-shake, so
+ *                    each rank chooses a slot that is free on its side),
  *   ctl              two zero-initialised uint32 of this rank (launch count, ticket).
  * All byte counts are multiples of 16.  The kernel waits for the peers' "buffer
  * free" signal before it stores and for their "stored" signal before it ends;
@@ -213,7 +217,8 @@ int mtfc_alltoall_peer_set_wait_ms(int ms);
 int mtfc_alltoall_peer(const void* src, void* const* peer_out, void* const* peer_flags,
                        int32_t nranks, int32_t rank, int32_t ndims, const int64_t* dims,
                        const int64_t* src_strides, const int64_t* dst_strides, int64_t row_bytes,
-                       int64_t src_part_stride, int64_t dst_part_stride, uint32_t* ctl, void* stream);
+                       int64_t src_part_stride, int64_t dst_part_stride, int32_t slot,
+                       int64_t slot_stride, uint32_t* ctl, void* stream);
 
 /* K1f on the tensor cores: fp32 [batch, rows, k] (element strides s_*) -> bf16
  * [batch, rows, 6k], every value split into three bf16 terms laid along K

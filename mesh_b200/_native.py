@@ -88,7 +88,7 @@ def _declare(lib):
       "mtfc_alltoall_peer_flag_bytes": [],
       "mtfc_alltoall_peer_set_wait_ms": [ctypes.c_int],
       "mtfc_alltoall_peer": [vp, ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i32, i32, p_i64, p_i64,
-                             p_i64, i64, i64, i64, vp, vp],
+                             p_i64, i64, i64, i64, i32, i64, vp, vp],
       "mtfc_split_bf16x3": [vp, i64, i64, i64, vp, i64, i64, i64, i32, vp],
       "mtfc_attention_set_variant": [i32],
       "mtfc_attention_supported": [i64, p_i64, p_i64, p_i64, p_i64],

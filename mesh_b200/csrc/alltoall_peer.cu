@@ -18,6 +18,10 @@
 //          peer: "my output buffer is free: whatever read its previous contents
 //          was enqueued before this launch".  A rank stores into any buffer
 //          only after all of its own ready slots have reached the epoch.
+//          With the signal travels the number of the slot of its buffer the rank
+//          wants this call's result in (a rank's buffer is a row of equal slots;
+//          the receiver alone decides which one is free), written to slot[r] at
+//          every peer just before the release-add.
 //   done   When a rank's last CTA has finished storing (system-scope fence,
 //          ticket), it adds 1 to `done` at every peer; a rank's output is
 //          complete when its `done` has reached epoch * n, which its last CTA
@@ -40,11 +44,15 @@ constexpr int kA2AUnroll = 4;
 constexpr long long kA2AChunkBytes = (long long)kA2AThreads * 16 * kA2AUnroll * 2;  // 32 KiB per work item
 constexpr int kFlagStride = 32;   // uint32 words between flags: one 128-byte line each
 constexpr int kFlagDone = kA2AMaxRanks;
+constexpr int kFlagSlot = kA2AMaxRanks + 1;   // slot[0..7] follow
+constexpr int kFlagLines = 2 * kA2AMaxRanks + 1;
 
 struct A2AArgs {
   const uint8_t* src;
-  uint8_t* out[kA2AMaxRanks];      // every rank's output buffer
-  uint32_t* flags[kA2AMaxRanks];   // every rank's flag array: ready[0..7], done
+  uint8_t* out[kA2AMaxRanks];      // every rank's output buffer (slot 0)
+  uint32_t* flags[kA2AMaxRanks];   // every rank's flag array: ready[0..7], done, slot[0..7]
+  uint32_t my_slot;                // where this rank wants its result
+  long long slot_stride;           // bytes between the slots of a buffer
   int n, me, ndims;
   long long dims[kA2AMaxDims];     // extents of one part in front of the row
   long long sstride[kA2AMaxDims];  // their strides in the source slice, bytes
@@ -85,6 +93,7 @@ __device__ __forceinline__ uint4 a2a_ld_stream(const uint4* p) {
 __global__ void __launch_bounds__(kA2AThreads)
 alltoall_peer_kernel(const A2AArgs a) {
   __shared__ uint32_t s_epoch;
+  __shared__ uint32_t s_slot[kA2AMaxRanks];
   __shared__ int s_ok, s_last;
   const int tid = threadIdx.x;
   if (tid == 0) {
@@ -95,9 +104,17 @@ alltoall_peer_kernel(const A2AArgs a) {
   __syncthreads();
   const uint32_t epoch = s_epoch;
   // this rank's buffer is free from here on: tell everybody (itself included)
-  if (blockIdx.x == 0 && tid < a.n) a2a_red_release_sys(a.flags[tid] + a.me * kFlagStride);
-  // ... and nobody's buffer is written before its owner said the same
-  if (tid < a.n && !a2a_wait_ge(a.flags[a.me] + tid * kFlagStride, epoch, a.wait_cycles)) s_ok = 0;
+  if (blockIdx.x == 0 && tid < a.n) {
+    *reinterpret_cast<volatile uint32_t*>(a.flags[tid] + (kFlagSlot + a.me) * kFlagStride) = a.my_slot;
+    a2a_red_release_sys(a.flags[tid] + a.me * kFlagStride);
+  }
+  // ... and nobody's buffer is written before its owner said the same, and where
+  if (tid < a.n) {
+    if (a2a_wait_ge(a.flags[a.me] + tid * kFlagStride, epoch, a.wait_cycles))
+      s_slot[tid] = *reinterpret_cast<volatile uint32_t*>(a.flags[a.me] + (kFlagSlot + tid) * kFlagStride);
+    else
+      s_ok = 0;
+  }
   __syncthreads();
   const bool ok = s_ok != 0;
 
@@ -121,7 +138,7 @@ alltoall_peer_kernel(const A2AArgs a) {
       const long long base = chunk * kA2AChunkBytes;
       const long long len = min(kA2AChunkBytes, a.row_bytes - base);
       const uint4* s = reinterpret_cast<const uint4*>(a.src + soff + base);
-      uint4* d = reinterpret_cast<uint4*>(a.out[dest] + doff + base);
+      uint4* d = reinterpret_cast<uint4*>(a.out[dest] + (long long)s_slot[dest] * a.slot_stride + doff + base);
       const int nvec = (int)(len >> 4);
       for (int v0 = tid; v0 < nvec; v0 += kA2AThreads * kA2AUnroll) {
         uint4 r[kA2AUnroll];
@@ -171,7 +188,7 @@ using namespace mtfc;
 extern "C" {
 
 int64_t mtfc_alltoall_peer_flag_bytes(void) {
-  return (int64_t)(kA2AMaxRanks + 1) * kFlagStride * sizeof(uint32_t);
+  return (int64_t)kFlagLines * kFlagStride * sizeof(uint32_t);
 }
 
 int mtfc_alltoall_peer_set_wait_ms(int ms) {
@@ -182,7 +199,8 @@ int mtfc_alltoall_peer_set_wait_ms(int ms) {
 int mtfc_alltoall_peer(const void* src, void* const* peer_out, void* const* peer_flags,
                        int32_t nranks, int32_t rank, int32_t ndims, const int64_t* dims,
                        const int64_t* src_strides, const int64_t* dst_strides, int64_t row_bytes,
-                       int64_t src_part_stride, int64_t dst_part_stride, uint32_t* ctl, void* stream) {
+                       int64_t src_part_stride, int64_t dst_part_stride, int32_t slot,
+                       int64_t slot_stride, uint32_t* ctl, void* stream) {
   if (!src || !peer_out || !peer_flags || !ctl)
     return fail(MTFC_ERR_SHAPE, "alltoall_peer: null argument");
   if (nranks < 1 || nranks > kA2AMaxRanks || rank < 0 || rank >= nranks)
@@ -193,6 +211,8 @@ int mtfc_alltoall_peer(const void* src, void* const* peer_out, void* const* peer
     return fail(MTFC_ERR_SHAPE, "alltoall_peer: rows and part strides must be multiples of 16 bytes");
   if (reinterpret_cast<uintptr_t>(src) % 16 != 0)
     return fail(MTFC_ERR_SHAPE, "alltoall_peer: source not 16-byte aligned");
+  if (slot < 0 || slot_stride < 0 || slot_stride % 16 != 0)
+    return fail(MTFC_ERR_SHAPE, "alltoall_peer: slot %d with stride %lld", slot, (long long)slot_stride);
   A2AArgs a;
   a.src = static_cast<const uint8_t*>(src);
   for (int i = 0; i < kA2AMaxRanks; ++i) {
@@ -217,6 +237,8 @@ int mtfc_alltoall_peer(const void* src, void* const* peer_out, void* const* peer
   a.row_bytes = row_bytes;
   a.src_part_stride = src_part_stride;
   a.dst_part_stride = dst_part_stride;
+  a.my_slot = (uint32_t)slot;
+  a.slot_stride = slot_stride;
   a.ctl = ctl;
   a.wait_cycles = g_a2a_wait_cycles;
   a.status = device_status_word();

@@ -496,7 +496,23 @@ def alltoall_peer_plan(shape, itemsize, n, split_axis, concat_axis):
 
 class _AlltoallWorkspace(object):
   """Buffers of one peer-memory alltoall size (see CudaMeshImpl._alltoall_workspace)."""
-  __slots__ = ("tensors", "handles", "out_tensor", "ctl", "out_ptrs", "flag_ptrs")
+  __slots__ = ("tensors", "handles", "out_tensor", "ctl", "out_ptrs", "flag_ptrs", "nbytes", "stride",
+               "free", "pinned")
+
+
+class _SlotOwner(object):
+  """One result slot of an alltoall workspace, exposed through the CUDA array
+  interface: a torch tensor made from it keeps this object alive for as long as
+  its storage (any view included) lives, and the slot goes back to the free list
+  when the object dies."""
+
+  def __init__(self, ptr, nbytes, workspace, slot):
+    self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                     "strides": None, "version": 2}
+    self._workspace, self._slot = workspace, slot
+
+  def __del__(self):
+    self._workspace.free.append(self._slot)
 
 
 class _PipelineWorkspace(object):
@@ -951,10 +967,16 @@ class CudaMeshImpl(SlicedMeshImpl):
   PEER_ALLTOALL = os.environ.get("MTFC_PEER_ALLTOALL", "1") == "1"
   PEER_ALLTOALL_MIN_BYTES = 64 * 1024
 
+  # Result slots per alltoall size beside the shared one (slot 0): a result lives in a slot
+  # of its own for as long as any tensor made from it does, so nothing has to be copied
+  # out; with every slot taken, slot 0 is used and its contents are copied.
+  PEER_ALLTOALL_SLOTS = 6
+  PEER_ALLTOALL_POOL_BYTES = 1 << 30
+
   def _alltoall_workspace(self, pg, members, pnum, nbytes):
-    """Peer-mapped output buffer of `nbytes` plus the flag array, per group and
-    size (created collectively on first use).  None when symmetric memory is
-    unavailable."""
+    """Peer-mapped result slots for alltoalls of `nbytes` plus the flag array, per
+    group and size (created collectively on first use).  None when symmetric
+    memory is unavailable."""
     import ctypes
     import torch
     import torch.distributed as dist
@@ -968,7 +990,9 @@ class CudaMeshImpl(SlicedMeshImpl):
     try:
       import torch.distributed._symmetric_memory as symm
       dev = torch.device("cuda", torch.cuda.current_device())
-      out_t = symm.empty(nbytes, dtype=torch.uint8, device=dev)
+      stride = (nbytes + 255) // 256 * 256
+      slots = 1 + max(0, min(self.PEER_ALLTOALL_SLOTS, self.PEER_ALLTOALL_POOL_BYTES // stride - 1))
+      out_t = symm.empty(slots * stride, dtype=torch.uint8, device=dev)
       out_h = symm.rendezvous(out_t, pg)
       flag_t = symm.empty(int(nat.lib().mtfc_alltoall_peer_flag_bytes()), dtype=torch.uint8, device=dev)
       flag_h = symm.rendezvous(flag_t, pg)
@@ -987,6 +1011,9 @@ class CudaMeshImpl(SlicedMeshImpl):
       ws.tensors, ws.handles = (out_t, flag_t), (out_h, flag_h)
       ws.out_tensor, ws.ctl = out_t, ctl
       ws.out_ptrs, ws.flag_ptrs = ptr_array(out_h), ptr_array(flag_h)
+      ws.nbytes, ws.stride = nbytes, stride
+      ws.free = list(range(slots - 1, 0, -1))     # slot 0 is the shared one
+      ws.pinned = []
     except Exception as e:  # pylint: disable=broad-except
       import warnings
       warnings.warn("peer memory for the alltoall unavailable (%r); using NCCL" % (e,))
@@ -1013,15 +1040,26 @@ class CudaMeshImpl(SlicedMeshImpl):
       return None
     ops = self._ops_for(pnum)
     src = ops.contiguous(s)
+    slot = ws.free.pop() if ws.free else 0
     i64s = lambda vals: (ctypes.c_int64 * max(1, len(vals)))(*vals)
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     nat.check(nat.lib().mtfc_alltoall_peer(
         ctypes.c_void_p(src.ptr), ws.out_ptrs, ws.flag_ptrs, n, members.index(pnum), len(lead),
         i64s([d for d, _, _ in lead]), i64s([a for _, a, _ in lead]), i64s([b for _, _, b in lead]),
-        row_bytes, src_part_stride, dst_part_stride, ctypes.c_void_p(ws.ctl.data_ptr()), stream))
-    shared = self._device_array(ws.out_tensor.view(_TORCH[s.dtype.name]), out_shape, s.dtype)
-    # the buffer is this group's for every alltoall of this size: hand back a copy
-    return _fresh_copy(ops, shared)
+        row_bytes, src_part_stride, dst_part_stride, slot, ws.stride,
+        ctypes.c_void_p(ws.ctl.data_ptr()), stream))
+    if slot == 0:
+      # every slot is taken: the shared one serves, and its contents are handed back as a copy
+      shared = ws.out_tensor[:nbytes].view(_TORCH[s.dtype.name])
+      return _fresh_copy(ops, self._device_array(shared, out_shape, s.dtype))
+    # The result stays where the peers stored it.  The slot returns to the free list when
+    # the last tensor over this memory is gone; a slot taken while a CUDA graph is being
+    # recorded belongs to the graph until release_graphs().
+    owner = _SlotOwner(ws.out_tensor.data_ptr() + slot * ws.stride, nbytes, ws, slot)
+    if getattr(self, "_capturing", False):
+      ws.pinned.append(owner)
+    flat = torch.as_tensor(owner, device=ws.out_tensor.device).view(_TORCH[s.dtype.name])
+    return self._device_array(flat, out_shape, s.dtype)
 
   def _peer_workspace(self, pg, members, pnum, m, n):
     """Peer-mapped staging / output / flag buffers for an [m, n] bf16 GEMM that
@@ -1153,8 +1191,12 @@ class CudaMeshImpl(SlicedMeshImpl):
         fn()
       torch.cuda.synchronize()
       graph = torch.cuda.CUDAGraph()
-      with torch.cuda.graph(graph):
-        result = fn()
+      self._capturing = True
+      try:
+        with torch.cuda.graph(graph):
+          result = fn()
+      finally:
+        self._capturing = False
       torch.cuda.synchronize()
     if not hasattr(self, "_graphs"):
       self._graphs = []
@@ -1171,6 +1213,9 @@ class CudaMeshImpl(SlicedMeshImpl):
     for graph in getattr(self, "_graphs", []):
       graph.reset()
     self._graphs = []
+    for ws in getattr(self, "_a2a_ws", {}).values():
+      if ws is not None:
+        ws.pinned = []
 
   def synchronize(self):
     """Waits for all enqueued work and raises if a kernel reported a timeout."""

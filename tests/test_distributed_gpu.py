@@ -89,6 +89,22 @@ def _worker(rank, world, port, out_dir):
       check(want, res)
     nat_a2a.device_status()   # raises if a bounded wait ran out
     peer.release_graphs()
+    # results live in slots of the peer-mapped buffer: more live results than slots (the
+    # extra ones are copies of the shared slot) all stay intact, and the slots come back
+    # when the results are dropped
+    ws_big = [w for (_, nbytes), w in peer._a2a_ws.items() if nbytes == big[0].nbytes][0]
+    import gc
+    res = run = None
+    gc.collect()
+    free_before = len(ws_big.free)
+    assert free_before == peer.PEER_ALLTOALL_SLOTS
+    held = [peer.alltoall(b2, 0, 1, 0) for _ in range(free_before + 2)]
+    assert len(ws_big.free) == 0
+    for h in held:
+      check(want, h)
+    del held, h
+    gc.collect()
+    assert len(ws_big.free) == free_before
 
     def ffn(backend):
       rr = rng(2)

@@ -97,7 +97,7 @@ def test_alltoall_peer_single_rank_and_wait_that_runs_out(cuda_device):
     arr = lambda ts: (ctypes.c_void_p * nranks)(*[ctypes.c_void_p(t.data_ptr()) for t in ts])
     dims, ss, ds, row = rows_as_dims
     nat.check(L.mtfc_alltoall_peer(x.data_ptr(), arr(outs), arr(flags), nranks, 0, len(dims), i64s(dims),
-                                   i64s(ss), i64s(ds), row, 0, 0, ctl.data_ptr(), stream))
+                                   i64s(ss), i64s(ds), row, 0, 0, 0, 0, ctl.data_ptr(), stream))
     return ctl
 
   # one rank, twice on the same flags: [6, 5, 64] copied as 6 x 5 rows of 256 bytes into a
