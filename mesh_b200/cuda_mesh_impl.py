@@ -15,7 +15,9 @@ collectives run
     process per GPU: rank r holds processor r's slice only, and each mesh-axis
     set gets its process groups once.  allreduce -> all_reduce, allconcat ->
     all_gather (+ strided-copy kernel when the concat axis is not outermost),
-    alltoall -> all_to_all_single bracketed by pack / unpack copy kernels,
+    alltoall -> one kernel that stores into the peers' mapped buffers
+    (mtfc_alltoall_peer), or all_to_all_single bracketed by pack / unpack copy
+    kernels for small or unaligned slices,
     receive -> batched isend / irecv.
 
 SlicedMeshImpl holds everything that does not depend on where a slice lives;

@@ -109,6 +109,8 @@ class DeviceOps(object):
   # longer contractions stay on the FFMA kernel: the tensor core truncates on
   # every accumulation, and beyond this many terms that bias nears 1e-5
   FP32_TENSOR_CORE_MAX_K = 2048
+  # products narrower than this waste most of the GEMM kernel's 256-wide tile
+  MIN_GEMM_N = 256
 
   def __init__(self, device):
     self._lib = nat.lib()
@@ -507,6 +509,19 @@ class DeviceOps(object):
     # The output is stored as [batch, M, N] and handed back as a view in the
     # requested dim order, so only the operands' layouts constrain the plan.
     plan = plan_for(batch, m_dims, n_dims)
+    if (plan is None and not batch and gemm_hook is None and len(n_dims) > 1
+        and _volume([sizes[l] for l in n_dims[1:]]) < self.MIN_GEMM_N
+        and 4 * b.size <= a.size and plan_for([], m_dims, []) is not None
+        and collapse(k_dims, sa) is not None):
+      # Only the second operand's free dims fail to collapse (weights [heads, io, kv]:
+      # heads and kv are apart), it is small beside the first, and taking its leading
+      # free dim as a batch axis would leave products narrower than the kernel's tile:
+      # a copy of it in [K, N] order makes ONE product of full width.  The result is
+      # stored [M, N] and handed back as a view in the requested order.
+      b = self.contiguous(self.transpose(b, [tb.index(l) for l in k_dims + n_dims]))
+      tb = "".join(k_dims + n_dims)
+      sb = dict(zip(tb, b.strides))
+      plan = plan_for(batch, m_dims, n_dims)
     if plan is None and not batch:
       # a leading free dim that breaks the collapse (weights [heads, io, kv]) can
       # serve as the batch axis: the other operand is simply reused for each
@@ -560,6 +575,35 @@ class DeviceOps(object):
       self._call(self._lib.mtfc_gemm, ctypes.byref(d), ctypes.c_void_p(a3.ptr),
                  ctypes.c_void_p(b3.ptr), ctypes.c_void_p(out.ptr), self._stream())
       return result
+    if (a.dtype.name == "float32" and out_dtype.name == "float32" and nb == 1
+        and k > self.FP32_TENSOR_CORE_MAX_K and epilogue == nat.EPILOGUE_NONE
+        and gemm_hook is None and m * n * k >= self.FP32_TENSOR_CORE_MIN_WORK):
+      # a long fp32 contraction (a weight gradient summed over all tokens): cut K into
+      # chunks short enough for the split-bf16 product, run them as one batched
+      # product into fp32 partial sums and add the partial sums in fp32
+      chunks = -(-k // self.FP32_TENSOR_CORE_MAX_K)
+      while chunks <= 8192 and (k % chunks or (k // chunks) % 4):
+        chunks += 1
+      if chunks <= 8192:
+        kk = k // chunks
+        a3 = self._empty([chunks, m, 6 * kk], G.bfloat16)
+        b3 = self._empty([chunks, n, 6 * kk], G.bfloat16)
+        self._call(self._lib.mtfc_split_bf16x3, ctypes.c_void_p(a.ptr), kk * a_k, a_m, a_k,
+                   ctypes.c_void_p(a3.ptr), chunks, m, kk, 0, self._stream())
+        self._call(self._lib.mtfc_split_bf16x3, ctypes.c_void_p(b.ptr), kk * b_k, b_n, b_k,
+                   ctypes.c_void_p(b3.ptr), chunks, n, kk, 1, self._stream())
+        part = self._empty([chunks, m, n], G.float32)
+        d = nat.GemmDesc()
+        d.batch, d.m, d.n, d.k = chunks, m, n, 6 * kk
+        d.a_batch, d.a_m, d.a_k = m * 6 * kk, 6 * kk, 1
+        d.b_batch, d.b_k, d.b_n = n * 6 * kk, 1, 6 * kk
+        d.c_batch, d.c_m, d.c_n = m * n, n, 1
+        d.in_dtype, d.out_dtype = nat.BF16, nat.F32
+        d.epilogue, d.force_path = nat.EPILOGUE_NONE, 0
+        self._call(self._lib.mtfc_gemm, ctypes.byref(d), ctypes.c_void_p(a3.ptr),
+                   ctypes.c_void_p(b3.ptr), ctypes.c_void_p(part.ptr), self._stream())
+        total = self.reshape(self.reduce("SUM", part, [0]), [sizes[l] for l in store])
+        return total if view_perm == list(range(len(store))) else self.transpose(total, view_perm)
     d = nat.GemmDesc()
     d.batch, d.m, d.n, d.k = nb, m, n, k
     d.a_batch, d.a_m, d.a_k = a_b, a_m, a_k
