@@ -214,6 +214,9 @@ int mtfc_add_n_bf16(const void* const* sources, int32_t n, void* dst, int64_t el
  * MTFC_ERR_TIMEOUT for mtfc_device_status when they run out. */
 int64_t mtfc_alltoall_peer_flag_bytes(void);
 int mtfc_alltoall_peer_set_wait_ms(int ms);
+/* CTAs per SM the copy grid is capped at (1..8, default 4): fewer leave room for a GEMM
+ * that runs beside it on another stream. */
+int mtfc_alltoall_peer_set_ctas_per_sm(int ctas);
 int mtfc_alltoall_peer(const void* src, void* const* peer_out, void* const* peer_flags,
                        int32_t nranks, int32_t rank, int32_t ndims, const int64_t* dims,
                        const int64_t* src_strides, const int64_t* dst_strides, int64_t row_bytes,

@@ -87,6 +87,7 @@ def _declare(lib):
       "mtfc_add_n_bf16": [ctypes.POINTER(vp), i32, vp, i64, vp],
       "mtfc_alltoall_peer_flag_bytes": [],
       "mtfc_alltoall_peer_set_wait_ms": [ctypes.c_int],
+      "mtfc_alltoall_peer_set_ctas_per_sm": [ctypes.c_int],
       "mtfc_alltoall_peer": [vp, ctypes.POINTER(vp), ctypes.POINTER(vp), i32, i32, i32, p_i64, p_i64,
                              p_i64, i64, i64, i64, i32, i64, vp, vp],
       "mtfc_split_bf16x3": [vp, i64, i64, i64, vp, i64, i64, i64, i32, vp],

@@ -179,6 +179,7 @@ alltoall_peer_kernel(const A2AArgs a) {
 }
 
 long long g_a2a_wait_cycles = 6000000000LL;  // ~3 s
+int g_a2a_ctas_per_sm = 4;
 
 }  // namespace
 }  // namespace mtfc
@@ -189,6 +190,11 @@ extern "C" {
 
 int64_t mtfc_alltoall_peer_flag_bytes(void) {
   return (int64_t)kFlagLines * kFlagStride * sizeof(uint32_t);
+}
+
+int mtfc_alltoall_peer_set_ctas_per_sm(int ctas) {
+  g_a2a_ctas_per_sm = ctas >= 1 && ctas <= 8 ? ctas : 4;
+  return MTFC_OK;
 }
 
 int mtfc_alltoall_peer_set_wait_ms(int ms) {
@@ -246,7 +252,7 @@ int mtfc_alltoall_peer(const void* src, void* const* peer_out, void* const* peer
   const long long items = (long long)nranks * a.rows * chunks;
   // the hand-shake runs even for an empty slice: every rank of the group makes the call
   long long grid = items < 1 ? 1 : items;
-  const long long cap = (long long)sm_count() * 4;
+  const long long cap = (long long)sm_count() * g_a2a_ctas_per_sm;
   if (grid > cap) grid = cap;
   alltoall_peer_kernel<<<(unsigned)grid, kA2AThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
   MTFC_LAUNCH_CHECK("alltoall_peer_kernel");

@@ -525,6 +525,36 @@ class _PipelineWorkspace(object):
                "part_rows", "tiles_n")
 
 
+class _DeferredEinsum(object):
+  """A product EinsumOperation.lower left pending (CudaMeshImpl.defer_einsum): it runs
+  when somebody asks for its slices, unless a contraction + allreduce took it over."""
+
+  def __init__(self, mesh_impl, fn, inputs, slice_shape, activation):
+    self._mesh_impl, self._fn = mesh_impl, fn
+    self.inputs, self.activation = inputs, activation
+    self._slice_shape = [int(d) for d in slice_shape]
+    self._value = None
+
+  @property
+  def pending(self):
+    return self._value is None
+
+  @property
+  def slice_shape(self):
+    return list(self._slice_shape)
+
+  def to_laid_out_tensor(self):
+    if self._value is None:
+      self._value = self._mesh_impl.slicewise(self._fn, *self.inputs)
+    return self._value
+
+
+class _FfnWorkspace(object):
+  """Buffers of one row-split FFN problem size (see CudaMeshImpl._ffn_workspace)."""
+  __slots__ = ("tensors", "handles", "wi_all", "wo_full", "y_recv", "flags", "peer_wi", "peer_wo",
+               "peer_y", "peer_flag_ptrs", "h", "epochs", "push", "pull", "rank")
+
+
 class _PendingAllreduce(object):
   """Result of einsum_allreduce: the reduced slice once its chunked allreduces
   are waited for (the wait is a stream dependency, not a host block)."""
@@ -737,6 +767,10 @@ class CudaMeshImpl(SlicedMeshImpl):
     if not self._distributed or not mesh_axes:
       return None
     import torch.distributed as dist
+    if isinstance(inputs[0], _DeferredEinsum) and inputs[0].pending:
+      resharded = self._ffn_resharded(inputs[0], equation, inputs[1], mesh_axes)
+      if resharded is not None:
+        return resharded
     inputs = convert_args_to_laid_out_tensors(inputs)
     a, b = inputs[0].tensor_list[0], inputs[1].tensor_list[0]
     lhs, out_term = equation.split("->")
@@ -779,6 +813,201 @@ class CudaMeshImpl(SlicedMeshImpl):
       works.append(dist.all_reduce(flat[i * chunk_elems:(i + 1) * chunk_elems],
                                    op=dist.ReduceOp.SUM, group=pg, async_op=True))
     return _PendingAllreduce(self, out, works)
+
+  # ---- x.wi -> activation -> .wo with the hidden dim split over a mesh axis ---------
+  # The reference's schedule gives every rank of the axis all rows and 1/n of the hidden
+  # dim, and allreduces the [rows, out] partial sums: 2 (n-1)/n of the output crosses
+  # every link, and the sums are added in bf16.  When the first product has no other
+  # reader, the same result is computed the other way round: every rank takes 1/n of the
+  # ROWS and the whole hidden dim (the weight slices, a few MB, are gathered first), so
+  # nothing is left to reduce, and the finished row blocks are gathered: (n-1)/n of the
+  # output per link, moved by the copy engines chunk by chunk while the next chunk is
+  # multiplied.  Inputs and result keep the layouts the graph gave them (rows replicated
+  # over the axis).  MTFC_RESHARDED_FFN=0 keeps the reference's schedule.
+  RESHARDED_FFN = os.environ.get("MTFC_RESHARDED_FFN", "1") == "1"
+  RESHARDED_FFN_MIN_BYTES = 4 << 20
+  RESHARDED_FFN_MAX_CHUNKS = 4
+  RESHARDED_FFN_MIN_CHUNK_ROWS = 4096   # fewer rows leave the second product too few tiles
+
+  def defer_einsum(self, fn, inputs, equation, activation):
+    """Hook of EinsumOperation.lower: leaves `[..., k] x [k, f] -> [..., f]` (bf16,
+    optional ReLU) pending when one process drives one GPU, so that einsum_allreduce
+    may meet it as its operand.  None = compute it now."""
+    if not (self._distributed and self.RESHARDED_FFN) or activation not in (None, "relu"):
+      return None
+    lhs, out_term = equation.split("->")
+    ta, tb = lhs.split(",")
+    if not (len(tb) == 2 and len(ta) >= 2 and ta[-1] == tb[0] and out_term == ta[:-1] + tb[1]
+            and len(set(ta + tb)) == len(ta) + 1):
+      return None
+    inputs = convert_args_to_laid_out_tensors(inputs)
+    a, b = inputs[0].tensor_list[0], inputs[1].tensor_list[0]
+    if not (a.dtype.name == "bfloat16" and b.dtype.name == "bfloat16" and a.is_contiguous
+            and b.is_contiguous and a.ptr % 16 == 0 and b.ptr % 16 == 0):
+      return None
+    return _DeferredEinsum(self, fn, inputs, list(a.shape[:-1]) + [b.shape[1]], activation)
+
+  def _ffn_resharded(self, first, equation, wo_input, mesh_axes):
+    """`first` (a pending x.wi [+ReLU]) contracted with wo over the hidden dim that is
+    split over `mesh_axes`: the row-split schedule described above, or None when it does
+    not apply (nothing has been launched then)."""
+    import ctypes
+    import torch
+    from mesh_b200 import _native as nat
+    if len(mesh_axes) != 1:
+      return None
+    lhs, out_term = equation.split("->")
+    ta, tb = lhs.split(",")
+    if not (len(tb) == 2 and len(ta) >= 2 and ta[-1] == tb[0] and out_term == ta[:-1] + tb[1]
+            and len(set(ta + tb)) == len(ta) + 1):
+      return None
+    pg, members = self._group(mesh_axes)
+    n = len(members)
+    pnum = self._local_pnums[0]
+    x, wi = first.inputs[0].tensor_list[0], first.inputs[1].tensor_list[0]
+    wo = convert_args_to_laid_out_tensors([wo_input])[0].tensor_list[0]
+    if not (n in (2, 4, 8) and wo.dtype.name == "bfloat16" and wo.is_contiguous and wo.ptr % 16 == 0
+            and len(wo.shape) == 2 and wo.shape[0] == wi.shape[1]):
+      return None
+    k1, fs, m2 = wi.shape[0], wi.shape[1], wo.shape[1]
+    rows = x.size // k1
+    if rows % (n * 256) != 0 or k1 % 8 != 0 or fs % 8 != 0 or m2 % 8 != 0 or fs < 256 or m2 < 256:
+      return None
+    if rows * m2 * 2 < self.RESHARDED_FFN_MIN_BYTES:
+      return None
+    mine = rows // n
+    chunks = 1
+    for c in range(self.RESHARDED_FFN_MAX_CHUNKS, 1, -1):
+      if mine % (c * 256) == 0 and mine // c >= self.RESHARDED_FFN_MIN_CHUNK_ROWS:
+        chunks = c
+        break
+    ws = self._ffn_workspace(pg, members, pnum, rows, k1, fs, m2, chunks)
+    if ws is None:
+      return None
+    lib = nat.lib()
+    me = ws.rank
+    others = [r for r in range(n) if r != me]
+    f = fs * n
+    rc = mine // chunks
+    main = torch.cuda.current_stream()
+    ms = ctypes.c_void_p(main.cuda_stream)
+    flags, epochs = ws.flags.data_ptr(), ws.epochs.data_ptr()
+    wi2d = wi.buf[wi.offset:wi.offset + wi.size].view(k1, fs)
+    wo2d = wo.buf[wo.offset:wo.offset + wo.size].view(fs, m2)
+    # 1. everything that read this rank's buffers was enqueued before this point
+    nat.check(lib.mtfc_signal_peers(ws.peer_flag_ptrs, n - 1, 0, ms))
+    nat.check(lib.mtfc_wait_counters(ctypes.c_void_p(flags), 1, n - 1, ctypes.c_void_p(epochs), ms))
+    # 2. the weight slices go to every rank (copy engines)
+    for r in others:
+      ws.peer_wi[r][me].copy_(wi2d, non_blocking=True)
+      ws.peer_wo[r][me * fs:(me + 1) * fs].copy_(wo2d, non_blocking=True)
+    ws.wi_all[me].copy_(wi2d, non_blocking=True)
+    ws.wo_full[me * fs:(me + 1) * fs].copy_(wo2d, non_blocking=True)
+    nat.check(lib.mtfc_signal_peers(ws.peer_flag_ptrs, n - 1, 1, ms))
+    nat.check(lib.mtfc_wait_counters(ctypes.c_void_p(flags + 4), 1, n - 1, ctypes.c_void_p(epochs + 4), ms))
+    # 3. this rank's rows, chunk by chunk; finished chunks travel while the next is multiplied
+    result = torch.empty(rows * m2, dtype=torch.bfloat16, device=ws.h.device)
+    res2d = result.view(rows, m2)
+    fork = torch.cuda.Event()
+    fork.record(main)
+    ws.push.wait_event(fork)
+    ws.pull.wait_event(fork)
+    relu = nat.EPILOGUE_RELU if first.activation == "relu" else nat.EPILOGUE_NONE
+    for c in range(chunks):
+      g0 = me * mine + c * rc
+      d1 = nat.GemmDesc()
+      d1.batch, d1.m, d1.n, d1.k = n, rc, fs, k1
+      d1.a_batch, d1.a_m, d1.a_k = 0, k1, 1
+      d1.b_batch, d1.b_k, d1.b_n = k1 * fs, fs, 1
+      d1.c_batch, d1.c_m, d1.c_n = fs, f, 1
+      d1.in_dtype = d1.out_dtype = nat.BF16
+      d1.epilogue, d1.force_path = relu, 0
+      nat.check(lib.mtfc_gemm(ctypes.byref(d1), ctypes.c_void_p(x.ptr + g0 * k1 * 2),
+                              ctypes.c_void_p(ws.wi_all.data_ptr()),
+                              ctypes.c_void_p(ws.h.data_ptr() + c * rc * f * 2), ms))
+      d2 = nat.GemmDesc()
+      d2.batch, d2.m, d2.n, d2.k = 1, rc, m2, f
+      d2.a_batch, d2.a_m, d2.a_k = 0, f, 1
+      d2.b_batch, d2.b_k, d2.b_n = 0, m2, 1
+      d2.c_batch, d2.c_m, d2.c_n = rc * m2, m2, 1
+      d2.in_dtype = d2.out_dtype = nat.BF16
+      d2.epilogue, d2.force_path = nat.EPILOGUE_NONE, 0
+      nat.check(lib.mtfc_gemm(ctypes.byref(d2), ctypes.c_void_p(ws.h.data_ptr() + c * rc * f * 2),
+                              ctypes.c_void_p(ws.wo_full.data_ptr()),
+                              ctypes.c_void_p(result.data_ptr() + g0 * m2 * 2), ms))
+      done = torch.cuda.Event()
+      done.record(main)
+      ws.push.wait_event(done)
+      with torch.cuda.stream(ws.push):
+        for r in others:
+          ws.peer_y[r][g0:g0 + rc].copy_(res2d[g0:g0 + rc], non_blocking=True)
+        nat.check(lib.mtfc_signal_peers(ws.peer_flag_ptrs, n - 1, 2 + c,
+                                        ctypes.c_void_p(ws.push.cuda_stream)))
+      with torch.cuda.stream(ws.pull):
+        # the peers' chunk c has landed in the receive buffer: into the result it goes
+        nat.check(lib.mtfc_wait_counters(ctypes.c_void_p(flags + 4 * (2 + c)), 1, n - 1,
+                                         ctypes.c_void_p(epochs + 4 * (2 + c)),
+                                         ctypes.c_void_p(ws.pull.cuda_stream)))
+        for r in others:
+          r0 = r * mine + c * rc
+          res2d[r0:r0 + rc].copy_(ws.y_recv[r0:r0 + rc], non_blocking=True)
+    main.wait_stream(ws.push)
+    main.wait_stream(ws.pull)
+    out = self._device_array(result, list(x.shape[:-1]) + [m2], x.dtype)
+    return self.LaidOutTensor([out])
+
+  def _ffn_workspace(self, pg, members, pnum, rows, k1, fs, m2, chunks):
+    """Peer-mapped buffers of the row-split FFN schedule for one problem size: every
+    rank's weight slices side by side, the receive buffer for the peers' row blocks,
+    the counters; plus the local hidden activations and two side streams."""
+    import ctypes
+    import torch
+    import torch.distributed as dist
+    key = (tuple(members), rows, k1, fs, m2, chunks)
+    if not hasattr(self, "_ffn_ws"):
+      self._ffn_ws = {}
+    if key in self._ffn_ws:
+      return self._ffn_ws[key]
+    ws = None
+    try:
+      import torch.distributed._symmetric_memory as symm
+      dev = torch.device("cuda", torch.cuda.current_device())
+      n = len(members)
+      me = members.index(pnum)
+
+      def alloc(count, dtype):
+        t = symm.empty(count, dtype=dtype, device=dev)
+        return t, symm.rendezvous(t, pg)
+      wi_t, wi_h = alloc(n * k1 * fs, torch.bfloat16)
+      wo_t, wo_h = alloc(n * fs * m2, torch.bfloat16)
+      y_t, y_h = alloc(rows * m2, torch.bfloat16)
+      flag_t, flag_h = alloc(2 + chunks, torch.int32)
+      flag_t.zero_()
+      if int(y_h.rank) != me or int(y_h.world_size) != n:
+        raise RuntimeError("symmetric-memory rank %d/%d does not match mesh group position %d/%d"
+                           % (y_h.rank, y_h.world_size, me, n))
+      ws = _FfnWorkspace()
+      ws.tensors, ws.handles = (wi_t, wo_t, y_t, flag_t), (wi_h, wo_h, y_h, flag_h)
+      ws.wi_all, ws.wo_full = wi_t.view(n, k1, fs), wo_t.view(n * fs, m2)
+      ws.y_recv, ws.flags = y_t.view(rows, m2), flag_t
+      others = [r for r in range(n) if r != me]
+      ws.peer_wi = {r: wi_h.get_buffer(r, (n, k1, fs), torch.bfloat16) for r in others}
+      ws.peer_wo = {r: wo_h.get_buffer(r, (n * fs, m2), torch.bfloat16) for r in others}
+      ws.peer_y = {r: y_h.get_buffer(r, (rows, m2), torch.bfloat16) for r in others}
+      ws.peer_flag_ptrs = (ctypes.c_void_p * len(others))(
+          *[ctypes.c_void_p(int(flag_h.buffer_ptrs[r])) for r in others])
+      ws.h = torch.empty((rows // n) * fs * n, dtype=torch.bfloat16, device=dev)
+      ws.epochs = torch.zeros(2 + chunks, dtype=torch.int32, device=dev)
+      ws.push, ws.pull = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+      ws.rank = me
+      torch.cuda.synchronize()
+      dist.barrier(group=pg)
+    except Exception as e:  # pylint: disable=broad-except
+      import warnings
+      warnings.warn("peer memory for the row-split FFN schedule unavailable (%r)" % (e,))
+      ws = None
+    self._ffn_ws[key] = ws
+    return ws
 
   # GEMM on the compute stream, exchange by the copy engines on a second stream
   # (mtfc_gemm_with_progress and friends).  Off by default: the copy engines do overlap
@@ -1232,4 +1461,6 @@ class CudaMeshImpl(SlicedMeshImpl):
       # counters out of step with the other ranks: never reuse those buffers
       self._peer_ws = {}
       self._pipe_ws = {}
+      self._ffn_ws = {}
+      self._a2a_ws = {}
       raise

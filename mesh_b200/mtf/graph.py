@@ -185,6 +185,7 @@ class Lowering(object):
     self.mesh_to_impl = mesh_to_impl
     self.graph = graph
     self._counters = []
+    self._consumers = None
     self.tensors = {}
     self.operations = {}
     self.variables = {}
@@ -198,6 +199,12 @@ class Lowering(object):
     if not isinstance(m, Mesh):
       m = m.mesh
     return self.mesh_to_impl[m]
+
+  def consumers(self, tensor):
+    """How many operation inputs of the graph read `tensor`."""
+    if self._consumers is None:
+      self._consumers = collections.Counter(t for op in self.graph.operations for t in op.inputs)
+    return self._consumers[tensor]
 
   def export_to_tf_tensor(self, x):
     """The full tensor on the host (a numpy array; bfloat16 widened to float32)."""

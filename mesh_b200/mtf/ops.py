@@ -787,7 +787,15 @@ class EinsumOperation(Operation):
         ops, act = impl.slice_ops, self._activation
         y = impl.slicewise(lambda t: ops.unary(act, t), y)
     else:
-      y = impl.slicewise(fn, *[lowering.tensors[x] for x in xs])
+      y = None
+      if (not reduced_mesh_axes and uses_hook and len(xs) == 2 and intersection == output_shape
+          and hasattr(impl, "defer_einsum") and lowering.consumers(self.outputs[0]) == 1):
+        # a product with a single reader may be left pending: a backend that sees it arrive
+        # as the operand of a contraction + allreduce can then schedule both together
+        # (anything else that touches it makes it run as usual); None = run it now
+        y = impl.defer_einsum(fn, [lowering.tensors[x] for x in xs], equation, self._activation)
+      if y is None:
+        y = impl.slicewise(fn, *[lowering.tensors[x] for x in xs])
     if reduced_mesh_axes and overlapped is None:
       y = LazyAllreduceSum(impl, y, reduced_mesh_axes, add_counter_fn=add_counter_fn)
       if self._activation is not None:

@@ -185,6 +185,54 @@ def _worker(rank, world, port, out_dir):
       assert int(hi.item()) == int(lo.item())
       fused.release_graphs()
 
+    # the row-split schedule of x.wi -> ReLU -> .wo (the first product stays pending and the
+    # contraction + allreduce takes both over): weight slices gathered, every rank multiplies
+    # its share of the rows with the whole hidden dim, row blocks gathered chunk by chunk
+    def ffn_wide(backend, replay=False):
+      rr = rng(5)
+      g = mtf.Graph()
+      m = mtf.Mesh(g, "m")
+      x = rr.standard_normal((8, 512, 256)).astype(np.float32)
+      wi = (rr.standard_normal((256, 1024)) / 16).astype(np.float32)
+      wo = (rr.standard_normal((1024, 256)) / 32).astype(np.float32)
+      X = mtf.import_tf_tensor(m, x, "batch:8,length:512,d_model:256", dtype=mtf.bfloat16)
+      WI = mtf.import_tf_tensor(m, wi, "d_model:256,d_ff:1024", dtype=mtf.bfloat16)
+      WO = mtf.import_tf_tensor(m, wo, "d_ff:1024,d_model:256", dtype=mtf.bfloat16)
+      y = mtf.layers.dense_relu_dense(X, mtf.Dimension("d_ff", 1024), wi=WI, wo=WO)
+      if not replay:
+        low = mtf.Lowering(g, {m: backend})
+        return low.export_to_tf_tensor(y), low.counter_totals()
+      res, run = backend.capture(lambda: mtf.Lowering(g, {m: backend}).tensors[y].to_laid_out_tensor())
+      outs = []
+      for _ in range(3):
+        run()
+        outs.append(ops.to_host(res.tensor_list[0]))
+      return outs
+    split = CudaMeshImpl(mesh_shape, "d_ff:all", list(range(world)))
+    split.RESHARDED_FFN_MIN_BYTES = 1
+    split.RESHARDED_FFN_MIN_CHUNK_ROWS = 256
+    ref_wide, counters_wide = ffn_wide(ora)
+    for _ in range(3):
+      got_wide, counters_got = ffn_wide(split)
+      assert rel_err(got_wide, ref_wide) < 2e-2 and counters_got == counters_wide
+    ws = list(getattr(split, "_ffn_ws", {}).values())
+    assert ws and all(w is not None for w in ws), "the row-split FFN schedule did not run"
+    nat_mod.device_status()
+    for o in ffn_wide(split, replay=True):
+      assert rel_err(o, ref_wide) < 2e-2
+    mine = torch.from_numpy(np.ascontiguousarray(got_wide).view(np.int32).astype(np.int64)).cuda().sum().reshape(1)
+    hi, lo = mine.clone(), mine.clone()
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    assert int(hi.item()) == int(lo.item())    # every rank holds the same bits
+    split.release_graphs()
+    exchange.append("row-split x%d chunks" % list(split._ffn_ws)[0][-1])
+    # the reference's schedule stays available
+    plain = CudaMeshImpl(mesh_shape, "d_ff:all", list(range(world)))
+    plain.RESHARDED_FFN = False
+    got_plain, _ = ffn_wide(plain)
+    assert rel_err(got_plain, ref_wide) < 2e-2 and not getattr(plain, "_ffn_ws", {})
+
     # the pipelined form: un-chunked GEMM with progress counters, exchange by the copy
     # engines on a second stream; eager three times (the counters' epochs advance),
     # then recorded once and replayed
