@@ -826,7 +826,7 @@ class CudaMeshImpl(SlicedMeshImpl):
   # over the axis).  MTFC_RESHARDED_FFN=0 keeps the reference's schedule.
   RESHARDED_FFN = os.environ.get("MTFC_RESHARDED_FFN", "1") == "1"
   RESHARDED_FFN_MIN_BYTES = 4 << 20
-  RESHARDED_FFN_MAX_CHUNKS = 4
+  RESHARDED_FFN_MAX_CHUNKS = 2
   RESHARDED_FFN_MIN_CHUNK_ROWS = 4096   # fewer rows leave the second product too few tiles
 
   def defer_einsum(self, fn, inputs, equation, activation):
@@ -876,11 +876,15 @@ class CudaMeshImpl(SlicedMeshImpl):
     if rows * m2 * 2 < self.RESHARDED_FFN_MIN_BYTES:
       return None
     mine = rows // n
-    chunks = 1
-    for c in range(self.RESHARDED_FFN_MAX_CHUNKS, 1, -1):
-      if mine % (c * 256) == 0 and mine // c >= self.RESHARDED_FFN_MIN_CHUNK_ROWS:
-        chunks = c
-        break
+    # Row chunks of this rank's share: a chunk's result travels while the next chunk is
+    # multiplied, and what travels after the last product is exposed, so the last chunk is
+    # the small one (a quarter); every further chunk costs a chain of dependent stream
+    # operations, so there are two at most.
+    bounds = [0, mine]
+    if self.RESHARDED_FFN_MAX_CHUNKS >= 2 and mine >= 2 * self.RESHARDED_FFN_MIN_CHUNK_ROWS:
+      last = max(256, (mine // 4) // 256 * 256)
+      bounds = [0, mine - last, mine]
+    chunks = len(bounds) - 1
     ws = self._ffn_workspace(pg, members, pnum, rows, k1, fs, m2, chunks)
     if ws is None:
       return None
@@ -888,22 +892,44 @@ class CudaMeshImpl(SlicedMeshImpl):
     me = ws.rank
     others = [r for r in range(n) if r != me]
     f = fs * n
-    rc = mine // chunks
     main = torch.cuda.current_stream()
     ms = ctypes.c_void_p(main.cuda_stream)
     flags, epochs = ws.flags.data_ptr(), ws.epochs.data_ptr()
     wi2d = wi.buf[wi.offset:wi.offset + wi.size].view(k1, fs)
     wo2d = wo.buf[wo.offset:wo.offset + wo.size].view(fs, m2)
-    # 1. everything that read this rank's buffers was enqueued before this point
+    # 1. "whatever read this rank's receive buffer was enqueued before this point": the
+    #    peers wait for it only before their first row block travels (on the push stream,
+    #    off the critical path).  The weight buffers need no such signal: a rank reads
+    #    them for the last time before its last row block leaves, and every rank has
+    #    waited for every peer's last block before it returns from the previous call.
     nat.check(lib.mtfc_signal_peers(ws.peer_flag_ptrs, n - 1, 0, ms))
-    nat.check(lib.mtfc_wait_counters(ctypes.c_void_p(flags), 1, n - 1, ctypes.c_void_p(epochs), ms))
-    # 2. the weight slices go to every rank (copy engines)
+    # 2. the weight slices go to every rank (copy engines).  A rank keeps the hidden dim in
+    #    rotated order, its own slice first: block j holds the slice of rank (me + j) mod n
+    #    (the sum over the hidden dim does not care), so the product with the own slice can
+    #    start at once and hides the journey of the others.
     for r in others:
-      ws.peer_wi[r][me].copy_(wi2d, non_blocking=True)
-      ws.peer_wo[r][me * fs:(me + 1) * fs].copy_(wo2d, non_blocking=True)
-    ws.wi_all[me].copy_(wi2d, non_blocking=True)
-    ws.wo_full[me * fs:(me + 1) * fs].copy_(wo2d, non_blocking=True)
+      j = (me - r) % n          # where this rank's slice sits in rank r's buffers
+      ws.peer_wi[r][j].copy_(wi2d, non_blocking=True)
+      ws.peer_wo[r][j * fs:(j + 1) * fs].copy_(wo2d, non_blocking=True)
+    ws.wo_full[0:fs].copy_(wo2d, non_blocking=True)
     nat.check(lib.mtfc_signal_peers(ws.peer_flag_ptrs, n - 1, 1, ms))
+    relu = nat.EPILOGUE_RELU if first.activation == "relu" else nat.EPILOGUE_NONE
+
+    def first_product(c, b_ptr, blocks, first_block):
+      """h[chunk c, blocks first_block .. first_block + blocks) = act(x[chunk c] . wi blocks)."""
+      r0, r1 = bounds[c], bounds[c + 1]
+      d1 = nat.GemmDesc()
+      d1.batch, d1.m, d1.n, d1.k = blocks, r1 - r0, fs, k1
+      d1.a_batch, d1.a_m, d1.a_k = 0, k1, 1
+      d1.b_batch, d1.b_k, d1.b_n = k1 * fs, fs, 1
+      d1.c_batch, d1.c_m, d1.c_n = fs, f, 1
+      d1.in_dtype = d1.out_dtype = nat.BF16
+      d1.epilogue, d1.force_path = relu, 0
+      nat.check(lib.mtfc_gemm(ctypes.byref(d1), ctypes.c_void_p(x.ptr + (me * mine + r0) * k1 * 2),
+                              ctypes.c_void_p(b_ptr),
+                              ctypes.c_void_p(ws.h.data_ptr() + (r0 * f + first_block * fs) * 2), ms))
+    for c in range(chunks):
+      first_product(c, wi.ptr, 1, 0)
     nat.check(lib.mtfc_wait_counters(ctypes.c_void_p(flags + 4), 1, n - 1, ctypes.c_void_p(epochs + 4), ms))
     # 3. this rank's rows, chunk by chunk; finished chunks travel while the next is multiplied
     result = torch.empty(rows * m2, dtype=torch.bfloat16, device=ws.h.device)
@@ -912,35 +938,29 @@ class CudaMeshImpl(SlicedMeshImpl):
     fork.record(main)
     ws.push.wait_event(fork)
     ws.pull.wait_event(fork)
-    relu = nat.EPILOGUE_RELU if first.activation == "relu" else nat.EPILOGUE_NONE
     for c in range(chunks):
-      g0 = me * mine + c * rc
-      d1 = nat.GemmDesc()
-      d1.batch, d1.m, d1.n, d1.k = n, rc, fs, k1
-      d1.a_batch, d1.a_m, d1.a_k = 0, k1, 1
-      d1.b_batch, d1.b_k, d1.b_n = k1 * fs, fs, 1
-      d1.c_batch, d1.c_m, d1.c_n = fs, f, 1
-      d1.in_dtype = d1.out_dtype = nat.BF16
-      d1.epilogue, d1.force_path = relu, 0
-      nat.check(lib.mtfc_gemm(ctypes.byref(d1), ctypes.c_void_p(x.ptr + g0 * k1 * 2),
-                              ctypes.c_void_p(ws.wi_all.data_ptr()),
-                              ctypes.c_void_p(ws.h.data_ptr() + c * rc * f * 2), ms))
+      r0, r1 = bounds[c], bounds[c + 1]
+      g0, g1 = me * mine + r0, me * mine + r1
+      first_product(c, ws.wi_all.data_ptr() + k1 * fs * 2, n - 1, 1)
       d2 = nat.GemmDesc()
-      d2.batch, d2.m, d2.n, d2.k = 1, rc, m2, f
+      d2.batch, d2.m, d2.n, d2.k = 1, r1 - r0, m2, f
       d2.a_batch, d2.a_m, d2.a_k = 0, f, 1
       d2.b_batch, d2.b_k, d2.b_n = 0, m2, 1
-      d2.c_batch, d2.c_m, d2.c_n = rc * m2, m2, 1
+      d2.c_batch, d2.c_m, d2.c_n = (r1 - r0) * m2, m2, 1
       d2.in_dtype = d2.out_dtype = nat.BF16
       d2.epilogue, d2.force_path = nat.EPILOGUE_NONE, 0
-      nat.check(lib.mtfc_gemm(ctypes.byref(d2), ctypes.c_void_p(ws.h.data_ptr() + c * rc * f * 2),
+      nat.check(lib.mtfc_gemm(ctypes.byref(d2), ctypes.c_void_p(ws.h.data_ptr() + r0 * f * 2),
                               ctypes.c_void_p(ws.wo_full.data_ptr()),
                               ctypes.c_void_p(result.data_ptr() + g0 * m2 * 2), ms))
       done = torch.cuda.Event()
       done.record(main)
       ws.push.wait_event(done)
       with torch.cuda.stream(ws.push):
+        if c == 0:
+          nat.check(lib.mtfc_wait_counters(ctypes.c_void_p(flags), 1, n - 1, ctypes.c_void_p(epochs),
+                                           ctypes.c_void_p(ws.push.cuda_stream)))
         for r in others:
-          ws.peer_y[r][g0:g0 + rc].copy_(res2d[g0:g0 + rc], non_blocking=True)
+          ws.peer_y[r][g0:g1].copy_(res2d[g0:g1], non_blocking=True)
         nat.check(lib.mtfc_signal_peers(ws.peer_flag_ptrs, n - 1, 2 + c,
                                         ctypes.c_void_p(ws.push.cuda_stream)))
       with torch.cuda.stream(ws.pull):
@@ -949,8 +969,8 @@ class CudaMeshImpl(SlicedMeshImpl):
                                          ctypes.c_void_p(epochs + 4 * (2 + c)),
                                          ctypes.c_void_p(ws.pull.cuda_stream)))
         for r in others:
-          r0 = r * mine + c * rc
-          res2d[r0:r0 + rc].copy_(ws.y_recv[r0:r0 + rc], non_blocking=True)
+          res2d[r * mine + r0:r * mine + r1].copy_(ws.y_recv[r * mine + r0:r * mine + r1],
+                                                   non_blocking=True)
     main.wait_stream(ws.push)
     main.wait_stream(ws.pull)
     out = self._device_array(result, list(x.shape[:-1]) + [m2], x.dtype)
