@@ -826,7 +826,8 @@ class CudaMeshImpl(SlicedMeshImpl):
   # over the axis).  MTFC_RESHARDED_FFN=0 keeps the reference's schedule.
   RESHARDED_FFN = os.environ.get("MTFC_RESHARDED_FFN", "1") == "1"
   RESHARDED_FFN_MIN_BYTES = 4 << 20
-  RESHARDED_FFN_MAX_CHUNKS = 2
+  RESHARDED_FFN_MAX_CHUNKS = 4
+  RESHARDED_FFN_LINK_BYTES_PER_S = 0.74e12   # measured peer-copy rate per direction
   RESHARDED_FFN_MIN_CHUNK_ROWS = 4096   # fewer rows leave the second product too few tiles
 
   def defer_einsum(self, fn, inputs, equation, activation):
@@ -877,13 +878,24 @@ class CudaMeshImpl(SlicedMeshImpl):
       return None
     mine = rows // n
     # Row chunks of this rank's share: a chunk's result travels while the next chunk is
-    # multiplied, and what travels after the last product is exposed, so the last chunk is
-    # the small one (a quarter); every further chunk costs a chain of dependent stream
-    # operations, so there are two at most.
+    # multiplied, what travels after the last product is exposed, and every chunk costs a
+    # chain of dependent stream operations.  With little to move beside the arithmetic
+    # (groups of two) two chunks, the last one a quarter; otherwise (a rank pushes n - 1
+    # copies of its rows) equal chunks, so that each journey fits behind the next product.
+    travel = (n - 1) * mine * m2 * 2 / self.RESHARDED_FFN_LINK_BYTES_PER_S
+    multiply = 4.0 * mine * k1 * fs * n / 1.4e15
     bounds = [0, mine]
     if self.RESHARDED_FFN_MAX_CHUNKS >= 2 and mine >= 2 * self.RESHARDED_FFN_MIN_CHUNK_ROWS:
-      last = max(256, (mine // 4) // 256 * 256)
-      bounds = [0, mine - last, mine]
+      if travel <= multiply / 3:
+        last = max(256, (mine // 4) // 256 * 256)
+        bounds = [0, mine - last, mine]
+      else:
+        count = 1
+        for c in range(self.RESHARDED_FFN_MAX_CHUNKS, 1, -1):
+          if mine % (c * 256) == 0 and mine // c >= self.RESHARDED_FFN_MIN_CHUNK_ROWS:
+            count = c
+            break
+        bounds = [mine // count * i for i in range(count + 1)]
     chunks = len(bounds) - 1
     ws = self._ffn_workspace(pg, members, pnum, rows, k1, fs, m2, chunks)
     if ws is None:

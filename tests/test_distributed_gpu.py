@@ -227,6 +227,16 @@ def _worker(rank, world, port, out_dir):
     assert int(hi.item()) == int(lo.item())    # every rank holds the same bits
     split.release_graphs()
     exchange.append("row-split x%d chunks" % list(split._ffn_ws)[0][-1])
+    # the other chunking (little to move beside the arithmetic: two chunks, the last a quarter)
+    split2 = CudaMeshImpl(mesh_shape, "d_ff:all", list(range(world)))
+    split2.RESHARDED_FFN_MIN_BYTES = 1
+    split2.RESHARDED_FFN_MIN_CHUNK_ROWS = 256
+    split2.RESHARDED_FFN_LINK_BYTES_PER_S = 1e15
+    for _ in range(2):
+      got_wide2, _ = ffn_wide(split2)
+      assert rel_err(got_wide2, ref_wide) < 2e-2
+    assert list(split2._ffn_ws)[0][-1] == 2 and all(w is not None for w in split2._ffn_ws.values())
+    nat_mod.device_status()
     # the reference's schedule stays available
     plain = CudaMeshImpl(mesh_shape, "d_ff:all", list(range(world)))
     plain.RESHARDED_FFN = False
