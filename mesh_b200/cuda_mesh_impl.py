@@ -462,6 +462,22 @@ class _PeerWorkspace(object):
                "rank", "nranks", "mc_stage", "mc_out", "exchange")
 
 
+def ffn_row_chunks(n, mine, k1, fs, m2, max_chunks, min_chunk_rows, link_bytes_per_s):
+  """Row boundaries (multiples of 256) of the chunks a rank's `mine` rows are multiplied
+  and sent in by the row-split FFN schedule: [0, ..., mine]."""
+  travel = (n - 1) * mine * m2 * 2 / link_bytes_per_s
+  multiply = 4.0 * mine * k1 * fs * n / 1.4e15
+  if max_chunks < 2 or mine < 2 * min_chunk_rows:
+    return [0, mine]
+  if travel <= multiply / 3:
+    last = max(256, (mine // 4) // 256 * 256)
+    return [0, mine - last, mine]
+  for c in range(max_chunks, 1, -1):
+    if mine % (c * 256) == 0 and mine // c >= min_chunk_rows:
+      return [mine // c * i for i in range(c + 1)]
+  return [0, mine]
+
+
 def alltoall_peer_plan(shape, itemsize, n, split_axis, concat_axis):
   """How mtfc_alltoall_peer walks a contiguous slice of `shape` whose
   `split_axis` is cut in n parts that are concatenated along `concat_axis`:
@@ -882,20 +898,8 @@ class CudaMeshImpl(SlicedMeshImpl):
     # chain of dependent stream operations.  With little to move beside the arithmetic
     # (groups of two) two chunks, the last one a quarter; otherwise (a rank pushes n - 1
     # copies of its rows) equal chunks, so that each journey fits behind the next product.
-    travel = (n - 1) * mine * m2 * 2 / self.RESHARDED_FFN_LINK_BYTES_PER_S
-    multiply = 4.0 * mine * k1 * fs * n / 1.4e15
-    bounds = [0, mine]
-    if self.RESHARDED_FFN_MAX_CHUNKS >= 2 and mine >= 2 * self.RESHARDED_FFN_MIN_CHUNK_ROWS:
-      if travel <= multiply / 3:
-        last = max(256, (mine // 4) // 256 * 256)
-        bounds = [0, mine - last, mine]
-      else:
-        count = 1
-        for c in range(self.RESHARDED_FFN_MAX_CHUNKS, 1, -1):
-          if mine % (c * 256) == 0 and mine // c >= self.RESHARDED_FFN_MIN_CHUNK_ROWS:
-            count = c
-            break
-        bounds = [mine // count * i for i in range(count + 1)]
+    bounds = ffn_row_chunks(n, mine, k1, fs, m2, self.RESHARDED_FFN_MAX_CHUNKS,
+                            self.RESHARDED_FFN_MIN_CHUNK_ROWS, self.RESHARDED_FFN_LINK_BYTES_PER_S)
     chunks = len(bounds) - 1
     ws = self._ffn_workspace(pg, members, pnum, rows, k1, fs, m2, chunks)
     if ws is None:
@@ -924,6 +928,12 @@ class CudaMeshImpl(SlicedMeshImpl):
       ws.peer_wi[r][j].copy_(wi2d, non_blocking=True)
       ws.peer_wo[r][j * fs:(j + 1) * fs].copy_(wo2d, non_blocking=True)
     ws.wo_full[0:fs].copy_(wo2d, non_blocking=True)
+    # In a group of two the own slice is half of the first product: worth launches of its
+    # own ahead of the wait.  In larger groups it is a small product per chunk that costs
+    # more in launches than the wait it hides, so one product takes all blocks.
+    own_first = n == 2
+    if not own_first:
+      ws.wi_all[0].copy_(wi2d, non_blocking=True)
     nat.check(lib.mtfc_signal_peers(ws.peer_flag_ptrs, n - 1, 1, ms))
     relu = nat.EPILOGUE_RELU if first.activation == "relu" else nat.EPILOGUE_NONE
 
@@ -940,8 +950,9 @@ class CudaMeshImpl(SlicedMeshImpl):
       nat.check(lib.mtfc_gemm(ctypes.byref(d1), ctypes.c_void_p(x.ptr + (me * mine + r0) * k1 * 2),
                               ctypes.c_void_p(b_ptr),
                               ctypes.c_void_p(ws.h.data_ptr() + (r0 * f + first_block * fs) * 2), ms))
-    for c in range(chunks):
-      first_product(c, wi.ptr, 1, 0)
+    if own_first:
+      for c in range(chunks):
+        first_product(c, wi.ptr, 1, 0)
     nat.check(lib.mtfc_wait_counters(ctypes.c_void_p(flags + 4), 1, n - 1, ctypes.c_void_p(epochs + 4), ms))
     # 3. this rank's rows, chunk by chunk; finished chunks travel while the next is multiplied
     result = torch.empty(rows * m2, dtype=torch.bfloat16, device=ws.h.device)
@@ -953,7 +964,10 @@ class CudaMeshImpl(SlicedMeshImpl):
     for c in range(chunks):
       r0, r1 = bounds[c], bounds[c + 1]
       g0, g1 = me * mine + r0, me * mine + r1
-      first_product(c, ws.wi_all.data_ptr() + k1 * fs * 2, n - 1, 1)
+      if own_first:
+        first_product(c, ws.wi_all.data_ptr() + k1 * fs * 2, n - 1, 1)
+      else:
+        first_product(c, ws.wi_all.data_ptr(), n, 0)
       d2 = nat.GemmDesc()
       d2.batch, d2.m, d2.n, d2.k = 1, r1 - r0, m2, f
       d2.a_batch, d2.a_m, d2.a_k = 0, f, 1

@@ -276,3 +276,21 @@ def test_alltoall_peer_plan_moves_every_part_to_its_place(shape, n):
       for dest in range(n):
         np.testing.assert_array_equal(got[dest].view(np.float32).reshape(plan[0]), want[dest].a)
   assert planned >= 1
+
+
+def test_ffn_row_chunks_cover_the_rows_in_multiples_of_256():
+  """Chunk boundaries of the row-split FFN schedule at the benchmark's group shapes."""
+  from mesh_b200.cuda_mesh_impl import ffn_row_chunks
+  cases = {(2, 16384): [0, 12288, 16384],                  # 2x2 mesh: little travels, last chunk a quarter
+           (4, 16384): [0, 4096, 8192, 12288, 16384],      # one group of four: equal chunks
+           (4, 8192): [0, 4096, 8192],                     # 2x4 mesh
+           (2, 32768): [0, 24576, 32768]}
+  for (n, mine), want in cases.items():
+    assert ffn_row_chunks(n, mine, 1024, 4096 // n, 1024, 4, 4096, 0.74e12) == want
+  for n in (2, 4, 8):
+    for mine in (256, 512, 2048, 3 * 256, 40 * 256):
+      for min_rows in (256, 4096):
+        b = ffn_row_chunks(n, mine, 256, 512, 256, 4, min_rows, 0.74e12)
+        assert b[0] == 0 and b[-1] == mine and all(x % 256 == 0 for x in b)
+        assert all(hi > lo for lo, hi in zip(b[:-1], b[1:]))
+  assert ffn_row_chunks(2, 16384, 1024, 2048, 1024, 1, 4096, 0.74e12) == [0, 16384]
