@@ -48,6 +48,7 @@ class HParams(object):
     self.moe_switch_dropout = 0.1
     self.moe_switch_jitter = 1e-2
     self.moe_z_loss = None
+    self.moe_ntlb_top_k = 4
     self.moe_use_fused_kernels = True
     for k, v in kwargs.items():
       if not hasattr(self, k):
@@ -191,6 +192,113 @@ def _switch_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gat
   aux = dict(index_1=expert_index, position_1=mtf.to_int32(position_flat), gate_1=expert_gate,
              raw_gates=raw_gates)
   return dispatch_tensor, combine_tensor, loss, aux
+
+
+# ------------------------------------------------- further top-1 style routers
+def _router_gates(inputs, experts_dim, hparams, train, gate_weights, name, reduced_dim=None,
+                  perturb_in_float=True, allow_dropout=True):
+  """What the Switch-family routers share up to the softmax: exploration noise on the
+  router's input (policies input_jitter / input_dropout), the gate dense layer, the
+  softmax over `reduced_dim` (the experts unless stated).  Returns (gate_logits, raw_gates)."""
+  policy = hparams.moe_switch_policy_train if train else hparams.moe_switch_policy_eval
+  if policy not in ("argmax", "input_jitter", "input_dropout"):
+    raise ValueError("Unknown Switch gating policy %s" % policy)
+  gate_inputs = mtf.to_float(inputs) if perturb_in_float else inputs
+  if policy == "input_dropout" and allow_dropout:
+    gate_inputs = mtf.dropout(gate_inputs, is_training=train, keep_prob=1.0 - hparams.moe_switch_dropout)
+  elif train and policy == "input_jitter":
+    gate_inputs = layers.multiplicative_jitter(gate_inputs, hparams.moe_switch_jitter)
+  gate_logits = layers.dense(gate_inputs, experts_dim, use_bias=False, kernel_weights=gate_weights,
+                             name=name)
+  raw_gates = mtf.softmax(gate_logits, reduced_dim or experts_dim)
+  return gate_logits, mtf.to_float(raw_gates)
+
+
+def _balance_loss(raw_gates, expert_mask, group_size_dim, experts_dim):
+  """mean over (group, expert) of [fraction of tokens choosing e] x [mean gate of e],
+  times E^2 (the loss of moe.py:1420-1424, shared by the top-1 routers)."""
+  density = mtf.reduce_mean(expert_mask, reduced_dim=group_size_dim)
+  density_proxy = mtf.reduce_mean(raw_gates, reduced_dim=group_size_dim)
+  return mtf.reduce_mean(density_proxy * density) * float(experts_dim.size * experts_dim.size)
+
+
+def _finish_router(combine_tensor, dispatch_source, loss, inputs):
+  combine_tensor = mtf.cast(combine_tensor, inputs.dtype)
+  source = combine_tensor if dispatch_source is None else dispatch_source
+  dispatch_tensor = mtf.cast(mtf.cast(source, G.bool_), combine_tensor.dtype)
+  return dispatch_tensor, combine_tensor, mtf.cast(loss, inputs.dtype)
+
+
+def _ntlb_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate_weights):
+  """"No token left behind" routing (moe.py:804-940): every token ranks its
+  hparams.moe_ntlb_top_k best experts; round i offers the still unrouted tokens
+  their i-th choice, first come first served within what is left of each
+  expert's capacity.  A token routed in round i carries its i-th gate."""
+  outer_batch_dim, batch_dim, group_size_dim = inputs.shape.dims[:3]
+  _, raw_gates = _router_gates(inputs, experts_dim, hparams, train, gate_weights, "ntlb_gating",
+                               perturb_in_float=False, allow_dropout=False)
+  k_dim = Dimension("k", hparams.moe_ntlb_top_k)
+  expert_gate, expert_index = mtf.top_k(raw_gates, reduced_dim=experts_dim, k_dim=k_dim)
+  expert_mask = mtf.one_hot(expert_index, experts_dim)
+  loss = _balance_loss(raw_gates, expert_mask, group_size_dim, experts_dim)
+  masks = mtf.split(expert_mask, k_dim, k_dim.size)
+  gates = mtf.split(expert_gate, k_dim, k_dim.size)
+  indices = mtf.split(expert_index, k_dim, k_dim.size)
+  mesh = inputs.mesh
+  token_shape = Shape([outer_batch_dim, batch_dim, group_size_dim])
+  combine_tensor = mtf.constant(mesh, 0, Shape([outer_batch_dim, batch_dim, experts_dim, expert_capacity_dim]))
+  taken = mtf.constant(mesh, 0, Shape([outer_batch_dim, batch_dim, experts_dim]))
+  unrouted = mtf.constant(mesh, 1.0, token_shape)
+  capacity = float(expert_capacity_dim.size)
+  for mask_i, gate_i, index_i in zip(masks, gates, indices):
+    mask_i = mtf.reshape(mask_i, Shape(token_shape.dims + [experts_dim])) * unrouted
+    gate_i = mtf.reshape(gate_i, token_shape)
+    index_i = mtf.reshape(index_i, token_shape)
+    # arrival number of each candidate at its expert, counting what earlier rounds placed
+    arrival = taken + mtf.cumsum(mask_i, group_size_dim)
+    placed = mask_i * mtf.to_float(mtf.less_equal(arrival, capacity))
+    taken += mtf.reduce_sum(placed, reduced_dim=group_size_dim)
+    placed_flat = mtf.reduce_sum(placed, reduced_dim=experts_dim)
+    unrouted -= placed_flat
+    combine_tensor += (gate_i * placed_flat * mtf.one_hot(index_i, experts_dim)
+                       * mtf.one_hot(mtf.to_int32(arrival - 1), expert_capacity_dim))
+  return _finish_router(combine_tensor, None, loss, inputs)
+
+
+def _switch_max_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate_weights):
+  """Top-1 routing in which an expert over capacity keeps its highest-gate
+  tokens instead of the first ones (moe.py:943-1054): top-`capacity` over the
+  group of (mask x gate) per expert."""
+  group_size_dim = inputs.shape.dims[-2]
+  _, raw_gates = _router_gates(inputs, experts_dim, hparams, train, gate_weights, "switch_max_gating")
+  expert_gate, expert_index = mtf.top_1(raw_gates, experts_dim)
+  expert_mask = mtf.one_hot(expert_index, experts_dim, dtype=raw_gates.dtype)
+  loss = _balance_loss(raw_gates, expert_mask, group_size_dim, experts_dim)
+  kept_gate, kept_token = mtf.top_k(expert_mask * expert_gate, reduced_dim=group_size_dim,
+                                    k_dim=expert_capacity_dim)
+  combine_tensor = mtf.one_hot(kept_token, group_size_dim, dtype=raw_gates.dtype) * kept_gate
+  return _finish_router(combine_tensor, None, loss, inputs)
+
+
+def _expert_selection_gating(inputs, experts_dim, group_size_dim, expert_capacity_dim, hparams, train,
+                             gate_weights, normalize_by_num_experts_routed=True):
+  """Experts choose tokens (moe.py:1057-1173): the softmax runs over the GROUP, every
+  expert takes its `capacity` most probable tokens, and a token's contributions are
+  divided by the number of experts that took it.  The loss pushes the mean (over
+  experts) token probability towards uniform."""
+  _, raw_gates = _router_gates(inputs, experts_dim, hparams, train, gate_weights,
+                               "expert_selection_gating", reduced_dim=group_size_dim)
+  token_prob, token_index = mtf.top_k(raw_gates, reduced_dim=group_size_dim, k_dim=expert_capacity_dim)
+  dispatch_tensor = mtf.one_hot(token_index, group_size_dim, dtype=raw_gates.dtype)
+  combine_tensor = dispatch_tensor * token_prob
+  if normalize_by_num_experts_routed:
+    times_taken = mtf.reduce_sum(
+        dispatch_tensor, output_shape=Shape(dispatch_tensor.shape.dims[:2] + [group_size_dim]))
+    combine_tensor /= mtf.maximum(times_taken, 1.0)
+  mean_prob = mtf.reduce_mean(raw_gates, reduced_dim=experts_dim)
+  group_size = float(group_size_dim.size)      # no padding mask: every token counts
+  loss = mtf.reduce_mean(mean_prob * mean_prob * group_size) * group_size
+  return _finish_router(combine_tensor, dispatch_tensor, loss, inputs)
 
 
 # -------------------------------------------------------------- fused gating
@@ -423,8 +531,9 @@ def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, lay
   capacity_dim = Dimension("expert_capacity", capacity)
   experts_dim_unsplit = Dimension("expert_unsplit", experts_dim.size)
   batch_dim_unsplit = Dimension("batch_unsplit", num_groups_dim.size)
-  if hparams.moe_gating not in ("top_2", "switch"):
-    raise ValueError("unknown gating %s: top_2 and switch are implemented" % hparams.moe_gating)
+  routers = ("top_2", "switch", "ntlb", "switch_max", "expert_selection")
+  if hparams.moe_gating not in routers:
+    raise ValueError("unknown hparams.moe_gating=%s" % hparams.moe_gating)
   if gate_weights.shape.dims[-1].name != experts_dim_unsplit.name:
     gate_weights = mtf.reshape(gate_weights, Shape([gate_weights.shape.dims[0], experts_dim_unsplit]))
   if second_noise is not None:
@@ -434,7 +543,7 @@ def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, lay
     second_noise = mtf.random_uniform(inputs.mesh, Shape(moe_input_dims[:-1]), dtype=G.float32)
 
   aux = {}
-  fused = hparams.moe_use_fused_kernels
+  fused = hparams.moe_use_fused_kernels and hparams.moe_gating in ("top_2", "switch")
   switch = hparams.moe_gating == "switch"
   if switch:
     # the single-pass kernel serves plain argmax routing; perturbed gate inputs and the
@@ -455,13 +564,23 @@ def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, lay
     expert_inputs = MoeDispatchOperation(inputs, routing, experts_dim_unsplit, capacity_dim,
                                          slot_table=slot_table).outputs[0]
   else:
-    if switch:
+    if hparams.moe_gating == "ntlb":
+      dispatch_tensor, combine_tensor, loss = _ntlb_gating(
+          inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights)
+    elif hparams.moe_gating == "switch_max":
+      dispatch_tensor, combine_tensor, loss = _switch_max_gating(
+          inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights)
+    elif hparams.moe_gating == "expert_selection":
+      dispatch_tensor, combine_tensor, loss = _expert_selection_gating(
+          inputs, experts_dim_unsplit, group_size_dim, capacity_dim, hparams, train, gate_weights)
+    elif switch:
       dispatch_tensor, combine_tensor, loss, aux = _switch_gating(
           inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights)
     else:
       dispatch_tensor, combine_tensor, loss, aux = _top_2_gating(
           inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights,
           second_noise=second_noise)
+    aux = dict(aux, combine_tensor=combine_tensor, dispatch_tensor=dispatch_tensor)
     expert_inputs = mtf.einsum(
         [inputs, dispatch_tensor],
         Shape([outer_batch_dim, experts_dim_unsplit, num_groups_dim, capacity_dim, input_dim]))

@@ -232,3 +232,44 @@ def test_fused_equals_unfused_on_device(cuda_device):
   for k in ("index_1", "index_2", "position_1", "position_2"):
     np.testing.assert_array_equal(a[k], b[k], err_msg=k)
   assert rel_err(a["output"], b["output"]) < 2e-2
+
+
+def _router_layer(impl_factory, gating, mesh_shape, layout):
+  """The MoE layer in float32 with one of the further routers (op chains only)."""
+  r = rng(31)
+  b, l, d, f, e = 8, 32, 64, 128, 8
+  g = mtf.Graph()
+  mesh = mtf.Mesh(g, "m")
+  x = r.standard_normal((b, l, d)).astype(np.float32)
+  wg = (r.standard_normal((d, e)) / np.sqrt(d) * 4).astype(np.float32)
+  wi = (r.standard_normal((e, d, f)) / np.sqrt(d)).astype(np.float32)
+  wo = (r.standard_normal((e, f, d)) / np.sqrt(f)).astype(np.float32)
+  X = mtf.import_tf_tensor(mesh, x, "batch:%d,length:%d,d_model:%d" % (b, l, d))
+  WG = mtf.import_tf_tensor(mesh, wg, "d_model:%d,expert_unsplit:%d" % (d, e))
+  WI = mtf.import_tf_tensor(mesh, wi, "experts:%d,d_model:%d,d_ff:%d" % (e, d, f))
+  WO = mtf.import_tf_tensor(mesh, wo, "experts:%d,d_ff:%d,d_model:%d" % (e, f, d))
+  hp = mtf.moe.HParams(moe_gating=gating, moe_group_size=l, moe_capacity_factor_train=1.0,
+                       moe_ntlb_top_k=3)
+  out, loss, aux = mtf.moe.transformer_moe_layer_v1(
+      X, mtf.Dimension("d_model", d), hp, True, mesh_shape, layout, WG, WI, WO, return_aux=True)
+  low = mtf.Lowering(g, {mesh: impl_factory(mesh_shape, layout)})
+  return (low.export_to_tf_tensor(out), low.export_to_tf_tensor(aux["combine_tensor"]),
+          float(low.export_to_tf_tensor(loss)))
+
+
+@pytest.mark.parametrize("mesh_shape", ["all:1", "all:2"])
+@pytest.mark.parametrize("gating", ["ntlb", "switch_max", "expert_selection"])
+def test_further_routers_match_oracle(cuda_device, gating, mesh_shape):
+  """ntlb / switch_max / expert_selection lowered on the device kernels (top-k, one-hot,
+  cumsum, einsums) against the oracle lowering of the same graph."""
+  from mesh_b200.cuda_mesh_impl import CudaMeshImpl
+  from oracle.numpy_mesh_impl import NumpyMeshImpl
+  layout = "batch:all;experts:all"
+  n = mtf.convert_to_shape(mesh_shape).size
+  ref_out, ref_combine, ref_loss = _router_layer(lambda s, l: NumpyMeshImpl(s, l), gating, mesh_shape, layout)
+  out, combine, loss = _router_layer(lambda s, l: CudaMeshImpl(s, l, [0] * n), gating, mesh_shape, layout)
+  # the same slots are filled (ranking ties aside: none with these seeded inputs) with the same gates
+  np.testing.assert_array_equal(combine != 0, ref_combine != 0)
+  assert rel_err(combine, ref_combine) < 1e-5
+  assert rel_err(out, ref_out) < 1e-5
+  assert abs(loss - ref_loss) <= 1e-5 * abs(ref_loss)

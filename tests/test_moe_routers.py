@@ -1,0 +1,147 @@
+"""The further routers of the MoE layer (no-token-left-behind, switch-max, expert
+selection) as op chains on the oracle backend, each against its routing rule
+written out directly in numpy, on one processor and on a mesh that splits the
+groups."""
+
+import numpy as np
+import pytest
+
+from mesh_b200 import mtf
+from oracle.numpy_mesh_impl import NumpyMeshImpl
+from helpers import rel_err, rng
+
+B, L, M, E, H = 4, 16, 8, 4, 12      # 4 groups of 16 tokens
+
+
+def _softmax(z, axis):
+  z = z - z.max(axis=axis, keepdims=True)
+  e = np.exp(z)
+  return e / e.sum(axis=axis, keepdims=True)
+
+
+def _layer(gating, mesh_shape, layout, seed, **hp):
+  r = rng(seed)
+  x = r.standard_normal((B, L, M)).astype(np.float32)
+  wg = (r.standard_normal((M, E)) * 0.7).astype(np.float32)
+  wi = (r.standard_normal((E, M, H)) / 3).astype(np.float32)
+  wo = (r.standard_normal((E, H, M)) / 3).astype(np.float32)
+  g = mtf.Graph()
+  m = mtf.Mesh(g, "m")
+  X = mtf.import_tf_tensor(m, x, "batch:%d,length:%d,d_model:%d" % (B, L, M))
+  WG = mtf.import_tf_tensor(m, wg, "d_model:%d,expert_unsplit:%d" % (M, E))
+  WI = mtf.import_tf_tensor(m, wi, "experts:%d,d_model:%d,d_ff:%d" % (E, M, H))
+  WO = mtf.import_tf_tensor(m, wo, "experts:%d,d_ff:%d,d_model:%d" % (E, H, M))
+  hparams = mtf.moe.HParams(moe_gating=gating, moe_group_size=L, moe_capacity_factor_train=1.0,
+                            moe_min_expert_capacity=2, **hp)
+  out, loss, aux = mtf.moe.transformer_moe_layer_v1(
+      X, mtf.Dimension("d_model", M), hparams, True, mesh_shape, layout, WG, WI, WO, return_aux=True)
+  low = mtf.Lowering(g, {m: NumpyMeshImpl(mesh_shape, layout)})
+  combine = aux["combine_tensor"]
+  names = [d.name for d in combine.shape.dims]
+  return dict(x=x, wg=wg, wi=wi, wo=wo, out=low.export_to_tf_tensor(out),
+              loss=float(low.export_to_tf_tensor(loss)), combine=low.export_to_tf_tensor(combine),
+              dispatch=low.export_to_tf_tensor(aux["dispatch_tensor"]), names=names)
+
+
+def _as_gsec(res):
+  """combine / dispatch as [group, token, expert, slot] whatever dim order the router built."""
+  order = [res["names"].index(n) for n in ("outer_batch", "batch", "group", "expert_unsplit", "expert_capacity")]
+  return (np.transpose(res["combine"], order)[0], np.transpose(res["dispatch"], order)[0])
+
+
+def _expected_output(res, combine):
+  """sum over (expert, slot) of combine x FFN_expert(the token dispatched to the slot)."""
+  x = res["x"].reshape(B, L, M)          # one group per batch row
+  dispatch = (combine != 0).astype(np.float64)
+  expert_in = np.einsum("gsm,gsec->egcm", x, dispatch)
+  h = np.maximum(np.einsum("egcm,emh->egch", expert_in, res["wi"]), 0)
+  y = np.einsum("egch,ehm->egcm", h, res["wo"])
+  return np.einsum("egcm,gsec->gsm", y, combine)
+
+
+def _balance_loss(raw, first_choice):
+  density = np.stack([(first_choice == e).mean(axis=1) for e in range(E)], axis=-1)
+  return float((raw.mean(axis=1) * density).mean() * E * E) * 1e-2
+
+
+MESHES = [("all:1", ""), ("all:2", "batch:all;experts:all")]
+
+
+@pytest.mark.parametrize("mesh_shape,layout", MESHES)
+def test_ntlb_routes_leftover_tokens_to_their_next_choices(mesh_shape, layout):
+  res = _layer("ntlb", mesh_shape, layout, 11, moe_ntlb_top_k=3)
+  combine, dispatch = _as_gsec(res)
+  C = combine.shape[-1]
+  raw = _softmax(res["x"].reshape(B, L, M) @ res["wg"], -1)
+  want = np.zeros_like(combine)
+  for g in range(B):
+    ranked = np.argsort(-raw[g], axis=-1, kind="stable")[:, :3]
+    taken = np.zeros(E, int)
+    unrouted = np.ones(L, bool)
+    for i in range(3):
+      arrivals = taken.copy()
+      placed_now = np.zeros(E, int)
+      for s in range(L):
+        if not unrouted[s]:
+          continue
+        e = ranked[s, i]
+        arrivals[e] += 1                     # every candidate counts, placed or not
+        if arrivals[e] <= C:
+          want[g, s, e, arrivals[e] - 1] = raw[g, s, e]
+          unrouted[s] = False
+          placed_now[e] += 1
+      taken += placed_now
+  np.testing.assert_allclose(combine, want, rtol=1e-5, atol=1e-7)
+  np.testing.assert_array_equal(dispatch, (want != 0).astype(np.float32))
+  assert (want != 0).sum(axis=(2, 3)).max() == 1                 # a token is routed once at most
+  # the loss averages over the three ranked choices as well (the mask keeps its k dim)
+  ranked_all = np.argsort(-raw, axis=-1, kind="stable")[..., :3]                   # [g, s, i]
+  density = np.stack([(ranked_all == e).mean(axis=1) for e in range(E)], axis=-1)   # [g, i, e]
+  want_loss = float((raw.mean(axis=1)[:, None, :] * density).mean() * E * E) * 1e-2
+  assert abs(res["loss"] - want_loss) < 1e-6
+  assert rel_err(res["out"].reshape(B, L, M), _expected_output(res, want)) < 1e-5
+
+
+@pytest.mark.parametrize("mesh_shape,layout", MESHES)
+def test_switch_max_keeps_the_highest_gates_of_an_over_full_expert(mesh_shape, layout):
+  res = _layer("switch_max", mesh_shape, layout, 12)
+  combine, dispatch = _as_gsec(res)
+  C = combine.shape[-1]
+  raw = _softmax(res["x"].reshape(B, L, M) @ res["wg"], -1)
+  choice = raw.argmax(-1)
+  want = np.zeros_like(combine)
+  for g in range(B):
+    for e in range(E):
+      score = np.where(choice[g] == e, raw[g, :, e], 0.0)
+      keep = np.argsort(-score, kind="stable")[:C]
+      for c, s in enumerate(keep):
+        want[g, s, e, c] = score[s]
+  np.testing.assert_allclose(combine, want, rtol=1e-5, atol=1e-7)
+  np.testing.assert_array_equal(dispatch, (want != 0).astype(np.float32))
+  assert abs(res["loss"] - _balance_loss(raw, choice)) < 1e-6
+  assert rel_err(res["out"].reshape(B, L, M), _expected_output(res, want)) < 1e-5
+
+
+@pytest.mark.parametrize("mesh_shape,layout", MESHES)
+def test_expert_selection_lets_every_expert_take_its_best_tokens(mesh_shape, layout):
+  res = _layer("expert_selection", mesh_shape, layout, 13)
+  combine, dispatch = _as_gsec(res)
+  C = combine.shape[-1]
+  prob = _softmax(res["x"].reshape(B, L, M) @ res["wg"], 1)      # over the tokens of a group
+  taken = np.zeros_like(combine)
+  for g in range(B):
+    for e in range(E):
+      for c, s in enumerate(np.argsort(-prob[g, :, e], kind="stable")[:C]):
+        taken[g, s, e, c] = 1.0
+  times = np.maximum(taken.sum(axis=(2, 3), keepdims=True), 1.0)
+  want = taken * prob[:, :, :, None] / times
+  np.testing.assert_allclose(combine, want, rtol=1e-5, atol=1e-8)
+  np.testing.assert_array_equal(dispatch, taken.astype(np.float32))
+  mean_prob = prob.mean(-1)
+  assert abs(res["loss"] - float((mean_prob * mean_prob * L).mean() * L) * 1e-2) < 1e-6
+  assert rel_err(res["out"].reshape(B, L, M), _expected_output(res, want)) < 1e-5
+
+
+def test_unknown_router_is_refused():
+  with pytest.raises(ValueError):
+    _layer("no_such_router", "all:1", "", 1)
