@@ -568,7 +568,7 @@ class _DeferredEinsum(object):
 class _FfnWorkspace(object):
   """Buffers of one row-split FFN problem size (see CudaMeshImpl._ffn_workspace)."""
   __slots__ = ("tensors", "handles", "wi_all", "wo_full", "y_recv", "flags", "peer_wi", "peer_wo",
-               "peer_y", "peer_flag_ptrs", "h", "epochs", "push", "pull", "rank")
+               "peer_y", "peer_flag_ptrs", "h", "epochs", "push", "pull", "lanes", "pull_lanes", "rank")
 
 
 class _PendingAllreduce(object):
@@ -923,11 +923,19 @@ class CudaMeshImpl(SlicedMeshImpl):
     #    rotated order, its own slice first: block j holds the slice of rank (me + j) mod n
     #    (the sum over the hidden dim does not care), so the product with the own slice can
     #    start at once and hides the journey of the others.
-    for r in others:
+    # (one side stream per peer: copies to different peers run on different copy engines
+    # instead of queueing behind each other)
+    start = torch.cuda.Event()
+    start.record(main)
+    for lane, r in zip(ws.lanes, others):
       j = (me - r) % n          # where this rank's slice sits in rank r's buffers
-      ws.peer_wi[r][j].copy_(wi2d, non_blocking=True)
-      ws.peer_wo[r][j * fs:(j + 1) * fs].copy_(wo2d, non_blocking=True)
+      lane.wait_event(start)
+      with torch.cuda.stream(lane):
+        ws.peer_wi[r][j].copy_(wi2d, non_blocking=True)
+        ws.peer_wo[r][j * fs:(j + 1) * fs].copy_(wo2d, non_blocking=True)
     ws.wo_full[0:fs].copy_(wo2d, non_blocking=True)
+    for lane in ws.lanes:
+      main.wait_stream(lane)
     # In a group of two the own slice is half of the first product: worth launches of its
     # own ahead of the wait.  In larger groups it is a small product per chunk that costs
     # more in launches than the wait it hides, so one product takes all blocks.
@@ -985,8 +993,14 @@ class CudaMeshImpl(SlicedMeshImpl):
         if c == 0:
           nat.check(lib.mtfc_wait_counters(ctypes.c_void_p(flags), 1, n - 1, ctypes.c_void_p(epochs),
                                            ctypes.c_void_p(ws.push.cuda_stream)))
-        for r in others:
+      go = torch.cuda.Event()
+      go.record(ws.push)
+      for lane, r in zip(ws.lanes, others):
+        lane.wait_event(go)
+        with torch.cuda.stream(lane):
           ws.peer_y[r][g0:g1].copy_(res2d[g0:g1], non_blocking=True)
+        ws.push.wait_stream(lane)
+      with torch.cuda.stream(ws.push):
         nat.check(lib.mtfc_signal_peers(ws.peer_flag_ptrs, n - 1, 2 + c,
                                         ctypes.c_void_p(ws.push.cuda_stream)))
       with torch.cuda.stream(ws.pull):
@@ -994,9 +1008,14 @@ class CudaMeshImpl(SlicedMeshImpl):
         nat.check(lib.mtfc_wait_counters(ctypes.c_void_p(flags + 4 * (2 + c)), 1, n - 1,
                                          ctypes.c_void_p(epochs + 4 * (2 + c)),
                                          ctypes.c_void_p(ws.pull.cuda_stream)))
-        for r in others:
+      landed = torch.cuda.Event()
+      landed.record(ws.pull)
+      for lane, r in zip(ws.pull_lanes, others):
+        lane.wait_event(landed)
+        with torch.cuda.stream(lane):
           res2d[r * mine + r0:r * mine + r1].copy_(ws.y_recv[r * mine + r0:r * mine + r1],
                                                    non_blocking=True)
+        ws.pull.wait_stream(lane)
     main.wait_stream(ws.push)
     main.wait_stream(ws.pull)
     out = self._device_array(result, list(x.shape[:-1]) + [m2], x.dtype)
@@ -1045,6 +1064,8 @@ class CudaMeshImpl(SlicedMeshImpl):
       ws.h = torch.empty((rows // n) * fs * n, dtype=torch.bfloat16, device=dev)
       ws.epochs = torch.zeros(2 + chunks, dtype=torch.int32, device=dev)
       ws.push, ws.pull = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+      ws.lanes = [torch.cuda.Stream(device=dev) for _ in others]
+      ws.pull_lanes = [torch.cuda.Stream(device=dev) for _ in others]
       ws.rank = me
       torch.cuda.synchronize()
       dist.barrier(group=pg)
