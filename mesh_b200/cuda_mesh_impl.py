@@ -277,6 +277,25 @@ class SlicedMeshImpl(mtf.MeshImpl):
               for p in pnums]
     return self._local_groups(x, [mesh_axis], collective)
 
+  def allreduce_start(self, x, mesh_axes, reduction_fn_string):
+    """allreduce whose result need not be there yet: one process per GPU starts the
+    collective now (on the process group's stream) and hands back an object whose
+    to_laid_out_tensor() waits for it, so that what is enqueued before the first reader
+    runs beside the exchange; otherwise the same as allreduce."""
+    mesh_axes = [a for a in mesh_axes if self.shape[a].size > 1]
+    if not self._distributed or not mesh_axes:
+      return self.allreduce(x, mesh_axes, reduction_fn_string)
+    if reduction_fn_string not in ("SUM", "MAX", "MIN"):
+      raise ValueError("unknown reduction %s" % reduction_fn_string)
+    import torch.distributed as dist
+    x = x.to_laid_out_tensor()
+    pg, _ = self._group(mesh_axes)
+    op = {"SUM": dist.ReduceOp.SUM, "MAX": dist.ReduceOp.MAX, "MIN": dist.ReduceOp.MIN}[reduction_fn_string]
+    s = x.tensor_list[0]
+    t = self._as_torch(s).clone()
+    work = dist.all_reduce(t, op=op, group=pg, async_op=True)
+    return _PendingAllreduce(self, self._from_torch(t, s.shape, s.dtype, self._local_pnums[0]), [work])
+
   def alltoall(self, x, mesh_axis, split_axis, concat_axis):
     x = x.to_laid_out_tensor()
     n = self.shape[mesh_axis].size

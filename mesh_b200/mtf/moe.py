@@ -388,7 +388,11 @@ class Top2GatingOperation(Operation):
     layout = impl.tensor_layout(Shape(x.shape.dims[:-2]))
     mesh_axes = [a for a in layout.tensor_axis_to_mesh_axis if a is not None]
     loss = results[6]
-    if mesh_axes:
+    if mesh_axes and hasattr(impl, "allreduce_start"):
+      # the sum over the other processors' groups starts now and is waited for by the
+      # loss's first reader (the layer puts it after the combine), not here
+      loss = impl.allreduce_start(loss, mesh_axes, "SUM")
+    elif mesh_axes:
       loss = LazyAllreduceSum(impl, loss, mesh_axes)
     lowering.set_tensor_lowering(self.outputs[6], loss)
 
@@ -559,7 +563,7 @@ def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, lay
                                  threshold, second_noise=second_noise)
     i1, i2, p1, p2, g1, g2, loss_sum, slot_table = gating.outputs
     routing = [i1, i2, p1, p2, g1, g2]
-    loss = mtf.cast(loss_sum, inputs.dtype)
+    loss = None     # read at the end of the layer: its allreduce runs beside everything between
     aux = dict(index_1=i1, index_2=i2, position_1=p1, position_2=p2, gate_1=g1, gate_2=g2)
     expert_inputs = MoeDispatchOperation(inputs, routing, experts_dim_unsplit, capacity_dim,
                                          slot_table=slot_table).outputs[0]
@@ -609,6 +613,8 @@ def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, lay
   else:
     output = mtf.einsum([expert_output, combine_tensor], Shape(moe_output_dims))
   output = mtf.reshape(output, batch_and_length_dims + [output_dim])
+  if loss is None:
+    loss = mtf.cast(loss_sum, inputs.dtype)
   loss = loss * hparams.moe_loss_coef
   if return_aux:
     return output, loss, aux

@@ -99,6 +99,10 @@ def _worker(rank, world, port, mesh, layout, out_dir):
       n = ora.shape[axis].size
       for name in ("SUM", "MAX", "MIN"):
         check(ora.allreduce(a, [axis], name), impl.allreduce(b, [axis], name), exact=(name != "SUM"))
+        # the same started now and waited for by its first reader
+        pending = impl.allreduce_start(b, [axis], name)
+        assert list(pending.slice_shape) == list(b.slice_shape)
+        check(ora.allreduce(a, [axis], name), pending.to_laid_out_tensor(), exact=(name != "SUM"))
       for ca in range(3):
         check(ora.allconcat(a, axis, ca), impl.allconcat(b, axis, ca))
         for sa in range(3):
