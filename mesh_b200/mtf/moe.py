@@ -36,6 +36,7 @@ class HParams(object):
     self.moe_group_size = 1024
     self.moe_capacity_factor_train = 1.25
     self.moe_capacity_factor_eval = 2.0
+    self.moe_capacity_factor_second_level = 1.0
     self.moe_use_second_place_loss = False
     self.moe_second_policy_train = "random"
     self.moe_second_policy_eval = "random"
@@ -80,8 +81,14 @@ def _second_policy(hparams, train):
 
 # ------------------------------------------------------------ unfused gating
 def _top_2_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate_weights,
-                  second_noise=None):
-  """The reference's op chain (moe.py:1380-1513); returns dispatch, combine, loss."""
+                  second_noise=None, importance=None):
+  """The reference's op chain (moe.py:1380-1513); returns dispatch, combine, loss.
+
+  `importance` [..., group] (1.0, 0.5 or 0.0 per position) is how the two-level
+  layer tells its inner routers what a position is: only positions of importance 1
+  take part as first choices (and in the loss), positions of importance 0 (empty
+  slots of the outer level) are not routed at all.  The gate kernel may carry
+  leading expert dims (one router per outer expert)."""
   group_size_dim = inputs.shape.dims[-2]
   gate_inputs = mtf.to_float(inputs)
   raw_gates = layers.dense(gate_inputs, experts_dim, use_bias=False,
@@ -92,9 +99,16 @@ def _top_2_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate
   gate_1, index_1 = mtf.top_1(raw_gates, experts_dim)
   mask_1 = mtf.one_hot(index_1, experts_dim, dtype=raw_gates.dtype)
   density_1_proxy = raw_gates
+  if importance is not None:
+    full = mtf.to_float(mtf.equal(importance, 1.0))
+    mask_1 *= full
+    gate_1 *= full
+    density_1_proxy *= full
   gates_without_top_1 = raw_gates * (1.0 - mask_1)
   gate_2, index_2 = mtf.top_1(gates_without_top_1, experts_dim)
   mask_2 = mtf.one_hot(index_2, experts_dim, dtype=raw_gates.dtype)
+  if importance is not None:
+    mask_2 *= mtf.to_float(mtf.greater(importance, 0.0))
 
   denom = gate_1 + gate_2 + 1e-9
   gate_1 /= denom
@@ -619,3 +633,96 @@ def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, lay
   if return_aux:
     return output, loss, aux
   return output, loss
+
+
+def transformer_moe_layer_v2(inputs, output_dim, hparams, train, mesh_shape, layout,
+                             gate_weights_outer, gate_weights_inner, wi, wo, activation=mtf.relu):
+  """Two-level top-2 MoE feed-forward layer (moe.py:528-801).
+
+  hparams.moe_num_experts = [x, y]: an outer router sends every position to up to two of
+  x expert groups; inside each group an inner router (one per group) sends the positions
+  that arrived to up to two of the group's y experts.  A slot of the outer level counts
+  fully in the inner routing if a first choice filled it, half if a second choice did,
+  and not at all if it stayed empty (the `importance` of `_top_2_gating`).
+
+  inputs [outer_batch?, batch, length, d_model]; gate_weights_outer [d_model,
+  expert_x_unsplit]; gate_weights_inner [expert_x, d_model, expert_y_unsplit];
+  wi [expert_y, expert_x, d_model, hidden]; wo [expert_y, expert_x, hidden, output_dim].
+  Four layout changes (alltoalls when the dims are split): groups -> expert_x,
+  inner groups -> expert_y, and back.  Returns (output, loss * moe_loss_coef).
+  """
+  if hparams.moe_gating != "top_2":
+    raise ValueError("unknown hparams.moe_gating=%s" % hparams.moe_gating)
+  if not isinstance(hparams.moe_num_experts, (list, tuple)) or len(hparams.moe_num_experts) != 2:
+    raise ValueError("the two-level layer needs moe_num_experts = [x, y]")
+  insert_outer_batch_dim = inputs.shape.ndims == 3
+  if insert_outer_batch_dim:
+    inputs = mtf.reshape(inputs, Shape([Dimension("outer_batch", 1)] + inputs.shape.dims))
+  a0, b1, l, m = inputs.shape.dims
+  x1 = Dimension("expert_x", hparams.moe_num_experts[0])
+  y0 = Dimension("expert_y", hparams.moe_num_experts[1])
+  x = Dimension("expert_x_unsplit", x1.size)
+  y = Dimension("expert_y_unsplit", y0.size)
+  n = output_dim
+
+  # outer level: groups of the (batch, length) positions
+  num_groups, group_size = _split_into_groups(
+      b1.size * l.size, hparams.moe_group_size, tensor_dim_to_mesh_dim_size(layout, mesh_shape, b1))
+  g1 = Dimension(b1.name, num_groups)
+  g = Dimension(b1.name + "_unsplit", num_groups)
+  s = Dimension("group_size_x", group_size)
+  cf = hparams.moe_capacity_factor_train if train else hparams.moe_capacity_factor_eval
+  c = Dimension("expert_capacity_x",
+                expert_capacity(s.size, x.size, cf, hparams.moe_min_expert_capacity))
+  # inner level: groups of the slots an expert group received
+  num_groups, group_size = _split_into_groups(
+      a0.size * g.size * c.size, hparams.moe_group_size,
+      tensor_dim_to_mesh_dim_size(layout, mesh_shape, a0))
+  t = Dimension("group_size_y", group_size)
+  h0 = Dimension(a0.name, num_groups)
+  h = Dimension(a0.name + "_unsplit", num_groups)
+  d = Dimension("expert_capacity_y",
+                expert_capacity(t.size, y.size, hparams.moe_capacity_factor_second_level,
+                                hparams.moe_min_expert_capacity))
+
+  def noise_for(shape):
+    if _second_policy(hparams, train)[0] != "random":
+      return None
+    return mtf.random_uniform(inputs.mesh, shape, dtype=G.float32)
+
+  inputs = mtf.reshape(inputs, Shape([a0, g1, s, m]))
+  dispatch_x, combine_x, loss_outer, _ = _top_2_gating(
+      inputs, x, c, hparams, train, gate_weights_outer, second_noise=noise_for(Shape([a0, g1, s])))
+  # expert groups first: that is the dim the layout change splits
+  expert_inputs_x = mtf.einsum([inputs, dispatch_x], Shape([x, a0, g1, c, m]))
+  weight_in_slot = mtf.reduce_sum(combine_x, output_shape=Shape([x, a0, g1, c]))
+  importance = 0.5 * (mtf.to_float(mtf.greater(weight_in_slot, 0.5))
+                      + mtf.to_float(mtf.greater(weight_in_slot, 0.0)))
+  expert_inputs_x = mtf.reshape(expert_inputs_x, Shape([x1, a0, g, c, m]))     # groups -> expert_x
+  importance = mtf.reshape(importance, Shape([x1, a0, g, c]))
+
+  inputs_y = mtf.reshape(expert_inputs_x, Shape([x1, h0, t, m]))
+  importance = mtf.reshape(importance, Shape([x1, h0, t]))
+  dispatch_y, combine_y, loss_inner, _ = _top_2_gating(
+      inputs_y, y, d, hparams, train, gate_weights_inner, importance=importance,
+      second_noise=noise_for(Shape([x1, h0, t])))
+  expert_inputs_y = mtf.einsum([inputs_y, dispatch_y], Shape([y, x1, h0, d, m]))
+  expert_inputs_y = mtf.reshape(expert_inputs_y, Shape([y0, x1, h, d, m]))     # inner groups -> expert_y
+
+  hidden_dim = wi.shape.dims[-1]
+  hidden = layers.dense(expert_inputs_y, hidden_dim, expert_dims=[y0, x1],
+                        reduced_dims=expert_inputs_y.shape.dims[-1:], activation=activation,
+                        use_bias=False, kernel_weights=wi, name="wi")
+  expert_output = layers.dense(hidden, n, expert_dims=[y0, x1], reduced_dims=hidden.shape.dims[-1:],
+                               use_bias=False, kernel_weights=wo, name="wo")
+
+  # and back, level by level
+  expert_output = mtf.reshape(expert_output, Shape([y, x1, h0, d, n]))         # expert_y -> inner groups
+  output_y = mtf.einsum([expert_output, combine_y], Shape([x1, h0, t, n]))
+  output = mtf.reshape(output_y, Shape([x1, a0, g, c, n]))
+  expert_output_x = mtf.reshape(output, Shape([x, a0, g1, c, n]))              # expert_x -> groups
+  output_x = mtf.einsum([expert_output_x, combine_x], Shape([a0, g1, s, n]))
+  output = mtf.reshape(output_x, Shape([a0, b1, l, n]))
+  if insert_outer_batch_dim:
+    output = mtf.reshape(output, Shape([b1, l, n]))
+  return output, (loss_outer + loss_inner) * hparams.moe_loss_coef

@@ -273,3 +273,39 @@ def test_further_routers_match_oracle(cuda_device, gating, mesh_shape):
   assert rel_err(combine, ref_combine) < 1e-5
   assert rel_err(out, ref_out) < 1e-5
   assert abs(loss - ref_loss) <= 1e-5 * abs(ref_loss)
+
+
+@pytest.mark.parametrize("mesh_shape,layout", [("all:1", ""), ("all:2", "batch:all;expert_x:all")])
+def test_two_level_layer_matches_oracle(cuda_device, mesh_shape, layout):
+  """transformer_moe_layer_v2 (float32, policy "all") lowered on the device kernels against
+  the oracle lowering of the same graph."""
+  from mesh_b200.cuda_mesh_impl import CudaMeshImpl
+  from oracle.numpy_mesh_impl import NumpyMeshImpl
+  b, l, d, f, ex, ey = 8, 32, 64, 96, 2, 4
+
+  def run(impl):
+    r = rng(51)
+    g = mtf.Graph()
+    m = mtf.Mesh(g, "m")
+    imp = lambda a, spec: mtf.import_tf_tensor(m, a.astype(np.float32), spec)
+    X = imp(r.standard_normal((b, l, d)), "batch:%d,length:%d,d_model:%d" % (b, l, d))
+    WGO = imp(r.standard_normal((d, ex)) / np.sqrt(d) * 4, "d_model:%d,expert_x_unsplit:%d" % (d, ex))
+    WGI = imp(r.standard_normal((ex, d, ey)) / np.sqrt(d) * 4,
+              "expert_x:%d,d_model:%d,expert_y_unsplit:%d" % (ex, d, ey))
+    WI = imp(r.standard_normal((ey, ex, d, f)) / np.sqrt(d),
+             "expert_y:%d,expert_x:%d,d_model:%d,expert_hidden:%d" % (ey, ex, d, f))
+    WO = imp(r.standard_normal((ey, ex, f, d)) / np.sqrt(f),
+             "expert_y:%d,expert_x:%d,expert_hidden:%d,d_model:%d" % (ey, ex, f, d))
+    hp = mtf.moe.HParams(moe_num_experts=[ex, ey], moe_group_size=l, moe_second_policy_train="all")
+    out, loss = mtf.moe.transformer_moe_layer_v2(
+        X, mtf.Dimension("d_model", d), hp, True, mesh_shape, layout, WGO, WGI, WI, WO)
+    low = mtf.Lowering(g, {m: impl})
+    return low.export_to_tf_tensor(out), float(low.export_to_tf_tensor(loss))
+  n = mtf.convert_to_shape(mesh_shape).size
+  ref, ref_loss = run(NumpyMeshImpl(mesh_shape, layout))
+  got, got_loss = run(CudaMeshImpl(mesh_shape, layout, [0] * n))
+  # a routing decision that flips on an ulp would move a whole row: compare the rows that agree
+  same = np.abs(got - ref).max(axis=-1) <= 1e-4 * np.abs(ref).max()
+  assert same.mean() > 0.97
+  assert rel_err(got[same], ref[same]) < 1e-5
+  assert abs(got_loss - ref_loss) <= 1e-4 * abs(ref_loss)
