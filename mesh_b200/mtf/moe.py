@@ -48,6 +48,7 @@ class HParams(object):
     self.moe_switch_policy_eval = "argmax"
     self.moe_switch_dropout = 0.1
     self.moe_switch_jitter = 1e-2
+    self.moe_switch_temperature = 1.0
     self.moe_z_loss = None
     self.moe_ntlb_top_k = 4
     self.moe_use_fused_kernels = True
@@ -166,12 +167,14 @@ def _top_2_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate
   return dispatch_tensor, combine_tensor, loss, aux
 
 
-def _switch_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate_weights):
+def _switch_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate_weights,
+                   importance=None):
   """Top-1 ("Switch") routing as the reference's op chain (moe.py:1184-1309):
   softmax, top_1 with the raw gate kept as it is, first-come positions within the
   expert's capacity, the same load-balancing loss as top-2 gating plus the
-  optional router z-loss.  Policies argmax, input_jitter and input_dropout;
-  "sample" needs a categorical sampler that is not lowered here."""
+  optional router z-loss.  Policies argmax, input_jitter, input_dropout and sample (the
+  expert drawn from the router's distribution at hparams.moe_switch_temperature).
+  `importance` [..., group]: positions that are not 1.0 (padding) are not routed."""
   policy = hparams.moe_switch_policy_train if train else hparams.moe_switch_policy_eval
   group_size_dim = inputs.shape.dims[-2]
   gate_inputs = mtf.to_float(inputs)
@@ -179,15 +182,28 @@ def _switch_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gat
     gate_inputs = mtf.dropout(gate_inputs, is_training=train, keep_prob=1.0 - hparams.moe_switch_dropout)
   elif train and policy == "input_jitter":
     gate_inputs = layers.multiplicative_jitter(gate_inputs, hparams.moe_switch_jitter)
-  elif policy not in ("argmax", "input_jitter"):
+  elif policy not in ("argmax", "input_jitter", "sample"):
     raise ValueError("Unknown Switch gating policy %s" % policy)
   gate_logits = layers.dense(gate_inputs, experts_dim, use_bias=False, kernel_weights=gate_weights,
                              name="switch_gating")
   raw_gates = mtf.softmax(gate_logits, experts_dim)
-  expert_gate, expert_index = mtf.top_1(raw_gates, experts_dim)
+  if policy == "sample":
+    # the expert is drawn from the router's distribution; the gate is its probability
+    expert_index = mtf.sample_with_temperature(gate_logits, experts_dim,
+                                               temperature=hparams.moe_switch_temperature)
+    expert_gate = mtf.reduce_sum(
+        raw_gates * mtf.one_hot(expert_index, experts_dim, dtype=raw_gates.dtype), reduced_dim=experts_dim)
+  else:
+    expert_gate, expert_index = mtf.top_1(raw_gates, experts_dim)
   expert_mask = mtf.one_hot(expert_index, experts_dim, dtype=raw_gates.dtype)
   density_1 = mtf.reduce_mean(expert_mask, reduced_dim=group_size_dim)
   density_1_proxy = mtf.reduce_mean(raw_gates, reduced_dim=group_size_dim)
+  if importance is not None:
+    # padding takes no slot, carries no gate and does not count in the loss's proxy
+    real = mtf.to_float(mtf.equal(importance, 1.0))
+    expert_mask *= real
+    expert_gate *= real
+    density_1_proxy *= real
   loss = mtf.reduce_mean(density_1_proxy * density_1) * float(experts_dim.size * experts_dim.size)
   if train and hparams.moe_z_loss is not None:
     log_z = mtf.reduce_logsumexp(gate_logits, experts_dim)
@@ -520,7 +536,7 @@ class MoeCombineGateGradOperation(Operation):
 # ------------------------------------------------------------------ the layer
 def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, layout,
                              gate_weights, wi, wo, second_noise=None, activation=mtf.relu,
-                             return_aux=False):
+                             return_aux=False, nonpadding=None):
   """Top-2 MoE feed-forward layer (moe.py:191-525).
 
   inputs: [<batch dims>, length, d_model]; gate_weights [d_model, experts_unsplit];
@@ -560,8 +576,15 @@ def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, lay
     # the uniform draw of moe.py:1461-1465, one value per token
     second_noise = mtf.random_uniform(inputs.mesh, Shape(moe_input_dims[:-1]), dtype=G.float32)
 
+  if nonpadding is not None:
+    # ones for real positions, zeros for padding ([<batch dims>, length]): padding is not routed
+    if hparams.moe_gating not in ("top_2", "switch"):
+      raise NotImplementedError("nonpadding with the %s router" % hparams.moe_gating)
+    nonpadding = mtf.zeros(inputs.mesh, Shape(batch_and_length_dims), dtype=inputs.dtype) + nonpadding
+    nonpadding = mtf.reshape(nonpadding, Shape(moe_input_dims[:-1]))
   aux = {}
-  fused = hparams.moe_use_fused_kernels and hparams.moe_gating in ("top_2", "switch")
+  fused = (hparams.moe_use_fused_kernels and hparams.moe_gating in ("top_2", "switch")
+           and nonpadding is None)
   switch = hparams.moe_gating == "switch"
   if switch:
     # the single-pass kernel serves plain argmax routing; perturbed gate inputs and the
@@ -593,11 +616,12 @@ def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, lay
           inputs, experts_dim_unsplit, group_size_dim, capacity_dim, hparams, train, gate_weights)
     elif switch:
       dispatch_tensor, combine_tensor, loss, aux = _switch_gating(
-          inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights)
+          inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights,
+          importance=nonpadding)
     else:
       dispatch_tensor, combine_tensor, loss, aux = _top_2_gating(
           inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights,
-          second_noise=second_noise)
+          second_noise=second_noise, importance=nonpadding)
     aux = dict(aux, combine_tensor=combine_tensor, dispatch_tensor=dispatch_tensor)
     expert_inputs = mtf.einsum(
         [inputs, dispatch_tensor],

@@ -1068,6 +1068,19 @@ def argmax(x, reduced_dim, name=None):
   return top_1(x, convert_to_dimension(reduced_dim), name=name)[1]
 
 
+def sample_with_temperature(logits, dim, temperature=1.0, name=None):
+  """An index along `dim` per position, drawn with probability proportional to
+  exp(logits / temperature) by the Gumbel trick (ops.py:5050-5086): temperature 0 is
+  the argmax, 1 samples from softmax(logits).  The uniform draws stay inside (0, 1) so
+  that -log(-log(u)) is finite; the arithmetic is float32."""
+  dim = convert_to_dimension(dim)
+  if temperature != 0.0:
+    logits = cast(logits, G.float32)
+    u = random_uniform(logits.mesh, logits.shape, minval=1e-9, maxval=1.0, dtype=G.float32)
+    logits = logits + (-log(-log(u))) * temperature
+  return argmax(logits, dim, name=name)
+
+
 class StackOperation(Operation):
   """Stacks same-shaped tensors along a new unsplit dim (ops.py:2592-2630)."""
 

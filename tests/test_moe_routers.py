@@ -145,3 +145,95 @@ def test_expert_selection_lets_every_expert_take_its_best_tokens(mesh_shape, lay
 def test_unknown_router_is_refused():
   with pytest.raises(ValueError):
     _layer("no_such_router", "all:1", "", 1)
+
+
+def _v1(gating, seed, nonpadding=None, **hp):
+  """The one-level layer on one processor; returns inputs, combine [g, s, e, c], loss, aux."""
+  r = rng(seed)
+  x = r.standard_normal((B, L, M)).astype(np.float32)
+  wg = (r.standard_normal((M, E)) * 0.7).astype(np.float32)
+  wi = (r.standard_normal((E, M, H)) / 3).astype(np.float32)
+  wo = (r.standard_normal((E, H, M)) / 3).astype(np.float32)
+  g = mtf.Graph()
+  m = mtf.Mesh(g, "m")
+  X = mtf.import_tf_tensor(m, x, "batch:%d,length:%d,d_model:%d" % (B, L, M))
+  WG = mtf.import_tf_tensor(m, wg, "d_model:%d,expert_unsplit:%d" % (M, E))
+  WI = mtf.import_tf_tensor(m, wi, "experts:%d,d_model:%d,d_ff:%d" % (E, M, H))
+  WO = mtf.import_tf_tensor(m, wo, "experts:%d,d_ff:%d,d_model:%d" % (E, H, M))
+  NP = None if nonpadding is None else mtf.import_tf_tensor(m, nonpadding, "batch:%d,length:%d" % (B, L))
+  hparams = mtf.moe.HParams(moe_gating=gating, moe_group_size=L, moe_capacity_factor_train=1.0,
+                            moe_min_expert_capacity=2, moe_second_policy_train="all",
+                            moe_use_fused_kernels=False, **hp)
+  out, loss, aux = mtf.moe.transformer_moe_layer_v1(
+      X, mtf.Dimension("d_model", M), hparams, True, "all:1", "", WG, WI, WO, return_aux=True,
+      nonpadding=NP)
+  low = mtf.Lowering(g, {m: NumpyMeshImpl("all:1", "")})
+  names = [d.name for d in aux["combine_tensor"].shape.dims]
+  order = [names.index(n) for n in ("outer_batch", "batch", "group", "expert_unsplit", "expert_capacity")]
+  combine = np.transpose(low.export_to_tf_tensor(aux["combine_tensor"]), order)[0]
+  res = dict(x=x, wg=wg, wi=wi, wo=wo, out=low.export_to_tf_tensor(out))
+  return res, combine, float(low.export_to_tf_tensor(loss)), {k: low.export_to_tf_tensor(v) for k, v in aux.items()}
+
+
+def test_padding_is_not_routed_by_top_2_gating():
+  from test_moe_v2 import _route
+  mask = (rng(21).uniform(size=(B, L)) > 0.3).astype(np.float32)
+  res, combine, loss, _ = _v1("top_2", 22, nonpadding=mask)
+  raw = _softmax(res["x"] @ res["wg"], -1)
+  routed = [_route(raw[g], combine.shape[-1], mask[g]) for g in range(B)]
+  want = np.stack([r[0] for r in routed])
+  np.testing.assert_allclose(combine, want, rtol=1e-5, atol=1e-7)
+  assert np.all(combine[mask == 0] == 0) and np.any(combine[mask == 1] != 0)
+  assert abs(loss - np.mean([r[1] for r in routed]) * 1e-2) < 1e-6
+  assert rel_err(res["out"], _expected_output(res, want)) < 1e-5
+  assert np.all(res["out"][mask == 0] == 0)            # a padded position gets no expert output
+
+
+def test_padding_is_not_routed_by_switch_gating():
+  mask = (rng(23).uniform(size=(B, L)) > 0.3).astype(np.float32)
+  res, combine, loss, _ = _v1("switch", 24, nonpadding=mask)
+  raw = _softmax(res["x"] @ res["wg"], -1)
+  C = combine.shape[-1]
+  want = np.zeros_like(combine)
+  for g in range(B):
+    seen = np.zeros(E, int)
+    for s in range(L):
+      if mask[g, s] == 0:
+        continue
+      e = raw[g, s].argmax()
+      if seen[e] < C:
+        want[g, s, e, seen[e]] = raw[g, s, e]
+      seen[e] += 1
+  np.testing.assert_allclose(combine, want, rtol=1e-5, atol=1e-7)
+  # the loss as the reference forms it (moe.py:1226-1236): the fraction of positions choosing
+  # an expert counts padding too, and the group's mean gates are scaled by the group's
+  # share of real positions (the mask meets the already averaged gates and broadcasts)
+  choice = raw.argmax(-1)
+  density = np.stack([(choice == e).mean(axis=1) for e in range(E)], axis=-1)
+  proxy = raw.mean(axis=1) * mask.mean(axis=1, keepdims=True)
+  assert abs(loss - float((proxy * density).mean() * E * E) * 1e-2) < 1e-6
+
+
+def test_sampled_switch_routing():
+  # temperature 0: the draw is the argmax
+  _, combine_argmax, loss_argmax, _ = _v1("switch", 25)
+  _, combine_t0, loss_t0, _ = _v1("switch", 25, moe_switch_policy_train="sample", moe_switch_temperature=0.0)
+  np.testing.assert_array_equal(combine_t0, combine_argmax)
+  assert loss_t0 == loss_argmax
+  # temperature 1: every routed position carries the probability of the expert drawn for it,
+  # experts other than the most probable one are drawn too, and the draw repeats (seeded by name)
+  res, combine, _, aux = _v1("switch", 25, moe_switch_policy_train="sample")
+  raw = _softmax(res["x"] @ res["wg"], -1)
+  index = aux["index_1"].reshape(B, L)
+  assert index.min() >= 0 and index.max() < E
+  assert (index != raw.argmax(-1)).mean() > 0.1
+  for g, s in zip(*np.nonzero(combine.sum(axis=(2, 3)))):
+    e = index[g, s]
+    assert abs(combine[g, s, e].sum() - raw[g, s, e]) < 1e-6 and combine[g, s].sum() == combine[g, s, e].sum()
+  _, again, _, _ = _v1("switch", 25, moe_switch_policy_train="sample")
+  np.testing.assert_array_equal(again, combine)
+
+
+def test_nonpadding_is_refused_where_it_is_not_implemented():
+  with pytest.raises(NotImplementedError):
+    _v1("ntlb", 26, nonpadding=np.ones((B, L), np.float32))
