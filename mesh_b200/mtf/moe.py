@@ -226,7 +226,7 @@ def _switch_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gat
 
 # ------------------------------------------------- further top-1 style routers
 def _router_gates(inputs, experts_dim, hparams, train, gate_weights, name, reduced_dim=None,
-                  perturb_in_float=True, allow_dropout=True):
+                  perturb_in_float=True, allow_dropout=True, logit_bias=None):
   """What the Switch-family routers share up to the softmax: exploration noise on the
   router's input (policies input_jitter / input_dropout), the gate dense layer, the
   softmax over `reduced_dim` (the experts unless stated).  Returns (gate_logits, raw_gates)."""
@@ -240,15 +240,22 @@ def _router_gates(inputs, experts_dim, hparams, train, gate_weights, name, reduc
     gate_inputs = layers.multiplicative_jitter(gate_inputs, hparams.moe_switch_jitter)
   gate_logits = layers.dense(gate_inputs, experts_dim, use_bias=False, kernel_weights=gate_weights,
                              name=name)
+  if logit_bias is not None:
+    gate_logits += logit_bias
   raw_gates = mtf.softmax(gate_logits, reduced_dim or experts_dim)
   return gate_logits, mtf.to_float(raw_gates)
 
 
-def _balance_loss(raw_gates, expert_mask, group_size_dim, experts_dim):
+def _balance_loss(raw_gates, expert_mask, group_size_dim, experts_dim, real=None):
   """mean over (group, expert) of [fraction of tokens choosing e] x [mean gate of e],
-  times E^2 (the loss of moe.py:1420-1424, shared by the top-1 routers)."""
+  times E^2 (the loss of moe.py:1420-1424, shared by the top-1 routers).  `real`
+  (1.0 for positions that are not padding) meets the already averaged gates, as in
+  the reference (moe.py:858-866): a group's term is scaled by its share of real
+  positions."""
   density = mtf.reduce_mean(expert_mask, reduced_dim=group_size_dim)
   density_proxy = mtf.reduce_mean(raw_gates, reduced_dim=group_size_dim)
+  if real is not None:
+    density_proxy *= real
   return mtf.reduce_mean(density_proxy * density) * float(experts_dim.size * experts_dim.size)
 
 
@@ -259,7 +266,8 @@ def _finish_router(combine_tensor, dispatch_source, loss, inputs):
   return dispatch_tensor, combine_tensor, mtf.cast(loss, inputs.dtype)
 
 
-def _ntlb_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate_weights):
+def _ntlb_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate_weights,
+                 importance=None):
   """"No token left behind" routing (moe.py:804-940): every token ranks its
   hparams.moe_ntlb_top_k best experts; round i offers the still unrouted tokens
   their i-th choice, first come first served within what is left of each
@@ -270,7 +278,12 @@ def _ntlb_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate_
   k_dim = Dimension("k", hparams.moe_ntlb_top_k)
   expert_gate, expert_index = mtf.top_k(raw_gates, reduced_dim=experts_dim, k_dim=k_dim)
   expert_mask = mtf.one_hot(expert_index, experts_dim)
-  loss = _balance_loss(raw_gates, expert_mask, group_size_dim, experts_dim)
+  real = None if importance is None else mtf.to_float(mtf.equal(importance, 1.0))
+  density_mask = expert_mask          # the loss's choice fractions are taken before the mask
+  if real is not None:
+    expert_mask *= real
+    expert_gate *= real
+  loss = _balance_loss(raw_gates, density_mask, group_size_dim, experts_dim, real)
   masks = mtf.split(expert_mask, k_dim, k_dim.size)
   gates = mtf.split(expert_gate, k_dim, k_dim.size)
   indices = mtf.split(expert_index, k_dim, k_dim.size)
@@ -295,7 +308,8 @@ def _ntlb_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate_
   return _finish_router(combine_tensor, None, loss, inputs)
 
 
-def _switch_max_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate_weights):
+def _switch_max_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate_weights,
+                       importance=None):
   """Top-1 routing in which an expert over capacity keeps its highest-gate
   tokens instead of the first ones (moe.py:943-1054): top-`capacity` over the
   group of (mask x gate) per expert."""
@@ -303,7 +317,12 @@ def _switch_max_gating(inputs, experts_dim, expert_capacity_dim, hparams, train,
   _, raw_gates = _router_gates(inputs, experts_dim, hparams, train, gate_weights, "switch_max_gating")
   expert_gate, expert_index = mtf.top_1(raw_gates, experts_dim)
   expert_mask = mtf.one_hot(expert_index, experts_dim, dtype=raw_gates.dtype)
-  loss = _balance_loss(raw_gates, expert_mask, group_size_dim, experts_dim)
+  real = None if importance is None else mtf.to_float(mtf.equal(importance, 1.0))
+  density_mask = expert_mask
+  if real is not None:
+    expert_mask *= real
+    expert_gate *= real
+  loss = _balance_loss(raw_gates, density_mask, group_size_dim, experts_dim, real)
   kept_gate, kept_token = mtf.top_k(expert_mask * expert_gate, reduced_dim=group_size_dim,
                                     k_dim=expert_capacity_dim)
   combine_tensor = mtf.one_hot(kept_token, group_size_dim, dtype=raw_gates.dtype) * kept_gate
@@ -311,13 +330,16 @@ def _switch_max_gating(inputs, experts_dim, expert_capacity_dim, hparams, train,
 
 
 def _expert_selection_gating(inputs, experts_dim, group_size_dim, expert_capacity_dim, hparams, train,
-                             gate_weights, normalize_by_num_experts_routed=True):
+                             gate_weights, normalize_by_num_experts_routed=True, importance=None):
   """Experts choose tokens (moe.py:1057-1173): the softmax runs over the GROUP, every
   expert takes its `capacity` most probable tokens, and a token's contributions are
   divided by the number of experts that took it.  The loss pushes the mean (over
   experts) token probability towards uniform."""
+  # padding gets -1e9 on its logits: the softmax runs over the positions of the group
   _, raw_gates = _router_gates(inputs, experts_dim, hparams, train, gate_weights,
-                               "expert_selection_gating", reduced_dim=group_size_dim)
+                               "expert_selection_gating", reduced_dim=group_size_dim,
+                               logit_bias=None if importance is None else
+                               mtf.to_float(mtf.equal(importance, 0.0)) * -1e9)
   token_prob, token_index = mtf.top_k(raw_gates, reduced_dim=group_size_dim, k_dim=expert_capacity_dim)
   dispatch_tensor = mtf.one_hot(token_index, group_size_dim, dtype=raw_gates.dtype)
   combine_tensor = dispatch_tensor * token_prob
@@ -326,8 +348,12 @@ def _expert_selection_gating(inputs, experts_dim, group_size_dim, expert_capacit
         dispatch_tensor, output_shape=Shape(dispatch_tensor.shape.dims[:2] + [group_size_dim]))
     combine_tensor /= mtf.maximum(times_taken, 1.0)
   mean_prob = mtf.reduce_mean(raw_gates, reduced_dim=experts_dim)
-  group_size = float(group_size_dim.size)      # no padding mask: every token counts
-  loss = mtf.reduce_mean(mean_prob * mean_prob * group_size) * group_size
+  if importance is None:
+    real_positions = float(group_size_dim.size)      # no padding mask: every position counts
+  else:
+    mean_prob *= mtf.to_float(mtf.equal(importance, 1.0))
+    real_positions = mtf.to_float(mtf.reduce_sum(importance, reduced_dim=group_size_dim))
+  loss = mtf.reduce_mean(mean_prob * mean_prob * real_positions) * float(group_size_dim.size)
   return _finish_router(combine_tensor, dispatch_tensor, loss, inputs)
 
 
@@ -578,8 +604,6 @@ def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, lay
 
   if nonpadding is not None:
     # ones for real positions, zeros for padding ([<batch dims>, length]): padding is not routed
-    if hparams.moe_gating not in ("top_2", "switch"):
-      raise NotImplementedError("nonpadding with the %s router" % hparams.moe_gating)
     nonpadding = mtf.zeros(inputs.mesh, Shape(batch_and_length_dims), dtype=inputs.dtype) + nonpadding
     nonpadding = mtf.reshape(nonpadding, Shape(moe_input_dims[:-1]))
   aux = {}
@@ -607,13 +631,14 @@ def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, lay
   else:
     if hparams.moe_gating == "ntlb":
       dispatch_tensor, combine_tensor, loss = _ntlb_gating(
-          inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights)
+          inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights, importance=nonpadding)
     elif hparams.moe_gating == "switch_max":
       dispatch_tensor, combine_tensor, loss = _switch_max_gating(
-          inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights)
+          inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights, importance=nonpadding)
     elif hparams.moe_gating == "expert_selection":
       dispatch_tensor, combine_tensor, loss = _expert_selection_gating(
-          inputs, experts_dim_unsplit, group_size_dim, capacity_dim, hparams, train, gate_weights)
+          inputs, experts_dim_unsplit, group_size_dim, capacity_dim, hparams, train, gate_weights,
+          importance=nonpadding)
     elif switch:
       dispatch_tensor, combine_tensor, loss, aux = _switch_gating(
           inputs, experts_dim_unsplit, capacity_dim, hparams, train, gate_weights,

@@ -234,6 +234,52 @@ def test_sampled_switch_routing():
   np.testing.assert_array_equal(again, combine)
 
 
-def test_nonpadding_is_refused_where_it_is_not_implemented():
-  with pytest.raises(NotImplementedError):
-    _v1("ntlb", 26, nonpadding=np.ones((B, L), np.float32))
+def test_padding_with_the_further_routers():
+  mask = (rng(27).uniform(size=(B, L)) > 0.3).astype(np.float32)
+  # no token left behind: padded positions are never candidates
+  res, combine, _, _ = _v1("ntlb", 28, nonpadding=mask, moe_ntlb_top_k=3)
+  raw = _softmax(res["x"] @ res["wg"], -1)
+  C = combine.shape[-1]
+  want = np.zeros_like(combine)
+  for g in range(B):
+    ranked = np.argsort(-raw[g], axis=-1, kind="stable")[:, :3]
+    taken, unrouted = np.zeros(E, int), mask[g] == 1
+    for i in range(3):
+      arrivals, placed_now = taken.copy(), np.zeros(E, int)
+      for s in range(L):
+        if unrouted[s]:
+          e = ranked[s, i]
+          arrivals[e] += 1
+          if arrivals[e] <= C:
+            want[g, s, e, arrivals[e] - 1] = raw[g, s, e]
+            unrouted[s] = False
+            placed_now[e] += 1
+      taken += placed_now
+  np.testing.assert_allclose(combine, want, rtol=1e-5, atol=1e-7)
+  assert np.all(combine[mask == 0] == 0)
+  # switch-max: an expert ranks the real positions that chose it
+  res, combine, _, _ = _v1("switch_max", 29, nonpadding=mask)
+  raw = _softmax(res["x"] @ res["wg"], -1)
+  choice = raw.argmax(-1)
+  want = np.zeros_like(combine)
+  for g in range(B):
+    for e in range(E):
+      score = np.where((choice[g] == e) & (mask[g] == 1), raw[g, :, e], 0.0)
+      for c, s in enumerate(np.argsort(-score, kind="stable")[:C]):
+        want[g, s, e, c] = score[s]
+  np.testing.assert_allclose(combine, want, rtol=1e-5, atol=1e-7)
+  # expert selection: padding is out of the softmax over the group
+  res, combine, loss, _ = _v1("expert_selection", 30, nonpadding=mask)
+  logits = res["x"] @ res["wg"] + (mask == 0)[..., None] * np.float32(-1e9)
+  prob = _softmax(logits, 1)
+  taken = np.zeros_like(combine)
+  for g in range(B):
+    for e in range(E):
+      for c, s in enumerate(np.argsort(-prob[g, :, e], kind="stable")[:C]):
+        taken[g, s, e, c] = 1.0
+  want = taken * prob[:, :, :, None] / np.maximum(taken.sum(axis=(2, 3), keepdims=True), 1.0)
+  np.testing.assert_allclose(combine, want, rtol=1e-5, atol=1e-8)
+  assert np.all(combine[mask == 0] == 0)
+  mean_prob = prob.mean(-1) * mask
+  want_loss = float((mean_prob * mean_prob * mask.sum(axis=1, keepdims=True)).mean() * L) * 1e-2
+  assert abs(loss - want_loss) < 1e-6
