@@ -480,6 +480,67 @@ def dot_product_attention(q, k, v, mask, is_training=False, dropout=0.0, extra_l
   return mtf.einsum([w, v], outputs_shape)
 
 
+def local_attention_1d(q, k, v, length_dim, key_dim, value_dim, fully_autoregressive=True,
+                       length_dim_num_splits=1, radius=128, sequence_id=1,
+                       write_priority=None, read_priority=None):
+  """Attention to a neighbourhood of each position
+  (mesh_tensorflow/transformer/attention.py:724-827).
+
+  Query position p sees memory positions in (p - radius, p] when
+  `fully_autoregressive`, else in (p - radius, p + radius]; positions of another
+  `sequence_id` and, if priorities are given, positions with
+  write_priority > read_priority[p] are hidden as well.  The length is cut into
+  blocks (the largest divisor of the per-processor length that is at most
+  max(radius, 128)); a block of queries attends to its own block of memory extended
+  by the margins of its neighbours (halo exchange: collective permutes between
+  neighbouring processors when the length is split over a mesh axis), so the logits
+  are [.., blocks, block, block + margins] instead of [.., length, length].
+  `v=None` uses the keys as values.  Returns q's shape with key_dim -> value_dim."""
+  length_per_split = length_dim.size // length_dim_num_splits
+  block_length = max(radius, 128)
+  while length_per_split % block_length != 0:
+    block_length -= 1
+  query_block = Dimension("query_block_length", block_length)
+  memory_block = Dimension("memory_block_length", block_length)
+  # the blocks dim takes the length dim's name, so the layout splits it the same way
+  num_blocks = Dimension(length_dim.name, length_dim.size // block_length)
+  exchange = mtf.left_halo_exchange if fully_autoregressive else mtf.halo_exchange
+
+  def as_queries(x):
+    return mtf.replace_dimensions(x, length_dim, [num_blocks, query_block])
+
+  def as_memory(x):
+    x = mtf.replace_dimensions(x, length_dim, [num_blocks, memory_block])
+    return exchange(x, num_blocks, memory_block, radius)
+  mesh = q.mesh
+  q = as_queries(q)
+  k = as_memory(k)
+  v = as_memory(v) if v is not None else k
+  if sequence_id is None:
+    sequence_id = 1
+  if not isinstance(sequence_id, mtf.Tensor) or length_dim not in sequence_id.shape.dims:
+    # margins that reach past the ends arrive as zeros: sequence 0, which nobody belongs to
+    sequence_id = mtf.zeros(mesh, Shape([length_dim]), dtype=G.int32) + sequence_id
+  position = mtf.mtf_range(mesh, length_dim, G.int32)
+  relative = as_memory(position) - as_queries(position)
+  visible = mtf.equal(as_queries(sequence_id), as_memory(sequence_id))
+  visible = mtf.logical_and(visible, mtf.greater(relative, -radius))
+  visible = mtf.logical_and(visible, mtf.less_equal(relative, 0 if fully_autoregressive else radius))
+  if read_priority is not None:
+    visible = mtf.logical_and(
+        visible, mtf.greater_equal(as_queries(read_priority), as_memory(write_priority)))
+  bias = mtf.cast(mtf.logical_not(visible), G.float32) * -1e9
+  padded_memory = Dimension("memory_block_length",
+                            (1 if fully_autoregressive else 2) * radius + block_length)
+  # logits and softmax in float32, weights back in v's type (attention.py:71-88)
+  logits = mtf.einsum([mtf.cast(q, G.float32), mtf.cast(k, G.float32)],
+                      reduced_dims=[key_dim]) + bias
+  weights = mtf.cast(mtf.softmax(logits, padded_memory), v.dtype)
+  out_dims = [d for d in q.shape.dims if d != key_dim] + [value_dim]
+  o = mtf.einsum([weights, v], output_shape=Shape(out_dims))
+  return mtf.replace_dimensions(o, [num_blocks, query_block], length_dim)
+
+
 def multihead_attention(query_antecedent, memory_antecedent, mask, kv_channels, heads,
                         is_training=False, dropout=0.0, weights=None, params=None,
                         float32_logits=True, fused=None, name="multihead_attention"):
