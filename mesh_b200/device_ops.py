@@ -62,7 +62,7 @@ class HookDeclined(Exception):
 
 class DeviceArray(object):
   """A strided view of a flat device buffer with an mtf dtype."""
-  __slots__ = ("buf", "shape", "strides", "offset", "dtype")
+  __slots__ = ("buf", "shape", "strides", "offset", "dtype", "origin")
 
   def __init__(self, buf, shape, dtype, strides=None, offset=0):
     self.buf = buf
@@ -70,6 +70,9 @@ class DeviceArray(object):
     self.strides = tuple(strides) if strides is not None else _contiguous_strides(self.shape)
     self.offset = offset
     self.dtype = dtype
+    # for a float32 array that is a widened bfloat16 array: that array (same shape and
+    # strides), whose values it holds exactly; None otherwise
+    self.origin = None
 
   @property
   def size(self):
@@ -300,7 +303,11 @@ class DeviceOps(object):
       return x
     if dtype.is_bool:
       return self._unary_code(_UNARY["nonzero"], x, dtype)
-    return self._unary_code(_UNARY["identity"], x, dtype)
+    out = self._unary_code(_UNARY["identity"], x, dtype)
+    if (x.dtype.name == "bfloat16" and dtype.name == "float32" and x.is_contiguous
+        and out.shape == x.shape and out.strides == x.strides):
+      out.origin = x      # an fp32 einsum can take the bf16 values as they are
+    return out
 
   def binary(self, name, a, b):
     if not isinstance(a, DeviceArray):
@@ -553,6 +560,46 @@ class DeviceOps(object):
       out = self._empty([sizes[l] for l in store], out_dtype)
     c_b, c_m, c_n = m * n, n, 1
     result = out if view_perm == list(range(len(store))) else self.transpose(out, view_perm)
+    if (a.dtype.name == "float32" and out_dtype.name == "float32" and nb == 1 and k % 4 == 0
+        and epilogue == nat.EPILOGUE_NONE and gemm_hook is None
+        and (a.origin is not None) != (b.origin is not None)
+        and m * n * k >= self.FP32_TENSOR_CORE_MIN_WORK):
+      # One operand is a widened bfloat16 array (activations meeting fp32 router weights or
+      # their gradients): its values go to the tensor cores as they are, only the other
+      # operand is split into three bf16 terms, and the three exact partial products
+      # (times the K chunks that keep each accumulation short) are added in fp32.  Half the
+      # tensor-core work of the six-term product and no pass over the large operand.
+      chunks = -(-k // self.FP32_TENSOR_CORE_MAX_K)
+      while chunks <= 8192 and (k % chunks or (k // chunks) % 4):
+        chunks += 1
+      if chunks <= 8192:
+        kk = k // chunks
+        a_exact = a.origin is not None
+        rows = n if a_exact else m
+        s_arr, s_row, s_k = (b, b_n, b_k) if a_exact else (a, a_m, a_k)
+        s3 = self._empty([chunks, rows, 6 * kk], G.bfloat16)
+        self._call(self._lib.mtfc_split_bf16x3, ctypes.c_void_p(s_arr.ptr), kk * s_k, s_row, s_k,
+                   ctypes.c_void_p(s3.ptr), chunks, rows, kk, 1 if a_exact else 0, self._stream())
+        part = self._empty([3, chunks, m, n], G.float32)
+        exact = (a if a_exact else b).origin
+        for term in range(3):      # the first three K blocks of a split row are its three terms
+          d = nat.GemmDesc()
+          d.batch, d.m, d.n, d.k = chunks, m, n, kk
+          if a_exact:
+            d.a_batch, d.a_m, d.a_k = kk * a_k, a_m, a_k
+            d.b_batch, d.b_k, d.b_n = rows * 6 * kk, 1, 6 * kk
+            pa, pb = exact.ptr, s3.ptr + term * kk * 2
+          else:
+            d.a_batch, d.a_m, d.a_k = rows * 6 * kk, 6 * kk, 1
+            d.b_batch, d.b_k, d.b_n = kk * b_k, b_k, b_n
+            pa, pb = s3.ptr + term * kk * 2, exact.ptr
+          d.c_batch, d.c_m, d.c_n = m * n, n, 1
+          d.in_dtype, d.out_dtype = nat.BF16, nat.F32
+          d.epilogue, d.force_path = nat.EPILOGUE_NONE, 0
+          self._call(self._lib.mtfc_gemm, ctypes.byref(d), ctypes.c_void_p(pa), ctypes.c_void_p(pb),
+                     ctypes.c_void_p(part.ptr + term * chunks * m * n * 4), self._stream())
+        total = self.reshape(self.reduce("SUM", part, [0, 1]), [sizes[l] for l in store])
+        return total if view_perm == list(range(len(store))) else self.transpose(total, view_perm)
     if (a.dtype.name == "float32" and out_dtype.name == "float32" and k % 4 == 0
         and k <= self.FP32_TENSOR_CORE_MAX_K
         and nb * m * n * k >= self.FP32_TENSOR_CORE_MIN_WORK):

@@ -200,6 +200,38 @@ def test_fp32_einsum_on_tensor_cores(both, eq, shapes):
   nat.device_status()
 
 
+@pytest.mark.parametrize("eq,shapes,widened", [
+    ("tm,me->te", [(4096, 1024), (1024, 32)], 0),        # router logits: activations x fp32 gate kernel
+    ("te,tm->me", [(16384, 32), (16384, 1024)], 1),      # its gradient: a contraction over 16384 tokens
+    ("te,tm->me", [(65536, 32), (65536, 512)], 1),       # ... and over 65536 (32 K chunks)
+    ("ab,bc->ac", [(512, 1024), (1024, 2048)], 0)])
+def test_fp32_einsum_with_a_widened_bf16_operand(both, eq, shapes, widened):
+  """float32 einsum where one operand is a bfloat16 array cast up (DeviceOps.cast records
+  that): the planner feeds the bfloat16 values to the tensor cores as they are and splits
+  only the other operand; the result is the float32 contraction to 1e-5."""
+  dev, ora = both
+  r = rng(33)
+  vals = [r.standard_normal(s).astype(np.float32) / np.sqrt(s[0] if i else 1.0) for i, s in enumerate(shapes)]
+  arrays = []
+  for i, v in enumerate(vals):
+    if i == widened:
+      narrow = dev.from_host(v, mtf.bfloat16)
+      wide = dev.cast(narrow, mtf.float32)
+      assert wide.origin is narrow
+      vals[i] = dev.to_host(wide).astype(np.float32)       # the values actually multiplied
+      arrays.append(wide)
+    else:
+      arrays.append(dev.from_host(v, mtf.float32))
+      assert arrays[-1].origin is None
+  got = dev.to_host(dev.einsum(eq, *arrays))
+  ref = np.einsum(eq, *[v.astype(np.float64) for v in vals])
+  assert rel_err(got, ref) < 1e-5
+  # a view of the cast result carries no such record and takes the general path
+  if len(shapes[widened]) == 2 and eq == "ab,bc->ac":
+    view = dev.transpose(arrays[widened], [1, 0])
+    assert view.origin is None
+
+
 @pytest.mark.parametrize("n,shape", [(4, (16, 128)), (3, (8, 96)), (4, (5, 7)), (2, (64, 64))])
 @pytest.mark.parametrize("dtype", [mtf.float32, mtf.bfloat16])
 def test_in_process_allreduce_follows_the_reference_association(cuda_device, n, shape, dtype):
