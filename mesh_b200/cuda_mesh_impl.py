@@ -136,6 +136,9 @@ class SlicedMeshImpl(mtf.MeshImpl):
   def _is_slice(self, x):
     raise NotImplementedError
 
+  def _raise_if_a_kernel_gave_up(self):
+    """Hook: raises if device code reported a failure since the last check."""
+
   def slicewise(self, fn, *inputs):
     inputs = convert_args_to_laid_out_tensors(inputs)
     n = len(self._local_pnums)
@@ -204,6 +207,9 @@ class SlicedMeshImpl(mtf.MeshImpl):
     """Slices -> full host array (combine_slices, ops.py:1271-1305)."""
     laid_out_x = laid_out_x.to_laid_out_tensor()
     host = [self._ops_for(p).to_host(s) for p, s in zip(self._local_pnums, laid_out_x.all_slices)]
+    # the copies above waited for the device: a kernel whose bounded wait ran out while
+    # producing these values has said so by now, and the values are not handed on
+    self._raise_if_a_kernel_gave_up()
     if self._distributed:
       import torch.distributed as dist
       gathered = [None] * self.size
@@ -1533,6 +1539,9 @@ class CudaMeshImpl(SlicedMeshImpl):
     for ws in getattr(self, "_a2a_ws", {}).values():
       if ws is not None:
         ws.pinned = []
+
+  def _raise_if_a_kernel_gave_up(self):
+    self.synchronize()
 
   def synchronize(self):
     """Waits for all enqueued work and raises if a kernel reported a timeout."""
