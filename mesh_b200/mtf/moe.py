@@ -120,7 +120,14 @@ def _top_2_gating(inputs, experts_dim, expert_capacity_dim, hparams, train, gate
   loss = (mtf.reduce_mean(density_1_proxy * density_1)
           * float(experts_dim.size * experts_dim.size))
   if hparams.moe_use_second_place_loss:
-    raise NotImplementedError("second-place loss is not part of the lowered path")
+    # the same product for the second choices, with the gates renormalised after the
+    # top one is taken out as the smooth stand-in, at half weight (moe.py:1428-1440)
+    density_2 = mtf.reduce_mean(mask_2, reduced_dim=group_size_dim)
+    normalized = gates_without_top_1 / (
+        mtf.reduce_sum(gates_without_top_1, reduced_dim=experts_dim) + 1e-9)
+    density_2_proxy = mtf.reduce_mean(normalized, reduced_dim=group_size_dim)
+    loss += (mtf.reduce_mean(density_2_proxy * density_2)
+             * float(experts_dim.size * experts_dim.size)) * 0.5
 
   policy, threshold = _second_policy(hparams, train)
   if policy == "all":

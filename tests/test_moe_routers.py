@@ -283,3 +283,28 @@ def test_padding_with_the_further_routers():
   mean_prob = prob.mean(-1) * mask
   want_loss = float((mean_prob * mean_prob * mask.sum(axis=1, keepdims=True)).mean() * L) * 1e-2
   assert abs(loss - want_loss) < 1e-6
+
+
+def test_second_place_loss_of_top_2_gating():
+  res, _, loss_plain, aux = _v1("top_2", 31)
+  _, _, loss_both, _ = _v1("top_2", 31, moe_use_second_place_loss=True)
+  raw = _softmax(res["x"] @ res["wg"], -1).astype(np.float32)
+  i1 = raw.argmax(-1)
+  without = raw * (1 - np.eye(E, dtype=np.float32)[i1])
+  i2 = without.argmax(-1)
+  density_2 = np.stack([(i2 == e).mean(axis=1) for e in range(E)], axis=-1)
+  proxy_2 = (without / (without.sum(-1, keepdims=True) + 1e-9)).mean(axis=1)
+  second = float((proxy_2 * density_2).mean() * E * E)
+  assert abs((loss_both - loss_plain) - 0.5 * second * 1e-2) < 1e-6
+  # the fused kernels do not form it
+  with pytest.raises(ValueError):
+    g = mtf.Graph()
+    m = mtf.Mesh(g, "m")
+    X = mtf.import_tf_tensor(m, res["x"], "batch:%d,length:%d,d_model:%d" % (B, L, M))
+    WG = mtf.import_tf_tensor(m, res["wg"], "d_model:%d,expert_unsplit:%d" % (M, E))
+    WI = mtf.import_tf_tensor(m, res["wi"], "experts:%d,d_model:%d,d_ff:%d" % (E, M, H))
+    WO = mtf.import_tf_tensor(m, res["wo"], "experts:%d,d_ff:%d,d_model:%d" % (E, H, M))
+    mtf.moe.transformer_moe_layer_v1(X, mtf.Dimension("d_model", M),
+                                     mtf.moe.HParams(moe_use_second_place_loss=True, moe_group_size=L,
+                                                     moe_second_policy_train="all"),
+                                     True, "all:1", "", WG, WI, WO)
