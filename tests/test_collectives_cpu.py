@@ -298,3 +298,76 @@ def test_ffn_row_chunks_cover_the_rows_in_multiples_of_256():
         assert b[0] == 0 and b[-1] == mine and all(x % 256 == 0 for x in b)
         assert all(hi > lo for lo, hi in zip(b[:-1], b[1:]))
   assert ffn_row_chunks(2, 16384, 1024, 2048, 1024, 1, 4096, 0.74e12) == [0, 16384]
+
+
+def test_a_product_with_one_reader_is_offered_for_deferral():
+  """EinsumOperation.lower offers a product that a single operation reads to the backend
+  (defer_einsum); the pending product runs when its reader asks for it, the result and the
+  lowering's counters are those of the plain lowering, and in a training graph - where the
+  hidden activations are read again by the backward pass - the first product is not offered."""
+  from oracle.numpy_mesh_impl import NumpyMeshImpl
+
+  class Pending(object):
+    def __init__(self, impl, fn, inputs, shape):
+      self._impl, self._fn, self._inputs, self._shape, self.runs = impl, fn, inputs, shape, 0
+
+    @property
+    def slice_shape(self):
+      return list(self._shape)
+
+    def to_laid_out_tensor(self):
+      self.runs += 1
+      if not hasattr(self, "_value"):
+        self._value = self._impl.slicewise(self._fn, *self._inputs)
+      return self._value
+
+  class Deferring(NumpyMeshImpl):
+    def __init__(self, *a):
+      super().__init__(*a)
+      self.offered = []
+
+    def defer_einsum(self, fn, inputs, equation, activation):
+      shape = self.slicewise(fn, *inputs).slice_shape     # (a real backend knows it without running)
+      self.offered.append((equation, activation))
+      return Pending(self, fn, inputs, shape)
+
+  def ffn(backend, train):
+    r = rng(5)
+    g = mtf.Graph()
+    m = mtf.Mesh(g, "m")
+    x = mtf.import_tf_tensor(m, r.standard_normal((4, 8, 16)).astype(np.float32), "batch:4,length:8,d_model:16")
+    wi = mtf.import_tf_tensor(m, r.standard_normal((16, 32)).astype(np.float32), "d_model:16,d_ff:32")
+    wo = mtf.import_tf_tensor(m, r.standard_normal((32, 16)).astype(np.float32), "d_ff:32,d_model:16")
+    y = mtf.layers.dense_relu_dense(x, mtf.Dimension("d_ff", 32), wi=wi, wo=wo)
+    fetch = [y] + (mtf.gradients([y], [wi]) if train else [])
+    low = mtf.Lowering(g, {m: backend})
+    return [low.export_to_tf_tensor(t) for t in fetch], low.counter_totals()
+  plain, counters = ffn(NumpyMeshImpl("all:2", "d_ff:all"), False)
+  backend = Deferring("all:2", "d_ff:all")
+  got, got_counters = ffn(backend, False)
+  assert len(backend.offered) == 1 and backend.offered[0][1] == "relu"
+  np.testing.assert_array_equal(got[0], plain[0])
+  assert got_counters == counters
+  backend = Deferring("all:2", "d_ff:all")
+  trained, _ = ffn(backend, True)
+  assert all(activation != "relu" for _, activation in backend.offered)
+  np.testing.assert_array_equal(trained[0], plain[0])
+
+
+def test_result_slots_return_when_their_owner_dies():
+  """_SlotOwner: the object torch ties to a result's storage gives its slot back to the
+  workspace's free list when it is collected (no CUDA involved here)."""
+  import gc
+  from mesh_b200.cuda_mesh_impl import _AlltoallWorkspace, _SlotOwner
+  ws = _AlltoallWorkspace()
+  ws.free = [3, 2]
+  owner = _SlotOwner(4096, 128, ws, 1)
+  assert owner.__cuda_array_interface__["data"] == (4096, False)
+  assert owner.__cuda_array_interface__["shape"] == (128,)
+  holder = [owner]
+  del owner
+  gc.collect()
+  assert ws.free == [3, 2]
+  holder.clear()
+  gc.collect()
+  assert ws.free == [3, 2, 1]
