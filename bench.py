@@ -445,6 +445,11 @@ def run_ours(args):
       torch.cuda.empty_cache()
       if n == 1:
         extra["einsum_fp32"] = bench_configs.measure_einsum_fp32(local_rank)
+        torch.cuda.empty_cache()
+        # forward + backward of the two layers (mtf.gradients lowered on the same kernels)
+        extra["ffn_train"] = bench_configs.measure_ffn_train(local_rank, iters=10, eager=args.eager)
+        torch.cuda.empty_cache()
+        extra["moe_train"] = bench_configs.measure_moe_train(1, 0, local_rank, iters=10, eager=args.eager)
     except Exception as e:  # the headline line must still be printed
       import traceback
       traceback.print_exc()

@@ -513,14 +513,14 @@ def config_einsum_fp32(args):
   _emit(config="einsum_fp32", **measure_einsum_fp32(0, args.iters))
 
 
-def config_ffn_train(args):
+def measure_ffn_train(local_rank=0, iters=10, eager=False):
   """Forward and backward of the dense FFN (x[64,1024,1024], wi[1024,4096],
   wo[4096,1024], bf16) on one GPU: y, then dx, dwi, dwo from a given dy through
   mtf.gradients - three GEMM pairs with permuted operand roles and the ReLU
   mask, lowered onto the same kernels and replayed as a CUDA graph."""
   pk = peaks()
-  torch.cuda.set_device(0)
-  impl = CudaMeshImpl("all:1", "", [0])
+  torch.cuda.set_device(local_rank)
+  impl = CudaMeshImpl("all:1", "", [local_rank])
   ops = impl.slice_ops
   b, l, d, f = 64, 1024, 1024, 4096
   r = np.random.Generator(np.random.PCG64(1238))
@@ -548,22 +548,27 @@ def config_ffn_train(args):
   launches = nat.launch_count() - before
   impl.synchronize()
   run = step
-  if not args.eager:
+  if not eager:
     _, run = impl.capture(step)
-  ms = time_fn(run, iters=args.iters, warmup=3)
+  ms = time_fn(run, iters=iters, warmup=3)
   flops = 3 * 2.0 * 2.0 * b * l * d * f     # forward + two gradient GEMMs per forward GEMM
-  _emit(config="ffn_train", quantity="dense_relu_dense forward + backward (dx, dwi, dwo)", ms=ms,
-        tflops=flops / (ms * 1e-3) / 1e12, frac_of_peak=flops / (ms * 1e-3) / 1e12 / pk["tflops"],
-        peak_tflops=pk["tflops"], peak_source=pk["source"], libmtfc_launches_per_step=launches,
-        stepping="eager" if args.eager else "cuda-graph replay")
+  rec = dict(quantity="dense_relu_dense forward + backward (dx, dwi, dwo)", ms=ms,
+             tflops=flops / (ms * 1e-3) / 1e12, frac_of_peak=flops / (ms * 1e-3) / 1e12 / pk["tflops"],
+             peak_tflops=pk["tflops"], peak_source=pk["source"], libmtfc_launches_per_step=launches,
+             stepping="eager" if eager else "cuda-graph replay")
+  impl.release_graphs()
+  return rec
 
 
-def config_moe_train(args):
+def config_ffn_train(args):
+  _emit(config="ffn_train", **measure_ffn_train(0, args.iters, args.eager))
+
+
+def measure_moe_train(n, rank, local_rank, iters=10, eager=False):
   """Forward and backward of the top-2 MoE layer at the benchmark shape: the
   output, then dx, d(gate kernel), dwi, dwo from a given d(output) through
   mtf.gradients (gating, dispatch and combine gradients on their own kernels,
   six expert GEMMs per step instead of two), replayed as a CUDA graph."""
-  n, rank, local_rank = _init(args)
   c = MOE
   B, L, M, E, H, S, C = (c[k] for k in "BLMEHSC")
   pk = peaks()
@@ -601,20 +606,27 @@ def config_moe_train(args):
   launches = nat.launch_count() - before
   impl.synchronize()
   run = step
-  if not args.eager:
+  if not eager:
     _, run = impl.capture(step)
-  ms, _ = time_steps(run, args.iters, 3, n)
+  ms, _ = time_steps(run, iters, 3, n)
   impl.synchronize()
   tokens = B * L
   flops = 3 * 2.0 * (E * (tokens // S) * C) * M * H * 2.0
-  if rank == 0:
-    _emit(config="moe_train", quantity="top-2 MoE layer forward + backward (dx, dwg, dwi, dwo)",
-          mesh=mesh_shape, layout=layout, n_gpus=n, ms_per_step=ms, tokens_per_s=tokens / (ms * 1e-3),
-          expert_tflops=flops / (ms * 1e-3) / 1e12, expert_flops_per_step=flops,
-          frac_of_peak=flops / (ms * 1e-3) / 1e12 / (pk["tflops"] * n), peak_tflops=pk["tflops"],
-          peak_source=pk["source"], libmtfc_launches_per_step=launches,
-          stepping="eager" if args.eager else "cuda-graph replay")
+  rec = dict(quantity="top-2 MoE layer forward + backward (dx, dwg, dwi, dwo)",
+             mesh=mesh_shape, layout=layout, n_gpus=n, ms_per_step=ms, tokens_per_s=tokens / (ms * 1e-3),
+             expert_tflops=flops / (ms * 1e-3) / 1e12, expert_flops_per_step=flops,
+             frac_of_peak=flops / (ms * 1e-3) / 1e12 / (pk["tflops"] * n), peak_tflops=pk["tflops"],
+             peak_source=pk["source"], libmtfc_launches_per_step=launches,
+             stepping="eager" if eager else "cuda-graph replay")
   impl.release_graphs()
+  return rec
+
+
+def config_moe_train(args):
+  n, rank, local_rank = _init(args)
+  rec = measure_moe_train(n, rank, local_rank, args.iters, args.eager)
+  if rank == 0:
+    _emit(config="moe_train", **rec)
   if n > 1:
     leave()
 
