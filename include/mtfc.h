@@ -491,6 +491,20 @@ int mtfc_moe_combine_gate_grad(const void* y, const void* dout, int dtype, const
                                int32_t group_size, int32_t experts, int32_t capacity,
                                int64_t row_elems, void* stream);
 
+/* Backward pass of the top-2 / top-1 gating (transformer/moe.py:1384-1424, 1485-1494,
+ * differentiated by the reference through its op chain): from the gate logits
+ * [groups, group_size, experts] (fp32, experts <= 64), the routing decisions and the
+ * gradients of gate_1, gate_2 (per token; null = none) and of the loss (a device
+ * scalar; null = none) to d logits.  Indices and capacity / policy masks are
+ * constants (gate_k as the forward pass returned it: 0 = dropped); the loss is
+ * mean over all num_groups_total groups and experts of mean_s raw * density_1, times
+ * experts^2; top1_only keeps the raw top-1 gate (no renormalisation, no gate_2). */
+int mtfc_moe_gate_grad(const float* logits, const int32_t* idx1, const int32_t* idx2,
+                       const float* gate1, const float* gate2, const float* dgate1,
+                       const float* dgate2, const float* dloss, int64_t groups, int32_t group_size,
+                       int32_t experts, int64_t num_groups_total, int32_t top1_only, float* dlogits,
+                       void* stream);
+
 /* ---- K8: row kernels of the rest of a transformer block ------------------- */
 /* y[r, :] = (x[r, :] - mean) * rsqrt(var + epsilon) * scale + bias over rows of
  * `cols` contiguous elements (centered: layer_norm, layers.py:950-979), or

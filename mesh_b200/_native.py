@@ -123,6 +123,7 @@ def _declare(lib):
       "mtfc_moe_dispatch_noalloc": [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64,
                                     i32, vp],
       "mtfc_moe_dispatch_weighted": [vp, i32, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64, vp],
+      "mtfc_moe_gate_grad": [vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i64, i32, vp, vp],
       "mtfc_moe_combine_gate_grad": [vp, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32,
                                      i32, i64, vp],
       "mtfc_moe_combine": [vp, i32, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, i64, vp],

@@ -915,6 +915,21 @@ class DeviceOps(object):
                num_experts, capacity, m, self._stream())
     return out
 
+  def moe_gate_grad(self, logits, i1, i2, g1, g2, dg1, dg2, dloss, num_groups_total, top1_only):
+    """d logits of the gating from the gradients of (gate_1, gate_2, loss); any of the three
+    may be None.  logits [..., S, E] float32, E <= 64."""
+    s, e = logits.shape[-2:]
+    groups = _volume(logits.shape[:-2])
+    logits = self.contiguous(logits)
+    fixed = [self.contiguous(t) for t in (i1, i2, g1, g2)]
+    grads = [None if t is None else self.contiguous(t) for t in (dg1, dg2, dloss)]
+    out = self._empty(logits.shape, G.float32)
+    ptr = lambda t: ctypes.c_void_p(0 if t is None else t.ptr)
+    self._call(self._lib.mtfc_moe_gate_grad, ptr(logits), *[ptr(t) for t in fixed],
+               *[ptr(t) for t in grads], groups, s, e, num_groups_total, 1 if top1_only else 0,
+               ptr(out), self._stream())
+    return out
+
   def moe_combine_gate_grad(self, y, dout, i1, i2, p1, p2, g1, g2):
     """Backward of moe_combine w.r.t. the two gates: per token, the dot product
     of its output gradient with the expert row each kept choice read."""

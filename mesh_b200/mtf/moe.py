@@ -393,6 +393,9 @@ class Top2GatingOperation(Operation):
         [Tensor(self, token_shape, G.float32, index=4), Tensor(self, token_shape, G.float32, index=5),
          Tensor(self, Shape([]), G.float32, index=6), Tensor(self, table_shape, G.int32, index=7)])
 
+  # False differentiates the restated op chain instead of using MoeGateGradOperation
+  fused_gradient = True
+
   @property
   def has_gradient(self):
     return True   # through the two gates and the loss; indices and positions carry none
@@ -408,6 +411,20 @@ class Top2GatingOperation(Operation):
     i1, i2, _, _, g1_out, g2_out, _, _ = self.outputs
     experts_dim = self._experts_dim
     group_size_dim = x.shape.dims[-2]
+    if experts_dim.size <= MoeGateGradOperation.MAX_EXPERTS and self.fused_gradient:
+      # the same derivative as one operation between two einsums: logits again,
+      # d logits from the kernel, then d inputs = d logits . W^T and d W = inputs^T . d logits
+      xf = mtf.to_float(x)
+      logits = layers.dense(xf, experts_dim, use_bias=False, kernel_weights=w, name="gate_grad")
+      dlogits = MoeGateGradOperation(
+          logits, i1, i2, g1_out, g2_out, grad_ys[4], grad_ys[5], grad_ys[6],
+          num_groups_total=Shape(x.shape.dims[:-2]).size,
+          top1_only=self._policy == "switch").outputs[0]
+      dx = mtf.einsum([dlogits, w], output_shape=x.shape)
+      dw = mtf.einsum([xf, dlogits], output_shape=w.shape)
+      if dx.dtype != x.dtype:
+        dx = mtf.cast(dx, x.dtype)
+      return [dx, dw] + [None] * (len(self.inputs) - 2)
 
     def chain(x_, w_):
       raw = layers.dense(mtf.to_float(x_), experts_dim, use_bias=False, kernel_weights=w_,
@@ -458,6 +475,44 @@ class Top2GatingOperation(Operation):
     elif mesh_axes:
       loss = LazyAllreduceSum(impl, loss, mesh_axes)
     lowering.set_tensor_lowering(self.outputs[6], loss)
+
+
+class MoeGateGradOperation(Operation):
+  """d logits [.., S, E] of the gating from the gradients of gate_1, gate_2 [.., S] and
+  of the loss (scalar), any of which may be missing: softmax backward of the picked and
+  renormalised gates and of the loss's mean-gate factor, with the routing decisions as
+  constants - what differentiating the op chain of moe.py:1384-1424, 1485-1494 gives,
+  as one operation."""
+
+  MAX_EXPERTS = 64
+
+  def __init__(self, logits, i1, i2, g1_out, g2_out, dg1, dg2, dloss, num_groups_total, top1_only,
+               name=None):
+    self._present = [t is not None for t in (dg1, dg2, dloss)]
+    super().__init__([logits, i1, i2, g1_out, g2_out] + [t for t in (dg1, dg2, dloss) if t is not None],
+                     name=name or "moe_gate_grad")
+    self._num_groups_total, self._top1_only = num_groups_total, top1_only
+    self._outputs = [Tensor(self, logits.shape, G.float32)]
+
+  @property
+  def has_gradient(self):
+    return False
+
+  def lower(self, lowering):
+    impl = lowering.mesh_impl(self)
+    logits = self.inputs[0]
+    if impl.tensor_dimension_to_mesh_axis(logits.shape.dims[-1]) is not None or (
+        impl.tensor_dimension_to_mesh_axis(logits.shape.dims[-2]) is not None):
+      raise ValueError("the gating gradient needs the group and expert dims unsplit")
+    ops = impl.slice_ops
+    present, total, top1 = self._present, self._num_groups_total, self._top1_only
+
+    def fn(z, a1, a2, g1, g2, *grads):
+      it = iter(grads)
+      dg1, dg2, dloss = [next(it) if p else None for p in present]
+      return ops.moe_gate_grad(z, a1, a2, g1, g2, dg1, dg2, dloss, total, top1)
+    lowering.set_tensor_lowering(
+        self.outputs[0], impl.slicewise(fn, *[lowering.tensors[t] for t in self.inputs]))
 
 
 class MoeDispatchOperation(Operation):

@@ -401,6 +401,36 @@ class NumpyOps(object):
     out = out.reshape(o, g, num_experts, capacity, m).transpose(0, 2, 1, 3, 4)
     return _finish(np.ascontiguousarray(out), x.dtype)
 
+  def moe_gate_grad(self, logits, i1, i2, g1, g2, dg1, dg2, dloss, num_groups_total, top1_only):
+    """d logits of the gating (moe.py:1384-1424, 1485-1494 differentiated by hand):
+    softmax backward of d raw, where d raw gathers the loss's mean-gate factor and
+    the two picked, renormalised gates; routing decisions are constants."""
+    z = logits.a.astype(np.float64)
+    s, e = z.shape[-2:]
+    z = z.reshape(-1, s, e)
+    raw = np.exp(z - z.max(-1, keepdims=True))
+    raw /= raw.sum(-1, keepdims=True)
+    a1, a2 = i1.a.reshape(-1, s), i2.a.reshape(-1, s)
+    k1 = (g1.a.reshape(-1, s) != 0).astype(np.float64)
+    k2 = (g2.a.reshape(-1, s) != 0).astype(np.float64)
+    d1 = (np.zeros_like(k1) if dg1 is None else dg1.a.reshape(-1, s).astype(np.float64)) * k1
+    d2 = (np.zeros_like(k2) if dg2 is None else dg2.a.reshape(-1, s).astype(np.float64)) * k2
+    dl = 0.0 if dloss is None else float(np.asarray(dloss.a).reshape(()))
+    density = np.stack([(a1 == j).mean(axis=1) for j in range(e)], axis=-1)          # [G, E]
+    draw = np.repeat((dl * e / (num_groups_total * s) * density)[:, None, :], s, axis=1)
+    gi, si = np.meshgrid(np.arange(z.shape[0]), np.arange(s), indexing="ij")
+    b1, b2 = raw[gi, si, a1], raw[gi, si, a2]
+    if top1_only:
+      at1, at2 = d1, np.zeros_like(d2)
+    else:
+      den = b1 + b2 + 1e-9
+      at1 = d1 * (1 / den - b1 / den ** 2) - d2 * b2 / den ** 2
+      at2 = d2 * (1 / den - b2 / den ** 2) - d1 * b1 / den ** 2
+    np.add.at(draw, (gi, si, a1), at1)
+    np.add.at(draw, (gi, si, a2), at2)
+    dz = raw * (draw - (raw * draw).sum(-1, keepdims=True))
+    return Arr(dz.reshape(logits.a.shape).astype(np.float32), mtf.float32)
+
   def moe_combine_gate_grad(self, y, dout, i1, i2, p1, p2, g1, g2):
     from oracle import moe_spec
     o, e, g, c, m = y.a.shape

@@ -80,7 +80,7 @@ def test_gradient_rules():
   np.testing.assert_allclose(_lower(g, m, [dsh], "all:1", "")[0], [[1, 1, 0], [1, 1, 0]])
 
 
-def _moe_total(arrays, mesh_shape, layout, grads, fused=False):
+def _moe_total(arrays, mesh_shape, layout, grads, fused=False, **hparams):
   x, wg, wi, wo = arrays
   g = mtf.Graph()
   m = mtf.Mesh(g, "m")
@@ -88,8 +88,10 @@ def _moe_total(arrays, mesh_shape, layout, grads, fused=False):
   WG = mtf.import_tf_tensor(m, wg, "d_model:8,expert_unsplit:4", dtype=mtf.float32)
   WI = mtf.import_tf_tensor(m, wi, "experts:4,d_model:8,d_ff:16", dtype=mtf.float32)
   WO = mtf.import_tf_tensor(m, wo, "experts:4,d_ff:16,d_model:8", dtype=mtf.float32)
-  hp = mtf.moe.HParams(moe_group_size=16, moe_second_policy_train="all",
-                       moe_use_fused_kernels=fused, moe_capacity_factor_train=1.5)
+  settings = dict(moe_group_size=16, moe_second_policy_train="all", moe_use_fused_kernels=fused,
+                  moe_capacity_factor_train=1.5)
+  settings.update(hparams)
+  hp = mtf.moe.HParams(**settings)
   out, loss = mtf.moe.transformer_moe_layer_v1(
       X, mtf.Dimension("d_model", 8), hp, True, mesh_shape, layout, WG, WI, WO)
   total = mtf.reduce_sum(mtf.square(out)) + loss * 10.0
@@ -137,6 +139,34 @@ def test_fused_moe_gradients_equal_the_op_chain():
     got = _moe_total(arrays, mesh_shape, layout, True, fused=True)
     for a, b in zip(got, ref):
       np.testing.assert_allclose(a, b, rtol=2e-4, atol=2e-5)
+
+
+@pytest.mark.parametrize("hparams", [dict(moe_gating="switch"),
+                                     dict(moe_second_policy_train="threshold", moe_second_threshold_train=0.3),
+                                     dict(moe_second_policy_train="none")])
+def test_fused_gating_gradient_for_other_policies(hparams):
+  """The gating backward operation (softmax backward of the picked, renormalised gates
+  and of the loss) against the differentiated op chain for top-1 routing and for
+  second-expert policies that drop second choices."""
+  r = rng(15)
+  arrays = [r.standard_normal((4, 16, 8)).astype(np.float32),
+            (r.standard_normal((8, 4)) / 2).astype(np.float32),
+            (r.standard_normal((4, 8, 16)) / 3).astype(np.float32),
+            (r.standard_normal((4, 16, 8)) / 4).astype(np.float32)]
+  for mesh_shape, layout in (("all:1", ""), ("all:2", "batch:all;experts:all")):
+    ref = _moe_total(arrays, mesh_shape, layout, True, fused=False, **hparams)
+    got = _moe_total(arrays, mesh_shape, layout, True, fused=True, **hparams)
+    for a, b in zip(got, ref):
+      np.testing.assert_allclose(a, b, rtol=2e-4, atol=2e-5)
+  # ... and against the restated chain the operation replaced
+  saved = mtf.moe.Top2GatingOperation.fused_gradient
+  try:
+    mtf.moe.Top2GatingOperation.fused_gradient = False
+    chain = _moe_total(arrays, "all:1", "", True, fused=True, **hparams)
+  finally:
+    mtf.moe.Top2GatingOperation.fused_gradient = saved
+  for a, b in zip(_moe_total(arrays, "all:1", "", True, fused=True, **hparams), chain):
+    np.testing.assert_allclose(a, b, rtol=2e-4, atol=2e-5)
 
 
 def test_fused_attention_gradient_equals_the_op_chain():

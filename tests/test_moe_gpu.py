@@ -309,3 +309,35 @@ def test_two_level_layer_matches_oracle(cuda_device, mesh_shape, layout):
   assert same.mean() > 0.97
   assert rel_err(got[same], ref[same]) < 1e-5
   assert abs(got_loss - ref_loss) <= 1e-4 * abs(ref_loss)
+
+
+@pytest.mark.parametrize("experts", [8, 32, 64])
+@pytest.mark.parametrize("top1_only", [False, True])
+def test_gate_grad_kernel_matches_oracle(dev_ops, experts, top1_only):
+  """mtfc_moe_gate_grad against the oracle's restatement (float64): d logits from the
+  gradients of both gates and the loss, with dropped choices, and with gradients missing."""
+  from oracle.numpy_ops import NumpyOps
+  ora = NumpyOps()
+  r = rng(81 + experts)
+  groups, s = 5, 200
+  logits = (r.standard_normal((1, groups, s, experts)) * 2).astype(np.float32)
+  i1 = logits.argmax(-1).astype(np.int32)
+  masked = logits.copy()
+  np.put_along_axis(masked, i1[..., None], -1e30, axis=-1)
+  i2 = masked.argmax(-1).astype(np.int32)
+  g1 = (r.uniform(size=i1.shape) * (r.uniform(size=i1.shape) > 0.2)).astype(np.float32)   # 0 = dropped
+  g2 = (r.uniform(size=i1.shape) * (r.uniform(size=i1.shape) > 0.4)).astype(np.float32)
+  dg1, dg2 = [r.standard_normal(i1.shape).astype(np.float32) for _ in range(2)]
+  dloss = np.float32(0.7)
+  both = lambda a, dt: (dev_ops.from_host(a, dt), ora.from_host(a, dt))
+  z, a1, a2 = both(logits, mtf.float32), both(i1, mtf.int32), both(i2, mtf.int32)
+  k1, k2 = both(g1, mtf.float32), both(g2, mtf.float32)
+  d1, d2, dl = both(dg1, mtf.float32), both(dg2, mtf.float32), both(np.asarray(dloss), mtf.float32)
+  total = 3 * groups                      # as if two more slices held groups of the same layer
+  for present in ((1, 1, 1), (1, 0, 0), (0, 0, 1), (0, 1, 1)):
+    pick = lambda k: [None if not p else t[k] for p, t in zip(present, (d1, d2, dl))]
+    got = dev_ops.to_host(dev_ops.moe_gate_grad(z[0], a1[0], a2[0], k1[0], k2[0], *pick(0), total, top1_only))
+    ref = ora.to_host(ora.moe_gate_grad(z[1], a1[1], a2[1], k1[1], k2[1], *pick(1), total, top1_only))
+    assert got.shape == logits.shape
+    assert rel_err(got, ref) < 1e-5, present
+    assert np.abs(ref).max() > 0
