@@ -187,6 +187,47 @@ def test_moe_layer_with_alltoall_over_gloo(tmp_path):
   assert sorted(os.listdir(str(tmp_path))) == ["ok0", "ok1"]
 
 
+def _moe_v2_worker(rank, world, port, out_dir):
+  os.environ["MASTER_ADDR"] = "127.0.0.1"
+  os.environ["MASTER_PORT"] = str(port)
+  dist.init_process_group("gloo", rank=rank, world_size=world)
+  try:
+    mesh_shape, layout = "all:%d" % world, "batch:all;expert_x:all"
+
+    def layer(backend):
+      r = rng(7)
+      g = mtf.Graph()
+      m = mtf.Mesh(g, "m")
+      b, l, d, f, ex, ey = 4, 16, 8, 12, 2, 2
+      imp = lambda a, spec: mtf.import_tf_tensor(m, a.astype(np.float32), spec)
+      X = imp(r.standard_normal((b, l, d)), "batch:4,length:16,d_model:8")
+      WGO = imp(r.standard_normal((d, ex)), "d_model:8,expert_x_unsplit:2")
+      WGI = imp(r.standard_normal((ex, d, ey)), "expert_x:2,d_model:8,expert_y_unsplit:2")
+      WI = imp(r.standard_normal((ey, ex, d, f)) / 3, "expert_y:2,expert_x:2,d_model:8,expert_hidden:12")
+      WO = imp(r.standard_normal((ey, ex, f, d)) / 3, "expert_y:2,expert_x:2,expert_hidden:12,d_model:8")
+      hp = mtf.moe.HParams(moe_num_experts=[ex, ey], moe_group_size=l, moe_second_policy_train="all",
+                           moe_min_expert_capacity=2)
+      out, loss = mtf.moe.transformer_moe_layer_v2(
+          X, mtf.Dimension("d_model", d), hp, True, mesh_shape, layout, WGO, WGI, WI, WO)
+      low = mtf.Lowering(g, {m: backend})
+      return low.export_to_tf_tensor(out), float(low.export_to_tf_tensor(loss)), low.counter_totals()
+    got, gl, cg = layer(NumpySlicedMeshImpl(mesh_shape, layout, distributed=True, rank=rank))
+    ref, rl, cr = layer(NumpyMeshImpl(mesh_shape, layout))
+    np.testing.assert_array_equal(got, ref)
+    assert abs(gl - rl) < 1e-7 and cg == cr
+    assert sum(v for k, v in cg.items() if k.startswith("alltoall")) > 0
+    open(os.path.join(out_dir, "ok%d" % rank), "w").write("ok")
+  finally:
+    dist.destroy_process_group()
+
+
+def test_two_level_moe_layer_over_gloo(tmp_path):
+  """transformer_moe_layer_v2 with one process per processor: its layout changes run as
+  real alltoalls between the processes and give the in-process oracle's bits."""
+  mp.spawn(_moe_v2_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+  assert sorted(os.listdir(str(tmp_path))) == ["ok0", "ok1"]
+
+
 def test_move_packs_on_the_source_device():
   """CudaMeshImpl._move with distinct device ordinals in one process: a strided slice
   must be packed by a kernel launched on the device that holds it, and only then
