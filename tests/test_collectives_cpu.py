@@ -228,6 +228,39 @@ def test_two_level_moe_layer_over_gloo(tmp_path):
   assert sorted(os.listdir(str(tmp_path))) == ["ok0", "ok1"]
 
 
+def _train_worker(rank, world, port, out_dir):
+  os.environ["MASTER_ADDR"] = "127.0.0.1"
+  os.environ["MASTER_PORT"] = str(port)
+  dist.init_process_group("gloo", rank=rank, world_size=world)
+  try:
+    from test_training_loop import _training_graph
+    mesh_shape, layout = "rows:2,cols:2", "batch:rows;experts:rows;heads:cols;vocab:cols"
+
+    def run(backend):
+      g, m, loss, variables = _training_graph(mesh_shape, layout)
+      losses = []
+      for _ in range(3):
+        low = mtf.Lowering(g, {m: backend})
+        losses.append(float(low.export_to_tf_tensor(loss)))
+      low.copy_slices_to_masters()
+      return losses, [v.operation.get_master() for v in variables]
+    got, got_vars = run(NumpySlicedMeshImpl(mesh_shape, layout, distributed=True, rank=rank))
+    ref, ref_vars = run(NumpyMeshImpl(mesh_shape, layout))
+    np.testing.assert_allclose(got, ref, rtol=1e-6)
+    for a, b in zip(got_vars, ref_vars):
+      np.testing.assert_allclose(a, b, rtol=1e-5, atol=1e-7)
+    open(os.path.join(out_dir, "ok%d" % rank), "w").write("ok")
+  finally:
+    dist.destroy_process_group()
+
+
+def test_training_steps_over_gloo(tmp_path):
+  """Three training steps of the small block (MoE, split vocabulary, Adafactor on variables)
+  with one process per processor: losses and updated weights equal the in-process oracle's."""
+  mp.spawn(_train_worker, args=(4, _free_port(), str(tmp_path)), nprocs=4, join=True)
+  assert sorted(os.listdir(str(tmp_path))) == ["ok0", "ok1", "ok2", "ok3"]
+
+
 def test_move_packs_on_the_source_device():
   """CudaMeshImpl._move with distinct device ordinals in one process: a strided slice
   must be packed by a kernel launched on the device that holds it, and only then
