@@ -560,6 +560,20 @@ class DeviceOps(object):
       out = self._empty([sizes[l] for l in store], out_dtype)
     c_b, c_m, c_n = m * n, n, 1
     result = out if view_perm == list(range(len(store))) else self.transpose(out, view_perm)
+    if (a.dtype.name == "float32" and out_dtype.name == "float32" and a.origin is not None
+        and b.origin is not None and k <= self.FP32_TENSOR_CORE_MAX_K and gemm_hook is None):
+      # both operands are widened bfloat16 arrays (float32 attention logits of bf16 queries
+      # and keys): the bf16 product with fp32 accumulation IS the float32 contraction
+      d = nat.GemmDesc()
+      d.batch, d.m, d.n, d.k = nb, m, n, k
+      d.a_batch, d.a_m, d.a_k = a_b, a_m, a_k
+      d.b_batch, d.b_k, d.b_n = b_b, b_k, b_n
+      d.c_batch, d.c_m, d.c_n = c_b, c_m, c_n
+      d.in_dtype, d.out_dtype = nat.BF16, nat.F32
+      d.epilogue, d.force_path = epilogue, 0
+      self._call(self._lib.mtfc_gemm, ctypes.byref(d), ctypes.c_void_p(a.origin.ptr),
+                 ctypes.c_void_p(b.origin.ptr), ctypes.c_void_p(out.ptr), self._stream())
+      return result
     if (a.dtype.name == "float32" and out_dtype.name == "float32" and nb == 1 and k % 4 == 0
         and epilogue == nat.EPILOGUE_NONE and gemm_hook is None
         and (a.origin is not None) != (b.origin is not None)

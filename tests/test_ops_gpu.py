@@ -232,6 +232,25 @@ def test_fp32_einsum_with_a_widened_bf16_operand(both, eq, shapes, widened):
     assert view.origin is None
 
 
+def test_fp32_einsum_of_two_widened_bf16_operands(both):
+  """float32 logits of bfloat16 queries and keys (both cast up): one bfloat16 product with
+  float32 accumulation, equal to the float32 contraction of the widened values."""
+  dev, ora = both
+  r = rng(34)
+  q = r.standard_normal((2, 4, 256, 64)).astype(np.float32)
+  k = r.standard_normal((2, 4, 384, 64)).astype(np.float32)
+  wide, exact = [], []
+  for v in (q, k):
+    w = dev.cast(dev.from_host(v, mtf.bfloat16), mtf.float32)
+    assert w.origin is not None
+    wide.append(w)
+    exact.append(dev.to_host(w).astype(np.float64))
+  before = __import__("mesh_b200._native", fromlist=["x"]).launch_count()
+  got = dev.to_host(dev.einsum("bhqd,bhkd->bhqk", *wide))
+  assert __import__("mesh_b200._native", fromlist=["x"]).launch_count() - before == 1   # no operand split
+  assert rel_err(got, np.einsum("bhqd,bhkd->bhqk", *exact)) < 1e-6
+
+
 @pytest.mark.parametrize("n,shape", [(4, (16, 128)), (3, (8, 96)), (4, (5, 7)), (2, (64, 64))])
 @pytest.mark.parametrize("dtype", [mtf.float32, mtf.bfloat16])
 def test_in_process_allreduce_follows_the_reference_association(cuda_device, n, shape, dtype):
