@@ -747,7 +747,8 @@ def transformer_moe_layer_v1(inputs, output_dim, hparams, train, mesh_shape, lay
 
 
 def transformer_moe_layer_v2(inputs, output_dim, hparams, train, mesh_shape, layout,
-                             gate_weights_outer, gate_weights_inner, wi, wo, activation=mtf.relu):
+                             gate_weights_outer, gate_weights_inner, wi, wo, activation=mtf.relu,
+                             nonpadding=None):
   """Two-level top-2 MoE feed-forward layer (moe.py:528-801).
 
   hparams.moe_num_experts = [x, y]: an outer router sends every position to up to two of
@@ -760,15 +761,21 @@ def transformer_moe_layer_v2(inputs, output_dim, hparams, train, mesh_shape, lay
   expert_x_unsplit]; gate_weights_inner [expert_x, d_model, expert_y_unsplit];
   wi [expert_y, expert_x, d_model, hidden]; wo [expert_y, expert_x, hidden, output_dim].
   Four layout changes (alltoalls when the dims are split): groups -> expert_x,
-  inner groups -> expert_y, and back.  Returns (output, loss * moe_loss_coef).
+  inner groups -> expert_y, and back.  `nonpadding` [<batch dims>, length] (ones for
+  real positions, zeros for padding) keeps padding out of the outer routing.
+  Returns (output, loss * moe_loss_coef).
   """
   if hparams.moe_gating != "top_2":
     raise ValueError("unknown hparams.moe_gating=%s" % hparams.moe_gating)
   if not isinstance(hparams.moe_num_experts, (list, tuple)) or len(hparams.moe_num_experts) != 2:
     raise ValueError("the two-level layer needs moe_num_experts = [x, y]")
+  if nonpadding is not None:
+    nonpadding = mtf.zeros(inputs.mesh, Shape(inputs.shape.dims[:-1]), dtype=inputs.dtype) + nonpadding
   insert_outer_batch_dim = inputs.shape.ndims == 3
   if insert_outer_batch_dim:
     inputs = mtf.reshape(inputs, Shape([Dimension("outer_batch", 1)] + inputs.shape.dims))
+    if nonpadding is not None:
+      nonpadding = mtf.reshape(nonpadding, Shape(inputs.shape.dims[:-1]))
   a0, b1, l, m = inputs.shape.dims
   x1 = Dimension("expert_x", hparams.moe_num_experts[0])
   y0 = Dimension("expert_y", hparams.moe_num_experts[1])
@@ -802,8 +809,11 @@ def transformer_moe_layer_v2(inputs, output_dim, hparams, train, mesh_shape, lay
     return mtf.random_uniform(inputs.mesh, shape, dtype=G.float32)
 
   inputs = mtf.reshape(inputs, Shape([a0, g1, s, m]))
+  if nonpadding is not None:
+    nonpadding = mtf.reshape(nonpadding, Shape([a0, g1, s]))
   dispatch_x, combine_x, loss_outer, _ = _top_2_gating(
-      inputs, x, c, hparams, train, gate_weights_outer, second_noise=noise_for(Shape([a0, g1, s])))
+      inputs, x, c, hparams, train, gate_weights_outer, second_noise=noise_for(Shape([a0, g1, s])),
+      importance=nonpadding)
   # expert groups first: that is the dim the layout change splits
   expert_inputs_x = mtf.einsum([inputs, dispatch_x], Shape([x, a0, g1, c, m]))
   weight_in_slot = mtf.reduce_sum(combine_x, output_shape=Shape([x, a0, g1, c]))

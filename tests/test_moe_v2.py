@@ -55,10 +55,11 @@ def _route(raw, capacity, importance=None):
   return combine, loss
 
 
-def _numpy_layer(x, wg_outer, wg_inner, wi, wo, c, h_groups, t, d):
+def _numpy_layer(x, wg_outer, wg_inner, wi, wo, c, h_groups, t, d, nonpadding=None):
   G, S = B, L
   xs = x.reshape(G, S, M)
-  routed = [_route(_softmax(xs[g] @ wg_outer), c) for g in range(G)]
+  routed = [_route(_softmax(xs[g] @ wg_outer), c, None if nonpadding is None else nonpadding[g])
+            for g in range(G)]
   combine_x = np.stack([r[0] for r in routed])                       # [G, S, X, C]
   loss_outer = np.mean([r[1] for r in routed])
   expert_in = np.einsum("gsm,gsxc->xgcm", xs, (combine_x != 0).astype(np.float32))
@@ -81,9 +82,11 @@ def _numpy_layer(x, wg_outer, wg_inner, wi, wo, c, h_groups, t, d):
   return output.reshape(B, L, M), (loss_outer + np.mean(inner_losses)) * 1e-2
 
 
+@pytest.mark.parametrize("padded", [False, True])
 @pytest.mark.parametrize("mesh_shape,layout", [("all:1", ""), ("all:2", "batch:all;expert_x:all")])
-def test_two_level_layer_matches_its_numpy_restatement(mesh_shape, layout):
+def test_two_level_layer_matches_its_numpy_restatement(mesh_shape, layout, padded):
   r = rng(41)
+  mask = (r.uniform(size=(B, L)) > 0.25).astype(np.float32) if padded else None
   x = r.standard_normal((B, L, M)).astype(np.float32)
   wg_outer = (r.standard_normal((M, X)) * 0.8).astype(np.float32)
   wg_inner = (r.standard_normal((X, M, Y)) * 0.8).astype(np.float32)
@@ -99,16 +102,20 @@ def test_two_level_layer_matches_its_numpy_restatement(mesh_shape, layout):
   hparams = mtf.moe.HParams(moe_num_experts=[X, Y], moe_group_size=L, moe_capacity_factor_train=1.0,
                             moe_capacity_factor_second_level=1.0, moe_min_expert_capacity=2,
                             moe_second_policy_train="all")
+  NP = None if mask is None else mtf.import_tf_tensor(m, mask, "batch:%d,length:%d" % (B, L))
   out, loss = mtf.moe.transformer_moe_layer_v2(
-      Xt, mtf.Dimension("d_model", M), hparams, True, mesh_shape, layout, WGO, WGI, WI, WO)
+      Xt, mtf.Dimension("d_model", M), hparams, True, mesh_shape, layout, WGO, WGI, WI, WO,
+      nonpadding=NP)
   low = mtf.Lowering(g, {m: NumpyMeshImpl(mesh_shape, layout)})
   got, got_loss = low.export_to_tf_tensor(out), float(low.export_to_tf_tensor(loss))
   c = max(min(L, int(L * 1.0 / X)), 2)
   slots = B * c                      # per expert group
   h_groups, t = slots // L, L        # inner groups of moe_group_size slots
   d = max(min(t, int(t * 1.0 / Y)), 2)
-  want, want_loss = _numpy_layer(x, wg_outer, wg_inner, wi, wo, c, h_groups, t, d)
+  want, want_loss = _numpy_layer(x, wg_outer, wg_inner, wi, wo, c, h_groups, t, d, mask)
   assert np.abs(want).max() > 0.05
+  if padded:
+    assert np.all(got[mask == 0] == 0)
   assert rel_err(got, want) < 1e-5
   assert abs(got_loss - want_loss) < 1e-6
   if mesh_shape != "all:1":
